@@ -1,0 +1,374 @@
+#!/usr/bin/env python
+"""Benchmark of the PAM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (per GPU, weak scaling): chunked PAM scan forward+backward on the PAM-layer
+shape of the v11_e3_k3-style training configuration -- B=8 sequences x H=6 heads x T=2048
+tokens, head dim 64, bf16 token tensors, one state (K=1), synthetic seeded inputs.  One "step"
+is one forward + one backward over that batch; the metric is tokens/s (B*T per step), summed
+over GPUs (units are independent (batch, head) pairs: no collective on the data path).
+
+One JSON line is printed by rank 0 (see README/DESIGN for the fields).  `--impl reference` times
+the CPU port of the reference's own code path (oracle/torch_port.py) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "pam_scan_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+WL = dict(B=8, H=6, T=2048, d=64, K=1, chunk=64)
+CPU_SAMPLE = dict(B=1, H=6, T=2048, d=64)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm=d["hbm_gbs"], tf=d["bf16_tflops"], tf_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_scan_baseline(seconds: float = 12.0):
+    """Time the CPU port of the reference path on a bounded sample; returns tokens/s."""
+    from oracle import torch_port
+    from qllm2_b200 import synthetic
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    s = CPU_SAMPLE
+    inp = synthetic.scan_inputs(s["B"], s["H"], s["T"], s["d"], seed=0)
+    torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])  # warm-up (autograd init)
+    times = []
+    t_end = time.perf_counter() + seconds
+    while len(times) < 2 or (time.perf_counter() < t_end and len(times) < 50):
+        t0 = time.perf_counter()
+        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+        times.append(time.perf_counter() - t0)
+    times.sort()
+    med = times[len(times) // 2]
+    # same head count as the workload, so tokens/s (B*T per second) is directly comparable
+    return dict(value=s["B"] * s["T"] / med, unit=UNIT, cores=cores, kind="port",
+                sample=f"B={s['B']} H={s['H']} T={s['T']} d={s['d']} fp32 fwd+bwd, median of {len(times)} runs "
+                       f"({med * 1e3:.1f} ms each), oracle/torch_port.py")
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's CPU code path (ported) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import torch_port
+    from qllm2_b200 import synthetic
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    s = CPU_SAMPLE
+    inp = synthetic.scan_inputs(s["B"], s["H"], s["T"], s["d"], seed=0)
+    for _ in range(max(args.warmup, 1)):
+        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+    dt = time.perf_counter() - t0
+    val = s["B"] * s["T"] * args.steps / dt
+    sample = (f"each step = B={s['B']} of the workload's B={WL['B']} sequences (H={s['H']} T={s['T']} d={s['d']}), "
+              f"fp32, CPU port of the reference path (oracle/torch_port.py); the reference itself is a Python "
+              f"project that is not present on the GPU box")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(n_gpus):
+    return {"workload": f"pam_scan fwd+bwd, per GPU B={WL['B']} H={WL['H']} T={WL['T']} d={WL['d']} K={WL['K']} "
+                        f"bf16 re/im interleaved (PAM-layer shape of the 8-block v11_e3_k3-style model)",
+            "global_batch": WL["B"] * n_gpus, "seq_len": WL["T"], "heads": WL["H"], "head_dim": WL["d"],
+            "parallelism": f"(batch,head) shards x{n_gpus}, no collective",
+            "l2": "3 rotating input sets; >250 MB touched per step (L2 is 126 MB)"}
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.tmp.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        if sm:
+            sm.sort()
+            # under load = upper half of the samples (idle samples before/after the region are lower)
+            out.update(sm_mhz=sm[len(sm) // 2], sm_max_mhz=mx, reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ----------------------------------------------------------------------------- GPU arm
+def scan_flops_per_token_head(d, C, K=1):
+    """Algorithmic (causal-useful) flops of the forward scan per token and head; backward = 2x."""
+    return 8 * (C + 1) * d + K * 16 * d * d
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the decode / CE side measurements")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch.distributed as dist
+    from qllm2_b200 import _lib, ops, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    peaks = load_peaks()
+
+    B, H, T, d, K, C = WL["B"], WL["H"], WL["T"], WL["d"], WL["K"], WL["chunk"]
+    nsets = 3
+    host_sets, dev_sets = [], []
+    for i in range(nsets):
+        inp = synthetic.scan_inputs(B, H, T, d, seed=100 * rank + i, dtype=torch.bfloat16)
+        hs = dict(q=inp.q.pin_memory(), k=inp.k.pin_memory(), v=inp.v.pin_memory(), dy=inp.dy.pin_memory(),
+                  gamma=inp.gamma.contiguous().pin_memory())
+        host_sets.append(hs)
+        dev_sets.append({k_: v_.to(dev) for k_, v_ in hs.items()})
+
+    def step_dev(s):
+        q, k, v = (s[n].detach().requires_grad_(True) for n in ("q", "k", "v"))
+        gam = s["gamma"].detach().requires_grad_(True)
+        y, _ = ops.pam_scan(q, k, v, gam, chunk=C)
+        return (y, *torch.autograd.grad(y, [q, k, v, gam], s["dy"]))
+
+    out_host = None
+
+    def step_e2e(hs):
+        nonlocal out_host
+        s = {k_: v_.to(dev, non_blocking=True) for k_, v_ in hs.items()}
+        outs = step_dev(s)
+        if out_host is None:
+            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for o, oh in zip(outs, out_host):
+            oh.copy_(o, non_blocking=True)
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, sets, steps, warmup):
+        for i in range(warmup):
+            fn(sets[i % nsets])
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count()
+        e0.record()
+        for i in range(steps):
+            fn(sets[i % nsets])
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        launches = _lib.launch_count() - l0
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, launches
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms, launches = timed(step_dev, dev_sets, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e, _ = timed(step_e2e, host_sets, args.steps, args.warmup)
+
+    tokens_step = B * T * world
+    value = tokens_step * args.steps / (ms * 1e-3)
+    e2e_value = tokens_step * args.steps / (ms_e2e * 1e-3)
+    elt = 2
+    h2d = sum(v_.numel() * v_.element_size() for v_ in host_sets[0].values())
+    d2h = 4 * B * H * T * d * 2 * elt + B * H * T * 4
+
+    # per-kernel split over a few extra steps (events behind every launch)
+    torch.cuda.synchronize()
+    _lib.profile_begin()
+    prof_steps = 5
+    for i in range(prof_steps):
+        step_dev(dev_sets[i % nsets])
+    prof = _lib.profile_end()
+    kernels = {n: {"launches": c, "ms_per_launch": t / c} for n, (c, t) in prof.items()}
+    total_prof = sum(t for _, t in prof.values())
+    th = B * H * T
+    f_fwd = scan_flops_per_token_head(d, C, K) * th
+    alg = {  # algorithmic flops (tensor-bound pieces) or bytes (HBM-bound pieces) per launch
+        "k_fwd_chunk": ("tensor", f_fwd - 8 * d * d * th),
+        "k_chunk_outer<state>": ("tensor", 8 * d * d * th),
+        "k_chunk_outer<dstate>": ("tensor", 8 * d * d * th),
+        "k_bwd_chunk": ("tensor", 2 * f_fwd - 8 * d * d * th),
+        "k_state_scan<fwd>": ("hbm", 2 * (T // C) * B * H * K * d * d * 8),
+        "k_state_scan<rev>": ("hbm", 2 * (T // C) * B * H * K * d * d * 8),
+    }
+    roof_all = {}
+    for n, kinfo in kernels.items():
+        if n in alg:
+            bound, amount = alg[n]
+            sec = kinfo["ms_per_launch"] * 1e-3
+            if bound == "tensor":
+                ach, peak, unit = amount / sec / 1e12, peaks["tf"], "TFLOP/s"
+            else:
+                ach, peak, unit = amount / sec / 1e9, peaks["hbm"], "GB/s"
+            roof_all[n] = {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                           "share_of_step": prof[n][1] / total_prof if total_prof else None}
+    dominant = max(roof_all, key=lambda n: prof[n][1]) if roof_all else None
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if dominant and os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get(dominant)
+    roofline = None
+    if dominant:
+        r = roof_all[dominant]
+        roofline = {"kernel": dominant, "bound": r["bound"], "achieved": r["achieved"], "peak": r["peak"],
+                    "unit": r["unit"], "frac": r["frac"], "traffic": traffic, "peak_source": peaks["src"] + " burst"}
+
+    extra = {}
+    if not args.no_extras and rank == 0:
+        extra = side_measurements(dev, peaks)
+
+    cpu = cpu_scan_baseline() if (rank == 0 and world == 1) else None
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 accumulate on bf16 tensors (CUDA-core FFMA path)", "data": "synthetic",
+            "config": workload_config(world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "roofline_all": roof_all,
+            "kernels": kernels, "cpu_baseline": cpu, "extra": extra,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def side_measurements(dev, peaks):
+    """Decode step (HBM-bound) and fused CE (config 2) timed on their own; reported under `extra`."""
+    from qllm2_b200 import fused_ce, ops, synthetic
+    out = {}
+
+    def time_ms(fn, iters, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    # continuous-batching decode step: 256 live sequences, 12 layers, H=12, d=64, K=3
+    n, L, K, H, d = 256, 12, 3, 12, 64
+    for sd, name in ((torch.bfloat16, "bf16"), (torch.float32, "f32")):
+        pool = torch.zeros(n + 16, L, K, H, d, d, 2, dtype=sd, device=dev)
+        slots = torch.randperm(n + 16, device=dev)[:n].int()
+        x = (torch.randn(n, H, d, 2, device=dev) * 0.1).bfloat16()
+        gam = torch.full((K, n, H), 0.97, device=dev)
+        cf = torch.randn(K, n, H, 2, device=dev)
+        layer = [0]
+
+        def dec():
+            ops.pam_decode_step(pool, slots, x, x, x, gam, cf, layer=layer[0] % L)
+            layer[0] += 1
+        ms = time_ms(dec, 48)
+        by = n * H * K * 2 * d * d * 2 * pool.element_size()
+        out[f"decode_step_{name}_state"] = {
+            "ms_per_layer_step": ms, "state_bytes_per_launch": by, "achieved_gbs": by / ms / 1e6,
+            "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm"],
+            "config": f"n={n} H={H} d={d} K={K}, pool {pool.numel() * pool.element_size() / 1e9:.2f} GB rotating over {L} layers"}
+        del pool
+    # fused tied-head CE, config 2
+    c2 = synthetic.config2()
+    h = c2.h.to(dev).requires_grad_(True)
+    w = c2.w.to(dev).requires_grad_(True)
+    t = c2.targets.to(dev)
+
+    def ce():
+        loss = fused_ce.fused_linear_cross_entropy(h, w, t)
+        torch.autograd.grad(loss, [h, w])
+    ms = time_ms(ce, 3, warm=1)
+    fl = 6 * 8192 * 50261 * 768
+    out["fused_ce_config2"] = {"ms_fwd_bwd": ms, "tokens_per_s": 8192 / ms * 1e3, "achieved_tflops": fl / ms / 1e9,
+                               "frac_of_bf16_peak": fl / ms / 1e9 / peaks["tf"]}
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,195 @@
+/*
+ * qllm2_pam.h -- C ABI of libqllm2_pam_b200.so: the Phase-Associative-Memory (PAM) hot path
+ * of QLLM (reference project gowrav-vishwakarma/qllm2, directory v11/) as hand-written CUDA
+ * for NVIDIA B200 (sm_100a).
+ *
+ * The reference has no FFI layer: its operator surface for this path is a set of Python
+ * functions operating on torch tensors.  Each entry point below names the reference function
+ * (file:line inside that project) whose arithmetic it replaces.  A maintainer binds these with
+ * ctypes (tensor.data_ptr(), torch.cuda.current_stream().cuda_stream).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing is allocated or freed here
+ *   - complex numbers are split-real: innermost axis of length 2, re at 0, im at 1
+ *     (v11/complex_ops.py:4-11)
+ *   - every function returns 0 on success, a QPAM_E* code otherwise; it never throws/aborts.
+ *     qpam_last_error() returns a thread-local, human-readable message for the last failure.
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); calls are asynchronous.
+ *   - functions are re-entrant for distinct streams and distinct output/workspace buffers.
+ */
+#ifndef QLLM2_PAM_H
+#define QLLM2_PAM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QPAM_OK 0
+#define QPAM_EINVAL 1      /* bad argument (shape, dtype, null pointer, alignment) */
+#define QPAM_EWORKSPACE 2  /* workspace too small */
+#define QPAM_ECUDA 3       /* a CUDA runtime call failed; see qpam_last_error() */
+#define QPAM_EUNSUPPORTED 4
+
+#define QPAM_F32 0
+#define QPAM_BF16 1
+
+#define QPAM_MAX_STATES 4  /* K, number of superposed states */
+
+/* ------------------------------------------------------------------------------------------
+ * Chunked dual-form scan (training / prefill).
+ *
+ * Replaces V11PAMLayer._forward_chunked_head (v11/model.py:378-417), _dual_form_block
+ * (:354-376), fused_decay_matrix (v11/triton_kernels.py:522-528,570-573), and for K>1
+ * _fused_chunk_step / _forward_multistate_fused (v11/model.py:657-781);
+ * flash_pam_chunked_head (v11/flash_pam.py:56-152) computes the same function.
+ *
+ *   S^k_t = (gamma^k_t + gamma_eps) S^k_{t-1} + v_t (x) conj(k_t)
+ *   y_t   = sum_k coef_{k,t} * S^k_t (q_t * q_scale)
+ *
+ * Token tensors q,k,v,y,dy,dq,dk,dv: [B,H,T,d,2] contiguous, dtype io_dtype.
+ * Packed ragged mode (cu_seqlens != NULL): B must be 1, T is the packed total, the layout is
+ * [H,T,d,2]; cu_seqlens is int32[S+1] on the device, the state restarts at each boundary.
+ * Without cu_seqlens there are S = B sequences of T tokens each.
+ * gamma: fp32 [K,B,H,T].  coef: fp32 [K,B,H,T,2] or NULL (== 1).
+ * s0 / s_final / ds_final / ds0: fp32 [K,S,H,d,d,2] (state[i][j]: i value channel, j key
+ * channel, v11/model.py:939-947) or NULL.
+ * d in {16,32,64}; 1 <= K <= QPAM_MAX_STATES.  `chunk` is accepted for interface
+ * compatibility only: the result of the scan does not depend on the chunk length and the
+ * kernels use their own tile of 64 tokens.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* gamma;
+  const float* coef;
+  const float* s0;
+  const int32_t* cu_seqlens;
+  void* y;
+  float* s_final;
+  void* workspace;        /* >= qpam_scan_workspace_bytes(args, ..); 256-byte aligned */
+  size_t workspace_bytes;
+  int32_t B, H, T, d, K, S;
+  int32_t chunk;
+  int32_t io_dtype;       /* QPAM_F32 | QPAM_BF16 */
+  float q_scale;          /* d^-0.5 in the reference (v11/model.py:381) */
+  float gamma_eps;        /* 1e-6 in the reference (v11/model.py:396) */
+} qpam_scan_args;
+
+/* Bytes of workspace: forward only (with_backward = 0) or forward + backward (1). */
+size_t qpam_scan_workspace_bytes(const qpam_scan_args* args, int32_t with_backward);
+
+/* Forward.  Leaves the per-chunk carried states in `workspace`; a following
+ * qpam_scan_bwd with the SAME workspace contents may pass states_valid=1 to reuse them. */
+int qpam_scan_fwd(const qpam_scan_args* args, void* stream);
+
+/* Backward of qpam_scan_fwd w.r.t. q, k, v, gamma (and coef when coef != NULL).
+ * Replaces torch autograd through the functions above, including _FusedDecayMatrixFn.backward
+ * (v11/triton_kernels.py:447-480).  Exact for gamma + gamma_eps <= 1.
+ * dgamma fp32 [K,B,H,T]; dcoef fp32 [K,B,H,T,2] or NULL; ds_final (gradient reaching
+ * s_final) and ds0 (gradient w.r.t. s0, output) may be NULL. */
+int qpam_scan_bwd(const qpam_scan_args* args, const void* dy, void* dq, void* dk, void* dv,
+                  float* dgamma, float* dcoef, const float* ds_final, float* ds0,
+                  int32_t states_valid, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * O(1) recurrent decode step over a pool of per-sequence state slots.
+ *
+ * Replaces V11PAMLayer._recur_step_additive (v11/model.py:927-965) and the K-state loop of
+ * _recurrent (:874-906):  S <- gamma S + v (x) conj(k);  y = sum_k coef_k S^k q
+ * (note: gamma is used as is, without gamma_eps, exactly as the reference's recurrent path).
+ *
+ * state_pool: [n_slots, L, K, H, d, d, 2] (state_dtype); the step updates, in place, layer
+ * `layer` of the slots named by slot_ids[n].  q (already scaled by d^-0.5), k, v, y: [n,H,d,2]
+ * io_dtype.  gamma fp32 [K,n,H]; coef fp32 [K,n,H,2] or NULL.
+ * ------------------------------------------------------------------------------------------ */
+int qpam_decode_step(void* state_pool, int32_t state_dtype, int64_t n_slots, int32_t L, int32_t layer,
+                     const int32_t* slot_ids, const void* q, const void* k, const void* v,
+                     const float* gamma, const float* coef, void* y, int32_t n, int32_t H, int32_t d,
+                     int32_t K, int32_t io_dtype, void* stream);
+
+/* Copy final prefill states [K,S,H,d,d,2] fp32 into pool slots (sequence s -> slot_ids[s]). */
+int qpam_pool_store(void* state_pool, int32_t state_dtype, int64_t n_slots, int32_t L, int32_t layer,
+                    const int32_t* slot_ids, const float* states, int32_t S, int32_t H, int32_t d,
+                    int32_t K, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused tied complex LM head + cross-entropy.
+ *
+ * Replaces _FusedLinearCE.forward/backward and fused_linear_cross_entropy
+ * (v11/fused_ce.py:26-94), linear_ce_per_token (:97-115), linear_ce_stats (:118-141) and the
+ * tied head of V11LM (v11/model.py:1136-1139,1175-1190):
+ *     logits = [lm_r | lm_i] @ [E_r | E_i]^T = h @ w^T,   h [N,F], w [V,F], F = 2*dim.
+ * The [N,V] logits are never written to memory.
+ *
+ * Vocabulary-parallel use: w holds rows [v_offset, v_offset+V) of the full matrix; targets are
+ * GLOBAL ids.  qpam_ce_partial writes per-row (max, sum exp(z-max), target logit or 0,
+ * argmax value, argmax index) for the local shard; the caller combines shards (all-gather or
+ * all-reduce), then qpam_ce_finalize turns combined stats into lse/loss, and qpam_ce_bwd
+ * produces local dW and a partial dH that the caller all-reduces.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  const void* h;          /* [N,F] io_dtype */
+  const void* w;          /* [V,F] io_dtype */
+  const int64_t* targets; /* [N] global ids; == ignore_index => row ignored */
+  const float* mask;      /* [N] or NULL */
+  int64_t N, V, v_offset;
+  int32_t F;
+  int32_t io_dtype;
+  int64_t ignore_index;
+  void* workspace;        /* >= qpam_ce_workspace_bytes(args, with_backward) */
+  size_t workspace_bytes;
+} qpam_ce_args;
+
+size_t qpam_ce_workspace_bytes(const qpam_ce_args* args, int32_t with_backward);
+
+/* Per-row shard statistics, each fp32/int64 [N]:
+ * row_max, row_sumexp (relative to row_max), row_tgt (target logit if the shard owns the
+ * target column, else 0), row_argmax (global column of the largest logit; lowest index wins
+ * ties). */
+int qpam_ce_partial(const qpam_ce_args* args, float* row_max, float* row_sumexp, float* row_tgt,
+                    int64_t* row_argmax, void* stream);
+
+/* From combined stats: lse[N] = max + log(sumexp); per_token[N] = (lse - tgt) or 0 when ignored;
+ * loss_sum[0] = sum per_token*mask; denom[0] = valid count or mask sum, clamped to >= 1;
+ * correct[0] = sum token_mask * [argmax == target] and tokens[0] = sum token_mask, with
+ * token_mask = mask if given else [target != ignore_index] (linear_ce_stats).
+ * Any output may be NULL except lse. */
+int qpam_ce_finalize(const qpam_ce_args* args, const float* row_max, const float* row_sumexp,
+                     const float* row_tgt, const int64_t* row_argmax, float* lse, float* per_token,
+                     float* loss_sum, float* denom, float* correct, float* tokens, void* stream);
+
+/* Gradients: dh [N,F], dw [V,F] (io_dtype) of  grad_scale[0] * loss_sum / denom[0]
+ * given lse from qpam_ce_finalize.  grad_scale and denom are device scalars. */
+int qpam_ce_bwd(const qpam_ce_args* args, const float* lse, const float* grad_scale,
+                const float* denom, void* dh, void* dw, void* stream);
+
+/* Decode head: argmax_v (h @ w^T)[n, v] -> ids[N] (int64) and the winning logit (fp32). */
+int qpam_head_argmax(const qpam_ce_args* args, int64_t* ids, float* best, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Launch accounting and per-kernel timing.  The reference times whole calls with
+ * time.perf_counter around torch.cuda.synchronize (v11/bench_flash_pam.py:73-84); these entry
+ * points give the per-kernel split of the same calls.
+ *   qpam_launch_count  kernels launched by this library in this process so far
+ *   qpam_profile_begin records a base event on `stream` and starts recording one event behind
+ *                      every kernel this library launches (all calls must use that stream)
+ *   qpam_profile_end   stops recording, waits for the last event and writes one line per kernel
+ *                      "name launches total_ms\n" into buf; the time of a kernel is the gap
+ *                      between its event and the previous one on the stream
+ * ------------------------------------------------------------------------------------------ */
+long long qpam_launch_count(void);
+int qpam_profile_begin(void* stream);
+int qpam_profile_end(char* buf, size_t buf_bytes);
+
+const char* qpam_last_error(void);
+/* "qllm2_pam_b200 <version> sm_100a" */
+const char* qpam_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLLM2_PAM_H */

@@ -1,0 +1,130 @@
+"""ctypes binding of libqllm2_pam_b200.so (the C ABI declared in include/qllm2_pam.h).
+
+There is no CPU fallback: if the library is missing or an entry point reports an error the
+caller gets a Python exception.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqllm2_pam_b200.so")
+
+QPAM_F32, QPAM_BF16 = 0, 1
+MAX_STATES = 4
+
+c_void_p, c_int32, c_int64, c_size_t, c_float = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t, C.c_float
+
+
+class ScanArgs(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p),
+        ("gamma", c_void_p), ("coef", c_void_p), ("s0", c_void_p), ("cu_seqlens", c_void_p),
+        ("y", c_void_p), ("s_final", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("B", c_int32), ("H", c_int32), ("T", c_int32), ("d", c_int32), ("K", c_int32), ("S", c_int32),
+        ("chunk", c_int32), ("io_dtype", c_int32),
+        ("q_scale", c_float), ("gamma_eps", c_float),
+    ]
+
+
+class CEArgs(C.Structure):
+    _fields_ = [
+        ("h", c_void_p), ("w", c_void_p), ("targets", c_void_p), ("mask", c_void_p),
+        ("N", c_int64), ("V", c_int64), ("v_offset", c_int64),
+        ("F", c_int32), ("io_dtype", c_int32),
+        ("ignore_index", c_int64),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
+# name -> (restype, argtypes); every symbol declared in include/qllm2_pam.h
+SIGNATURES = {
+    "qpam_scan_workspace_bytes": (c_size_t, [C.POINTER(ScanArgs), c_int32]),
+    "qpam_scan_fwd": (c_int32, [C.POINTER(ScanArgs), c_void_p]),
+    "qpam_scan_bwd": (c_int32, [C.POINTER(ScanArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
+    "qpam_decode_step": (c_int32, [c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                   c_int32, c_void_p]),
+    "qpam_pool_store": (c_int32, [c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_int32,
+                                  c_int32, c_int32, c_int32, c_void_p]),
+    "qpam_ce_workspace_bytes": (c_size_t, [C.POINTER(CEArgs), c_int32]),
+    "qpam_ce_partial": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qpam_ce_finalize": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qpam_ce_bwd": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qpam_head_argmax": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p]),
+    "qpam_launch_count": (C.c_longlong, []),
+    "qpam_profile_begin": (c_int32, [c_void_p]),
+    "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),
+    "qpam_last_error": (C.c_char_p, []),
+    "qpam_version": (C.c_char_p, []),
+}
+
+_lib = None
+
+
+class QPamError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise QPamError(
+                f"{LIB_PATH} is missing: build it with `python -m qllm2_b200.build` "
+                "(there is no CPU or PyTorch fallback for the PAM kernels)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().qpam_last_error().decode("utf-8", "replace")
+        raise QPamError(f"{what} failed with code {rc}: {msg}")
+
+
+def dtype_code(dtype) -> int:
+    import torch
+    if dtype == torch.float32:
+        return QPAM_F32
+    if dtype == torch.bfloat16:
+        return QPAM_BF16
+    raise QPamError(f"unsupported dtype {dtype}: the PAM kernels take float32 or bfloat16")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr() -> int:
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def launch_count() -> int:
+    return int(lib().qpam_launch_count())
+
+
+def profile_begin() -> None:
+    check(lib().qpam_profile_begin(stream_ptr()), "qpam_profile_begin")
+
+
+def profile_end() -> dict:
+    """{kernel name: (launches, total_ms)} since profile_begin()."""
+    buf = C.create_string_buffer(1 << 16)
+    check(lib().qpam_profile_end(buf, len(buf)), "qpam_profile_end")
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, cnt, ms = line.rsplit(" ", 2)
+        out[name] = (int(cnt), float(ms))
+    return out

@@ -1,0 +1,208 @@
+// Host side of the chunked PAM scan: argument checks, workspace carving, launches.
+#include "pam_scan_chunk.cuh"
+
+namespace qpam {
+
+static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+struct ScanLayout {
+  int64_t nslots;
+  int32_t nc_uniform;
+  int32_t grid_chunks;  // upper bound on the number of chunks (grid.x of the chunk kernels)
+  size_t off_prefix, off_states, off_decay, off_dstates, total_fwd, total_bwd;
+};
+
+static ScanLayout scan_layout(const qpam_scan_args* a) {
+  ScanLayout L{};
+  const int64_t S = a->S;
+  const int64_t dd = (int64_t)a->d * a->d;
+  if (a->cu_seqlens == nullptr) {
+    L.nc_uniform = (a->T + CH - 1) / CH;
+    L.nslots = S * (L.nc_uniform + 1);
+    L.grid_chunks = (int32_t)(S * L.nc_uniform);
+  } else {
+    L.nc_uniform = 0;
+    L.nslots = a->T / CH + 2 * S;
+    L.grid_chunks = (int32_t)(a->T / CH + S);
+  }
+  size_t off = 0;
+  L.off_prefix = off;
+  off += align256(sizeof(int32_t) * (size_t)(S + 1));
+  L.off_states = off;
+  off += align256(sizeof(float2) * (size_t)a->K * a->H * L.nslots * dd);
+  L.off_decay = off;
+  off += align256(sizeof(float) * (size_t)a->K * a->H * L.nslots);
+  L.total_fwd = off;
+  L.off_dstates = off;
+  off += align256(sizeof(float2) * (size_t)a->K * a->H * L.nslots * dd);
+  L.total_bwd = off;
+  return L;
+}
+
+static int check_scan_args(const qpam_scan_args* a) {
+  QPAM_REQUIRE(a != nullptr, "scan: args is NULL");
+  QPAM_REQUIRE(a->d == 16 || a->d == 32 || a->d == 64, "scan: head dim d=%d not in {16,32,64}", a->d);
+  QPAM_REQUIRE(a->K >= 1 && a->K <= QPAM_MAX_STATES, "scan: K=%d outside [1,%d]", a->K, QPAM_MAX_STATES);
+  QPAM_REQUIRE(a->B >= 1 && a->H >= 1 && a->T >= 0, "scan: bad B/H/T = %d/%d/%d", a->B, a->H, a->T);
+  QPAM_REQUIRE(a->H <= 65535 && a->H * a->K <= 65535, "scan: H*K too large for the launch grid");
+  QPAM_REQUIRE(a->io_dtype == QPAM_F32 || a->io_dtype == QPAM_BF16, "scan: io_dtype %d unknown", a->io_dtype);
+  if (a->cu_seqlens != nullptr) {
+    QPAM_REQUIRE(a->B == 1, "scan: packed mode (cu_seqlens) needs B == 1, got %d", a->B);
+    QPAM_REQUIRE(a->S >= 1, "scan: packed mode needs S >= 1");
+  } else {
+    QPAM_REQUIRE(a->S == a->B, "scan: without cu_seqlens S must equal B (%d vs %d)", a->S, a->B);
+  }
+  QPAM_REQUIRE(a->q && a->k && a->v && a->gamma, "scan: q/k/v/gamma must not be NULL");
+  QPAM_REQUIRE(a->workspace != nullptr && ((uintptr_t)a->workspace & 255) == 0,
+               "scan: workspace NULL or not 256-byte aligned");
+  QPAM_REQUIRE((int64_t)a->B * a->H * a->T * a->d * 2 < ((int64_t)1 << 40), "scan: tensors too large");
+  return QPAM_OK;
+}
+
+static ScanParams make_params(const qpam_scan_args* a, const ScanLayout& L) {
+  ScanParams p{};
+  char* ws = reinterpret_cast<char*>(a->workspace);
+  p.q = a->q; p.k = a->k; p.v = a->v;
+  p.gamma = a->gamma; p.coef = a->coef;
+  p.y = a->y;
+  p.states = reinterpret_cast<float2*>(ws + L.off_states);
+  p.chunk_decay = reinterpret_cast<float*>(ws + L.off_decay);
+  p.dstates = reinterpret_cast<float2*>(ws + L.off_dstates);
+  p.s0 = a->s0; p.s_final = a->s_final;
+  p.geom.cu_seqlens = a->cu_seqlens;
+  p.geom.chunk_prefix = reinterpret_cast<const int32_t*>(ws + L.off_prefix);
+  p.geom.S = a->S; p.geom.T = a->T; p.geom.nc_uniform = L.nc_uniform;
+  p.nslots = L.nslots;
+  p.B = a->B; p.H = a->H; p.T = a->T; p.K = a->K;
+  p.q_scale = a->q_scale; p.eps = a->gamma_eps;
+  return p;
+}
+
+template <typename KernelT>
+static int set_smem(KernelT kern, size_t bytes) {
+  if (bytes > 48 * 1024) QPAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return QPAM_OK;
+}
+
+template <int D>
+constexpr size_t outer_smem() { return sizeof(float2) * 2 * CH * (D + 1) + sizeof(float) * CH; }
+
+template <int D, typename T>
+static int launch_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
+  // chunk-local state sums, then the carry over the chunk axis
+  if (a->cu_seqlens != nullptr) {
+    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S);
+    QPAM_LAUNCH_CHECK("k_chunk_prefix");
+  }
+  if (L.grid_chunks > 0) {
+    auto kern = k_chunk_outer<D, T, false>;
+    int rc = set_smem(kern, outer_smem<D>());
+    if (rc) return rc;
+    kern<<<dim3(L.grid_chunks, a->H, a->K), NT, outer_smem<D>(), st>>>(p);
+    QPAM_LAUNCH_CHECK("k_chunk_outer<state>");
+  }
+  const int n4 = D * D / 2;
+  k_state_scan<false><<<dim3(a->S, a->H * a->K, (n4 + 255) / 256), 256, 0, st>>>(p, D);
+  QPAM_LAUNCH_CHECK("k_state_scan<fwd>");
+  return QPAM_OK;
+}
+
+template <int D, typename T>
+static int scan_fwd_t(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  int rc = launch_states<D, T>(p, L, a, st);
+  if (rc) return rc;
+  if (L.grid_chunks > 0 && a->y != nullptr) {
+    auto kern = k_fwd_chunk<D, T>;
+    rc = set_smem(kern, fwd_chunk_smem<D>());
+    if (rc) return rc;
+    kern<<<dim3(L.grid_chunks, a->H), NT, fwd_chunk_smem<D>(), st>>>(p);
+    QPAM_LAUNCH_CHECK("k_fwd_chunk");
+  }
+  return QPAM_OK;
+}
+
+template <int D, typename T>
+static int scan_bwd_t(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk,
+                      void* dv, float* dgamma, float* dcoef, const float* ds_final, float* ds0,
+                      int states_valid, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  p.dy = dy; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.dgamma = dgamma; p.dcoef = dcoef; p.ds_final = ds_final; p.ds0 = ds0;
+  int rc;
+  if (!states_valid) {
+    ScanParams pf = p;
+    pf.s_final = nullptr;
+    rc = launch_states<D, T>(pf, L, a, st);
+    if (rc) return rc;
+  }
+  if (L.grid_chunks > 0) {
+    auto kern = k_chunk_outer<D, T, true>;
+    rc = set_smem(kern, outer_smem<D>());
+    if (rc) return rc;
+    kern<<<dim3(L.grid_chunks, a->H, a->K), NT, outer_smem<D>(), st>>>(p);
+    QPAM_LAUNCH_CHECK("k_chunk_outer<dstate>");
+  }
+  const int n4 = D * D / 2;
+  k_state_scan<true><<<dim3(a->S, a->H * a->K, (n4 + 255) / 256), 256, 0, st>>>(p, D);
+  QPAM_LAUNCH_CHECK("k_state_scan<rev>");
+  if (L.grid_chunks > 0) {
+    auto kern = k_bwd_chunk<D, T>;
+    rc = set_smem(kern, bwd_chunk_smem<D>());
+    if (rc) return rc;
+    kern<<<dim3(L.grid_chunks, a->H), NT, bwd_chunk_smem<D>(), st>>>(p);
+    QPAM_LAUNCH_CHECK("k_bwd_chunk");
+    k_dgamma_finalize<<<dim3(a->S, a->H, a->K), 256, 0, st>>>(p, D);
+    QPAM_LAUNCH_CHECK("k_dgamma_finalize");
+  }
+  return QPAM_OK;
+}
+
+}  // namespace qpam
+
+using namespace qpam;
+
+extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t with_backward) {
+  if (a == nullptr || a->d <= 0 || a->K <= 0 || a->H <= 0 || a->S <= 0 || a->T < 0) return 0;
+  const ScanLayout L = scan_layout(a);
+  return with_backward ? L.total_bwd : L.total_fwd;
+}
+
+#define QPAM_DISPATCH_SCAN(FN, ...)                                                      \
+  do {                                                                                   \
+    const bool bf = a->io_dtype == QPAM_BF16;                                            \
+    switch (a->d) {                                                                      \
+      case 16: return bf ? FN<16, __nv_bfloat16>(__VA_ARGS__) : FN<16, float>(__VA_ARGS__); \
+      case 32: return bf ? FN<32, __nv_bfloat16>(__VA_ARGS__) : FN<32, float>(__VA_ARGS__); \
+      default: return bf ? FN<64, __nv_bfloat16>(__VA_ARGS__) : FN<64, float>(__VA_ARGS__); \
+    }                                                                                    \
+  } while (0)
+
+extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) {
+  int rc = check_scan_args(a);
+  if (rc) return rc;
+  const ScanLayout L = scan_layout(a);
+  if (a->workspace_bytes < L.total_fwd) {
+    set_error("scan fwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_fwd);
+    return QPAM_EWORKSPACE;
+  }
+  QPAM_REQUIRE(a->y != nullptr || a->s_final != nullptr, "scan fwd: both y and s_final are NULL");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  QPAM_DISPATCH_SCAN(scan_fwd_t, a, L, st);
+}
+
+extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, void* dk, void* dv,
+                             float* dgamma, float* dcoef, const float* ds_final, float* ds0,
+                             int32_t states_valid, void* stream) {
+  int rc = check_scan_args(a);
+  if (rc) return rc;
+  QPAM_REQUIRE(dy && dq && dk && dv && dgamma, "scan bwd: dy/dq/dk/dv/dgamma must not be NULL");
+  QPAM_REQUIRE(dcoef == nullptr || a->coef != nullptr, "scan bwd: dcoef requested but coef is NULL");
+  const ScanLayout L = scan_layout(a);
+  if (a->workspace_bytes < L.total_bwd) {
+    set_error("scan bwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_bwd);
+    return QPAM_EWORKSPACE;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  QPAM_DISPATCH_SCAN(scan_bwd_t, a, L, dy, dq, dk, dv, dgamma, dcoef, ds_final, ds0, states_valid, st);
+}

@@ -1,0 +1,221 @@
+"""torch-facing wrappers of the C ABI: autograd functions over raw device pointers.
+
+torch is used here for what it is good at on this path -- owning device memory, the current
+stream and autograd bookkeeping.  All arithmetic happens in libqllm2_pam_b200.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import CEArgs, ScanArgs, check, dtype_code, ptr, stream_ptr
+
+GAMMA_EPS = 1e-6
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.QPamError("PAM kernels need CUDA tensors (there is no CPU path in this package)")
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# --------------------------------------------------------------------------------------- scan
+def _scan_args(q, k, v, gamma, coef, s0, cu_seqlens, y, s_final, q_scale, eps, chunk):
+    B, H, T, d = q.shape[0], q.shape[1], q.shape[2], q.shape[3]
+    K = gamma.shape[0]
+    S = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    a = ScanArgs()
+    a.q, a.k, a.v = ptr(q), ptr(k), ptr(v)
+    a.gamma, a.coef, a.s0, a.cu_seqlens = ptr(gamma), ptr(coef), ptr(s0), ptr(cu_seqlens)
+    a.y, a.s_final = ptr(y), ptr(s_final)
+    a.B, a.H, a.T, a.d, a.K, a.S = B, H, T, d, K, S
+    a.chunk, a.io_dtype = int(chunk), dtype_code(q.dtype)
+    a.q_scale, a.gamma_eps = float(q_scale), float(eps)
+    return a
+
+
+class _PamScanFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, gamma, coef, s0, cu_seqlens, q_scale, eps, chunk, save_states):
+        L = _lib.lib()
+        _require_cuda(q, k, v, gamma)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        gamma = gamma.float().contiguous()
+        coef = None if coef is None else coef.float().contiguous()
+        s0 = None if s0 is None else s0.float().contiguous()
+        B, H, T, d = q.shape[:4]
+        K = gamma.shape[0]
+        S = B if cu_seqlens is None else cu_seqlens.numel() - 1
+        y = torch.empty_like(q)
+        s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=q.device)
+        need_bwd = any(t is not None and t.requires_grad for t in (q, k, v, gamma, coef, s0))
+        a = _scan_args(q, k, v, gamma, coef, s0, cu_seqlens, y, s_final, q_scale, eps, chunk)
+        nbytes = L.qpam_scan_workspace_bytes(C.byref(a), 1 if (need_bwd and save_states) else 0)
+        ws = _workspace(nbytes, q.device)
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        check(L.qpam_scan_fwd(C.byref(a), stream_ptr()), "qpam_scan_fwd")
+        ctx.save_for_backward(q, k, v, gamma, coef, s0, cu_seqlens, ws if (need_bwd and save_states) else None)
+        ctx.cfg = (q_scale, eps, chunk)
+        ctx.set_materialize_grads(False)
+        return y, s_final
+
+    @staticmethod
+    def backward(ctx, dy, ds_final):
+        L = _lib.lib()
+        q, k, v, gamma, coef, s0, cu_seqlens, ws = ctx.saved_tensors
+        q_scale, eps, chunk = ctx.cfg
+        dy = torch.zeros_like(q) if dy is None else dy.contiguous().to(q.dtype)
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dgamma = torch.empty_like(gamma)
+        dcoef = torch.empty_like(coef) if coef is not None else None
+        ds0 = torch.empty_like(s0) if (s0 is not None and ctx.needs_input_grad[5]) else None
+        if ds_final is not None:
+            ds_final = ds_final.float().contiguous()
+        a = _scan_args(q, k, v, gamma, coef, s0, cu_seqlens, None, None, q_scale, eps, chunk)
+        states_valid = 1
+        if ws is None:
+            ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 1), q.device)
+            states_valid = 0
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        check(L.qpam_scan_bwd(C.byref(a), ptr(dy), ptr(dq), ptr(dk), ptr(dv), ptr(dgamma), ptr(dcoef),
+                              ptr(ds_final), ptr(ds0), states_valid, stream_ptr()), "qpam_scan_bwd")
+        return dq, dk, dv, dgamma, dcoef, ds0, None, None, None, None, None
+
+
+def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: Optional[int] = None,
+             eps: float = GAMMA_EPS, chunk: int = 64, save_states: bool = True):
+    """Chunked dual-form PAM scan on the GPU.
+
+    q, k, v  [B,H,T,d,2] (float32 or bfloat16; q unscaled -- it is multiplied by head_dim**-0.5
+             inside, as V11PAMLayer._forward_chunked_head does, v11/model.py:381-382)
+    gamma    [B,H,T] or [K,B,H,T] decay in (0,1];  coef optional [K,B,H,T,2] read-out weights
+    s0       optional [K,S,H,d,d,2] initial state;  cu_seqlens optional int32 [S+1] (then B == 1)
+    Returns (y [B,H,T,d,2] in q's dtype, s_final float32 [K,S,H,d,d,2]).
+    """
+    gamma = gamma.float()
+    if gamma.dim() == 3:
+        gamma = gamma.unsqueeze(0)
+    if coef is not None:
+        coef = coef.float()
+        if coef.dim() == 4:
+            coef = coef.unsqueeze(0)
+    if s0 is not None:
+        s0 = s0.float()
+    d = q.shape[3]
+    head_dim = d if head_dim is None else head_dim
+    if cu_seqlens is not None:
+        cu_seqlens = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+    return _PamScanFn.apply(q, k, v, gamma, coef, s0, cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
+
+
+# --------------------------------------------------------------------------------------- decode
+def pam_decode_step(state_pool, slot_ids, q_scaled, k, v, gamma, coef=None, *, layer: int = 0):
+    """One recurrent step, in place on ``state_pool`` [n_slots, L, K, H, d, d, 2].
+
+    q_scaled, k, v [n,H,d,2]; gamma [K,n,H] (or [n,H]); coef optional [K,n,H,2];
+    slot_ids int32 [n].  Returns y [n,H,d,2].  (v11/model.py:927-965)
+    """
+    L = _lib.lib()
+    _require_cuda(state_pool, q_scaled)
+    n_slots, n_layers, K, H, d = state_pool.shape[:5]
+    if gamma.dim() == 2:
+        gamma = gamma.unsqueeze(0)
+    if coef is not None and coef.dim() == 3:
+        coef = coef.unsqueeze(0)
+    gamma = gamma.float().contiguous()
+    coef = None if coef is None else coef.float().contiguous()
+    q_scaled, k, v = q_scaled.contiguous(), k.contiguous(), v.contiguous()
+    slot_ids = slot_ids.to(device=state_pool.device, dtype=torch.int32).contiguous()
+    n = q_scaled.shape[0]
+    if gamma.shape != (K, n, H):
+        raise _lib.QPamError(f"gamma shape {tuple(gamma.shape)} != {(K, n, H)}")
+    if not state_pool.is_contiguous():
+        raise _lib.QPamError("state_pool must be contiguous")
+    y = torch.empty_like(q_scaled)
+    check(L.qpam_decode_step(state_pool.data_ptr(), dtype_code(state_pool.dtype), n_slots, n_layers, layer,
+                             ptr(slot_ids), ptr(q_scaled), ptr(k), ptr(v), ptr(gamma), ptr(coef), ptr(y),
+                             n, H, d, K, dtype_code(q_scaled.dtype), stream_ptr()), "qpam_decode_step")
+    return y
+
+
+def pam_pool_store(state_pool, slot_ids, states, *, layer: int = 0):
+    """Write prefill states [K,S,H,d,d,2] (float32) into pool slots ``slot_ids`` [S]."""
+    L = _lib.lib()
+    n_slots, n_layers, K, H, d = state_pool.shape[:5]
+    states = states.float().contiguous()
+    S = states.shape[1]
+    slot_ids = slot_ids.to(device=state_pool.device, dtype=torch.int32).contiguous()
+    check(L.qpam_pool_store(state_pool.data_ptr(), dtype_code(state_pool.dtype), n_slots, n_layers, layer,
+                            ptr(slot_ids), ptr(states), S, H, d, K, stream_ptr()), "qpam_pool_store")
+
+
+# --------------------------------------------------------------------------------------- CE
+def _ce_args(h, w, targets, mask, ignore_index, v_offset=0):
+    a = CEArgs()
+    a.h, a.w, a.targets, a.mask = ptr(h), ptr(w), ptr(targets), ptr(mask)
+    a.N, a.V, a.v_offset = h.shape[0], w.shape[0], int(v_offset)
+    a.F, a.io_dtype = h.shape[1], dtype_code(h.dtype)
+    a.ignore_index = int(ignore_index)
+    return a
+
+
+def ce_row_stats(h, w, targets, *, ignore_index=-100, v_offset=0):
+    """Per-row shard statistics (max, sumexp, target logit, argmax) without forming logits."""
+    L = _lib.lib()
+    _require_cuda(h, w)
+    h, w = h.contiguous(), w.contiguous()
+    if h.dtype != w.dtype:
+        w = w.to(h.dtype)
+    N = h.shape[0]
+    f32 = dict(dtype=torch.float32, device=h.device)
+    row_max, row_sum, row_tgt = torch.empty(N, **f32), torch.empty(N, **f32), torch.empty(N, **f32)
+    row_arg = torch.empty(N, dtype=torch.int64, device=h.device)
+    a = _ce_args(h, w, targets, None, ignore_index, v_offset)
+    ws = _workspace(L.qpam_ce_workspace_bytes(C.byref(a), 0), h.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(L.qpam_ce_partial(C.byref(a), ptr(row_max), ptr(row_sum), ptr(row_tgt if targets is not None else None),
+                            ptr(row_arg), stream_ptr()), "qpam_ce_partial")
+    return row_max, row_sum, row_tgt, row_arg
+
+
+def ce_finalize(h, w, targets, mask, stats, *, ignore_index=-100):
+    """Combined stats -> dict(lse, per_token, loss_sum, denom, correct, tokens) (device tensors)."""
+    L = _lib.lib()
+    row_max, row_sum, row_tgt, row_arg = stats
+    N = h.shape[0]
+    f32 = dict(dtype=torch.float32, device=h.device)
+    out = dict(lse=torch.empty(N, **f32), per_token=torch.empty(N, **f32), loss_sum=torch.zeros(1, **f32),
+               denom=torch.ones(1, **f32), correct=torch.zeros(1, **f32), tokens=torch.zeros(1, **f32))
+    a = _ce_args(h, w, targets, mask, ignore_index)
+    ws = _workspace(256, h.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(L.qpam_ce_finalize(C.byref(a), ptr(row_max), ptr(row_sum), ptr(row_tgt), ptr(row_arg), ptr(out["lse"]),
+                             ptr(out["per_token"]), ptr(out["loss_sum"]), ptr(out["denom"]), ptr(out["correct"]),
+                             ptr(out["tokens"]), stream_ptr()), "qpam_ce_finalize")
+    return out
+
+
+def ce_backward(h, w, targets, mask, lse, grad_scale, denom, *, ignore_index=-100, v_offset=0):
+    """dH [N,F], dW [V,F] (dtype of h / w) for  grad_scale * loss_sum / denom."""
+    L = _lib.lib()
+    dh = torch.empty_like(h)
+    dw = torch.empty_like(w)
+    a = _ce_args(h, w, targets, mask, ignore_index, v_offset)
+    ws = _workspace(L.qpam_ce_workspace_bytes(C.byref(a), 1), h.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(L.qpam_ce_bwd(C.byref(a), ptr(lse), ptr(grad_scale), ptr(denom), ptr(dh), ptr(dw), stream_ptr()),
+          "qpam_ce_bwd")
+    return dh, dw
+
+
+def head_argmax(h, w):
+    """Greedy decode head: (ids int64 [N], best logit float32 [N]) of argmax_v (h @ w^T)."""
+    row_max, _, _, row_arg = ce_row_stats(h, w, None)
+    return row_arg, row_max

@@ -1,0 +1,70 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from qllm2_b200 import _lib, build
+    build.build()
+    return _lib.lib()
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "qllm2_pam.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(qpam_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(lib):
+    from qllm2_b200 import _lib
+    names = _declared()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/qllm2_pam.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) == set(names)
+    assert b"sm_100a" in lib.qpam_version()
+
+
+def test_argument_errors_do_not_touch_the_gpu(lib):
+    from qllm2_b200 import _lib
+    a = _lib.ScanArgs()
+    a.d, a.K, a.B, a.H, a.T, a.S = 48, 1, 1, 1, 8, 1
+    assert lib.qpam_scan_fwd(C.byref(a), None) == 1
+    assert b"head dim" in lib.qpam_last_error()
+    a.d, a.K = 64, 9
+    assert lib.qpam_scan_fwd(C.byref(a), None) == 1
+    assert b"K=9" in lib.qpam_last_error()
+    ce = _lib.CEArgs()
+    assert lib.qpam_ce_partial(C.byref(ce), None, None, None, None, None) == 1
+    assert lib.qpam_decode_step(None, 0, 1, 1, 0, None, None, None, None, None, None, None, 1, 1, 64, 1, 0, None) == 1
+
+
+def test_workspace_sizes(lib):
+    from qllm2_b200 import _lib
+    a = _lib.ScanArgs()
+    a.B, a.H, a.T, a.d, a.K, a.S = 2, 4, 512, 32, 1, 2
+    fwd = lib.qpam_scan_workspace_bytes(C.byref(a), 0)
+    bwd = lib.qpam_scan_workspace_bytes(C.byref(a), 1)
+    slots = 2 * (512 // 64 + 1)
+    assert fwd >= 4 * slots * 32 * 32 * 8
+    assert bwd >= 2 * 4 * slots * 32 * 32 * 8 and bwd > fwd
+    ce = _lib.CEArgs()
+    ce.N, ce.V, ce.F, ce.io_dtype = 8192, 50261, 768, 1
+    assert lib.qpam_ce_workspace_bytes(C.byref(ce), 1) > lib.qpam_ce_workspace_bytes(C.byref(ce), 0) > 0
+
+
+def test_ops_fail_loudly_without_cuda():
+    import torch
+    from qllm2_b200 import _lib, ops
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    q = torch.zeros(1, 1, 8, 16, 2)
+    with pytest.raises(_lib.QPamError):
+        ops.pam_scan(q, q, q, torch.ones(1, 1, 8))

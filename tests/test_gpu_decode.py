@@ -1,0 +1,67 @@
+"""GPU parity of the recurrent decode step over a slot pool (v11/model.py:927-965)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import pam_oracle as po
+from qllm2_b200 import ops
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_step_matches_reference_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "recur_step.npz"))
+    B, H, d = g["S"].shape[:3]
+    pool = torch.zeros(B + 3, 1, 1, H, d, d, 2, device=DEV)
+    slots = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    ops.pam_pool_store(pool, slots, torch.from_numpy(g["S"]).float()[None].to(DEV))
+    f = lambda name: torch.from_numpy(g[name]).float().to(DEV)
+    y = ops.pam_decode_step(pool, slots, f("q"), f("k"), f("v"), f("gamma"))
+    assert_close(y.cpu().numpy(), g["y"], 1e-5, "y")
+    assert_close(pool[slots.long(), 0, 0].cpu().numpy(), g["S_new"], 1e-5, "S_new")
+    untouched = [i for i in range(B + 3) if i not in (4, 1)]
+    assert float(pool[untouched].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("d,K,state_dtype,io_dtype", [
+    (64, 3, torch.float32, torch.float32), (64, 3, torch.bfloat16, torch.bfloat16),
+    (32, 1, torch.float32, torch.bfloat16), (16, 2, torch.bfloat16, torch.float32),
+    (64, 1, torch.float32, torch.float32)])
+def test_multi_step_vs_oracle(d, K, state_dtype, io_dtype):
+    """Several steps with sequences joining/leaving (slot ids change between steps)."""
+    n_slots, L, H = 9, 2, 3
+    gen = torch.Generator().manual_seed(d + K)
+    pool = torch.zeros(n_slots, L, K, H, d, d, 2, dtype=state_dtype, device=DEV)
+    ref = np.zeros((n_slots, L, K, H, d, d), dtype=np.complex128)
+    tol = 1e-5 if (state_dtype == torch.float32 and io_dtype == torch.float32) else 2e-2
+    live_sets = [[0, 5, 2], [0, 5, 2, 7], [5, 7], [8, 5, 7, 1, 3]]
+    for step, live in enumerate(live_sets):
+        n = len(live)
+        layer = step % L
+        q, k, v = (torch.randn(n, H, d, 2, generator=gen).to(io_dtype) * 0.3 for _ in range(3))
+        gamma = torch.sigmoid(torch.randn(K, n, H, generator=gen) + 2)
+        coef = torch.randn(K, n, H, 2, generator=gen)
+        slots = torch.tensor(live, dtype=torch.int32)
+        y = ops.pam_decode_step(pool, slots.to(DEV), q.to(DEV), k.to(DEV), v.to(DEV), gamma.to(DEV),
+                                coef.to(DEV), layer=layer)
+        S_in = np.transpose(ref[live, layer], (1, 0, 2, 3, 4))          # [K,n,H,d,d]
+        y_ref, S_new = po.recurrent_step(S_in, gamma.double().numpy(), po.to_complex(v.float().numpy()),
+                                         po.to_complex(k.float().numpy()), po.to_complex(q.float().numpy()),
+                                         coef=po.to_complex(coef.numpy()))
+        if state_dtype == torch.bfloat16:   # the pool rounds the stored state
+            S_new = po.to_complex(torch.from_numpy(po.to_split(S_new)).bfloat16().double().numpy())
+        ref[live, layer] = np.transpose(S_new, (1, 0, 2, 3, 4))
+        assert_close(y.float().cpu().numpy(), po.to_split(y_ref), tol, f"y step {step}")
+    assert_close(pool.float().cpu().numpy(), po.to_split(ref), tol, "pool")
+
+
+def test_out_of_range_slot_is_skipped():
+    pool = torch.zeros(2, 1, 1, 1, 16, 16, 2, device=DEV)
+    x = torch.ones(2, 1, 16, 2, device=DEV)
+    ops.pam_decode_step(pool, torch.tensor([-1, 1], dtype=torch.int32, device=DEV), x, x, x,
+                        torch.ones(1, 2, 1, device=DEV))
+    assert float(pool[0].abs().max()) == 0.0 and float(pool[1].abs().max()) > 0.0

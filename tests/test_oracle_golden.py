@@ -138,3 +138,26 @@ def test_ce_c2_loss(golden_dir):
     assert_close(r["dH"][g["rows"]], g["dh32"], 1e-5, "dH rows")
     assert_close(r["dW"][g["vrows"]], g["dw32"], 1e-5, "dW rows")
     assert_close(r["dH"][g["rows"]], g["dh"], 1e-2, "dH rows (reference bf16 grads)")
+
+
+def test_torch_port_matches_oracle():
+    """The multi-threaded CPU port used as the timed baseline computes what the oracle computes."""
+    from oracle import torch_port
+    inp = synthetic.scan_inputs(1, 2, 150, 16, seed=11)
+    y, dq, dk, dv, dg = torch_port.scan_fwd_bwd(inp.q.double(), inp.k.double(), inp.v.double(), inp.g.double(),
+                                                inp.dy.double(), 64)
+    q, k, v, dy = (po.to_complex(t.numpy()) for t in (inp.q, inp.k, inp.v, inp.dy))
+    gam = torch.sigmoid(inp.g.double()).numpy()
+    y_ref, _ = po.scan_recurrence(q, k, v, gam)
+    b = po.scan_backward(q, k, v, gam, dy)
+    assert_close(y.numpy(), po.to_split(y_ref), 1e-10, "Y")
+    assert_close(dq.numpy(), po.to_split(b["dq"]), 1e-10, "dq")
+    assert_close(dk.numpy(), po.to_split(b["dk"]), 1e-10, "dk")
+    assert_close(dv.numpy(), po.to_split(b["dv"]), 1e-10, "dv")
+    assert_close(dg.numpy(), b["dgamma"][0] * gam * (1 - gam), 1e-9, "dg")
+    c = synthetic.ce_inputs(100, 8, 300, seed=2, dtype=torch.float32)
+    loss, dh, dw = torch_port.linear_ce_fwd_bwd(c.h, c.w, c.targets, chunk=32)
+    r = ce_oracle.linear_ce(c.h.numpy(), c.w.numpy(), c.targets.numpy())
+    assert abs(float(loss) - r["loss"]) < 1e-5 * r["loss"]
+    assert_close(dh.numpy(), r["dH"], 1e-5, "dH")
+    assert_close(dw.numpy(), r["dW"], 1e-5, "dW")
