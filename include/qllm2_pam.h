@@ -185,6 +185,11 @@ long long qpam_launch_count(void);
 int qpam_profile_begin(void* stream);
 int qpam_profile_end(char* buf, size_t buf_bytes);
 
+/* Status word written by the tensor-core kernels: 0 = ok; a non-zero value means that a bounded
+ * on-device wait (mbarrier) gave up and the affected outputs are invalid.  Synchronises the
+ * device.  clear != 0 resets the word.  (No counterpart in the reference.) */
+int qpam_device_status(int32_t* status, int32_t clear);
+
 const char* qpam_last_error(void);
 /* "qllm2_pam_b200 <version> sm_100a" */
 const char* qpam_version(void);

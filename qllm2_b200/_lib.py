@@ -59,6 +59,7 @@ SIGNATURES = {
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),
+    "qpam_device_status": (c_int32, [C.POINTER(c_int32), c_int32]),
     "qpam_last_error": (C.c_char_p, []),
     "qpam_version": (C.c_char_p, []),
 }
@@ -128,3 +129,10 @@ def profile_end() -> dict:
         name, cnt, ms = line.rsplit(" ", 2)
         out[name] = (int(cnt), float(ms))
     return out
+
+
+def device_status(clear: bool = True) -> int:
+    """0 when every tensor-core kernel so far completed its on-device handshakes."""
+    v = c_int32(0)
+    check(lib().qpam_device_status(C.byref(v), 1 if clear else 0), "qpam_device_status")
+    return int(v.value)

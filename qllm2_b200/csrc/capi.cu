@@ -92,6 +92,18 @@ extern "C" int qpam_profile_end(char* buf, size_t buf_bytes) {
   return QPAM_OK;
 }
 
+namespace qpam {
+int ce_tc_device_status(int* value, bool clear);
+}
+
+extern "C" int qpam_device_status(int32_t* status, int32_t clear) {
+  int v = 0;
+  int rc = qpam::ce_tc_device_status(&v, clear != 0);
+  if (rc) return rc;
+  if (status) *status = v;
+  return QPAM_OK;
+}
+
 extern "C" const char* qpam_last_error(void) { return qpam::g_err; }
 
 extern "C" const char* qpam_version(void) { return "qllm2_pam_b200 0.1 sm_100a"; }

@@ -1,0 +1,285 @@
+// Warp-specialised bf16 GEMM on the 5th-generation tensor cores (tcgen05) for the tied-head
+// cross-entropy: D[128 x BN] tiles accumulate in TMEM (fp32), operands arrive through a TMA ->
+// shared-memory ring, and the epilogue reads TMEM with tcgen05.ld while the next tile's MMAs run
+// into the second accumulator buffer.
+//
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + MMA issue (one elected lane)
+//   warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4) .. +31 (= tile rows)
+//
+// A CTA owns one 128-row tile and walks the N tiles [n_begin, n_end) over the K blocks
+// [kb_begin, kb_end).  Operands may be K-major (rows of 64 K elements) or MN-major (rows of 64
+// M/N elements); both are 128-byte swizzled TMA boxes, see umma.cuh.
+#pragma once
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace qpam {
+namespace tc {
+
+constexpr int BM = 128, BK = 64;
+constexpr int NTHREADS = 192;
+
+enum Epi { EPI_STATS = 0, EPI_PROBS = 1, EPI_STORE = 2 };
+
+struct GemmParams {
+  // tile walk
+  int32_t n_tiles;          // N tiles in total
+  int32_t tiles_per_cta;    // N tiles walked by one CTA (blockIdx.x selects the range)
+  int32_t kb_total;         // K blocks in total
+  int32_t kb_per_split;     // K blocks per blockIdx.z
+  int64_t M, N;             // logical extents (rows / columns of D)
+  // EPI_STATS
+  const int64_t* targets;
+  int64_t v_offset, ignore_index;
+  float *pm, *ps, *pt, *pbest;
+  int32_t* pidx;
+  int64_t stats_ld;         // = rows of the whole problem (partials are [split][rows])
+  int64_t row_base;         // global row of tile row 0 of blockIdx.y == 0
+  // EPI_PROBS
+  __nv_bfloat16* pbuf;
+  int64_t ldp;
+  const float* lse;
+  const float* mask;
+  const float* grad_scale;
+  const float* denom;
+  // EPI_STORE
+  float* c;                 // [splits][M][ldc] fp32
+  int64_t ldc;
+  int32_t beta;             // 1: accumulate into c
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;                // 16 KB
+  static constexpr int B_BYTES = BN * BK * 2;                // 16 / 32 KB
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN, int EPI, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NTHREADS, 1)
+k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using namespace umma;
+  using C = Cfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;                      // [STAGES]
+  uint64_t* empty = bars + C::STAGES;         // [STAGES]
+  uint64_t* tfull = bars + 2 * C::STAGES;     // [2]
+  uint64_t* tempty = bars + 2 * C::STAGES + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_tile = blockIdx.y;
+  const int n_begin = blockIdx.x * p.tiles_per_cta;
+  const int n_end = min(p.n_tiles, n_begin + p.tiles_per_cta);
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
+  // after a failed handshake anywhere on the device, later CTAs do not start new work
+  const bool has_work = (n_begin < n_end) && (kb_begin < kb_end) &&
+                        (*reinterpret_cast<volatile int*>(&g_device_error) == 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc<C::TMEM_COLS>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (has_work) {
+    if (warp == 0) {
+      // ------------------------------------------------------------- TMA producer
+      if (elect_one()) {
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int n = n_begin; n < n_end && ok; ++n) {
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(&empty[stage], phase ^ 1, 101)) { ok = false; break; }
+            unsigned char* sa = smem + (size_t)stage * C::STAGE_BYTES;
+            unsigned char* sb = sa + C::A_BYTES;
+            mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
+            if (!A_MN) {
+              tma_load_2d(sa, &tmA, &full[stage], kb * BK, m_tile * BM);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_tile * BM + j * 64, kb * BK);
+            }
+            if (!B_MN) {
+              tma_load_2d(sb, &tmB, &full[stage], kb * BK, n * BN);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * 8192, &tmB, &full[stage], n * BN + j * 64, kb * BK);
+            }
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------- MMA issuer
+      if (elect_one()) {
+        constexpr uint32_t idesc = idesc_bf16(BM, BN, A_MN, B_MN);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int it = 0;
+        for (int n = n_begin; n < n_end && ok; ++n, ++it) {
+          const int buf = it & 1;
+          const uint32_t bphase = (it >> 1) & 1;
+          if (!mbar_wait(&tempty[buf], bphase ^ 1, 102)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!mbar_wait(&full[stage], phase, 103)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + (size_t)stage * C::STAGE_BYTES);
+            const uint32_t sb = sa + C::A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) {
+              const uint64_t ad = A_MN ? smem_desc_sw128(sa + kk * 2048, 8192, 1024) : smem_desc_sw128(sa + kk * 32, 16, 1024);
+              const uint64_t bd = B_MN ? smem_desc_sw128(sb + kk * 2048, 8192, 1024) : smem_desc_sw128(sb + kk * 32, 16, 1024);
+              mma_bf16(d_tmem, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
+            }
+            mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (ok) mma_commit(&tfull[buf]);
+        }
+      }
+    } else {
+      // ------------------------------------------------------------- epilogue (4 warps)
+      const int quarter = warp & 3;
+      const int r_tile = quarter * 32 + lane;                  // row within the tile == TMEM lane
+      const int64_t row = (int64_t)m_tile * BM + r_tile;       // row of D
+      const bool row_ok = row < p.M;
+      const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+      // EPI_STATS running state
+      float m_run = -INFINITY, s_run = 0.f, best = -INFINITY, tz = 0.f;
+      int bidx = 0x7fffffff;
+      int64_t tcol = -1;
+      float lse_r = 0.f, sc_r = 0.f;
+      if (EPI == EPI_STATS && row_ok && p.targets != nullptr) {
+        const int64_t t = p.targets[p.row_base + row];
+        if (t != p.ignore_index) tcol = t - p.v_offset;
+      }
+      if (EPI == EPI_PROBS && row_ok) {
+        const int64_t grow = p.row_base + row;
+        const int64_t t = p.targets[grow];
+        const bool valid = t != p.ignore_index;
+        tcol = valid ? t - p.v_offset : -1;
+        lse_r = p.lse[grow];
+        sc_r = valid ? (p.grad_scale[0] / p.denom[0]) * (p.mask ? p.mask[grow] : 1.f) : 0.f;
+      }
+      bool ok = true;
+      int it = 0;
+      for (int n = n_begin; n < n_end && ok; ++n, ++it) {
+        const int buf = it & 1;
+        const uint32_t bphase = (it >> 1) & 1;
+        if (!mbar_wait(&tfull[buf], bphase, 104)) { ok = false; break; }
+        tc_fence_after();
+        const int64_t col0 = (int64_t)n * BN;
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 32; ++cc) {
+          float v[32];
+          tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
+          const int64_t cbase = col0 + cc * 32;
+          if (EPI == EPI_STATS) {
+            if (cbase >= p.N) continue;
+            const int nvalid = (int)min((int64_t)32, p.N - cbase);
+            float cmax = -INFINITY;
+            int ci = 0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid && v[j] > cmax) { cmax = v[j]; ci = j; }
+            if (cmax > best) { best = cmax; bidx = (int)cbase + ci; }
+            const float m_new = fmaxf(m_run, cmax);
+            float se = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) se += __expf(v[j] - m_new);
+            s_run = s_run * __expf(m_run - m_new) + se;
+            m_run = m_new;
+            if (tcol >= cbase && tcol < cbase + 32) {
+              const int tj = (int)(tcol - cbase);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j == tj) tz = v[j];
+            }
+          } else if (EPI == EPI_PROBS) {
+            if (!row_ok || cbase >= p.ldp) continue;
+            __nv_bfloat16* dst = p.pbuf + row * p.ldp + cbase;
+            const int tj = (tcol >= cbase && tcol < cbase + 32) ? (int)(tcol - cbase) : -1;
+#pragma unroll
+            for (int g8 = 0; g8 < 4; ++g8) {
+              if (cbase + g8 * 8 + 8 > p.ldp) break;
+              uint4 pk;
+              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int j0 = g8 * 8 + 2 * j;
+                float a = __expf(v[j0] - lse_r);
+                float b = __expf(v[j0 + 1] - lse_r);
+                if (j0 == tj) a -= 1.f;
+                if (j0 + 1 == tj) b -= 1.f;
+                h2[j] = __floats2bfloat162_rn(a * sc_r, b * sc_r);
+              }
+              *reinterpret_cast<uint4*>(dst + g8 * 8) = pk;
+            }
+          } else {  // EPI_STORE
+            if (!row_ok || cbase >= p.N) continue;
+            float* dst = p.c + ((size_t)blockIdx.z * p.M + row) * p.ldc + cbase;
+#pragma unroll
+            for (int g4 = 0; g4 < 8; ++g4) {
+              if (cbase + g4 * 4 + 4 > p.N) break;
+              float4 o = make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+              if (p.beta) {
+                const float4 c0 = *reinterpret_cast<const float4*>(dst + g4 * 4);
+                o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+              }
+              *reinterpret_cast<float4*>(dst + g4 * 4) = o;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[buf]);
+      }
+      if (EPI == EPI_STATS && ok && row_ok) {
+        const size_t o = (size_t)blockIdx.x * p.stats_ld + p.row_base + row;
+        p.pm[o] = m_run;
+        p.ps[o] = s_run;
+        p.pt[o] = tz;
+        p.pbest[o] = best;
+        p.pidx[o] = bidx;
+      }
+    }
+  }
+  // ------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<C::TMEM_COLS>(tmem_base);
+  }
+}
+
+}  // namespace tc
+}  // namespace qpam

@@ -1,5 +1,6 @@
 // Host side of the fused tied-head cross-entropy: argument checks, workspace carving, launches.
 #include "tied_ce_kernels.cuh"
+#include "tied_ce_tc.cuh"
 
 namespace qpam {
 
@@ -10,7 +11,8 @@ struct CELayout {
   int32_t nsplit, tiles_per_split;
   int64_t ldp, chunk_rows;
   size_t off_pm, off_ps, off_pt, off_pbest, off_pidx, total_fwd;
-  size_t off_pbuf, off_dwacc, total_bwd;
+  size_t off_pbuf, off_dwacc, off_dhpart, total_bwd;
+  CETcPlan tc;  // tensor-core path (bf16 inputs)
 };
 
 static CELayout ce_layout(const qpam_ce_args* a) {
@@ -25,7 +27,9 @@ static CELayout ce_layout(const qpam_ce_args* a) {
   if (L.tiles_per_split < 1) L.tiles_per_split = 1;
   L.nsplit = (int32_t)((nvt + L.tiles_per_split - 1) / L.tiles_per_split);
   if (L.nsplit < 1) L.nsplit = 1;
-  const size_t n = (size_t)L.nsplit * (size_t)(a->N > 0 ? a->N : 1);
+  L.tc = ce_tc_plan(a);
+  const int32_t split_cap = (L.tc.enabled && L.tc.nsplit > L.nsplit) ? L.tc.nsplit : L.nsplit;
+  const size_t n = (size_t)split_cap * (size_t)(a->N > 0 ? a->N : 1);
   size_t off = 0;
   L.off_pm = off; off += ce_align(n * 4);
   L.off_ps = off; off += ce_align(n * 4);
@@ -41,9 +45,13 @@ static CELayout ce_layout(const qpam_ce_args* a) {
   const int64_t n_up = ((a->N + CE_TM - 1) / CE_TM) * CE_TM;
   if (rows > n_up) rows = n_up > 0 ? n_up : CE_TM;
   L.chunk_rows = rows;
-  L.off_pbuf = off; off += ce_align((size_t)rows * row_bytes);
+  size_t pbuf_bytes = (size_t)rows * row_bytes;
+  if (L.tc.enabled && (size_t)L.tc.chunk_rows * row_bytes > pbuf_bytes) pbuf_bytes = (size_t)L.tc.chunk_rows * row_bytes;
+  L.off_pbuf = off; off += ce_align(pbuf_bytes);
   L.off_dwacc = off;
   if (a->io_dtype != QPAM_F32) off += ce_align((size_t)a->V * a->F * 4);
+  L.off_dhpart = off;
+  if (L.tc.enabled) off += ce_align((size_t)L.tc.ksplit * L.tc.chunk_rows * a->F * 4);
   L.total_bwd = off;
   return L;
 }
@@ -72,6 +80,25 @@ static CEParams ce_params(const qpam_ce_args* a, const CELayout& L) {
   p.nsplit = L.nsplit; p.tiles_per_split = L.tiles_per_split;
   p.pbuf = ws + L.off_pbuf; p.ldp = L.ldp;
   return p;
+}
+
+static bool tc_usable(const qpam_ce_args* a, const CELayout& L) {
+  return L.tc.enabled && (((uintptr_t)a->h | (uintptr_t)a->w) & 15) == 0;
+}
+
+static CETcBuffers tc_buffers(const qpam_ce_args* a, const CELayout& L) {
+  char* ws = reinterpret_cast<char*>(a->workspace);
+  CETcBuffers b{};
+  b.pm = reinterpret_cast<float*>(ws + L.off_pm);
+  b.ps = reinterpret_cast<float*>(ws + L.off_ps);
+  b.pt = reinterpret_cast<float*>(ws + L.off_pt);
+  b.pbest = reinterpret_cast<float*>(ws + L.off_pbest);
+  b.pidx = reinterpret_cast<int32_t*>(ws + L.off_pidx);
+  b.pbuf = ws + L.off_pbuf;
+  b.ldp = L.ldp;
+  b.dh_part = reinterpret_cast<float*>(ws + L.off_dhpart);
+  b.dwacc = reinterpret_cast<float*>(ws + L.off_dwacc);
+  return b;
 }
 
 template <typename T>
@@ -145,6 +172,15 @@ extern "C" int qpam_ce_partial(const qpam_ce_args* a, float* row_max, float* row
   }
   if (a->N == 0) return QPAM_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tc_usable(a, L)) {
+    rc = ce_tc_partial(a, L.tc, tc_buffers(a, L), st);
+    if (rc) return rc;
+    CEParams p = ce_params(a, L);
+    p.nsplit = L.tc.nsplit;
+    k_ce_merge<<<(unsigned)((a->N + 255) / 256), 256, 0, st>>>(p, row_max, row_sumexp, row_tgt, row_argmax);
+    QPAM_LAUNCH_CHECK("k_ce_merge");
+    return QPAM_OK;
+  }
   return a->io_dtype == QPAM_BF16 ? ce_partial_t<__nv_bfloat16>(a, L, row_max, row_sumexp, row_tgt, row_argmax, st)
                                   : ce_partial_t<float>(a, L, row_max, row_sumexp, row_tgt, row_argmax, st);
 }
@@ -176,6 +212,8 @@ extern "C" int qpam_ce_bwd(const qpam_ce_args* a, const float* lse, const float*
     return QPAM_EWORKSPACE;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a->N > 0 && tc_usable(a, L) && ((uintptr_t)dh & 15) == 0 && ((uintptr_t)dw & 15) == 0)
+    return ce_tc_backward(a, L.tc, tc_buffers(a, L), lse, grad_scale, denom, dh, dw, st);
   return a->io_dtype == QPAM_BF16 ? ce_bwd_t<__nv_bfloat16>(a, L, lse, grad_scale, denom, dh, dw, st)
                                   : ce_bwd_t<float>(a, L, lse, grad_scale, denom, dh, dw, st);
 }

@@ -1,0 +1,209 @@
+// Tensor-core path of the fused tied-head cross-entropy (bf16 inputs): TMA descriptors, tile
+// plans and launches of k_tc_gemm.
+#include "tc_gemm.cuh"
+#include "tied_ce_tc.cuh"
+
+namespace qpam {
+
+// ------------------------------------------------------------------ TMA descriptors
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// Row-major bf16 matrix [outer][inner] with `row_stride` elements between rows; boxes of
+// box_inner x box_outer elements, 128-byte swizzle, out-of-range elements read as zero.
+static int make_map(CUtensorMap* m, const void* base, int64_t inner, int64_t outer, int64_t row_stride,
+                    int box_inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return QPAM_ECUDA;
+  }
+  QPAM_REQUIRE(((uintptr_t)base & 15) == 0 && (row_stride * 2) % 16 == 0, "TMA operand is not 16-byte aligned");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)row_stride * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (inner=%lld outer=%lld stride=%lld box=%dx%d)", (int)r,
+              (long long)inner, (long long)outer, (long long)row_stride, box_inner, box_outer);
+    return QPAM_ECUDA;
+  }
+  return QPAM_OK;
+}
+
+template <typename K>
+static int opt_in_smem(K kern, size_t bytes) {
+  QPAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  return QPAM_OK;
+}
+
+// ------------------------------------------------------------------ plan
+CETcPlan ce_tc_plan(const qpam_ce_args* a) {
+  CETcPlan pl{};
+  pl.enabled = a->io_dtype == QPAM_BF16 && (a->F % 8) == 0 && a->N > 0;
+  pl.n_tiles = (int32_t)((a->V + 255) / 256);
+  const int64_t row_tiles = (a->N + tc::BM - 1) / tc::BM;
+  // vocabulary splits: fill the 148 SMs in whole waves (one CTA per SM: the ring takes ~193 KB)
+  int best = 1;
+  double best_eff = -1.0;
+  const int max_split = pl.n_tiles < 64 ? pl.n_tiles : 64;
+  for (int s = 1; s <= max_split; ++s) {
+    const int tps = (pl.n_tiles + s - 1) / s;
+    const int real = (pl.n_tiles + tps - 1) / tps;
+    if (real != s) continue;
+    const double ctas = (double)row_tiles * s;
+    const double waves = (ctas + 147) / 148;
+    const double eff = ctas / ((double)(int64_t)waves * 148) * ((double)pl.n_tiles / ((double)tps * s));
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+  }
+  pl.nsplit = best;
+  pl.tiles_per_split = (pl.n_tiles + best - 1) / best;
+  int64_t rows = ((a->N + tc::BM - 1) / tc::BM) * tc::BM;
+  if (rows > 4096) rows = 4096;
+  if (rows < tc::BM) rows = tc::BM;
+  pl.chunk_rows = rows;
+  const int64_t f_tiles = (a->F + 255) / 256;
+  int64_t ks = (296 + f_tiles * (rows / tc::BM) - 1) / (f_tiles * (rows / tc::BM));
+  const int64_t kb_total = (a->V + tc::BK - 1) / tc::BK;
+  if (ks > 8) ks = 8;
+  if (ks > kb_total) ks = kb_total;
+  if (ks < 1) ks = 1;
+  pl.ksplit = (int32_t)ks;
+  return pl;
+}
+
+// ------------------------------------------------------------------ forward statistics
+int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& b, cudaStream_t st) {
+  CUtensorMap tmH, tmW;
+  int rc = make_map(&tmH, a->h, a->F, a->N, a->F, tc::BK, tc::BM);
+  if (rc) return rc;
+  rc = make_map(&tmW, a->w, a->F, a->V, a->F, tc::BK, 256);
+  if (rc) return rc;
+  tc::GemmParams p{};
+  p.n_tiles = pl.n_tiles;
+  p.tiles_per_cta = pl.tiles_per_split;
+  p.kb_total = (a->F + tc::BK - 1) / tc::BK;
+  p.kb_per_split = p.kb_total;
+  p.M = a->N; p.N = a->V;
+  p.targets = a->targets; p.v_offset = a->v_offset; p.ignore_index = a->ignore_index;
+  p.pm = b.pm; p.ps = b.ps; p.pt = b.pt; p.pbest = b.pbest; p.pidx = b.pidx;
+  p.stats_ld = a->N; p.row_base = 0;
+  auto kern = tc::k_tc_gemm<256, tc::EPI_STATS, false, false>;
+  rc = opt_in_smem(kern, tc::Cfg<256>::SMEM_BYTES);
+  if (rc) return rc;
+  const unsigned row_tiles = (unsigned)((a->N + tc::BM - 1) / tc::BM);
+  kern<<<dim3(pl.nsplit, row_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmH, tmW, p);
+  QPAM_LAUNCH_CHECK("k_tc_gemm<stats>");
+  return QPAM_OK;
+}
+
+// ------------------------------------------------------------------ backward
+__global__ void k_reduce_splits_bf16(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int64_t n,
+                                     int splits, int64_t split_stride) {
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(part + i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 x = *reinterpret_cast<const float4*>(part + s * split_stride + i);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + i) = pk;
+  }
+}
+
+int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& b, const float* lse,
+                   const float* grad_scale, const float* denom, void* dh, void* dw, cudaStream_t st) {
+  const int F = a->F;
+  const int64_t V = a->V;
+  auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false>;
+  auto k_dh = tc::k_tc_gemm<256, tc::EPI_STORE, false, true>;
+  auto k_dw = tc::k_tc_gemm<256, tc::EPI_STORE, true, true>;
+  int rc = opt_in_smem(k_probs, tc::Cfg<256>::SMEM_BYTES);
+  if (rc) return rc;
+  rc = opt_in_smem(k_dh, tc::Cfg<256>::SMEM_BYTES);
+  if (rc) return rc;
+  rc = opt_in_smem(k_dw, tc::Cfg<256>::SMEM_BYTES);
+  if (rc) return rc;
+  CUtensorMap tmWk, tmWmn;
+  rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 256);   // K-major B of the logits GEMM
+  if (rc) return rc;
+  rc = make_map(&tmWmn, a->w, F, V, F, 64, 64);        // MN-major B of dH = P W   ([K=V][N=F])
+  if (rc) return rc;
+  const int f_tiles = (F + 255) / 256;
+  int first = 1;
+  for (int64_t r0 = 0; r0 < a->N; r0 += pl.chunk_rows) {
+    const int64_t rows = (a->N - r0 < pl.chunk_rows) ? a->N - r0 : pl.chunk_rows;
+    const unsigned row_tiles = (unsigned)((rows + tc::BM - 1) / tc::BM);
+    const __nv_bfloat16* hchunk = reinterpret_cast<const __nv_bfloat16*>(a->h) + r0 * F;
+    CUtensorMap tmHk, tmHmn, tmPk, tmPmn;
+    if ((rc = make_map(&tmHk, hchunk, F, rows, F, tc::BK, tc::BM))) return rc;       // A of logits
+    if ((rc = make_map(&tmHmn, hchunk, F, rows, F, 64, 64))) return rc;              // MN-major B of dW ([K=rows][N=F])
+    if ((rc = make_map(&tmPk, b.pbuf, V, rows, b.ldp, tc::BK, tc::BM))) return rc;   // K-major A of dH ([M=rows][K=V])
+    if ((rc = make_map(&tmPmn, b.pbuf, V, rows, b.ldp, 64, 64))) return rc;          // MN-major A of dW ([K=rows][M=V])
+    // 1) P = (softmax - onehot) * scale, bf16, one 128 x 256 tile per CTA
+    tc::GemmParams p{};
+    p.n_tiles = pl.n_tiles; p.tiles_per_cta = 1;
+    p.kb_total = (F + tc::BK - 1) / tc::BK; p.kb_per_split = p.kb_total;
+    p.M = rows; p.N = V;
+    p.targets = a->targets; p.v_offset = a->v_offset; p.ignore_index = a->ignore_index;
+    p.row_base = r0;
+    p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
+    p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
+    k_probs<<<dim3(pl.n_tiles, row_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
+    QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
+    // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
+    tc::GemmParams g{};
+    g.n_tiles = f_tiles; g.tiles_per_cta = 1;
+    g.kb_total = (int32_t)((V + tc::BK - 1) / tc::BK);
+    g.kb_per_split = (g.kb_total + pl.ksplit - 1) / pl.ksplit;
+    const int ks = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
+    g.M = rows; g.N = F;
+    g.c = b.dh_part; g.ldc = F; g.beta = 0;
+    k_dh<<<dim3(f_tiles, row_tiles, ks), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmPk, tmWmn, g);
+    QPAM_LAUNCH_CHECK("k_tc_gemm<dH>");
+    k_reduce_splits_bf16<<<592, 256, 0, st>>>(b.dh_part, reinterpret_cast<__nv_bfloat16*>(dh) + r0 * F, rows * F, ks,
+                                             rows * F);
+    QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
+    // 3) dW (+)= P^T H[r0:r0+rows]
+    tc::GemmParams w{};
+    w.n_tiles = f_tiles; w.tiles_per_cta = 1;
+    w.kb_total = (int32_t)((rows + tc::BK - 1) / tc::BK); w.kb_per_split = w.kb_total;
+    w.M = V; w.N = F;
+    w.c = b.dwacc; w.ldc = F; w.beta = first ? 0 : 1;
+    k_dw<<<dim3(f_tiles, (unsigned)((V + tc::BM - 1) / tc::BM), 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(
+        tmPmn, tmHmn, w);
+    QPAM_LAUNCH_CHECK("k_tc_gemm<dW>");
+    first = 0;
+  }
+  k_reduce_splits_bf16<<<1184, 256, 0, st>>>(b.dwacc, reinterpret_cast<__nv_bfloat16*>(dw), V * (int64_t)F, 1, 0);
+  QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
+  return QPAM_OK;
+}
+
+}  // namespace qpam
+
+namespace qpam {
+int ce_tc_device_status(int* value, bool clear) {
+  QPAM_CUDA(umma::read_device_error(value, clear));
+  return QPAM_OK;
+}
+}  // namespace qpam

@@ -1,0 +1,53 @@
+"""Tensor-core (tcgen05) path of the fused cross-entropy: bf16 inputs of assorted shapes vs the
+fp64 oracle on the same bf16-rounded values.  Loss 1e-5 relative, gradients 2e-2 relative."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ce_oracle
+from qllm2_b200 import _lib, fused_ce, ops, synthetic
+from tests.helpers import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("N,D,V", [(128, 32, 256), (300, 64, 1000), (64, 32, 130), (1000, 96, 5003), (129, 8, 257)])
+def test_bf16_shapes(N, D, V):
+    c = synthetic.ce_inputs(N, D, V, seed=N + V, dtype=torch.bfloat16)
+    w_host = (c.w.float() * 20).bfloat16()          # spread the logits so softmax is not flat
+    t_host = c.targets.clone()
+    t_host[::5] = -100
+    h = c.h.to(DEV).requires_grad_(True)
+    w = w_host.to(DEV).requires_grad_(True)
+    t = t_host.to(DEV)
+    loss = fused_ce.fused_linear_cross_entropy(h, w, t)
+    loss.backward()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    r = ce_oracle.linear_ce(c.h.float().numpy(), w_host.float().numpy(), t_host.numpy())
+    assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"]), (float(loss.detach()), r["loss"])
+    assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
+    assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
+    ids, best = ops.head_argmax(h.detach(), w.detach())
+    z = ce_oracle.head_logits(c.h.float().numpy(), w_host.float().numpy())
+    top2 = np.sort(z, axis=1)[:, -2:]
+    clear = (top2[:, 1] - top2[:, 0]) > 1e-4       # ignore numerically tied rows
+    assert np.array_equal(ids.cpu().numpy()[clear], z.argmax(1)[clear])
+    assert_close(best.cpu().numpy(), z.max(1), 1e-5, "best logit")
+
+
+def test_masked_and_scaled():
+    c = synthetic.ce_inputs(260, 64, 700, seed=3, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(1)
+    mask = (torch.rand(260, generator=gen) > 0.4).float()
+    h = c.h.to(DEV).requires_grad_(True)
+    w = (c.w.float() * 20).bfloat16().to(DEV).requires_grad_(True)
+    loss = fused_ce.fused_linear_cross_entropy(h, w, c.targets.to(DEV), mask=mask.to(DEV))
+    (2.5 * loss).backward()
+    r = ce_oracle.linear_ce(c.h.float().numpy(), w.detach().float().cpu().numpy(), c.targets.numpy(),
+                            mask=mask.numpy(), grad_output=2.5)
+    assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"])
+    assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
+    assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
+    assert _lib.device_status() == 0
