@@ -86,6 +86,23 @@ size_t qpam_scan_workspace_bytes(const qpam_scan_args* args, int32_t with_backwa
  * qpam_scan_bwd with the SAME workspace contents may pass states_valid=1 to reuse them. */
 int qpam_scan_fwd(const qpam_scan_args* args, void* stream);
 
+/* Forward scan with no workspace argument, for hosts that are not allowed to allocate device
+ * memory: a server whose memory pool took the whole GPU at start-up, a sandboxed plugin, or a
+ * latency-critical loop where cudaMalloc (which may synchronise the device) is forbidden.  The
+ * workspace lives in a QPAM_STATIC_SCRATCH_BYTES array inside the library image; every GPU that
+ * loads the library holds that much memory until the process exits.  `workspace` and
+ * `workspace_bytes` of `args` are ignored; all other fields mean what they mean for
+ * qpam_scan_fwd and the results are identical.  Shapes whose forward workspace
+ * (qpam_scan_workspace_bytes(args, 0)) exceeds the array are refused with QPAM_EWORKSPACE.
+ * The first call on each device looks up the array's device address (device must be current;
+ * make that first call before any stream capture).  No cudaMalloc/cudaFree is issued.  All calls
+ * share the one array: it keeps the previous call's contents (every byte that is read is
+ * written first, so nothing needs clearing) and two calls that overlap on the GPU -- different
+ * streams or processes' threads -- race on it.  The backward pass is not offered in this form.
+ * This entry point has no counterpart in the reference. */
+#define QPAM_STATIC_SCRATCH_BYTES (32u << 20)
+int qpam_scan_fwd_static(const qpam_scan_args* args, void* stream);
+
 /* Backward of qpam_scan_fwd w.r.t. q, k, v, gamma (and coef when coef != NULL).
  * Replaces torch autograd through the functions above, including _FusedDecayMatrixFn.backward
  * (v11/triton_kernels.py:447-480).  Exact for gamma + gamma_eps <= 1.

@@ -1,4 +1,6 @@
 // Host side of the chunked PAM scan: argument checks, workspace carving, launches.
+#include <mutex>
+
 #include "pam_scan_chunk.cuh"
 
 namespace qpam {
@@ -205,4 +207,49 @@ extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, 
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   QPAM_DISPATCH_SCAN(scan_bwd_t, a, L, dy, dq, dk, dv, dgamma, dcoef, ds_final, ds0, states_valid, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Forward scan for callers that cannot allocate device memory.
+//
+// Some hosts hand the whole GPU to one memory pool at start-up (an inference server, a plugin
+// sandbox) or run a latency-critical loop in which cudaMalloc -- which may synchronise the
+// device -- is off limits.  Such a caller has nowhere to get the scan's workspace from.  This
+// entry point keeps that workspace in a fixed array that is part of the library image itself.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_scan_static_scratch[QPAM_STATIC_SCRATCH_BYTES];
+
+namespace qpam {
+static std::mutex g_static_mu;
+static void* g_static_ptr[64] = {nullptr};  // device address of the array, per device ordinal
+}  // namespace qpam
+
+extern "C" int qpam_scan_fwd_static(const qpam_scan_args* a, void* stream) {
+  QPAM_REQUIRE(a != nullptr, "scan (static scratch): args is NULL");
+  int dev = -1;
+  QPAM_CUDA(cudaGetDevice(&dev));
+  QPAM_REQUIRE(dev >= 0 && dev < 64, "scan (static scratch): device ordinal %d out of range", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      // In host code the array's name is only a handle; the kernels need its device address.
+      void* ptr = nullptr;
+      QPAM_CUDA(cudaGetSymbolAddress(&ptr, g_scan_static_scratch));
+      g_static_ptr[dev] = ptr;
+    }
+    scratch = g_static_ptr[dev];
+  }
+  qpam_scan_args b = *a;
+  b.workspace = scratch;
+  b.workspace_bytes = QPAM_STATIC_SCRATCH_BYTES;
+  int rc = check_scan_args(&b);
+  if (rc) return rc;
+  const ScanLayout L = scan_layout(&b);
+  if (L.total_fwd > (size_t)QPAM_STATIC_SCRATCH_BYTES) {
+    set_error("scan (static scratch): this shape needs %zu bytes of workspace, the built-in scratch holds %zu; "
+              "use qpam_scan_fwd with a caller-provided workspace", L.total_fwd, (size_t)QPAM_STATIC_SCRATCH_BYTES);
+    return QPAM_EWORKSPACE;
+  }
+  return qpam_scan_fwd(&b, stream);
 }
