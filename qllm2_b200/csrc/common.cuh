@@ -83,7 +83,7 @@ __device__ __forceinline__ void cfma(float2& acc, float2 a, float2 b) {
 
 // ------------------------------------------------------------------ chunk geometry
 // The scan tiles every sequence into chunks of CH tokens; chunks never straddle a sequence
-// boundary.  Sequence s owns state slots [slot_base(s), slot_base(s)+nchunks(s)] (one more
+// boundary (CH is the tile of the FFMA kernels; ChunkGeom::ch is the tile in use).  Sequence s owns state slots [slot_base(s), slot_base(s)+nchunks(s)] (one more
 // slot than chunks: slot c holds the state BEFORE chunk c, the last the final state).
 constexpr int CH = 64;
 
@@ -93,6 +93,7 @@ struct ChunkGeom {
   int32_t S;                    // sequences
   int32_t T;                    // tokens per sequence (batch mode) / packed total
   int32_t nc_uniform;           // chunks per sequence in batch mode
+  int32_t ch;                   // tokens per chunk (64 for the FFMA kernels, 128 for the tensor-core ones)
 };
 
 struct ChunkLoc {
@@ -116,8 +117,8 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const ChunkGeom& g, int32_t x) 
     L.c = x - seq * g.nc_uniform;
     L.nc = g.nc_uniform;
     L.b = seq;
-    L.t0 = L.c * CH;
-    L.len = min(CH, g.T - L.t0);
+    L.t0 = L.c * g.ch;
+    L.len = min(g.ch, g.T - L.t0);
     L.slot0 = (int64_t)seq * (g.nc_uniform + 1);
     L.valid = true;
     return L;
@@ -133,8 +134,8 @@ __device__ __forceinline__ ChunkLoc locate_chunk(const ChunkGeom& g, int32_t x) 
   L.nc = g.chunk_prefix[lo + 1] - g.chunk_prefix[lo];
   L.b = 0;
   const int32_t a = g.cu_seqlens[lo], e = g.cu_seqlens[lo + 1];
-  L.t0 = a + L.c * CH;
-  L.len = min(CH, e - L.t0);
+  L.t0 = a + L.c * g.ch;
+  L.len = min(g.ch, e - L.t0);
   L.slot0 = (int64_t)g.chunk_prefix[lo] + lo;
   L.valid = true;
   return L;

@@ -2,6 +2,8 @@
 #include <mutex>
 
 #include "pam_scan_chunk.cuh"
+#include "pam_scan_tc.cuh"
+#include "tma_host.cuh"
 
 namespace qpam {
 
@@ -9,23 +11,35 @@ static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 struct ScanLayout {
   int64_t nslots;
+  int32_t ch;           // tokens per chunk of this layout
   int32_t nc_uniform;
   int32_t grid_chunks;  // upper bound on the number of chunks (grid.x of the chunk kernels)
   size_t off_prefix, off_states, off_decay, off_dstates, total_fwd, total_bwd;
 };
 
-static ScanLayout scan_layout(const qpam_scan_args* a) {
+// Tensor-core kernels take bf16 token tensors with head dim 64 and a single state; their chunk is
+// 128 tokens.  Everything else runs the FFMA kernels on 64-token chunks.
+static bool tc_fwd_eligible(const qpam_scan_args* a) {
+  return a->io_dtype == QPAM_BF16 && a->d == 64 && a->K == 1 && a->coef == nullptr &&
+         (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->y) & 15) == 0 &&
+         (int64_t)a->B * a->H * a->T < ((int64_t)1 << 31);
+}
+static int fwd_chunk_len(const qpam_scan_args* a) { return tc_fwd_eligible(a) ? tcs::TC : CH; }
+static int bwd_chunk_len(const qpam_scan_args*) { return CH; }
+
+static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   ScanLayout L{};
   const int64_t S = a->S;
   const int64_t dd = (int64_t)a->d * a->d;
+  L.ch = ch;
   if (a->cu_seqlens == nullptr) {
-    L.nc_uniform = (a->T + CH - 1) / CH;
+    L.nc_uniform = (a->T + ch - 1) / ch;
     L.nslots = S * (L.nc_uniform + 1);
     L.grid_chunks = (int32_t)(S * L.nc_uniform);
   } else {
     L.nc_uniform = 0;
-    L.nslots = a->T / CH + 2 * S;
-    L.grid_chunks = (int32_t)(a->T / CH + S);
+    L.nslots = a->T / ch + 2 * S;
+    L.grid_chunks = (int32_t)(a->T / ch + S);
   }
   size_t off = 0;
   L.off_prefix = off;
@@ -73,7 +87,7 @@ static ScanParams make_params(const qpam_scan_args* a, const ScanLayout& L) {
   p.s0 = a->s0; p.s_final = a->s_final;
   p.geom.cu_seqlens = a->cu_seqlens;
   p.geom.chunk_prefix = reinterpret_cast<const int32_t*>(ws + L.off_prefix);
-  p.geom.S = a->S; p.geom.T = a->T; p.geom.nc_uniform = L.nc_uniform;
+  p.geom.S = a->S; p.geom.T = a->T; p.geom.nc_uniform = L.nc_uniform; p.geom.ch = L.ch;
   p.nslots = L.nslots;
   p.B = a->B; p.H = a->H; p.T = a->T; p.K = a->K;
   p.q_scale = a->q_scale; p.eps = a->gamma_eps;
@@ -93,7 +107,7 @@ template <int D, typename T>
 static int launch_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
   // chunk-local state sums, then the carry over the chunk axis
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S);
+    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   if (L.grid_chunks > 0) {
@@ -120,6 +134,36 @@ static int scan_fwd_t(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t
     if (rc) return rc;
     kern<<<dim3(L.grid_chunks, a->H), NT, fwd_chunk_smem<D>(), st>>>(p);
     QPAM_LAUNCH_CHECK("k_fwd_chunk");
+  }
+  return QPAM_OK;
+}
+
+// bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
+static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  if (a->cu_seqlens != nullptr) {
+    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+    QPAM_LAUNCH_CHECK("k_chunk_prefix");
+  }
+  int rc;
+  if (L.grid_chunks > 0) {
+    rc = set_smem(tcs::k_tc_chunk_outer, tcs::OUTER_SMEM);
+    if (rc) return rc;
+    tcs::k_tc_chunk_outer<<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
+  }
+  k_state_scan<false><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
+  QPAM_LAUNCH_CHECK("k_state_scan<fwd>");
+  if (L.grid_chunks > 0 && a->y != nullptr) {
+    tcs::TcMaps maps;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&maps.q, a->q, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.k, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.v, a->v, 128, rows, 128, 64, 128))) return rc;
+    rc = set_smem(tcs::k_tc_fwd_chunk, tcs::FWD_SMEM);
+    if (rc) return rc;
+    tcs::k_tc_fwd_chunk<<<dim3(L.grid_chunks, a->H), 256, tcs::FWD_SMEM, st>>>(maps, p);
+    QPAM_LAUNCH_CHECK("k_tc_fwd_chunk");
   }
   return QPAM_OK;
 }
@@ -166,7 +210,7 @@ using namespace qpam;
 
 extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t with_backward) {
   if (a == nullptr || a->d <= 0 || a->K <= 0 || a->H <= 0 || a->S <= 0 || a->T < 0) return 0;
-  const ScanLayout L = scan_layout(a);
+  const ScanLayout L = scan_layout(a, CH);  // the 64-token layout is the larger one
   return with_backward ? L.total_bwd : L.total_fwd;
 }
 
@@ -183,13 +227,14 @@ extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t wit
 extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) {
   int rc = check_scan_args(a);
   if (rc) return rc;
-  const ScanLayout L = scan_layout(a);
+  const ScanLayout L = scan_layout(a, fwd_chunk_len(a));
   if (a->workspace_bytes < L.total_fwd) {
     set_error("scan fwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_fwd);
     return QPAM_EWORKSPACE;
   }
   QPAM_REQUIRE(a->y != nullptr || a->s_final != nullptr, "scan fwd: both y and s_final are NULL");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (L.ch == tcs::TC) return scan_fwd_tc(a, L, st);
   QPAM_DISPATCH_SCAN(scan_fwd_t, a, L, st);
 }
 
@@ -200,7 +245,8 @@ extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, 
   if (rc) return rc;
   QPAM_REQUIRE(dy && dq && dk && dv && dgamma, "scan bwd: dy/dq/dk/dv/dgamma must not be NULL");
   QPAM_REQUIRE(dcoef == nullptr || a->coef != nullptr, "scan bwd: dcoef requested but coef is NULL");
-  const ScanLayout L = scan_layout(a);
+  const ScanLayout L = scan_layout(a, bwd_chunk_len(a));
+  if (fwd_chunk_len(a) != L.ch) states_valid = 0;  // the forward left states of another chunking
   if (a->workspace_bytes < L.total_bwd) {
     set_error("scan bwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_bwd);
     return QPAM_EWORKSPACE;
@@ -245,7 +291,7 @@ extern "C" int qpam_scan_fwd_static(const qpam_scan_args* a, void* stream) {
   b.workspace_bytes = QPAM_STATIC_SCRATCH_BYTES;
   int rc = check_scan_args(&b);
   if (rc) return rc;
-  const ScanLayout L = scan_layout(&b);
+  const ScanLayout L = scan_layout(&b, CH);
   if (L.total_fwd > (size_t)QPAM_STATIC_SCRATCH_BYTES) {
     set_error("scan (static scratch): this shape needs %zu bytes of workspace, the built-in scratch holds %zu; "
               "use qpam_scan_fwd with a caller-provided workspace", L.total_fwd, (size_t)QPAM_STATIC_SCRATCH_BYTES);

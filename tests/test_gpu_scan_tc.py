@@ -1,0 +1,57 @@
+"""Tensor-core (tcgen05) scan kernels: bf16 token tensors, head dim 64, one state.
+Reference = fp64 oracle on the same bf16-rounded inputs; tolerance 2e-2 relative."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import pam_oracle as po
+from qllm2_b200 import _lib, ops, synthetic
+from tests.helpers import assert_close, rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 2e-2
+
+
+@pytest.mark.parametrize("B,H,T", [(1, 1, 128), (2, 3, 300), (1, 2, 1), (1, 1, 129), (2, 2, 1024), (1, 1, 77)])
+def test_forward_shapes(B, H, T):
+    inp = synthetic.scan_inputs(B, H, T, 64, seed=60 + T, dtype=torch.bfloat16)
+    y, s = ops.pam_scan(inp.q.to(DEV), inp.k.to(DEV), inp.v.to(DEV), inp.gamma.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    q, k, v = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v))
+    y_ref, s_ref = po.scan_recurrence(q, k, v, inp.gamma.double().numpy())
+    assert_close(y.float().cpu().numpy(), po.to_split(y_ref), TOL, "Y")
+    assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S")
+    # typical error is far below the bar; catch silent degradations early
+    assert rel_err(y.float().cpu().numpy(), po.to_split(y_ref)) < 8e-3
+
+
+def test_forward_initial_state_and_varlen():
+    p = synthetic.packed_inputs(4, 100, 600, 3, 64, seed=9, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(2)
+    s0 = torch.randn(1, 4, 3, 64, 64, 2, generator=gen) * 0.05
+    q, k, v = (t.unsqueeze(0).to(DEV) for t in (p.q, p.k, p.v))
+    y, s = ops.pam_scan(q, k, v, p.gamma.unsqueeze(0).to(DEV), s0=s0.to(DEV), cu_seqlens=p.cu_seqlens)
+    assert _lib.device_status() == 0
+    qc, kc, vc = (po.to_complex(t.float().numpy()) for t in (p.q, p.k, p.v))
+    y_ref, s_ref = po.scan_varlen(qc, kc, vc, p.gamma.double().numpy(), p.cu_seqlens.numpy(),
+                                  s0=po.to_complex(s0.numpy()))
+    assert_close(y[0].float().cpu().numpy(), po.to_split(y_ref), TOL, "Y packed")
+    assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S packed")
+
+
+def test_forward_then_backward_mixed_paths():
+    """Forward on tensor cores, backward on its own chunking: gradients still match the oracle."""
+    inp = synthetic.scan_inputs(1, 2, 260, 64, seed=70, dtype=torch.bfloat16)
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+    g = inp.g.to(DEV).requires_grad_(True)
+    y, _ = ops.pam_scan(q, k, v, torch.sigmoid(g))
+    dq, dk, dv, dg = torch.autograd.grad(y, [q, k, v, g], inp.dy.to(DEV))
+    qc, kc, vc, dyc = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v, inp.dy))
+    gam = torch.sigmoid(inp.g.double()).numpy()
+    b = po.scan_backward(qc, kc, vc, gam, dyc)
+    assert_close(dq.float().cpu().numpy(), po.to_split(b["dq"]), TOL, "dq")
+    assert_close(dk.float().cpu().numpy(), po.to_split(b["dk"]), TOL, "dk")
+    assert_close(dv.float().cpu().numpy(), po.to_split(b["dv"]), TOL, "dv")
+    assert_close(dg.cpu().numpy(), b["dgamma"][0] * gam * (1 - gam), TOL, "dg")
