@@ -25,7 +25,6 @@ static bool tc_fwd_eligible(const qpam_scan_args* a) {
          (int64_t)a->B * a->H * a->T < ((int64_t)1 << 31);
 }
 static int fwd_chunk_len(const qpam_scan_args* a) { return tc_fwd_eligible(a) ? tcs::TC : CH; }
-static int bwd_chunk_len(const qpam_scan_args*) { return CH; }
 
 static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   ScanLayout L{};
@@ -138,6 +137,36 @@ static int scan_fwd_t(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t
   return QPAM_OK;
 }
 
+// chunk-local state sums on tensor cores, then the carry over the chunk axis
+static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
+  if (L.grid_chunks > 0) {
+    int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);
+    if (rc) return rc;
+    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
+  }
+  k_state_scan<false><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
+  QPAM_LAUNCH_CHECK("k_state_scan<fwd>");
+  return QPAM_OK;
+}
+
+template <int MODE>
+static int tc_chunk_launch(const qpam_scan_args* a, const ScanLayout& L, const ScanParams& p, const void* a1,
+                           const void* b1, const void* x2, const char* name, cudaStream_t st) {
+  tcs::ChunkMaps maps;
+  const int64_t rows = (int64_t)a->B * a->H * a->T;
+  int rc;
+  if ((rc = make_map(&maps.a1, a1, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.b1, b1, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.x2, x2, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = set_smem(tcs::k_tc_chunk<MODE>, tcs::CHUNK_SMEM))) return rc;
+  tcs::k_tc_chunk<MODE><<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK_SMEM, st>>>(maps, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, name);
+  note_launch(name, st);
+  return QPAM_OK;
+}
+
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
 static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
   ScanParams p = make_params(a, L);
@@ -146,24 +175,45 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   int rc;
-  if (L.grid_chunks > 0) {
-    rc = set_smem(tcs::k_tc_chunk_outer, tcs::OUTER_SMEM);
-    if (rc) return rc;
-    tcs::k_tc_chunk_outer<<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
-    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
-  }
-  k_state_scan<false><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
-  QPAM_LAUNCH_CHECK("k_state_scan<fwd>");
+  rc = tc_states(p, L, a, st);
+  if (rc) return rc;
   if (L.grid_chunks > 0 && a->y != nullptr) {
-    tcs::TcMaps maps;
-    const int64_t rows = (int64_t)a->B * a->H * a->T;
-    if ((rc = make_map(&maps.q, a->q, 128, rows, 128, 64, 128))) return rc;
-    if ((rc = make_map(&maps.k, a->k, 128, rows, 128, 64, 128))) return rc;
-    if ((rc = make_map(&maps.v, a->v, 128, rows, 128, 64, 128))) return rc;
-    rc = set_smem(tcs::k_tc_fwd_chunk, tcs::FWD_SMEM);
+    rc = tc_chunk_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
     if (rc) return rc;
-    tcs::k_tc_fwd_chunk<<<dim3(L.grid_chunks, a->H), 256, tcs::FWD_SMEM, st>>>(maps, p);
-    QPAM_LAUNCH_CHECK("k_tc_fwd_chunk");
+  }
+  return QPAM_OK;
+}
+
+static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk, void* dv,
+                       float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  p.dy = dy; p.dq = dq; p.dk = dk; p.dv = dv;
+  p.dgamma = dgamma; p.dcoef = nullptr; p.ds_final = ds_final; p.ds0 = ds0;
+  int rc;
+  if (!states_valid) {
+    ScanParams pf = p;
+    pf.s_final = nullptr;
+    if (a->cu_seqlens != nullptr) {
+      k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+      QPAM_LAUNCH_CHECK("k_chunk_prefix");
+    }
+    rc = tc_states(pf, L, a, st);
+    if (rc) return rc;
+  }
+  if (L.grid_chunks > 0) {
+    rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
+    if (rc) return rc;
+    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<dstate>");
+  }
+  k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
+  QPAM_LAUNCH_CHECK("k_state_scan<rev>");
+  if (L.grid_chunks > 0) {
+    if ((rc = tc_chunk_launch<tcs::M_DV>(a, L, p, a->q, a->k, dy, "k_tc_chunk<dv>", st))) return rc;
+    if ((rc = tc_chunk_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
+    if ((rc = tc_chunk_launch<tcs::M_DK>(a, L, p, dy, a->v, a->q, "k_tc_chunk<dk>", st))) return rc;
+    k_dgamma_finalize<<<dim3(a->S, a->H, 1), 256, 0, st>>>(p, 64);
+    QPAM_LAUNCH_CHECK("k_dgamma_finalize");
   }
   return QPAM_OK;
 }
@@ -245,13 +295,16 @@ extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, 
   if (rc) return rc;
   QPAM_REQUIRE(dy && dq && dk && dv && dgamma, "scan bwd: dy/dq/dk/dv/dgamma must not be NULL");
   QPAM_REQUIRE(dcoef == nullptr || a->coef != nullptr, "scan bwd: dcoef requested but coef is NULL");
-  const ScanLayout L = scan_layout(a, bwd_chunk_len(a));
+  const bool tc_bwd = tc_fwd_eligible(a) && a->T > 0 && dcoef == nullptr &&
+                      (((uintptr_t)dy | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv) & 15) == 0;
+  const ScanLayout L = scan_layout(a, tc_bwd ? tcs::TC : CH);
   if (fwd_chunk_len(a) != L.ch) states_valid = 0;  // the forward left states of another chunking
   if (a->workspace_bytes < L.total_bwd) {
     set_error("scan bwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_bwd);
     return QPAM_EWORKSPACE;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tc_bwd) return scan_bwd_tc(a, L, dy, dq, dk, dv, dgamma, ds_final, ds0, states_valid, st);
   QPAM_DISPATCH_SCAN(scan_bwd_t, a, L, dy, dq, dk, dv, dgamma, dcoef, ds_final, ds0, states_valid, st);
 }
 

@@ -63,6 +63,9 @@ struct TcMaps {
 // ---------------------------------------------------------------------------------------------
 constexpr size_t OUTER_SMEM = 1024 + 65536 + 32768 + 1024;
 
+// DSTATE == true computes the gradient counterpart  G = sum_t scale e^{A_t} dy_t (x) conj(q_t)  (dy in
+// place of v, q in place of k) into dstate slot c.
+template <bool DSTATE>
 __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
@@ -88,8 +91,8 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
   const uint32_t tmem = *tmem_slot;
   const float a_last = Acum[TC - 1];
   const size_t tb = token_base(p, L.b, h, L.t0, TD);
-  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + tb);
-  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.v) + tb);
+  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.q : p.k) + tb);
+  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.dy : p.v) + tb);
 #pragma unroll 4
   for (int it = 0; it < 16; ++it) {
     const int idx = tid + 128 * it;
@@ -99,7 +102,7 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
       kx = __ldg(kg + idx);
       vx = __ldg(vg + idx);
     }
-    const float w = __expf(fminf(0.f, a_last - Acum[row]));
+    const float w = DSTATE ? p.q_scale * __expf(Acum[row]) : __expf(fminf(0.f, a_last - Acum[row]));
     const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w};
     const uint32_t vw[4] = {vx.x, vx.y, vx.z, vx.w};
     uint32_t lo[4], hi[4];
@@ -136,7 +139,9 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
   tc_fence_after();
   if (ok) {
     // lane n' = 2j+c of the tile holds column i: state[i][j][c] sits at float offset i*128 + n'
-    float* dst = reinterpret_cast<float*>(p.states + state_base(p, 0, h, L.slot0 + L.c + 1, TD)) + (warp * 32 + lane);
+    float2* slot = DSTATE ? p.dstates + state_base(p, 0, h, L.slot0 + L.c, TD)
+                          : p.states + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    float* dst = reinterpret_cast<float*>(slot) + (warp * 32 + lane);
     const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
     }
-    if (tid == 0) p.chunk_decay[(size_t)h * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
+    if (!DSTATE && tid == 0) p.chunk_decay[(size_t)h * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
   }
   tc_fence_before();
   __syncthreads();
@@ -156,31 +161,51 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Forward output of one 128-token chunk.  grid = (chunks, H); 256 threads; 192 KB shared memory.
-//   GEMM1  [Wr | Wi] = Q [K ; rot K]^T                      M128 N256 K128   (TMA operands)
-//   epi 1  M = scale * D .* W  -> bf16 [Mr | Mi]  (overlays K),  Q <- scale * e^{A_t} Q
-//   GEMM2  Y  = [Mr | Mi] [V ; rot V]                       M128 N128 K256
-//   GEMM3  Y += Q' Bs^T,  Bs rows 2i: cj(S[i,:]), 2i+1: (Si, Sr)   M128 N128 K128 (carried state)
-//   epi 2  Y -> bf16 -> global
+// One 128-token chunk of the forward output or of one gradient.  All four share the structure
+//
+//   stage 1  [Xr | Xi] = A1 [B1 ; rot B1]^T                 M128 N256 K128   X[t][s], t: A1 row, s: B1 row
+//   epi 1    T = scale * D[t,s] .* X   (s <= t, D = exp(min(0, A_t - A_s)))  -> bf16 in shared memory
+//   stage 2  out  = T (.) [X2 ; rot X2]                     M128 N128 K256
+//   stage 3  out += A3 B3^T  through the carried state      M128 N128 K128
+//   epi 2    out -> bf16 -> global (+ the decay-gradient dot product for DQ / DK)
+//
+//   MODE  A1  B1  X2  T used as                 A3 (row-scaled in place)   B3 (bf16 image of)
+//   FWD   q   k   v   [Tr | Ti]  rows t         scale e^{A_t} q            S   rows 2i: cj(S[i,:]), 2i+1: (Si,Sr)
+//   DQ    dy  v   k   [Tr | Ti]  rows t         scale e^{A_t} dy           S   rows 2j: (Sr,Si)[:,j], 2j+1: (-Si,Sr)[:,j]
+//   DV    q   k   dy  [Tr ; -Ti]^T rows s       w_s k                      dS  as FWD
+//   DK    dy  v   q   [Tr ; -Ti]^T rows s       w_s v                      dS  as DQ
+//
+// with w_s = exp(min(0, A_last - A_s)), S the state before the chunk and dS the gradient reaching
+// the state after it.  grid = (chunks, H); 256 threads; 192 KB shared memory; 384 TMEM columns.
 // ---------------------------------------------------------------------------------------------
-constexpr size_t FWD_SMEM = 1024 + 65536 + 32768 + 65536 + 32768 + 1024;
+enum ChunkMode { M_FWD = 0, M_DQ = 1, M_DV = 2, M_DK = 3 };
 
-__global__ void __launch_bounds__(256, 1) k_tc_fwd_chunk(const __grid_constant__ TcMaps maps, ScanParams p) {
+struct ChunkMaps {
+  CUtensorMap a1, b1, x2;  // [B*H*T rows][128 bf16], boxes of 64 x 128, 128-byte swizzle
+};
+
+constexpr size_t CHUNK_SMEM = 1024 + 32768 + 65536 + 65536 + 32768 + 2048;
+
+template <int MODE>
+__global__ void __launch_bounds__(256, 1) k_tc_chunk(const __grid_constant__ ChunkMaps maps, ScanParams p) {
   using namespace umma;
+  constexpr bool ROWS_T = (MODE == M_FWD || MODE == M_DQ);   // output rows follow A1's tokens
+  constexpr bool OP_TRANSPOSED = (MODE == M_DQ || MODE == M_DK);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* R1 = smem;                    // K | rot K : [2 kb][256 rows][128 B]; later [Mr|Mi]: [4 kb][128 rows][128 B]
-  unsigned char* R2 = R1 + 65536;              // Q         : [2 kb][128 rows][128 B]
-  unsigned char* R3 = R2 + 32768;              // V | rot V : [2 nb][256 rows][128 B]
-  unsigned char* R4 = R3 + 65536;              // Bs        : [2 kb][128 rows][128 B]
-  float* Acum = reinterpret_cast<float*>(R4 + 32768);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Acum + TC);  // [0] tma, [1] gemm1, [2] gemm2+3
+  unsigned char* RA = smem;                  // A1        : [2 kb][128 rows][128 B]
+  unsigned char* RB = RA + 32768;            // B1 | rot  : [2 kb][256 rows][128 B]
+  unsigned char* RC = RB + 65536;            // X2 | rot  : [2 nb][256 rows][128 B]
+  unsigned char* RD = RC + 65536;            // B3        : [2 kb][128 rows][128 B]
+  float* Acum = reinterpret_cast<float*>(RD + 32768);   // [128]
+  float* dots = Acum + TC;                              // [2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(dots + 2 * TC);  // [0] tma, [1] stage 1, [2] stages 2+3
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
   const int h = blockIdx.y;
-  const bool has_prev = (L.c > 0) || (p.s0 != nullptr);
+  const bool has_state = ROWS_T ? ((L.c > 0) || (p.s0 != nullptr)) : ((L.c < L.nc - 1) || (p.ds_final != nullptr));
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
@@ -198,64 +223,86 @@ __global__ void __launch_bounds__(256, 1) k_tc_fwd_chunk(const __grid_constant__
     mbar_arrive_expect_tx(&bars[0], 6 * 16384);
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {
-      tma_load_2d(R2 + kb * 16384, &maps.q, &bars[0], kb * 64, row0);
-      tma_load_2d(R1 + kb * 32768, &maps.k, &bars[0], kb * 64, row0);
-      tma_load_2d(R3 + kb * 32768, &maps.v, &bars[0], kb * 64, row0);
+      tma_load_2d(RA + kb * 16384, &maps.a1, &bars[0], kb * 64, row0);
+      tma_load_2d(RB + kb * 32768, &maps.b1, &bars[0], kb * 64, row0);
+      tma_load_2d(RC + kb * 32768, &maps.x2, &bars[0], kb * 64, row0);
     }
   }
-  if (has_prev) {
-    // carried state (fp32 [i][j] complex) -> bf16 K-major rows 2i = cj(S[i,:]), 2i+1 = (Si, Sr)
-    const float4* sg = reinterpret_cast<const float4*>(p.states + state_base(p, 0, h, L.slot0 + L.c, TD));
+  if (has_state) {
+    const float2* st = ROWS_T ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
+                              : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    const float4* sg = reinterpret_cast<const float4*>(st);
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it;       // (i, c16): 4 complex = 2 float4
+      const int idx = tid + 256 * it;       // (i, c16): state[i][4*c16 .. +3]
       const int i = idx >> 4, c16 = idx & 15;
       const float4 s01 = __ldg(sg + idx * 2), s23 = __ldg(sg + idx * 2 + 1);
-      const uint4 even = make_uint4(pack_bf162(s01.x, -s01.y), pack_bf162(s01.z, -s01.w), pack_bf162(s23.x, -s23.y), pack_bf162(s23.z, -s23.w));
-      const uint4 odd = make_uint4(pack_bf162(s01.y, s01.x), pack_bf162(s01.w, s01.z), pack_bf162(s23.y, s23.x), pack_bf162(s23.w, s23.z));
-      unsigned char* blk = R4 + (c16 >> 3) * 16384;
-      *reinterpret_cast<uint4*>(blk + sw128(2 * i, c16 & 7)) = even;
-      *reinterpret_cast<uint4*>(blk + sw128(2 * i + 1, c16 & 7)) = odd;
+      if (!OP_TRANSPOSED) {
+        const uint4 even = make_uint4(pack_bf162(s01.x, -s01.y), pack_bf162(s01.z, -s01.w), pack_bf162(s23.x, -s23.y), pack_bf162(s23.z, -s23.w));
+        const uint4 odd = make_uint4(pack_bf162(s01.y, s01.x), pack_bf162(s01.w, s01.z), pack_bf162(s23.y, s23.x), pack_bf162(s23.w, s23.z));
+        unsigned char* blk = RD + (c16 >> 3) * 16384;
+        *reinterpret_cast<uint4*>(blk + sw128(2 * i, c16 & 7)) = even;
+        *reinterpret_cast<uint4*>(blk + sw128(2 * i + 1, c16 & 7)) = odd;
+      } else {
+        // rows 2j / 2j+1, K position 2i: 4-byte words scattered along the (transposed) state
+        const float sr[4] = {s01.x, s01.z, s23.x, s23.z}, si[4] = {s01.y, s01.w, s23.y, s23.w};
+        unsigned char* blk = RD + (i >> 5) * 16384;
+        const int c = (i & 31) >> 2;
+        const uint32_t woff = (uint32_t)(i & 3) * 4u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = 4 * c16 + e;
+          *reinterpret_cast<uint32_t*>(blk + sw128(2 * j, c) + woff) = pack_bf162(sr[e], si[e]);
+          *reinterpret_cast<uint32_t*>(blk + sw128(2 * j + 1, c) + woff) = pack_bf162(-si[e], sr[e]);
+        }
+      }
     }
   }
   bool ok = mbar_wait(&bars[0], 0, 211);
-  // rot K and rot V: element-wise on the swizzled bytes, same position 128 rows further down
+  // rot B1 and rot X2: element-wise on the swizzled bytes, same position 128 rows further down
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int ci = tid + 256 * it;          // 2 blocks x 128 rows x 8 chunks
     const uint32_t off = (uint32_t)(ci >> 10) * 32768u + (uint32_t)(ci & 1023) * 16u;
-    const uint4 kx = *reinterpret_cast<const uint4*>(R1 + off);
-    const uint4 vx = *reinterpret_cast<const uint4*>(R3 + off);
-    const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w}, vw[4] = {vx.x, vx.y, vx.z, vx.w};
-    uint32_t kr[4], vr[4];
+    const uint4 bx = *reinterpret_cast<const uint4*>(RB + off);
+    const uint4 xx = *reinterpret_cast<const uint4*>(RC + off);
+    const uint32_t bw[4] = {bx.x, bx.y, bx.z, bx.w}, xw[4] = {xx.x, xx.y, xx.z, xx.w};
+    uint32_t br[4], xr[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       // (re, im) -> (-im, re): swap the halves and flip the sign bit of the new low half
-      kr[e] = ((kw[e] >> 16) | (kw[e] << 16)) ^ 0x00008000u;
-      vr[e] = ((vw[e] >> 16) | (vw[e] << 16)) ^ 0x00008000u;
+      br[e] = ((bw[e] >> 16) | (bw[e] << 16)) ^ 0x00008000u;
+      xr[e] = ((xw[e] >> 16) | (xw[e] << 16)) ^ 0x00008000u;
     }
-    *reinterpret_cast<uint4*>(R1 + off + 16384) = make_uint4(kr[0], kr[1], kr[2], kr[3]);
-    *reinterpret_cast<uint4*>(R3 + off + 16384) = make_uint4(vr[0], vr[1], vr[2], vr[3]);
+    *reinterpret_cast<uint4*>(RB + off + 16384) = make_uint4(br[0], br[1], br[2], br[3]);
+    *reinterpret_cast<uint4*>(RC + off + 16384) = make_uint4(xr[0], xr[1], xr[2], xr[3]);
   }
   fence_proxy_async();
   __syncthreads();
   if (warp == 0 && elect_one()) {
     tc_fence_after();
     constexpr uint32_t idesc = idesc_bf16(128, 256, false, false);
-    const uint32_t q0 = smem_u32(R2), k0 = smem_u32(R1);
+    const uint32_t a0 = smem_u32(RA), b0 = smem_u32(RB);
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk)
-        mma_bf16(tmem, smem_desc_sw128(q0 + kb * 16384 + kk * 32, 16, 1024),
-                 smem_desc_sw128(k0 + kb * 32768 + kk * 32, 16, 1024), idesc, (kb | kk) != 0);
+        mma_bf16(tmem, smem_desc_sw128(a0 + kb * 16384 + kk * 32, 16, 1024),
+                 smem_desc_sw128(b0 + kb * 32768 + kk * 32, 16, 1024), idesc, (kb | kk) != 0);
     mma_commit(&bars[1]);
   }
   __syncwarp();
   ok = mbar_wait(&bars[1], 0, 212) && ok;
   tc_fence_after();
+  const float a_last = Acum[TC - 1];
   {
-    // epilogue 1: decay-masked scores to bf16 [Mr | Mi] (K-major, 4 k-blocks) over the K | rot K region
+    // epilogue 1: decay-masked X to bf16.  The 64-wide column blocks of Tr and Ti are four 16 KB
+    // pieces [128 rows t][128 B]; where they go depends on how stage 2 reads them.
+    unsigned char* piece_r0 = ROWS_T ? RB : RA;                   // Tr, s in [0,64)
+    unsigned char* piece_r1 = ROWS_T ? RB + 16384 : RA + 16384;   // Tr, s in [64,128)
+    unsigned char* piece_i0 = ROWS_T ? RB + 32768 : RB + 16384;   // Ti (ROWS_T) or -Ti
+    unsigned char* piece_i1 = ROWS_T ? RB + 49152 : RB + 49152;
+    const float isign = ROWS_T ? 1.f : -1.f;
     const int q4 = warp & 3, hf = warp >> 2;
     const int t = q4 * 32 + lane;
     const float a_t = Acum[t];
@@ -274,29 +321,33 @@ __global__ void __launch_bounds__(256, 1) k_tc_fwd_chunk(const __grid_constant__
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           const int s = s0 + j;
-          const float d0 = (s <= t) ? p.q_scale * __expf(fminf(0.f, a_t - Acum[s])) : 0.f;
-          const float d1 = (s + 1 <= t) ? p.q_scale * __expf(fminf(0.f, a_t - Acum[s + 1])) : 0.f;
+          // rows past the end of a ragged chunk hold other sequences' tokens: they must not reach
+          // the transposed products (DV, DK), where t is the contraction index
+          const float d0 = (s <= t && t < L.len) ? p.q_scale * __expf(fminf(0.f, a_t - Acum[s])) : 0.f;
+          const float d1 = (s + 1 <= t && t < L.len) ? p.q_scale * __expf(fminf(0.f, a_t - Acum[s + 1])) : 0.f;
           mr[j >> 1] = pack_bf162(d0 * wr[j], d1 * wr[j + 1]);
-          mi[j >> 1] = pack_bf162(d0 * wi[j], d1 * wi[j + 1]);
+          mi[j >> 1] = pack_bf162(isign * d0 * wi[j], isign * d1 * wi[j + 1]);
         }
       }
-      unsigned char* br = R1 + (s0 >> 6) * 16384;          // Mr: k = s
-      unsigned char* bi = R1 + (2 + (s0 >> 6)) * 16384;    // Mi: k = 128 + s
-      const int c0 = (s0 & 63) >> 3;
+      unsigned char* br = hf ? piece_r1 : piece_r0;
+      unsigned char* bi = hf ? piece_i1 : piece_i0;
+      const int c0 = cc * 4;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         *reinterpret_cast<uint4*>(br + sw128(t, c0 + g)) = make_uint4(mr[4 * g], mr[4 * g + 1], mr[4 * g + 2], mr[4 * g + 3]);
         *reinterpret_cast<uint4*>(bi + sw128(t, c0 + g)) = make_uint4(mi[4 * g], mi[4 * g + 1], mi[4 * g + 2], mi[4 * g + 3]);
       }
     }
-    if (has_prev) {
-      // Q <- scale * exp(A_t) * Q in place (the row of a 16-byte chunk follows from its offset)
+    if (has_state) {
+      // A3: scale the rows of A1 (FWD, DQ: scale e^{A_t}) or of the raw B1 (DV, DK: w_s) in place;
+      // the row of a 16-byte chunk follows from its offset, the swizzle only permutes inside rows
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
         const int ci = tid + 256 * it;      // 2 kb x 128 rows x 8 chunks
         const int row = (ci >> 3) & 127;
-        const float f = p.q_scale * __expf(Acum[row]);
-        uint4* ptr = reinterpret_cast<uint4*>(R2 + (size_t)ci * 16);
+        const float f = ROWS_T ? p.q_scale * __expf(Acum[row]) : __expf(fminf(0.f, a_last - Acum[row]));
+        unsigned char* base = ROWS_T ? RA + (size_t)ci * 16 : RB + (size_t)(ci >> 10) * 32768 + (size_t)(ci & 1023) * 16;
+        uint4* ptr = reinterpret_cast<uint4*>(base);
         const uint4 x = *ptr;
         const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
         uint32_t o[4];
@@ -314,42 +365,81 @@ __global__ void __launch_bounds__(256, 1) k_tc_fwd_chunk(const __grid_constant__
   __syncthreads();
   if (warp == 0 && elect_one()) {
     tc_fence_after();
-    constexpr uint32_t idesc2 = idesc_bf16(128, 128, false, true);
-    constexpr uint32_t idesc3 = idesc_bf16(128, 128, false, false);
-    const uint32_t m0 = smem_u32(R1), v0 = smem_u32(R3), q0 = smem_u32(R2), b0 = smem_u32(R4);
-    const uint32_t dY = tmem + 256;
+    const uint32_t ra = smem_u32(RA), rb = smem_u32(RB), rc = smem_u32(RC), rd = smem_u32(RD);
+    const uint32_t dOut = tmem + 256;
+    if (ROWS_T) {
+      constexpr uint32_t idesc2 = idesc_bf16(128, 128, false, true);
 #pragma unroll
-    for (int kk = 0; kk < 16; ++kk)
-      mma_bf16(dY, smem_desc_sw128(m0 + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
-               smem_desc_sw128(v0 + kk * 2048, 32768, 1024), idesc2, kk > 0);
-    if (has_prev) {
+      for (int kk = 0; kk < 16; ++kk)
+        mma_bf16(dOut, smem_desc_sw128(rb + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024),
+                 smem_desc_sw128(rc + kk * 2048, 32768, 1024), idesc2, kk > 0);
+    } else {
+      constexpr uint32_t idesc2 = idesc_bf16(128, 128, true, true);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)    // K = t over Tr rows, against X2 rows t
+        mma_bf16(dOut, smem_desc_sw128(ra + kk * 2048, 16384, 1024), smem_desc_sw128(rc + kk * 2048, 32768, 1024),
+                 idesc2, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)    // K = t over -Ti rows, against rot X2 rows t
+        mma_bf16(dOut, smem_desc_sw128(rb + 16384 + kk * 2048, 32768, 1024),
+                 smem_desc_sw128(rc + 16384 + kk * 2048, 32768, 1024), idesc2, true);
+    }
+    if (has_state) {
+      constexpr uint32_t idesc3 = idesc_bf16(128, 128, false, false);
+      const uint32_t a3 = ROWS_T ? ra : rb;
+      const uint32_t a3_stride = ROWS_T ? 16384u : 32768u;
 #pragma unroll
       for (int kb = 0; kb < 2; ++kb)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          mma_bf16(dY, smem_desc_sw128(q0 + kb * 16384 + kk * 32, 16, 1024),
-                   smem_desc_sw128(b0 + kb * 16384 + kk * 32, 16, 1024), idesc3, true);
+          mma_bf16(dOut, smem_desc_sw128(a3 + kb * a3_stride + kk * 32, 16, 1024),
+                   smem_desc_sw128(rd + kb * 16384 + kk * 32, 16, 1024), idesc3, true);
     }
     mma_commit(&bars[2]);
   }
   __syncwarp();
   ok = mbar_wait(&bars[2], 0, 213) && ok;
   tc_fence_after();
-  if (ok) {
+  {
     const int q4 = warp & 3, hf = warp >> 2;
     const int t = q4 * 32 + lane;
     const uint32_t taddr = tmem + 256 + ((uint32_t)(q4 * 32) << 16) + hf * 64;
-    __nv_bfloat16* yrow = reinterpret_cast<__nv_bfloat16*>(p.y) + token_base(p, L.b, h, L.t0 + t, TD) + hf * 64;
+    void* outp = MODE == M_FWD ? p.y : MODE == M_DQ ? p.dq : MODE == M_DV ? p.dv : p.dk;
+    const size_t rb = token_base(p, L.b, h, L.t0 + t, TD) + hf * 64;
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(outp) + rb;
+    const __nv_bfloat16* drow = reinterpret_cast<const __nv_bfloat16*>(MODE == M_DQ ? p.q : p.k) + rb;
+    float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       float v[32];
       tmem_ld32(taddr + cc * 32, v);
-      if (t < L.len) {
+      if (ok && t < L.len) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(yrow + cc * 32 + g * 8) =
+        for (int g = 0; g < 4; ++g) {
+          *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) =
               make_uint4(pack_bf162(v[8 * g], v[8 * g + 1]), pack_bf162(v[8 * g + 2], v[8 * g + 3]),
                          pack_bf162(v[8 * g + 4], v[8 * g + 5]), pack_bf162(v[8 * g + 6], v[8 * g + 7]));
+          if (MODE == M_DQ || MODE == M_DK) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(drow + cc * 32 + g * 8));
+            const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x2 = unpack_bf162(xw[e]);
+              dot = fmaf(x2.x, v[8 * g + 2 * e], dot);
+              dot = fmaf(x2.y, v[8 * g + 2 * e + 1], dot);
+            }
+          }
+        }
+      }
+    }
+    if (MODE == M_DQ || MODE == M_DK) {
+      // raw decay gradient dA_t = Re<q_t, dq_t> - Re<k_t, dk_t>: DQ stores its half, DK subtracts
+      dots[hf * TC + t] = dot;
+      __syncthreads();
+      if (tid < L.len && ok) {
+        const float d2 = dots[tid] + dots[TC + tid];
+        float* g = p.dgamma + gamma_base(p, 0, L.b, h, L.t0 + tid);
+        if (MODE == M_DQ) *g = d2; else *g -= d2;
       }
     }
   }

@@ -1,0 +1,201 @@
+"""Continuous-batching greedy decode on a pool of per-sequence PAM state slots.
+
+The reference decodes one batch with a single `step_offset` for all rows (v11/model.py:785,
+1206-1245), so sequences of different lengths cannot share a step.  Here every live sequence owns
+a slot of a preallocated state pool `[n_slots, L, K, H, d, d, 2]`; a decode step gathers nothing
+and reallocates nothing -- `qpam_decode_step` updates the slots named by `slot_ids` in place, with
+per-sequence RoPE positions.  New sequences are prefetched in one packed ragged prefill
+(`cu_seqlens`), their final states are written into free slots, and they join the next step.
+
+`SlotScheduler` is pure host logic (no GPU) and is unit-tested on CPU.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+import torch
+
+from . import ops
+from .model import V11LM, _complex_mul, _concat_planes, _magnitude
+
+
+# ------------------------------------------------------------------------------------ scheduler
+@dataclass
+class Request:
+    rid: int
+    prompt: List[int]
+    max_new_tokens: int
+    generated: List[int] = field(default_factory=list)
+    slot: int = -1
+
+    @property
+    def position(self) -> int:
+        """Absolute position of the next token to be fed (prompt length + tokens generated so far - 1)."""
+        return len(self.prompt) + len(self.generated) - 1
+
+    @property
+    def done(self) -> bool:
+        return len(self.generated) >= self.max_new_tokens
+
+
+class SlotScheduler:
+    """Admission and retirement of sequences over a fixed number of state slots."""
+
+    def __init__(self, n_slots: int, max_prefill_tokens: int = 1 << 17):
+        if n_slots <= 0:
+            raise ValueError("n_slots must be positive")
+        self.n_slots = n_slots
+        self.max_prefill_tokens = max_prefill_tokens
+        self.free: Deque[int] = deque(range(n_slots))
+        self.waiting: Deque[Request] = deque()
+        self.live: Dict[int, Request] = {}       # slot -> request
+        self.finished: List[Request] = []
+        self._next_id = 0
+
+    def submit(self, prompt: Sequence[int], max_new_tokens: int) -> int:
+        if len(prompt) == 0:
+            raise ValueError("empty prompt")
+        rid = self._next_id
+        self._next_id += 1
+        self.waiting.append(Request(rid, list(prompt), max_new_tokens))
+        return rid
+
+    def admit(self) -> List[Request]:
+        """Move waiting requests into free slots (FIFO), bounded by slots and a prefill token budget."""
+        batch, tokens = [], 0
+        while self.waiting and self.free:
+            nxt = self.waiting[0]
+            if batch and tokens + len(nxt.prompt) > self.max_prefill_tokens:
+                break
+            self.waiting.popleft()
+            nxt.slot = self.free.popleft()
+            self.live[nxt.slot] = nxt
+            batch.append(nxt)
+            tokens += len(nxt.prompt)
+        return batch
+
+    def retire_finished(self) -> List[Request]:
+        out = [r for r in self.live.values() if r.done]
+        for r in out:
+            del self.live[r.slot]
+            self.free.append(r.slot)
+            self.finished.append(r)
+        return out
+
+    @property
+    def idle(self) -> bool:
+        return not self.waiting and not self.live
+
+    def live_requests(self) -> List[Request]:
+        return [self.live[s] for s in sorted(self.live)]
+
+
+# ------------------------------------------------------------------------------------ engine
+class ContinuousBatcher:
+    """Greedy decode of many sequences through a V11LM with continuous batching."""
+
+    def __init__(self, model: V11LM, n_slots: int, state_dtype: Optional[torch.dtype] = None,
+                 max_prefill_tokens: int = 1 << 17):
+        self.model = model.eval()
+        cfg = model.config
+        p = next(model.parameters())
+        self.device, self.dtype = p.device, p.dtype
+        self.state_dtype = state_dtype or (torch.float32 if p.dtype == torch.float32 else torch.bfloat16)
+        self.pool = torch.zeros(n_slots, cfg.n_layers, cfg.n_states, cfg.n_heads, cfg.head_dim, cfg.head_dim, 2,
+                                dtype=self.state_dtype, device=self.device)
+        self.sched = SlotScheduler(n_slots, max_prefill_tokens)
+        self.steps = 0
+        self.decoded_tokens = 0
+
+    def submit(self, prompt, max_new_tokens):
+        return self.sched.submit([int(t) for t in prompt], max_new_tokens)
+
+    # -- layer pieces with explicit per-token positions ------------------------------------
+    def _qkv(self, pam, x, positions):
+        """x [B,T,D,2], positions [B,T] -> q,k,v [B,H,T,d,2] with per-token RoPE."""
+        B, T = x.shape[0], x.shape[1]
+        H, d = pam.num_heads, pam.head_dim
+        qkv = pam.qkv_proj(x).view(B, T, 3, H, d, 2)
+        q, k, v = (qkv[:, :, i].transpose(1, 2).contiguous() for i in range(3))
+        if pam.use_rope:
+            need = int(positions.max()) + 1
+            if need > pam.rope_cache.shape[0]:
+                from .model import build_rope_cache
+                pam.register_buffer("rope_cache", build_rope_cache(need * 2, d).to(x.device), persistent=False)
+            rot = pam.rope_cache[positions].to(x.dtype).unsqueeze(1)       # [B,1,T,d,2]
+            q, k = _complex_mul(q, rot), _complex_mul(k, rot)
+        return q, k, v
+
+    @torch.no_grad()
+    def _prefill(self, batch: List[Request]):
+        m = self.model
+        lens = [len(r.prompt) for r in batch]
+        ids = torch.tensor([t for r in batch for t in r.prompt], dtype=torch.long, device=self.device)[None]
+        positions = torch.cat([torch.arange(n, device=self.device) for n in lens])[None]
+        cu = torch.zeros(len(batch) + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(lens).cumsum(0).int()
+        cu = cu.to(self.device)
+        slots = torch.tensor([r.slot for r in batch], dtype=torch.int32, device=self.device)
+        z = m.embed_norm(m.embed(ids))
+        for li, blk in enumerate(m.blocks):
+            z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
+            xn = blk.norm2(z)
+            pam = blk.pam
+            q, k, v = self._qkv(pam, xn, positions)
+            gamma, vprime = pam._gamma_all_and_vprime(xn, v)
+            coef = pam._coef(xn)
+            y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, cu_seqlens=cu, head_dim=pam.head_dim)
+            ops.pam_pool_store(self.pool, slots, s, layer=li)
+            out = pam.o_proj(y.transpose(1, 2).contiguous().view(1, ids.shape[1], pam.inner_dim, 2))
+            z = z + out * blk.pam_scale
+        last = (cu[1:] - 1).long()
+        lm = m._head_hidden(z[:, last])                                     # [1, n, D, 2]
+        nxt = m.greedy_next(lm[0])
+        for r, t in zip(batch, nxt.tolist()):
+            r.generated.append(int(t))
+
+    @torch.no_grad()
+    def _decode(self, live: List[Request]):
+        m = self.model
+        n = len(live)
+        ids = torch.tensor([r.generated[-1] for r in live], dtype=torch.long, device=self.device)[:, None]
+        positions = torch.tensor([r.position for r in live], dtype=torch.long, device=self.device)[:, None]
+        slots = torch.tensor([r.slot for r in live], dtype=torch.int32, device=self.device)
+        z = m.embed_norm(m.embed(ids))                                      # [n,1,D,2]
+        for li, blk in enumerate(m.blocks):
+            z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
+            xn = blk.norm2(z)
+            pam = blk.pam
+            q, k, v = self._qkv(pam, xn, positions)
+            gamma, vprime = pam._gamma_all_and_vprime(xn, v)                # [K,n,H,1]
+            coef = pam._coef(xn)
+            y = ops.pam_decode_step(self.pool, slots, (q[:, :, 0] * pam.head_dim ** -0.5).contiguous(),
+                                    k[:, :, 0].contiguous(), vprime[:, :, 0].contiguous(),
+                                    gamma[..., 0].contiguous(), None if coef is None else coef[:, :, :, 0].contiguous(),
+                                    layer=li)
+            out = pam.o_proj(y.reshape(n, 1, pam.inner_dim, 2))
+            z = z + out * blk.pam_scale
+        nxt = m.greedy_next(m._head_hidden(z)[:, 0])
+        for r, t in zip(live, nxt.tolist()):
+            r.generated.append(int(t))
+        self.decoded_tokens += n
+
+    def step(self) -> int:
+        """Admit + prefill waiting sequences, then advance every live sequence by one token."""
+        self.sched.retire_finished()
+        live_before = [r for r in self.sched.live_requests() if not r.done]
+        batch = self.sched.admit()
+        if batch:
+            self._prefill(batch)
+        if live_before:
+            self._decode(live_before)
+        self.sched.retire_finished()
+        self.steps += 1
+        return len(live_before) + len(batch)
+
+    def run(self) -> Dict[int, List[int]]:
+        while not self.sched.idle:
+            self.step()
+        return {r.rid: r.generated for r in self.sched.finished}

@@ -55,3 +55,52 @@ def test_forward_then_backward_mixed_paths():
     assert_close(dk.float().cpu().numpy(), po.to_split(b["dk"]), TOL, "dk")
     assert_close(dv.float().cpu().numpy(), po.to_split(b["dv"]), TOL, "dv")
     assert_close(dg.cpu().numpy(), b["dgamma"][0] * gam * (1 - gam), TOL, "dg")
+
+
+def _grads_vs_oracle(inp, s0=None, ds_final=None, cu=None, packed=False):
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+    g = inp.g.to(DEV).requires_grad_(True)
+    s0d = None if s0 is None else s0.to(DEV).requires_grad_(True)
+    y, s = ops.pam_scan(q, k, v, torch.sigmoid(g), s0=s0d)
+    outs, gos = [y], [inp.dy.to(DEV)]
+    if ds_final is not None:
+        outs.append(s)
+        gos.append(ds_final.to(DEV))
+    leaves = [q, k, v, g] + ([s0d] if s0 is not None else [])
+    grads = torch.autograd.grad(outs, leaves, gos)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    qc, kc, vc, dyc = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v, inp.dy))
+    gam = torch.sigmoid(inp.g.double()).numpy()
+    b = po.scan_backward(qc, kc, vc, gam, dyc, s0=None if s0 is None else po.to_complex(s0.numpy()),
+                         dS_final=None if ds_final is None else po.to_complex(ds_final.numpy()))
+    assert_close(grads[0].float().cpu().numpy(), po.to_split(b["dq"]), TOL, "dq")
+    assert_close(grads[1].float().cpu().numpy(), po.to_split(b["dk"]), TOL, "dk")
+    assert_close(grads[2].float().cpu().numpy(), po.to_split(b["dv"]), TOL, "dv")
+    assert_close(grads[3].cpu().numpy(), b["dgamma"][0] * gam * (1 - gam), TOL, "dg")
+    if s0 is not None:
+        assert_close(grads[4].cpu().numpy(), po.to_split(b["dS0"]), TOL, "ds0")
+
+
+@pytest.mark.parametrize("B,H,T", [(1, 1, 128), (2, 2, 300), (1, 1, 50), (1, 2, 1024), (1, 1, 129)])
+def test_backward_shapes(B, H, T):
+    _grads_vs_oracle(synthetic.scan_inputs(B, H, T, 64, seed=80 + T, dtype=torch.bfloat16))
+
+
+def test_backward_with_state_gradients():
+    gen = torch.Generator().manual_seed(6)
+    s0 = torch.randn(1, 1, 2, 64, 64, 2, generator=gen) * 0.05
+    dsf = torch.randn(1, 1, 2, 64, 64, 2, generator=gen) * 0.05
+    _grads_vs_oracle(synthetic.scan_inputs(1, 2, 400, 64, seed=91, dtype=torch.bfloat16), s0=s0, ds_final=dsf)
+
+
+def test_backward_is_deterministic():
+    inp = synthetic.scan_inputs(2, 2, 500, 64, seed=95, dtype=torch.bfloat16)
+    res = []
+    for _ in range(2):
+        q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+        g = inp.g.to(DEV).requires_grad_(True)
+        y, _ = ops.pam_scan(q, k, v, torch.sigmoid(g))
+        res.append([y.detach()] + list(torch.autograd.grad(y, [q, k, v, g], inp.dy.to(DEV))))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)

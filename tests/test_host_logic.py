@@ -1,0 +1,86 @@
+"""Host-side logic that needs no GPU: the slot scheduler of the continuous batcher and the
+vocabulary-parallel combination of cross-entropy statistics (2 gloo ranks on CPU)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import ce_oracle
+from qllm2_b200.serving import SlotScheduler
+
+
+def test_scheduler_join_leave_without_reallocation():
+    s = SlotScheduler(n_slots=3, max_prefill_tokens=100)
+    for i in range(5):
+        s.submit([1] * (10 + i), max_new_tokens=2 + (i % 2))
+    first = s.admit()
+    assert [r.rid for r in first] == [0, 1, 2] and sorted(r.slot for r in first) == [0, 1, 2]
+    assert s.admit() == []                       # pool exhausted: the rest waits
+    for r in first:
+        r.generated.append(7)
+    assert s.retire_finished() == []
+    first[0].generated.append(7)                 # rid 0 reaches max_new_tokens == 2
+    done = s.retire_finished()
+    assert [r.rid for r in done] == [0]
+    nxt = s.admit()
+    assert [r.rid for r in nxt] == [3] and nxt[0].slot == done[0].slot   # the freed slot is reused
+    assert first[1].position == len(first[1].prompt) + 1 - 1
+    with pytest.raises(ValueError):
+        s.submit([], 1)
+    with pytest.raises(ValueError):
+        SlotScheduler(0)
+
+
+def test_scheduler_prefill_token_budget():
+    s = SlotScheduler(n_slots=8, max_prefill_tokens=25)
+    for n in (10, 10, 10, 40):
+        s.submit([0] * n, 1)
+    assert [len(r.prompt) for r in s.admit()] == [10, 10]
+    assert [len(r.prompt) for r in s.admit()] == [10]
+    assert [len(r.prompt) for r in s.admit()] == [40]   # an over-budget prompt still runs, alone
+    assert s.admit() == [] and not s.idle
+
+
+def _free_port():
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+def _rank_main(rank, world, port, V, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from qllm2_b200.fused_ce import _combine_stats
+    gen = torch.Generator().manual_seed(0)
+    N, F = 37, 8
+    h = torch.randn(N, F, generator=gen, dtype=torch.float64)
+    w = torch.randn(V, F, generator=gen, dtype=torch.float64)
+    t = torch.randint(0, V, (N,), generator=gen)
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    z = h @ w[lo:hi].T                                           # this rank's logits (stand-in for the kernel)
+    row_max = z.max(1).values
+    row_sum = torch.exp(z - row_max[:, None]).sum(1)
+    own = (t >= lo) & (t < hi)
+    row_tgt = torch.where(own, z[torch.arange(N), (t - lo).clamp(0, hi - lo - 1)], torch.zeros(N, dtype=torch.float64))
+    row_arg = z.argmax(1) + lo
+    gmax, gsum, gtgt, garg = _combine_stats((row_max, row_sum, row_tgt, row_arg), None)
+    if rank == 0:
+        ref = ce_oracle.linear_ce(h.numpy(), w.numpy(), t.numpy(), want_grads=False)
+        lse = (gmax + torch.log(gsum)).numpy()
+        ret["lse_err"] = float(np.abs(lse - ref["lse"]).max())
+        ret["loss_err"] = float(abs((lse - gtgt.numpy()).mean() - ref["loss"]))
+        ret["argmax_ok"] = bool(np.array_equal(garg.numpy(), ref["argmax"]))
+    dist.destroy_process_group()
+
+
+def test_vocab_parallel_stats_two_ranks():
+    """Sharded (max, sum-exp, target logit, arg-max) combine to the unsharded values."""
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rank_main, args=(2, port, 101, ret), nprocs=2, join=True)
+    assert ret["lse_err"] < 1e-12 and ret["loss_err"] < 1e-12 and ret["argmax_ok"]
