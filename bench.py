@@ -265,13 +265,18 @@ def main():
     total_prof = sum(t for _, t in prof.values())
     th = B * H * T
     f_fwd = scan_flops_per_token_head(d, C, K) * th
+    CT = 128  # tokens per chunk of the tensor-core kernels
+    bwd_each = (2 * f_fwd - 8 * d * d * th) / 3.0
+    scan_bytes = 2 * (T // CT) * B * H * K * d * d * 8
     alg = {  # algorithmic flops (tensor-bound pieces) or bytes (HBM-bound pieces) per launch
-        "k_fwd_chunk": ("tensor", f_fwd - 8 * d * d * th),
-        "k_chunk_outer<state>": ("tensor", 8 * d * d * th),
-        "k_chunk_outer<dstate>": ("tensor", 8 * d * d * th),
-        "k_bwd_chunk": ("tensor", 2 * f_fwd - 8 * d * d * th),
-        "k_state_scan<fwd>": ("hbm", 2 * (T // C) * B * H * K * d * d * 8),
-        "k_state_scan<rev>": ("hbm", 2 * (T // C) * B * H * K * d * d * 8),
+        "k_tc_chunk<fwd>": ("tensor", f_fwd - 8 * d * d * th),
+        "k_tc_chunk_outer<state>": ("tensor", 8 * d * d * th),
+        "k_tc_chunk_outer<dstate>": ("tensor", 8 * d * d * th),
+        "k_tc_chunk<dv>": ("tensor", bwd_each),
+        "k_tc_chunk<dq>": ("tensor", bwd_each),
+        "k_tc_chunk<dk>": ("tensor", bwd_each),
+        "k_state_scan<fwd>": ("hbm", scan_bytes),
+        "k_state_scan<rev>": ("hbm", scan_bytes),
     }
     roof_all = {}
     for n, kinfo in kernels.items():
@@ -305,7 +310,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 accumulate on bf16 tensors (CUDA-core FFMA path)", "data": "synthetic",
+            "vs_baseline": None, "dtype": "bf16 (tcgen05 MMA, fp32 accumulate in TMEM)", "data": "synthetic",
             "config": workload_config(world),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": ms_e2e / args.steps},

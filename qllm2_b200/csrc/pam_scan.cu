@@ -142,7 +142,7 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   if (L.grid_chunks > 0) {
     int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
+    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
   }
   k_state_scan<false><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
@@ -203,7 +203,7 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   if (L.grid_chunks > 0) {
     rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 128, tcs::OUTER_SMEM, st>>>(p);
+    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outer<dstate>");
   }
   k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);

@@ -59,14 +59,14 @@ struct TcMaps {
 //                                                           rows 128+s  : w_s * (ki, kr)
 //   B (MN-major, N = 64 value channels,          K = 256): rows s      : Re v_s
 //                                                           rows 128+s  : Im v_s
-// grid = (chunks, H); 128 threads; ~97 KB shared memory, 64 TMEM columns (two CTAs per SM).
+// grid = (chunks, H); 256 threads; ~97 KB shared memory, 64 TMEM columns (two CTAs per SM).
 // ---------------------------------------------------------------------------------------------
 constexpr size_t OUTER_SMEM = 1024 + 65536 + 32768 + 1024;
 
 // DSTATE == true computes the gradient counterpart  G = sum_t scale e^{A_t} dy_t (x) conj(q_t)  (dy in
 // place of v, q in place of k) into dstate slot c.
 template <bool DSTATE>
-__global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
+__global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -79,6 +79,21 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
   const int h = blockIdx.y;
+  const size_t tb = token_base(p, L.b, h, L.t0, TD);
+  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.q : p.k) + tb);
+  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.dy : p.v) + tb);
+  // every global load of this thread is in flight before the first barrier
+  uint4 kxa[8], vxa[8];
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = tid + 256 * it;
+    kxa[it] = make_uint4(0, 0, 0, 0);
+    vxa[it] = make_uint4(0, 0, 0, 0);
+    if ((idx >> 4) < L.len) {
+      kxa[it] = __ldg(kg + idx);
+      vxa[it] = __ldg(vg + idx);
+    }
+  }
   if (tid == 0) {
     mbar_init(bar, 1);
     fence_barrier_init();
@@ -90,18 +105,11 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const float a_last = Acum[TC - 1];
-  const size_t tb = token_base(p, L.b, h, L.t0, TD);
-  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.q : p.k) + tb);
-  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.dy : p.v) + tb);
-#pragma unroll 4
-  for (int it = 0; it < 16; ++it) {
-    const int idx = tid + 128 * it;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = tid + 256 * it;
     const int row = idx >> 4, c16 = idx & 15;
-    uint4 kx = make_uint4(0, 0, 0, 0), vx = make_uint4(0, 0, 0, 0);
-    if (row < L.len) {
-      kx = __ldg(kg + idx);
-      vx = __ldg(vg + idx);
-    }
+    const uint4 kx = kxa[it], vx = vxa[it];
     const float w = DSTATE ? p.q_scale * __expf(Acum[row]) : __expf(fminf(0.f, a_last - Acum[row]));
     const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w};
     const uint32_t vw[4] = {vx.x, vx.y, vx.z, vx.w};
@@ -141,15 +149,12 @@ __global__ void __launch_bounds__(128) k_tc_chunk_outer(ScanParams p) {
     // lane n' = 2j+c of the tile holds column i: state[i][j][c] sits at float offset i*128 + n'
     float2* slot = DSTATE ? p.dstates + state_base(p, 0, h, L.slot0 + L.c, TD)
                           : p.states + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
-    float* dst = reinterpret_cast<float*>(slot) + (warp * 32 + lane);
-    const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int q4 = warp & 3, cc = warp >> 2;   // TMEM lane quarter, column half
+    float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
+    float v[32];
+    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + cc * 32, v);
 #pragma unroll
-    for (int cc = 0; cc < 2; ++cc) {
-      float v[32];
-      tmem_ld32(taddr + cc * 32, v);
-#pragma unroll
-      for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
-    }
+    for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
     if (!DSTATE && tid == 0) p.chunk_decay[(size_t)h * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
   }
   tc_fence_before();
@@ -234,9 +239,13 @@ __global__ void __launch_bounds__(256, 1) k_tc_chunk(const __grid_constant__ Chu
     const float4* sg = reinterpret_cast<const float4*>(st);
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it;       // (i, c16): state[i][4*c16 .. +3]
-      const int i = idx >> 4, c16 = idx & 15;
-      const float4 s01 = __ldg(sg + idx * 2), s23 = __ldg(sg + idx * 2 + 1);
+      // (i, c16): state[i][4*c16 .. +3].  The transposed image is written with 4-byte stores whose
+      // bank follows i, so there consecutive lanes take consecutive i (conflict-free); the plain
+      // image keeps consecutive lanes on consecutive c16 (coalesced 512-byte reads).
+      const int idx = tid + 256 * it;
+      const int i = OP_TRANSPOSED ? (idx & 63) : (idx >> 4);
+      const int c16 = OP_TRANSPOSED ? (idx >> 6) : (idx & 15);
+      const float4 s01 = __ldg(sg + (i * 16 + c16) * 2), s23 = __ldg(sg + (i * 16 + c16) * 2 + 1);
       if (!OP_TRANSPOSED) {
         const uint4 even = make_uint4(pack_bf162(s01.x, -s01.y), pack_bf162(s01.z, -s01.w), pack_bf162(s23.x, -s23.y), pack_bf162(s23.z, -s23.w));
         const uint4 odd = make_uint4(pack_bf162(s01.y, s01.x), pack_bf162(s01.w, s01.z), pack_bf162(s23.y, s23.x), pack_bf162(s23.w, s23.z));
@@ -398,8 +407,6 @@ __global__ void __launch_bounds__(256, 1) k_tc_chunk(const __grid_constant__ Chu
     mma_commit(&bars[2]);
   }
   __syncwarp();
-  ok = mbar_wait(&bars[2], 0, 213) && ok;
-  tc_fence_after();
   {
     const int q4 = warp & 3, hf = warp >> 2;
     const int t = q4 * 32 + lane;
@@ -408,6 +415,13 @@ __global__ void __launch_bounds__(256, 1) k_tc_chunk(const __grid_constant__ Chu
     const size_t rb = token_base(p, L.b, h, L.t0 + t, TD) + hf * 64;
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(outp) + rb;
     const __nv_bfloat16* drow = reinterpret_cast<const __nv_bfloat16*>(MODE == M_DQ ? p.q : p.k) + rb;
+    uint4 dpre[8];   // q (DQ) or k (DK) row for the decay-gradient dot product, fetched under the MMAs
+    if ((MODE == M_DQ || MODE == M_DK) && t < L.len) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) dpre[g] = __ldg(reinterpret_cast<const uint4*>(drow) + g);
+    }
+    ok = mbar_wait(&bars[2], 0, 213) && ok;
+    tc_fence_after();
     float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
@@ -420,7 +434,7 @@ __global__ void __launch_bounds__(256, 1) k_tc_chunk(const __grid_constant__ Chu
               make_uint4(pack_bf162(v[8 * g], v[8 * g + 1]), pack_bf162(v[8 * g + 2], v[8 * g + 3]),
                          pack_bf162(v[8 * g + 4], v[8 * g + 5]), pack_bf162(v[8 * g + 6], v[8 * g + 7]));
           if (MODE == M_DQ || MODE == M_DK) {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(drow + cc * 32 + g * 8));
+            const uint4 x = dpre[cc * 4 + g];
             const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
