@@ -372,7 +372,60 @@ def side_measurements(dev, peaks):
     fl = 6 * 8192 * 50261 * 768
     out["fused_ce_config2"] = {"ms_fwd_bwd": ms, "tokens_per_s": 8192 / ms * 1e3, "achieved_tflops": fl / ms / 1e9,
                                "frac_of_bf16_peak": fl / ms / 1e9 / peaks["tf"]}
+    del h, w, t
+    torch.cuda.empty_cache()
+    out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
+    out["continuous_decode"] = continuous_decode(dev)
     return out
+
+
+def packed_prefill(dev, peaks, time_ms):
+    """Config 4: 32 packed sequences, lengths uniform in [512,16384], H=16, d=64, bf16, forward only."""
+    from qllm2_b200 import ops
+    gen = torch.Generator().manual_seed(0)
+    lengths = torch.randint(512, 16385, (32,), generator=gen)
+    total = int(lengths.sum())
+    cu = torch.zeros(33, dtype=torch.int32)
+    cu[1:] = lengths.cumsum(0).int()
+    H, d = 16, 64
+    g = torch.Generator(device=dev).manual_seed(0)
+    mk = lambda: (torch.randn(1, H, total, d, 2, device=dev, generator=g) * (1.0 / (2 * d) ** 0.5)).bfloat16()
+    q, k, v = mk(), mk(), mk()
+    gamma = torch.sigmoid(torch.randn(1, H, total, device=dev, generator=g) + 3.0)
+    cud = cu.to(dev)
+
+    def run():
+        ops.pam_scan(q, k, v, gamma, cu_seqlens=cud, chunk=128)
+    ms = time_ms(run, 5, warm=2)
+    by = H * total * (8 * d * 2 + 4)
+    return {"ms": ms, "tokens": total, "tokens_per_s": total / ms * 1e3, "algorithmic_gbs": by / ms / 1e6,
+            "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm"],
+            "config": "32 sequences, lengths U[512,16384] (seed 0), H=16 d=64 K=1 bf16, forward (Y + per-sequence states); "
+                      "inputs drawn on the device"}
+
+
+def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=1024):
+    """Continuous-batching greedy decode through the 12-block model of config 5 (bounded sample)."""
+    from qllm2_b200 import model as M, synthetic
+    from qllm2_b200.serving import ContinuousBatcher
+    torch.manual_seed(0)
+    cfg = M.V11Config(vocab_size=50261, dim=768, n_heads=12, head_dim=64, n_layers=12, n_states=3,
+                      gate_content_aware=True, dropout=0.0, gradient_checkpointing=False, max_seq_len=8192)
+    net = M.V11LM(cfg).to(dev).bfloat16().eval()
+    prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
+    eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16)
+    for p_ in prompts:
+        eng.submit(p_.tolist(), new_tokens)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = eng.run()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    gen_tokens = sum(len(v_) for v_ in res.values())
+    return {"generated_tokens": gen_tokens, "seconds": dt, "decode_tokens_per_s": gen_tokens / dt,
+            "prompt_tokens": int(sum(len(p_) for p_ in prompts)), "engine_steps": eng.steps,
+            "config": f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
+                      f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init; wall time includes the packed prefills"}
 
 
 if __name__ == "__main__":
