@@ -255,9 +255,12 @@ def main():
     d2h = 4 * B * H * T * d * 2 * elt + B * H * T * 4
 
     # per-kernel split over a few extra steps (events behind every launch)
-    torch.cuda.synchronize()
+    # (the stream is kept busy by a few unprofiled steps first: a kernel's time is the gap between its
+    # event and the previous one, which is only its duration while the queue never runs dry)
+    for i in range(8):
+        step_dev(dev_sets[i % nsets])
     _lib.profile_begin()
-    prof_steps = 5
+    prof_steps = 10
     for i in range(prof_steps):
         step_dev(dev_sets[i % nsets])
     prof = _lib.profile_end()
