@@ -1,8 +1,10 @@
 // Host side of the chunked PAM scan: argument checks, workspace carving, launches.
 #include <mutex>
+#include <stdlib.h>
 
 #include "pam_scan_chunk.cuh"
 #include "pam_scan_tc.cuh"
+#include "pam_scan_tc2.cuh"
 #include "tma_host.cuh"
 
 namespace qpam {
@@ -167,6 +169,29 @@ static int tc_chunk_launch(const qpam_scan_args* a, const ScanLayout& L, const S
   return QPAM_OK;
 }
 
+// planar two-CTA-per-SM variant (operand roles differ: output rows always follow A1)
+template <int MODE>
+static int tc_chunk2_launch(const qpam_scan_args* a, const ScanLayout& L, const ScanParams& p, const void* a1,
+                            const void* b1, const void* x2, const char* name, cudaStream_t st) {
+  tcs::ChunkMaps maps;
+  const int64_t rows = (int64_t)a->B * a->H * a->T;
+  int rc;
+  if ((rc = make_map(&maps.a1, a1, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.b1, b1, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.x2, x2, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = set_smem(tcs::k_tc_chunk2<MODE>, tcs::CHUNK2_SMEM))) return rc;
+  tcs::k_tc_chunk2<MODE><<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, name);
+  note_launch(name, st);
+  return QPAM_OK;
+}
+static bool use_chunk2() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("QPAM_CHUNK2"); v = (e && e[0] == '1') ? 1 : 0; }
+  return v == 1;
+}
+
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
 static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
   ScanParams p = make_params(a, L);
@@ -178,7 +203,8 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
   rc = tc_states(p, L, a, st);
   if (rc) return rc;
   if (L.grid_chunks > 0 && a->y != nullptr) {
-    rc = tc_chunk_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
+    rc = use_chunk2() ? tc_chunk2_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk2<fwd>", st)
+                      : tc_chunk_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
     if (rc) return rc;
   }
   return QPAM_OK;
@@ -209,9 +235,15 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
   QPAM_LAUNCH_CHECK("k_state_scan<rev>");
   if (L.grid_chunks > 0) {
-    if ((rc = tc_chunk_launch<tcs::M_DV>(a, L, p, a->q, a->k, dy, "k_tc_chunk<dv>", st))) return rc;
-    if ((rc = tc_chunk_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
-    if ((rc = tc_chunk_launch<tcs::M_DK>(a, L, p, dy, a->v, a->q, "k_tc_chunk<dk>", st))) return rc;
+    if (use_chunk2()) {
+      if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk2<dv>", st))) return rc;
+      if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk2<dq>", st))) return rc;
+      if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk2<dk>", st))) return rc;
+    } else {
+      if ((rc = tc_chunk_launch<tcs::M_DV>(a, L, p, a->q, a->k, dy, "k_tc_chunk<dv>", st))) return rc;
+      if ((rc = tc_chunk_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
+      if ((rc = tc_chunk_launch<tcs::M_DK>(a, L, p, dy, a->v, a->q, "k_tc_chunk<dk>", st))) return rc;
+    }
     k_dgamma_finalize<<<dim3(a->S, a->H, 1), 256, 0, st>>>(p, 64);
     QPAM_LAUNCH_CHECK("k_dgamma_finalize");
   }
