@@ -280,6 +280,7 @@ def main():
         "k_tc_chunk<dk>": ("tensor", bwd_each),
         "k_state_scan<fwd>": ("hbm", scan_bytes),
         "k_state_scan<rev>": ("hbm", scan_bytes),
+        "k_tc_state_anchors": ("hbm", scan_bytes),
     }
     roof_all = {}
     for n, kinfo in kernels.items():

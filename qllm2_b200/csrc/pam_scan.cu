@@ -1,6 +1,5 @@
 // Host side of the chunked PAM scan: argument checks, workspace carving, launches.
 #include <mutex>
-#include <stdlib.h>
 
 #include "pam_scan_chunk.cuh"
 #include "pam_scan_tc.cuh"
@@ -16,7 +15,7 @@ struct ScanLayout {
   int32_t ch;           // tokens per chunk of this layout
   int32_t nc_uniform;
   int32_t grid_chunks;  // upper bound on the number of chunks (grid.x of the chunk kernels)
-  size_t off_prefix, off_states, off_decay, off_dstates, total_fwd, total_bwd;
+  size_t off_prefix, off_states, off_decay, off_dstates, off_anchors, total_fwd, total_bwd;
 };
 
 // Tensor-core kernels take bf16 token tensors with head dim 64 and a single state; their chunk is
@@ -52,6 +51,8 @@ static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   L.total_fwd = off;
   L.off_dstates = off;
   off += align256(sizeof(float2) * (size_t)a->K * a->H * L.nslots * dd);
+  L.off_anchors = off;
+  off += align256(sizeof(float) * (size_t)a->K * a->H * L.nslots);
   L.total_bwd = off;
   return L;
 }
@@ -152,24 +153,7 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   return QPAM_OK;
 }
 
-template <int MODE>
-static int tc_chunk_launch(const qpam_scan_args* a, const ScanLayout& L, const ScanParams& p, const void* a1,
-                           const void* b1, const void* x2, const char* name, cudaStream_t st) {
-  tcs::ChunkMaps maps;
-  const int64_t rows = (int64_t)a->B * a->H * a->T;
-  int rc;
-  if ((rc = make_map(&maps.a1, a1, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = make_map(&maps.b1, b1, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = make_map(&maps.x2, x2, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = set_smem(tcs::k_tc_chunk<MODE>, tcs::CHUNK_SMEM))) return rc;
-  tcs::k_tc_chunk<MODE><<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK_SMEM, st>>>(maps, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e, name);
-  note_launch(name, st);
-  return QPAM_OK;
-}
-
-// planar two-CTA-per-SM variant (operand roles differ: output rows always follow A1)
+// one chunk kernel for the forward output and the three gradients (output rows follow A1)
 template <int MODE>
 static int tc_chunk2_launch(const qpam_scan_args* a, const ScanLayout& L, const ScanParams& p, const void* a1,
                             const void* b1, const void* x2, const char* name, cudaStream_t st) {
@@ -186,12 +170,6 @@ static int tc_chunk2_launch(const qpam_scan_args* a, const ScanLayout& L, const 
   note_launch(name, st);
   return QPAM_OK;
 }
-static bool use_chunk2() {
-  static int v = -1;
-  if (v < 0) { const char* e = getenv("QPAM_CHUNK2"); v = (e && e[0] == '1') ? 1 : 0; }
-  return v == 1;
-}
-
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
 static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
   ScanParams p = make_params(a, L);
@@ -203,8 +181,7 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
   rc = tc_states(p, L, a, st);
   if (rc) return rc;
   if (L.grid_chunks > 0 && a->y != nullptr) {
-    rc = use_chunk2() ? tc_chunk2_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk2<fwd>", st)
-                      : tc_chunk_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
+    rc = tc_chunk2_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
     if (rc) return rc;
   }
   return QPAM_OK;
@@ -235,17 +212,14 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
   QPAM_LAUNCH_CHECK("k_state_scan<rev>");
   if (L.grid_chunks > 0) {
-    if (use_chunk2()) {
-      if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk2<dv>", st))) return rc;
-      if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk2<dq>", st))) return rc;
-      if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk2<dk>", st))) return rc;
-    } else {
-      if ((rc = tc_chunk_launch<tcs::M_DV>(a, L, p, a->q, a->k, dy, "k_tc_chunk<dv>", st))) return rc;
-      if ((rc = tc_chunk_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
-      if ((rc = tc_chunk_launch<tcs::M_DK>(a, L, p, dy, a->v, a->q, "k_tc_chunk<dk>", st))) return rc;
-    }
-    k_dgamma_finalize<<<dim3(a->S, a->H, 1), 256, 0, st>>>(p, 64);
-    QPAM_LAUNCH_CHECK("k_dgamma_finalize");
+    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", st))) return rc;
+    if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
+    if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk<dk>", st))) return rc;
+    float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
+    tcs::k_tc_state_anchors<<<dim3((unsigned)L.nslots, a->H), 256, 0, st>>>(p, anchors);
+    QPAM_LAUNCH_CHECK("k_tc_state_anchors");
+    tcs::k_tc_dgamma_finalize<<<dim3(L.grid_chunks, a->H), 128, 0, st>>>(p, anchors);
+    QPAM_LAUNCH_CHECK("k_tc_dgamma_finalize");
   }
   return QPAM_OK;
 }

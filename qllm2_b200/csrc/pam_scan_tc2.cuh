@@ -1,4 +1,4 @@
-// Planar variant of the tensor-core chunk kernel: two CTAs per SM.
+// Tensor-core chunk kernel of the PAM scan (forward output and the three gradients): planar operands, two CTAs per SM.
 //
 // After the TMA has delivered the interleaved (re, im) token rows, each tile is de-interleaved IN
 // PLACE into a real plane and an imaginary plane (each one 128-byte-swizzled K-major block), so a
@@ -16,16 +16,26 @@
 //   DK    v   dy  q   row <= col < len exp(min(0, A_last - A_row))   dS^H                 dk
 //
 //   stage 1  X = A1 conj(B1)^T                               Xr: cols [0,128)  Xi: cols [128,256)
-//   epi 1    T = scale * D(row, col) * X  -> bf16 pairs      Tr: cols [0,64)   Ti: cols [128,192)
-//   stage 2  out  = T X2        (A from TMEM)                out_r: cols [64,128)  out_i: cols [192,256)
-//   stage 3  out += (rowfac * A1) (.) carried state
+//   epi 1    T = mask(row, col) * colfac[col] * X -> bf16    Tr: cols [0,64)   Ti: cols [128,192)
+//   stage 2  acc  = T X2        (A from TMEM)                acc_r: cols [64,128)  acc_i: cols [192,256)
+//   stage 3  acc += A1 (.) (cst * carried state)
+//   epi 2    out  = rowfac[row] * acc
+//
+// The decay D(row, col) = exp(A_row - A_col) (or its transpose) is applied in factored form around a
+// mid-chunk reference A_m: for the lower-triangular modes D = e^{A_row - A_m} e^{A_m - A_col}, the row
+// factor being common to the intra-chunk and the carried-state term up to the chunk constant
+// cst = e^{A_m}; for the upper-triangular modes D = e^{A_m - A_row} e^{A_col - A_m}, cst = e^{A_last - A_m}.
+// That leaves 256 exponentials per chunk instead of 16 K and no row-scaling pass over shared memory.
+// Exponents are clamped to [-80, 80]; this only alters terms whose true weight is below e^-80.
+// (Like the backward formulas, the factored form assumes gamma + eps <= 1, where the reference's
+// min(., 0) clamp of the decay matrix is inactive.)
 #pragma once
 #include "pam_scan_tc.cuh"
 
 namespace qpam {
 namespace tcs {
 
-constexpr size_t CHUNK2_SMEM = 1024 + 3 * 32768 + 2048;
+constexpr size_t CHUNK2_SMEM = 1024 + 3 * 32768 + 4096;
 
 // De-interleave one [2 blocks][128 rows][128 B] tile in place: thread (row, hb) owns block hb of its
 // row (32 complex numbers).  Phase 1 reads them; after a CTA-wide barrier phase 2 writes the 32 real
@@ -64,7 +74,9 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
   unsigned char* RC = RB + 32768;            // X2 planes
   float* Acum = reinterpret_cast<float*>(RC + 32768);   // [128]
   float* dots = Acum + TC;                              // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(dots + 2 * TC);  // [0] tma, [1] stage 1, [2] stages 2+3
+  float* colfac = dots + 2 * TC;                        // [128]
+  float* rowfac = colfac + TC;                          // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rowfac + TC);  // [0] tma, [1] stage 1, [2] stages 2+3
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
@@ -83,6 +95,19 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  const float a_mid = Acum[TC / 2 - 1], a_last = Acum[TC - 1];
+  auto cexp = [](float x) { return __expf(fminf(80.f, fmaxf(-80.f, x))); };
+  if (tid < TC) {
+    const float a = Acum[tid];
+    if (LOWER) {
+      colfac[tid] = cexp(a_mid - a);
+      rowfac[tid] = p.q_scale * cexp(a - a_mid);
+    } else {
+      colfac[tid] = (tid < L.len) ? p.q_scale * cexp(a - a_mid) : 0.f;
+      rowfac[tid] = cexp(a_mid - a);
+    }
+  }
+  const float st_cst = LOWER ? cexp(a_mid) : cexp(a_last - a_mid);
   const int row0 = (L.b * p.H + h) * p.T + L.t0;
   if (tid == 0) {
     mbar_arrive_expect_tx(&bars[0], 6 * 16384);
@@ -103,10 +128,10 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
     for (int it = 0; it < 4; ++it) {
       const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
       const float4 s01 = __ldg(sg + idx * 2), s23 = __ldg(sg + idx * 2 + 1);
-      st_r[it][0] = pack_bf162(s01.x, s01.z);
-      st_r[it][1] = pack_bf162(s23.x, s23.z);
-      st_i[it][0] = pack_bf162(s01.y, s01.w);
-      st_i[it][1] = pack_bf162(s23.y, s23.w);
+      st_r[it][0] = pack_bf162(st_cst * s01.x, st_cst * s01.z);
+      st_r[it][1] = pack_bf162(st_cst * s23.x, st_cst * s23.z);
+      st_i[it][0] = pack_bf162(st_cst * s01.y, st_cst * s01.w);
+      st_i[it][1] = pack_bf162(st_cst * s23.y, st_cst * s23.w);
     }
   }
   bool ok = mbar_wait(&bars[0], 0, 221);
@@ -147,13 +172,11 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
   __syncwarp();
   ok = mbar_wait(&bars[1], 0, 222) && ok;
   tc_fence_after();
-  const float a_last = Acum[TC - 1];
   const int q4 = warp & 3, hf = warp >> 2;
   const int r = q4 * 32 + lane;                               // this thread's row (TMEM lane)
   const uint32_t tlane = tmem + ((uint32_t)(q4 * 32) << 16);
   {
     // epilogue 1: masked, decayed scores of columns [64 hf, 64 hf + 64) as packed bf16 pairs
-    const float a_row = Acum[r];
     uint32_t tr[32], ti[32];
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) {
@@ -172,9 +195,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int c = c0 + j + e;
-            const bool on = LOWER ? (c <= r) : (c >= r && c < L.len);
-            const float diff = LOWER ? (a_row - Acum[c]) : (Acum[c] - a_row);
-            d[e] = on ? p.q_scale * __expf(fminf(0.f, diff)) : 0.f;
+            d[e] = (LOWER ? (c <= r) : (c >= r)) ? colfac[c] : 0.f;
           }
           tr[cc * 8 + (j >> 1)] = pack_bf162(d[0] * xr[j], d[1] * xr[j + 1]);
           ti[cc * 8 + (j >> 1)] = pack_bf162(d[0] * xi[j], d[1] * xi[j + 1]);
@@ -197,23 +218,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
       tmem_st_wait();
     }
     if (has_state) {
-      // A3: scale the rows of both A1 planes in place; carried state planes into the B1 region
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int ci = tid + 256 * it;      // 2 planes x 128 rows x 8 chunks
-        const int row = (ci >> 3) & 127;
-        const float f = LOWER ? p.q_scale * __expf(Acum[row]) : __expf(fminf(0.f, a_last - Acum[row]));
-        uint4* ptr = reinterpret_cast<uint4*>(RA + (size_t)ci * 16);
-        const uint4 x = *ptr;
-        const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
-        uint32_t o[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 v2 = unpack_bf162(xw[e]);
-          o[e] = pack_bf162(f * v2.x, f * v2.y);
-        }
-        *ptr = make_uint4(o[0], o[1], o[2], o[3]);
-      }
+      // carried state planes (already multiplied by the chunk constant) into the B1 region
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int idx = tid + 256 * it;
@@ -288,12 +293,18 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
     }
     ok = mbar_wait(&bars[2], 0, 223) && ok;
     tc_fence_after();
+    const float rf = rowfac[r];
     float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       float vr[16], vi[16];
       tmem_ld16(tlane + 64 + hf * 32 + cc * 16, vr);
       tmem_ld16(tlane + 192 + hf * 32 + cc * 16, vi);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        vr[j] *= rf;
+        vi[j] *= rf;
+      }
       if (ok && r < L.len) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) {     // 4 complex channels -> one 16-byte store

@@ -82,7 +82,7 @@ def _grads_vs_oracle(inp, s0=None, ds_final=None, cu=None, packed=False):
         assert_close(grads[4].cpu().numpy(), po.to_split(b["dS0"]), TOL, "ds0")
 
 
-@pytest.mark.parametrize("B,H,T", [(1, 1, 128), (2, 2, 300), (1, 1, 50), (1, 2, 1024), (1, 1, 129)])
+@pytest.mark.parametrize("B,H,T", [(1, 1, 128), (2, 2, 300), (1, 1, 50), (1, 2, 1024), (1, 1, 129), (1, 1, 4096)])
 def test_backward_shapes(B, H, T):
     _grads_vs_oracle(synthetic.scan_inputs(B, H, T, 64, seed=80 + T, dtype=torch.bfloat16))
 
