@@ -206,16 +206,38 @@ def main():
         y, _ = ops.pam_scan(q, k, v, gam, chunk=C)
         return (y, *torch.autograd.grad(y, [q, k, v, gam], s["dy"]))
 
-    out_host = None
+    # end-to-end: host (pinned) -> device -> kernels -> host (pinned), software-pipelined over three
+    # streams with two device-side input slots, so copies of neighbouring steps overlap the kernels
+    cur = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    slots = [dict() for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    out_host = [None, None]
+    e2e_i = [0]
 
     def step_e2e(hs):
-        nonlocal out_host
-        s = {k_: v_.to(dev, non_blocking=True) for k_, v_ in hs.items()}
-        outs = step_dev(s)
-        if out_host is None:
-            out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
-        for o, oh in zip(outs, out_host):
-            oh.copy_(o, non_blocking=True)
+        i = e2e_i[0] % 2
+        e2e_i[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[i])                       # slot i no longer read by its previous step
+            for k_, v_ in hs.items():
+                if k_ not in slots[i]:
+                    slots[i][k_] = torch.empty(v_.shape, dtype=v_.dtype, device=dev)
+                slots[i][k_].copy_(v_, non_blocking=True)
+            ev_in[i].record(s_in)
+        cur.wait_event(ev_in[i])
+        outs = step_dev(slots[i])
+        ev_done = torch.cuda.Event()
+        ev_done.record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_done)
+            if out_host[i] is None:
+                out_host[i] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+            for o, oh in zip(outs, out_host[i]):
+                o.record_stream(s_out)
+                oh.copy_(o, non_blocking=True)
+            ev_free[i].record(s_out)
         return outs
 
     def barrier():
@@ -223,7 +245,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, sets, steps, warmup):
+    def timed(fn, sets, steps, warmup, join=None):
         for i in range(warmup):
             fn(sets[i % nsets])
         barrier()
@@ -232,6 +254,8 @@ def main():
         e0.record()
         for i in range(steps):
             fn(sets[i % nsets])
+        if join is not None:
+            join()          # the timed region ends when the side streams' copies have landed
         e1.record()
         barrier()
         ms = e0.elapsed_time(e1)
@@ -245,7 +269,8 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     ms, launches = timed(step_dev, dev_sets, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
-    ms_e2e, _ = timed(step_e2e, host_sets, args.steps, args.warmup)
+    ms_e2e, _ = timed(step_e2e, host_sets, args.steps, args.warmup,
+                      join=lambda: (cur.wait_stream(s_in), cur.wait_stream(s_out)))
 
     tokens_step = B * T * world
     value = tokens_step * args.steps / (ms * 1e-3)
