@@ -405,7 +405,36 @@ def side_measurements(dev, peaks):
     torch.cuda.empty_cache()
     out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
     out["continuous_decode"] = continuous_decode(dev)
+    torch.cuda.empty_cache()
+    out["train_step_config3"] = train_step(dev, time_ms)
     return out
+
+
+def train_step(dev, time_ms, B=8, T=2048):
+    """Config 3: 8-block v11_e3_k3-style model (dim 384, H=6, d=64, K=3, chunk 64, vocab 50261), random init,
+    bf16 autocast, forward + fused-CE loss + backward.  The scan (K=3) and the tied head run in this library;
+    projections / norms / gated units are torch modules."""
+    from qllm2_b200 import model as M
+    torch.manual_seed(0)
+    cfg = M.get_config("v11_e3_k3_chat")
+    cfg.n_layers, cfg.chunk_size, cfg.dropout, cfg.gradient_checkpointing = 8, 64, 0.0, False
+    net = M.V11LM(cfg).to(dev).train()
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg.vocab_size, (B, T + 1), generator=gen).to(dev)
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    last = [0.0]
+
+    def step():
+        net.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            lm, aux, _ = net._hidden_to_lm(x)
+        loss = net.ce_from_lm(lm.bfloat16(), y)
+        loss.backward()
+        last[0] = loss
+    ms = time_ms(step, 3, warm=2)
+    return {"ms_per_step": ms, "tokens_per_s": B * T / ms * 1e3, "loss": float(last[0].detach()),
+            "params": sum(p_.numel() for p_ in net.parameters()),
+            "config": f"B={B} T={T}, 8 blocks, dim 384, H6 d64 K3, vocab 50261, bf16 autocast, fwd+loss+bwd, no optimizer step"}
 
 
 def packed_prefill(dev, peaks, time_ms):

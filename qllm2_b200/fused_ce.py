@@ -42,6 +42,8 @@ class _FusedLinearCE(torch.autograd.Function):
             w = w.to(h.dtype)
         targets = targets.contiguous()
         maskf = None if mask is None else mask.float().contiguous()
+        if maskf is not None and maskf.numel() != h.shape[0]:
+            raise ValueError("mask must have one entry per row of hidden_rows")
         ctx.empty = h.shape[0] == 0
         if ctx.empty:   # nothing to launch; the reference returns 0 / clamp_min(1) = 0
             ctx.save_for_backward(h, w)

@@ -72,6 +72,10 @@ class _PamScanFn(torch.autograd.Function):
         q, k, v, gamma, coef, s0, cu_seqlens, ws = ctx.saved_tensors
         q_scale, eps, chunk = ctx.cfg
         dy = torch.zeros_like(q) if dy is None else dy.contiguous().to(q.dtype)
+        if dy.shape != q.shape:
+            raise _lib.QPamError(f"dy shape {tuple(dy.shape)} != y shape {tuple(q.shape)}")
+        if ds_final is not None and ds_final.numel() != gamma.shape[0] * (q.shape[0] if cu_seqlens is None else cu_seqlens.numel() - 1) * q.shape[1] * q.shape[3] ** 2 * 2:
+            raise _lib.QPamError("ds_final has the wrong number of elements")
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dgamma = torch.empty_like(gamma)
         dcoef = torch.empty_like(coef) if coef is not None else None
@@ -99,15 +103,36 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
     s0       optional [K,S,H,d,d,2] initial state;  cu_seqlens optional int32 [S+1] (then B == 1)
     Returns (y [B,H,T,d,2] in q's dtype, s_final float32 [K,S,H,d,d,2]).
     """
+    # one dtype for the token tensors: under bf16 autocast the reference's matmuls round their inputs to
+    # bf16 anyway, so mixed fp32/bf16 operands (RoPE promotes q and k to fp32) are taken as bf16;
+    # otherwise they are promoted to the widest dtype present.  The C ABI reads all three through
+    # q's dtype, so they must agree before the pointers are handed over.
+    if torch.is_autocast_enabled() and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+        io = torch.bfloat16
+    else:
+        io = torch.promote_types(torch.promote_types(q.dtype, k.dtype), v.dtype)
+    q, k, v = q.to(io), k.to(io), v.to(io)
+    if not (q.shape == k.shape == v.shape and q.dim() == 5 and q.shape[-1] == 2):
+        raise _lib.QPamError(f"q, k, v must share one shape [B,H,T,d,2]; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    B_, H_, T_ = q.shape[:3]
     gamma = gamma.float()
     if gamma.dim() == 3:
         gamma = gamma.unsqueeze(0)
+    if gamma.shape[1:] != (B_, H_, T_):
+        raise _lib.QPamError(f"gamma shape {tuple(gamma.shape)} does not match q {tuple(q.shape)}")
     if coef is not None:
         coef = coef.float()
         if coef.dim() == 4:
             coef = coef.unsqueeze(0)
+    if coef is not None and coef.shape != gamma.shape + (2,):
+        raise _lib.QPamError(f"coef shape {tuple(coef.shape)} != gamma shape + (2,)")
+    n_seq = B_ if cu_seqlens is None else cu_seqlens.numel() - 1
     if s0 is not None:
         s0 = s0.float()
+        if s0.shape != (gamma.shape[0], n_seq, H_, q.shape[3], q.shape[3], 2):
+            raise _lib.QPamError(f"s0 shape {tuple(s0.shape)} != [K,S,H,d,d,2]")
+    if cu_seqlens is not None and B_ != 1:
+        raise _lib.QPamError("packed mode (cu_seqlens) needs B == 1")
     d = q.shape[3]
     head_dim = d if head_dim is None else head_dim
     if cu_seqlens is not None:
@@ -131,9 +156,16 @@ def pam_decode_step(state_pool, slot_ids, q_scaled, k, v, gamma, coef=None, *, l
         coef = coef.unsqueeze(0)
     gamma = gamma.float().contiguous()
     coef = None if coef is None else coef.float().contiguous()
+    k, v = k.to(q_scaled.dtype), v.to(q_scaled.dtype)
     q_scaled, k, v = q_scaled.contiguous(), k.contiguous(), v.contiguous()
     slot_ids = slot_ids.to(device=state_pool.device, dtype=torch.int32).contiguous()
     n = q_scaled.shape[0]
+    if not (q_scaled.shape == k.shape == v.shape == (n, H, d, 2)):
+        raise _lib.QPamError(f"q, k, v must be [n,H,d,2] = {(n, H, d, 2)}; got {tuple(q_scaled.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if slot_ids.numel() != n:
+        raise _lib.QPamError("slot_ids must have one entry per sequence")
+    if coef is not None and coef.shape != (K, n, H, 2):
+        raise _lib.QPamError(f"coef shape {tuple(coef.shape)} != {(K, n, H, 2)}")
     if gamma.shape != (K, n, H):
         raise _lib.QPamError(f"gamma shape {tuple(gamma.shape)} != {(K, n, H)}")
     if not state_pool.is_contiguous():
@@ -151,6 +183,8 @@ def pam_pool_store(state_pool, slot_ids, states, *, layer: int = 0):
     n_slots, n_layers, K, H, d = state_pool.shape[:5]
     states = states.float().contiguous()
     S = states.shape[1]
+    if states.shape != (K, S, H, d, d, 2) or slot_ids.numel() != S:
+        raise _lib.QPamError(f"states must be [K,S,H,d,d,2] with one slot id per sequence; got {tuple(states.shape)}")
     slot_ids = slot_ids.to(device=state_pool.device, dtype=torch.int32).contiguous()
     check(L.qpam_pool_store(state_pool.data_ptr(), dtype_code(state_pool.dtype), n_slots, n_layers, layer,
                             ptr(slot_ids), ptr(states), S, H, d, K, stream_ptr()), "qpam_pool_store")
@@ -173,6 +207,10 @@ def ce_row_stats(h, w, targets, *, ignore_index=-100, v_offset=0):
     h, w = h.contiguous(), w.contiguous()
     if h.dtype != w.dtype:
         w = w.to(h.dtype)
+    if h.dim() != 2 or w.dim() != 2 or h.shape[1] != w.shape[1]:
+        raise _lib.QPamError(f"h [N,F] and w [V,F] expected; got {tuple(h.shape)}, {tuple(w.shape)}")
+    if targets is not None and (targets.dtype != torch.int64 or targets.numel() != h.shape[0]):
+        raise _lib.QPamError("targets must be int64 with one entry per row of h")
     N = h.shape[0]
     f32 = dict(dtype=torch.float32, device=h.device)
     row_max, row_sum, row_tgt = torch.empty(N, **f32), torch.empty(N, **f32), torch.empty(N, **f32)

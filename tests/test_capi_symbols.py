@@ -68,3 +68,17 @@ def test_ops_fail_loudly_without_cuda():
     q = torch.zeros(1, 1, 8, 16, 2)
     with pytest.raises(_lib.QPamError):
         ops.pam_scan(q, q, q, torch.ones(1, 1, 8))
+
+
+def test_wrappers_reject_inconsistent_tensors_before_any_launch():
+    """Shape / dtype mismatches are caught in Python: the C ABI reads k and v through q's dtype, so a
+    mismatch would otherwise read past the end of a buffer on the device."""
+    import torch
+    from qllm2_b200 import _lib, ops
+    q = torch.zeros(1, 2, 8, 16, 2)
+    with pytest.raises(_lib.QPamError):
+        ops.pam_scan(q, q[:, :1], q, torch.ones(1, 2, 8))
+    with pytest.raises(_lib.QPamError):
+        ops.pam_scan(q, q, q, torch.ones(1, 2, 9))
+    with pytest.raises(_lib.QPamError):
+        ops.pam_scan(q, q, q, torch.ones(1, 2, 8), coef=torch.ones(1, 1, 2, 8))

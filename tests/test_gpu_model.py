@@ -65,3 +65,20 @@ def test_bf16_model_tracks_reference(golden_dir):
     with torch.no_grad():
         logits, _, _ = net(x)
     assert_close(logits.float().cpu().numpy(), g["logits"], 2e-2, "bf16 logits")
+
+
+def test_autocast_mixed_dtypes_are_unified(golden_dir):
+    """Under bf16 autocast RoPE leaves q, k in fp32 while v is bf16: the scan wrapper must bring them to
+    one dtype (a mismatch used to be read through q's dtype)."""
+    g, net = _load(golden_dir, "k3")
+    x = torch.from_numpy(g["ids"]).to(DEV)[:, :-1]
+    labels = torch.from_numpy(g["labels"]).to(DEV)
+    net.train()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        lm, _, _ = net._hidden_to_lm(x)
+    loss = net.ce_from_lm(lm.bfloat16(), labels)
+    loss.backward()
+    torch.cuda.synchronize()
+    ref = float(g["loss"])
+    assert abs(float(loss.detach()) - ref) <= 2e-2 * ref
+    assert all(torch.isfinite(p.grad).all() for p in net.parameters() if p.grad is not None)
