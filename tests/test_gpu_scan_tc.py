@@ -104,3 +104,32 @@ def test_backward_is_deterministic():
         res.append([y.detach()] + list(torch.autograd.grad(y, [q, k, v, g], inp.dy.to(DEV))))
     for a, b in zip(*res):
         assert torch.equal(a, b)
+
+
+def test_multistate_bf16_on_tensor_cores(golden_dir):
+    """K=3 phase-routed scan, bf16, d=64: the sum of K single-state tensor-core scans equals the oracle's
+    K-state scan (forward, final states, and every gradient incl. dgamma_k and dcoef)."""
+    B, H, T, d, K = 1, 2, 300, 64, 3
+    inp = synthetic.scan_inputs(B, H, T, d, seed=33, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(4)
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=gen) + torch.tensor([1.0, 3.0, 5.0]).view(K, 1, 1, 1))
+    phase = torch.randn(K, B, H, T, generator=gen)
+    alpha = 0.5 + torch.rand(K, B, H, T, generator=gen)
+    coef = torch.stack([alpha * torch.cos(phase), alpha * torch.sin(phase)], dim=-1)
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+    gd = gamma.to(DEV).requires_grad_(True)
+    cd = coef.to(DEV).requires_grad_(True)
+    y, s = ops.pam_scan(q, k, v, gd, coef=cd)
+    dq, dk, dv, dgam, dcoef = torch.autograd.grad(y, [q, k, v, gd, cd], inp.dy.to(DEV))
+    assert _lib.device_status() == 0
+    qc, kc, vc, dyc = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v, inp.dy))
+    cf = po.to_complex(coef.numpy())
+    y_ref, s_ref = po.scan_recurrence(qc, kc, vc, gamma.double().numpy(), coef=cf)
+    b = po.scan_backward(qc, kc, vc, gamma.double().numpy(), dyc, coef=cf)
+    assert_close(y.detach().float().cpu().numpy(), po.to_split(y_ref), TOL, "Y")
+    assert_close(s.detach().cpu().numpy(), po.to_split(s_ref), TOL, "S")
+    assert_close(dq.float().cpu().numpy(), po.to_split(b["dq"]), TOL, "dq")
+    assert_close(dk.float().cpu().numpy(), po.to_split(b["dk"]), TOL, "dk")
+    assert_close(dv.float().cpu().numpy(), po.to_split(b["dv"]), TOL, "dv")
+    assert_close(dgam.cpu().numpy(), b["dgamma"], TOL, "dgamma")
+    assert_close(dcoef.cpu().numpy(), po.to_split(b["dcoef"]), TOL, "dcoef")
