@@ -28,6 +28,7 @@ struct GemmParams {
   int32_t tiles_per_cta;    // N tiles walked by one CTA (blockIdx.x selects the range)
   int32_t kb_total;         // K blocks in total
   int32_t kb_per_split;     // K blocks per blockIdx.z
+  int32_t swap_xy;          // 1: blockIdx.x walks the M tiles (neighbouring CTAs share the B tile in L2)
   int64_t M, N;             // logical extents (rows / columns of D)
   // EPI_STATS
   const int64_t* targets;
@@ -74,8 +75,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tile = blockIdx.y;
-  const int n_begin = blockIdx.x * p.tiles_per_cta;
+  const int m_tile = p.swap_xy ? blockIdx.x : blockIdx.y;
+  const int n_begin = (p.swap_xy ? blockIdx.y : blockIdx.x) * p.tiles_per_cta;
   const int n_end = min(p.n_tiles, n_begin + p.tiles_per_cta);
   const int kb_begin = blockIdx.z * p.kb_per_split;
   const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);

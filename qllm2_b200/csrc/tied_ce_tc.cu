@@ -127,7 +127,8 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     p.row_base = r0;
     p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
     p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
-    k_probs<<<dim3(pl.n_tiles, row_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
+    p.swap_xy = 1;   // consecutive CTAs take the row tiles of one vocabulary tile: W is read from DRAM once
+    k_probs<<<dim3(row_tiles, pl.n_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
     QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
     // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
     tc::GemmParams g{};
