@@ -295,28 +295,31 @@ def main():
     f_fwd = scan_flops_per_token_head(d, C, K) * th
     CT = 128  # tokens per chunk of the tensor-core kernels
     bwd_each = (2 * f_fwd - 8 * d * d * th) / 3.0
-    scan_bytes = 2 * (T // CT) * B * H * K * d * d * 8
-    alg = {  # algorithmic flops (tensor-bound pieces) or bytes (HBM-bound pieces) per launch
-        "k_tc_chunk<fwd>": ("tensor", f_fwd - 8 * d * d * th),
-        "k_tc_chunk_outer<state>": ("tensor", 8 * d * d * th),
-        "k_tc_chunk_outer<dstate>": ("tensor", 8 * d * d * th),
-        "k_tc_chunk<dv>": ("tensor", bwd_each),
-        "k_tc_chunk<dq>": ("tensor", bwd_each),
-        "k_tc_chunk<dk>": ("tensor", bwd_each),
-        "k_state_scan<fwd>": ("hbm", scan_bytes),
-        "k_state_scan<rev>": ("hbm", scan_bytes),
-        "k_tc_state_anchors": ("hbm", scan_bytes),
+    TT = th * d * 2 * 2                                   # one bf16 token tensor [B,H,T,d,2]
+    ST = (T // CT) * B * H * K * d * d * 8                # one pass over the fp32 chunk states
+    # Per kernel: the bytes it must move once (inputs + outputs) and its share of the algorithmic flops.
+    # Every piece of the scan is HBM-bound at this shape (<= 120 flop/B against a ridge of ~255 flop/B), so
+    # the roofline fraction is taken against the measured copy bandwidth; TFLOP/s is reported beside it.
+    alg = {
+        "k_tc_chunk<fwd>": (4 * TT + ST, f_fwd - 8 * d * d * th),          # q,k,v,S -> y
+        "k_tc_chunk_outer<state>": (2 * TT + ST, 8 * d * d * th),          # k,v -> U
+        "k_tc_chunk_outer<dstate>": (2 * TT + ST, 8 * d * d * th),         # dy,q -> G
+        "k_tc_chunk<dv>": (4 * TT + ST, bwd_each),                         # k,q,dy,dS -> dv
+        "k_tc_chunk<dq>": (5 * TT + ST, bwd_each),                         # dy,v,k,S,q -> dq
+        "k_tc_chunk<dk>": (5 * TT + ST, bwd_each),                         # v,dy,q,dS,k -> dk
+        "k_state_scan<fwd>": (2 * ST, 0.0),
+        "k_state_scan<rev>": (2 * ST, 0.0),
+        "k_tc_state_anchors": (2 * ST, 0.0),
     }
     roof_all = {}
     for n, kinfo in kernels.items():
         if n in alg:
-            bound, amount = alg[n]
+            nbytes, nflops = alg[n]
             sec = kinfo["ms_per_launch"] * 1e-3
-            if bound == "tensor":
-                ach, peak, unit = amount / sec / 1e12, peaks["tf"], "TFLOP/s"
-            else:
-                ach, peak, unit = amount / sec / 1e9, peaks["hbm"], "GB/s"
-            roof_all[n] = {"bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+            ach = nbytes / sec / 1e9
+            roof_all[n] = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm"], "unit": "GB/s",
+                           "frac": ach / peaks["hbm"], "algorithmic_bytes": nbytes,
+                           "tflops": nflops / sec / 1e12, "frac_of_bf16_peak": nflops / sec / 1e12 / peaks["tf"],
                            "share_of_step": prof[n][1] / total_prof if total_prof else None}
     dominant = max(roof_all, key=lambda n: prof[n][1]) if roof_all else None
     traffic = None
