@@ -474,19 +474,38 @@ def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=102
                       gate_content_aware=True, dropout=0.0, gradient_checkpointing=False, max_seq_len=8192)
     net = M.V11LM(cfg).to(dev).bfloat16().eval()
     prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
-    eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16)
-    for p_ in prompts:
-        eng.submit(p_.tolist(), new_tokens)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    res = eng.run()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
-    gen_tokens = sum(len(v_) for v_ in res.values())
-    return {"generated_tokens": gen_tokens, "seconds": dt, "decode_tokens_per_s": gen_tokens / dt,
-            "prompt_tokens": int(sum(len(p_) for p_ in prompts)), "engine_steps": eng.steps,
-            "config": f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
-                      f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init; wall time includes the packed prefills"}
+    out = {}
+    for mode in ("graph", "eager"):
+        eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, cuda_graph=(mode == "graph"))
+        for p_ in prompts:
+            eng.submit(p_.tolist(), new_tokens)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = eng.run()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        gen_tokens = sum(len(v_) for v_ in res.values())
+        out[mode] = {"generated_tokens": gen_tokens, "seconds": dt, "decode_tokens_per_s": gen_tokens / dt,
+                     "engine_steps": eng.steps}
+        if mode == "graph" and eng._graph is not None:
+            # the decode step alone, every slot busy: replay the captured step on idle rows re-pointed at slots
+            eng._g_slots.copy_(torch.arange(n_slots, dtype=torch.int32, device=dev))
+            for _ in range(3):
+                eng._graph.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(20):
+                eng._graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 20
+            out[mode]["decode_step_ms"] = ms
+            out[mode]["steady_decode_tokens_per_s"] = n_slots / ms * 1e3
+    out["prompt_tokens"] = int(sum(len(p_) for p_ in prompts))
+    out["config"] = (f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
+                     f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init; wall time includes the packed prefills; "
+                     f"graph = decode step replayed from one CUDA graph, eager = the Python layer loop")
+    return out
 
 
 if __name__ == "__main__":

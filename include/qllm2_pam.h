@@ -188,6 +188,52 @@ int qpam_ce_bwd(const qpam_ce_args* args, const float* lse, const float* grad_sc
 int qpam_head_argmax(const qpam_ce_args* args, int64_t* ids, float* best, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Fused element-wise complex operators of a V11 block (interleaved [..., C, 2] rows, N rows).
+ * They replace the reference's fused operators and their autograd functions:
+ *   qpam_cnorm_*     fused_complex_norm   v11/triton_kernels.py:48-80, 209-263, 489-494
+ *   qpam_modact_*    fused_mod_swish (beta != NULL) / fused_mod_relu (beta == NULL)
+ *                                          v11/triton_kernels.py:82-137, 266-361, 497-508
+ *   qpam_cgu_gate_*  fused_cgu_gate        v11/triton_kernels.py:139-166, 364-417, 511-519
+ *   qpam_pam_prep_*  the head split, rotary rotation and protect-gate scaling of
+ *                    PhaseAssociativeLayer._project / _gamma_and_vprime (v11/model.py:271-350)
+ * Parameters (scale, bias, beta, rope, omp) are fp32.  Parameter gradients come back as P partial
+ * rows [P, C] that the caller sums over P.  C must be a multiple of 4; rows must be 16-byte
+ * aligned.  ld_* are row strides in scalars, so gate/up (and their gradients) may be column
+ * blocks of one wider matrix.
+ * ------------------------------------------------------------------------------------------ */
+/* out = z/(|z|+1e-8) * (|z|/rms) * scale, |z| = sqrt(re^2+im^2+1e-8), rms = sqrt(mean|z|^2 + eps).
+ * dtypes: f32->f32, f32->bf16, bf16->bf16.  D <= 3072. */
+int qpam_cnorm_fwd(const void* z, int32_t z_dtype, const float* scale, void* out, int32_t out_dtype,
+                   int64_t N, int32_t D, float eps, void* stream);
+/* P (a multiple of 4) partial rows of d(scale); dz has z's dtype, dout out's. */
+int qpam_cnorm_bwd(const void* z, int32_t z_dtype, const float* scale, const void* dout,
+                   int32_t out_dtype, void* dz, float* dscale_partials, int32_t P, int64_t N,
+                   int32_t D, float eps, void* stream);
+int qpam_modact_fwd(const void* z, int32_t dtype, const float* bias, const float* beta, void* out,
+                    int64_t N, int32_t C, void* stream);
+/* 1 <= P <= min(N, 65535) partial rows of d(bias) and (modSwish) d(beta). */
+int qpam_modact_bwd(const void* z, int32_t dtype, const float* bias, const float* beta,
+                    const void* dout, void* dz, float* dbias_partials, float* dbeta_partials,
+                    int32_t P, int64_t N, int32_t C, void* stream);
+/* out = gate/(|gate|+1e-8) * up * sigmoid(|gate|)  (complex product), out dense [N, C, 2]. */
+int qpam_cgu_gate_fwd(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up, int32_t dtype,
+                      void* out, int64_t N, int32_t C, void* stream);
+int qpam_cgu_gate_bwd(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up,
+                      const void* dout, int32_t dtype, void* dgate, int64_t ld_dgate, void* dup,
+                      int64_t ld_dup, int64_t N, int32_t C, void* stream);
+/* qkv [B,T,3,H,d,2] -> q,k,v [B,H,T,d,2]:  q,k *= rope[pos] (rope fp32 [rope_len,d,2] = cos,sin;
+ * NULL = no rotation), v *= omp[b,t,h] (fp32 [B,T,H]; NULL = 1).  pos = positions[b,t] (int64,
+ * clamped to the table) or offset + t when positions is NULL.  d a power of two in [4,128]. */
+int qpam_pam_prep_fwd(const void* qkv, int32_t dtype, const float* rope, int64_t rope_len,
+                      const int64_t* positions, int64_t offset, const float* omp, void* q, void* k,
+                      void* v, int32_t B, int32_t T, int32_t H, int32_t d, void* stream);
+/* dqkv [B,T,3,H,d,2] and, when omp is given, domp [B,T,H] (fp32). */
+int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* rope, int64_t rope_len,
+                      const int64_t* positions, int64_t offset, const float* omp, const void* dq,
+                      const void* dk, const void* dv, void* dqkv, float* domp, int32_t B, int32_t T,
+                      int32_t H, int32_t d, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Launch accounting and per-kernel timing.  The reference times whole calls with
  * time.perf_counter around torch.cuda.synchronize (v11/bench_flash_pam.py:73-84); these entry
  * points give the per-kernel split of the same calls.

@@ -57,6 +57,19 @@ SIGNATURES = {
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "qpam_ce_bwd": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "qpam_head_argmax": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p]),
+    "qpam_cnorm_fwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int64, c_int32, C.c_float, c_void_p]),
+    "qpam_cnorm_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int64,
+                                 c_int32, C.c_float, c_void_p]),
+    "qpam_modact_fwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+    "qpam_modact_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int32, c_int64, c_int32, c_void_p]),
+    "qpam_cgu_gate_fwd": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p]),
+    "qpam_cgu_gate_bwd": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64,
+                                    c_void_p, c_int64, c_int64, c_int32, c_void_p]),
+    "qpam_pam_prep_fwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "qpam_pam_prep_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

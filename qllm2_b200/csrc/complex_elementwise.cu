@@ -1,0 +1,593 @@
+// Fused element-wise complex operators of the V11 blocks, forward and backward, on the interleaved
+// [..., C, 2] layout: magnitude-RMS norm, modSwish / modReLU, the gated-unit product, and the
+// head split + rotary rotation + protect-gate scaling that feeds the PAM scan.
+//
+// The reference runs these as Triton kernels in the forward pass and as chains of torch operators in
+// the backward pass (v11/triton_kernels.py:48-166 kernels, :209-417 autograd functions, :489-520 the
+// plain arithmetic).  Here each direction is ONE pass over the tensors (HBM-bound): 16-byte vector
+// loads of 4 complex channels per thread, fp32 arithmetic, per-channel parameter gradients kept in
+// registers over the rows a thread walks and written as partial rows that the caller sums.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace qpam {
+namespace {
+
+constexpr float MAG_EPS = 1e-8f;  // inside the square root and beside the magnitude, as the reference
+
+// 4 complex channels (re,im interleaved) <-> registers
+template <typename T>
+struct V4;
+template <>
+struct V4<float> {
+  static __device__ __forceinline__ void ld(const float* p, float (&r)[4], float (&i)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    r[0] = a.x; i[0] = a.y; r[1] = a.z; i[1] = a.w; r[2] = b.x; i[2] = b.y; r[3] = b.z; i[3] = b.w;
+  }
+  static __device__ __forceinline__ void st(float* p, const float (&r)[4], const float (&i)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(r[0], i[0], r[1], i[1]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(r[2], i[2], r[3], i[3]);
+  }
+};
+template <>
+struct V4<__nv_bfloat16> {
+  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&r)[4], float (&i)[4]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      r[j] = __uint_as_float(w[j] << 16);
+      i[j] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&r)[4], const float (&i)[4]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(r[j], i[j]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------
+// Magnitude-RMS norm.  out = z / (|z| + e) * (|z| / rms) * scale,  |z| = sqrt(re^2 + im^2 + e),
+// rms = sqrt(mean_j |z_j|^2 + eps).  One warp per row; a lane owns the same channels in every row
+// it visits, so d(scale) accumulates in registers (MAXV vectors of 4 channels per lane).
+// ------------------------------------------------------------------------------------------------
+template <typename TI, typename TO, int MAXV, bool CACHE>
+__global__ void __launch_bounds__(128) k_cnorm_fwd(const TI* __restrict__ z, const float* __restrict__ scale,
+                                                   TO* __restrict__ out, int64_t N, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int groups = D >> 2;
+  constexpr int NV = CACHE ? MAXV : 1;  // rows wider than the register cache are read a second time (L1/L2 hits)
+  for (int64_t row = warp; row < N; row += nwarps) {
+    const TI* zr = z + row * (int64_t)D * 2;
+    float re[NV][4], im[NV][4], ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int g = v * 32 + lane, cv = CACHE ? v : 0;
+      if (g < groups) {
+        V4<TI>::ld(zr + g * 8, re[cv], im[cv]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss += re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS;
+      }
+    }
+    ss = warp_sum(ss);
+    const float rrms = rsqrtf(ss / (float)D + eps);
+    TO* orow = out + row * (int64_t)D * 2;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int g = v * 32 + lane, cv = CACHE ? v : 0;
+      if (g < groups) {
+        if (!CACHE) V4<TI>::ld(zr + g * 8, re[cv], im[cv]);
+        const float4 sc = *reinterpret_cast<const float4*>(scale + g * 4);
+        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+        float orr[4], oi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mag = sqrtf(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
+          const float w = mag / (mag + MAG_EPS) * rrms * s4[j];
+          orr[j] = re[cv][j] * w;
+          oi[j] = im[cv][j] * w;
+        }
+        V4<TO>::st(orow + g * 8, orr, oi);
+      }
+    }
+  }
+}
+
+// With w_j = scale_j m_j / rms, m_j = |z_j| / (|z_j| + e), s_j = Re(conj(z_j) dout_j):
+//   dz_j = dout_j w_j + z_j [ s_j scale_j e / (rms (|z_j|+e)^2 |z_j|) - c / (rms D) ],
+//   c = sum_j s_j scale_j m_j / rms^2,    dscale_j = sum_rows s_j m_j / rms.
+template <typename TI, typename TO, int MAXV, bool CACHE>
+__global__ void __launch_bounds__(128) k_cnorm_bwd(const TI* __restrict__ z, const float* __restrict__ scale,
+                                                   const TO* __restrict__ dout, TI* __restrict__ dz,
+                                                   float* __restrict__ dscale_part, int64_t N, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int groups = D >> 2;
+  constexpr int NV = CACHE ? MAXV : 1;
+  float acc[MAXV][4];
+#pragma unroll
+  for (int v = 0; v < MAXV; ++v)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[v][j] = 0.f;
+  for (int64_t row = warp; row < N; row += nwarps) {
+    const TI* zr = z + row * (int64_t)D * 2;
+    const TO* dr = dout + row * (int64_t)D * 2;
+    float re[NV][4], im[NV][4], gr[NV][4], gi[NV][4], ss = 0.f, cs = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int g = v * 32 + lane, cv = CACHE ? v : 0;
+      if (g < groups) {
+        V4<TI>::ld(zr + g * 8, re[cv], im[cv]);
+        V4<TO>::ld(dr + g * 8, gr[cv], gi[cv]);
+        const float4 sc = *reinterpret_cast<const float4*>(scale + g * 4);
+        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float m2 = re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS;
+          const float mag = sqrtf(m2);
+          ss += m2;
+          cs += (gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j]) * s4[j] * (mag / (mag + MAG_EPS));
+        }
+      }
+    }
+    ss = warp_sum(ss);
+    cs = warp_sum(cs);
+    const float rrms = rsqrtf(ss / (float)D + eps);
+    const float common = cs * rrms * rrms * rrms / (float)D;  // c / (rms D)
+    TI* dzr = dz + row * (int64_t)D * 2;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int g = v * 32 + lane, cv = CACHE ? v : 0;
+      if (g < groups) {
+        if (!CACHE) {
+          V4<TI>::ld(zr + g * 8, re[cv], im[cv]);
+          V4<TO>::ld(dr + g * 8, gr[cv], gi[cv]);
+        }
+        const float4 sc = *reinterpret_cast<const float4*>(scale + g * 4);
+        const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+        float orr[4], oi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float mag = sqrtf(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
+          const float inv = 1.f / (mag + MAG_EPS);
+          const float m = mag * inv;
+          const float s = gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j];
+          const float w = m * rrms * s4[j];
+          const float k = s * s4[j] * MAG_EPS * rrms * inv * inv / mag - common;
+          orr[j] = gr[cv][j] * w + re[cv][j] * k;
+          oi[j] = gi[cv][j] * w + im[cv][j] * k;
+          acc[v][j] += s * m * rrms;
+        }
+        V4<TI>::st(dzr + g * 8, orr, oi);
+      }
+    }
+  }
+  {  // every warp writes its row of partial sums (zeros when it had no rows): the caller adds all of them
+    float* prow = dscale_part + warp * (int64_t)D;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int g = v * 32 + lane;
+      if (g < groups) *reinterpret_cast<float4*>(prow + g * 4) = make_float4(acc[v][0], acc[v][1], acc[v][2], acc[v][3]);
+    }
+  }
+}
+
+template <typename TI, typename TO>
+int cnorm_launch(bool bwd, const void* z, const float* scale, const void* dout_or_out, void* dz, float* part,
+                 int P, int64_t N, int D, float eps, cudaStream_t st) {
+  const int groups = D / 4;
+  const int maxv = (groups + 31) / 32;
+  const int blocks = (P + 3) / 4;
+#define QPAM_CNORM(MV, CA)                                                                                          \
+  if (bwd)                                                                                                          \
+    k_cnorm_bwd<TI, TO, MV, CA><<<blocks, 128, 0, st>>>((const TI*)z, scale, (const TO*)dout_or_out, (TI*)dz, part, \
+                                                        N, D, eps);                                                 \
+  else                                                                                                              \
+    k_cnorm_fwd<TI, TO, MV, CA><<<blocks, 128, 0, st>>>((const TI*)z, scale, (TO*)const_cast<void*>(dout_or_out), N, D, eps);
+  if (maxv <= 3) { QPAM_CNORM(3, true) }
+  else if (maxv <= 6) { QPAM_CNORM(6, true) }
+  else if (maxv <= 12) { QPAM_CNORM(12, false) }
+  else { QPAM_CNORM(24, false) }
+#undef QPAM_CNORM
+  if (bwd) { QPAM_LAUNCH_CHECK("k_cnorm_bwd"); } else { QPAM_LAUNCH_CHECK("k_cnorm_fwd"); }
+  return QPAM_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// modSwish  out = z / (|z|+e) * |z| sigmoid(beta |z| + bias)      (beta != nullptr)
+// modReLU   out = z / (|z|+e) * relu(|z| + bias)                  (beta == nullptr)
+// A thread owns one group of 4 channels and walks rows blockIdx.y, blockIdx.y + gridDim.y, ...
+// ------------------------------------------------------------------------------------------------
+template <typename T, bool SWISH>
+__global__ void __launch_bounds__(256) k_modact_fwd(const T* __restrict__ z, const float* __restrict__ bias,
+                                                    const float* __restrict__ beta, T* __restrict__ out,
+                                                    int64_t N, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= (C >> 2)) return;
+  float b4[4], be4[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b4[j] = bias[g * 4 + j];
+    be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
+  }
+  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
+    float re[4], im[4];
+    V4<T>::ld(z + (row * C + g * 4) * 2, re, im);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mag = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+      const float act = SWISH ? mag * sigmoidf_(be4[j] * mag + b4[j]) : fmaxf(mag + b4[j], 0.f);
+      const float f = act / (mag + MAG_EPS);
+      re[j] *= f;
+      im[j] *= f;
+    }
+    V4<T>::st(out + (row * C + g * 4) * 2, re, im);
+  }
+}
+
+// out = z f(|z|):  dz = dout f + z s f'(|z|) / |z|,  s = Re(conj(z) dout).
+template <typename T, bool SWISH>
+__global__ void __launch_bounds__(256) k_modact_bwd(const T* __restrict__ z, const float* __restrict__ bias,
+                                                    const float* __restrict__ beta, const T* __restrict__ dout,
+                                                    T* __restrict__ dz, float* __restrict__ dbias_part,
+                                                    float* __restrict__ dbeta_part, int64_t N, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= (C >> 2)) return;
+  float b4[4], be4[4], ab[4] = {0.f, 0.f, 0.f, 0.f}, abe[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b4[j] = bias[g * 4 + j];
+    be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
+  }
+  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
+    float re[4], im[4], gr[4], gi[4];
+    V4<T>::ld(z + (row * C + g * 4) * 2, re, im);
+    V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mag = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+      const float inv = 1.f / (mag + MAG_EPS);
+      const float s = gr[j] * re[j] + gi[j] * im[j];
+      float act, dact;  // act(|z|) and its derivative
+      if (SWISH) {
+        const float sg = sigmoidf_(be4[j] * mag + b4[j]);
+        const float t = mag * sg * (1.f - sg);
+        act = mag * sg;
+        dact = sg + t * be4[j];
+        ab[j] += s * t * inv;
+        abe[j] += s * t * mag * inv;
+      } else {
+        const bool on = mag + b4[j] > 0.f;
+        act = on ? mag + b4[j] : 0.f;
+        dact = on ? 1.f : 0.f;
+        ab[j] += on ? s * inv : 0.f;
+      }
+      const float f = act * inv;
+      const float k = s * (dact * inv - act * inv * inv) / mag;
+      const float r0 = re[j], i0 = im[j];
+      re[j] = gr[j] * f + r0 * k;
+      im[j] = gi[j] * f + i0 * k;
+    }
+    V4<T>::st(dz + (row * C + g * 4) * 2, re, im);
+  }
+  float* pb = dbias_part + (int64_t)blockIdx.y * C + g * 4;
+  *reinterpret_cast<float4*>(pb) = make_float4(ab[0], ab[1], ab[2], ab[3]);
+  if (SWISH) {
+    float* pe = dbeta_part + (int64_t)blockIdx.y * C + g * 4;
+    *reinterpret_cast<float4*>(pe) = make_float4(abe[0], abe[1], abe[2], abe[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Gated-unit product  out = gate/(|gate|+e) * up * sigmoid(|gate|)   (complex product).
+// gate / up / dgate / dup rows may sit inside wider matrices: ld_* are row strides in scalars.
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) k_cgu_gate_fwd(const T* __restrict__ gate, int64_t ld_gate,
+                                                      const T* __restrict__ up, int64_t ld_up,
+                                                      T* __restrict__ out, int64_t N, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= (C >> 2)) return;
+  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
+    float ar[4], ai[4], ur[4], ui[4];
+    V4<T>::ld(gate + row * ld_gate + g * 8, ar, ai);
+    V4<T>::ld(up + row * ld_up + g * 8, ur, ui);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mag = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float h = sigmoidf_(mag) / (mag + MAG_EPS);
+      const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
+      ar[j] = pr * h;
+      ai[j] = pi * h;
+    }
+    V4<T>::st(out + (row * C + g * 4) * 2, ar, ai);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_cgu_gate_bwd(const T* __restrict__ gate, int64_t ld_gate,
+                                                      const T* __restrict__ up, int64_t ld_up,
+                                                      const T* __restrict__ dout, T* __restrict__ dgate,
+                                                      int64_t ld_dgate, T* __restrict__ dup, int64_t ld_dup,
+                                                      int64_t N, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= (C >> 2)) return;
+  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
+    float ar[4], ai[4], ur[4], ui[4], gr[4], gi[4], dur[4], dui[4];
+    V4<T>::ld(gate + row * ld_gate + g * 8, ar, ai);
+    V4<T>::ld(up + row * ld_up + g * 8, ur, ui);
+    V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float mag = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float inv = 1.f / (mag + MAG_EPS);
+      const float sg = sigmoidf_(mag);
+      const float h = sg * inv;
+      const float dh = sg * (1.f - sg) * inv - sg * inv * inv;
+      const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
+      const float s = gr[j] * pr + gi[j] * pi;
+      // d(up) = conj(gate) dout h ;  d(gate) = conj(up) dout h + gate s h'(|gate|) / |gate|
+      dur[j] = h * (ar[j] * gr[j] + ai[j] * gi[j]);
+      dui[j] = h * (ar[j] * gi[j] - ai[j] * gr[j]);
+      const float k = s * dh / mag;
+      const float dgr = h * (ur[j] * gr[j] + ui[j] * gi[j]) + ar[j] * k;
+      const float dgi = h * (ur[j] * gi[j] - ui[j] * gr[j]) + ai[j] * k;
+      ar[j] = dgr;
+      ai[j] = dgi;
+    }
+    V4<T>::st(dgate + row * ld_dgate + g * 8, ar, ai);
+    V4<T>::st(dup + row * ld_dup + g * 8, dur, dui);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// PAM input stage: the fused projection output qkv [B,T,3,H,d,2] is split into Q, K, V'
+// [B,H,T,d,2]; Q and K are rotated by rope[pos] (cos,sin per channel), V' = (1-p) V with the
+// protect gate's complement omp [B,T,H] (fp32).  pos = positions[b,t] when given, else offset + t.
+// A thread moves one group of 4 channels of one of the three tensors; gph = d/4 groups per head.
+// ------------------------------------------------------------------------------------------------
+struct PrepParams {
+  const void* qkv;
+  const float* rope;
+  const int64_t* positions;
+  const float* omp;
+  void *q, *k, *v;      // fwd: outputs; bwd: incoming gradients
+  void* dqkv;           // bwd
+  float* domp;          // bwd (may be null)
+  int64_t offset, rope_len;
+  int B, T, H, d;
+};
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) k_pam_prep(PrepParams p) {
+  const int gph = p.d >> 2;
+  const int per_tok = 3 * p.H * gph;
+  const int per_tok_pad = (per_tok + 31) & ~31;
+  const int64_t ntok = (int64_t)p.B * p.T;
+  for (int64_t tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
+    const int b = (int)(tok / p.T), t = (int)(tok - (int64_t)b * p.T);
+    int64_t pos = p.positions ? p.positions[tok] : p.offset + t;
+    pos = pos < 0 ? 0 : (pos >= p.rope_len ? p.rope_len - 1 : pos);
+    for (int idx = threadIdx.x; idx < per_tok_pad; idx += blockDim.x) {
+      const bool on = idx < per_tok;
+      const int which = on ? idx / (p.H * gph) : 0;
+      const int rem = on ? idx - which * p.H * gph : 0;
+      const int h = rem / gph, g = rem - h * gph;
+      const int64_t src = ((tok * 3 + which) * p.H + h) * (int64_t)p.d * 2 + g * 8;
+      const int64_t dst = (((int64_t)b * p.H + h) * p.T + t) * (int64_t)p.d * 2 + g * 8;
+      T* side = reinterpret_cast<T*>(which == 0 ? p.q : which == 1 ? p.k : p.v);
+      float re[4] = {0.f, 0.f, 0.f, 0.f}, im[4] = {0.f, 0.f, 0.f, 0.f};
+      const float keep = (which == 2 && p.omp) ? p.omp[tok * p.H + h] : 1.f;
+      float dot = 0.f;
+      if (on) {
+        if (!BWD) {
+          V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src, re, im);
+        } else {
+          V4<T>::ld(side + dst, re, im);
+          if (which == 2 && p.domp) {
+            float vr[4], vi[4];
+            V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src, vr, vi);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dot += vr[j] * re[j] + vi[j] * im[j];
+          }
+        }
+        if (which < 2 && p.rope) {
+          const float4 c0 = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2);
+          const float4 c1 = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2 + 4);
+          const float cs[4] = {c0.x, c0.z, c1.x, c1.z};
+          const float sn[4] = {c0.y, c0.w, c1.y, c1.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float s_ = BWD ? -sn[j] : sn[j];  // the gradient rotates back
+            const float r0 = re[j], i0 = im[j];
+            re[j] = r0 * cs[j] - i0 * s_;
+            im[j] = r0 * s_ + i0 * cs[j];
+          }
+        } else if (which == 2) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            re[j] *= keep;
+            im[j] *= keep;
+          }
+        }
+        if (!BWD) V4<T>::st(side + dst, re, im);
+        else V4<T>::st(reinterpret_cast<T*>(p.dqkv) + src, re, im);
+      }
+      if (BWD && p.domp) {  // sum over the head's channels: gph consecutive lanes (gph divides 32)
+        for (int o = gph >> 1; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (on && which == 2 && g == 0) p.domp[tok * p.H + h] = dot;
+      }
+    }
+  }
+}
+
+inline bool is_dtype(int32_t d) { return d == QPAM_F32 || d == QPAM_BF16; }
+inline int act_grid_y(int64_t N, int xblocks, int P) {
+  int64_t y = P > 0 ? P : std::max<int64_t>(1, (148 * 8) / xblocks);
+  return (int)std::min<int64_t>(std::min<int64_t>(y, N), 65535);
+}
+
+}  // namespace
+}  // namespace qpam
+
+using namespace qpam;
+
+extern "C" int qpam_cnorm_fwd(const void* z, int32_t z_dtype, const float* scale, void* out, int32_t out_dtype,
+                              int64_t N, int32_t D, float eps, void* stream) {
+  QPAM_REQUIRE(z && scale && out, "cnorm_fwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(z_dtype) && is_dtype(out_dtype) && !(z_dtype == QPAM_BF16 && out_dtype == QPAM_F32),
+               "cnorm_fwd: dtypes must be f32->f32, f32->bf16 or bf16->bf16");
+  QPAM_REQUIRE(N >= 0 && D > 0 && D % 4 == 0 && D <= 3072, "cnorm_fwd: D must be a multiple of 4 and <= 3072 (got %d)", D);
+  if (N == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int P = (int)std::min<int64_t>(N, 148 * 32);
+  if (z_dtype == QPAM_F32 && out_dtype == QPAM_F32) return cnorm_launch<float, float>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
+  if (z_dtype == QPAM_F32) return cnorm_launch<float, __nv_bfloat16>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
+  return cnorm_launch<__nv_bfloat16, __nv_bfloat16>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
+}
+
+extern "C" int qpam_cnorm_bwd(const void* z, int32_t z_dtype, const float* scale, const void* dout,
+                              int32_t out_dtype, void* dz, float* dscale_partials, int32_t P, int64_t N,
+                              int32_t D, float eps, void* stream) {
+  QPAM_REQUIRE(z && scale && dout && dz && dscale_partials, "cnorm_bwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(z_dtype) && is_dtype(out_dtype) && !(z_dtype == QPAM_BF16 && out_dtype == QPAM_F32),
+               "cnorm_bwd: dtypes must be f32->f32, f32->bf16 or bf16->bf16");
+  QPAM_REQUIRE(N > 0 && D > 0 && D % 4 == 0 && D <= 3072, "cnorm_bwd: D must be a multiple of 4 and <= 3072 (got %d)", D);
+  QPAM_REQUIRE(P > 0 && P % 4 == 0, "cnorm_bwd: the number of partial rows must be a positive multiple of 4");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (z_dtype == QPAM_F32 && out_dtype == QPAM_F32) return cnorm_launch<float, float>(true, z, scale, dout, dz, dscale_partials, P, N, D, eps, st);
+  if (z_dtype == QPAM_F32) return cnorm_launch<float, __nv_bfloat16>(true, z, scale, dout, dz, dscale_partials, P, N, D, eps, st);
+  return cnorm_launch<__nv_bfloat16, __nv_bfloat16>(true, z, scale, dout, dz, dscale_partials, P, N, D, eps, st);
+}
+
+extern "C" int qpam_modact_fwd(const void* z, int32_t dtype, const float* bias, const float* beta, void* out,
+                               int64_t N, int32_t C, void* stream) {
+  QPAM_REQUIRE(z && bias && out, "modact_fwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && C > 0 && C % 4 == 0, "modact_fwd: C must be a multiple of 4 (got %d)", C);
+  if (N == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, 0));
+#define QPAM_ACT(T)                                                                                      \
+  if (beta) k_modact_fwd<T, true><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (T*)out, N, C);     \
+  else k_modact_fwd<T, false><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (T*)out, N, C);
+  if (dtype == QPAM_F32) { QPAM_ACT(float) } else { QPAM_ACT(__nv_bfloat16) }
+#undef QPAM_ACT
+  QPAM_LAUNCH_CHECK("k_modact_fwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_modact_bwd(const void* z, int32_t dtype, const float* bias, const float* beta,
+                               const void* dout, void* dz, float* dbias_partials, float* dbeta_partials,
+                               int32_t P, int64_t N, int32_t C, void* stream) {
+  QPAM_REQUIRE(z && bias && dout && dz && dbias_partials && (!beta || dbeta_partials), "modact_bwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && N > 0 && C > 0 && C % 4 == 0, "modact_bwd: C must be a multiple of 4 (got %d)", C);
+  QPAM_REQUIRE(P > 0 && P <= N && P <= 65535, "modact_bwd: partial rows must be in [1, min(N, 65535)]");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, P);
+#define QPAM_ACT(T)                                                                                              \
+  if (beta) k_modact_bwd<T, true><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (const T*)dout, (T*)dz,      \
+                                                            dbias_partials, dbeta_partials, N, C);               \
+  else k_modact_bwd<T, false><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (const T*)dout, (T*)dz,          \
+                                                        dbias_partials, dbeta_partials, N, C);
+  if (dtype == QPAM_F32) { QPAM_ACT(float) } else { QPAM_ACT(__nv_bfloat16) }
+#undef QPAM_ACT
+  QPAM_LAUNCH_CHECK("k_modact_bwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_cgu_gate_fwd(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up, int32_t dtype,
+                                 void* out, int64_t N, int32_t C, void* stream) {
+  QPAM_REQUIRE(gate && up && out, "cgu_gate_fwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && C > 0 && C % 4 == 0, "cgu_gate_fwd: C must be a multiple of 4 (got %d)", C);
+  const int64_t al = dtype == QPAM_F32 ? 4 : 8;  // 16-byte rows
+  QPAM_REQUIRE(ld_gate >= 2 * C && ld_up >= 2 * C && ld_gate % al == 0 && ld_up % al == 0,
+               "cgu_gate_fwd: row strides must cover 2*C scalars and keep rows 16-byte aligned");
+  if (N == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, 0));
+  if (dtype == QPAM_F32) k_cgu_gate_fwd<float><<<grid, threads, 0, st>>>((const float*)gate, ld_gate, (const float*)up, ld_up, (float*)out, N, C);
+  else k_cgu_gate_fwd<__nv_bfloat16><<<grid, threads, 0, st>>>((const __nv_bfloat16*)gate, ld_gate, (const __nv_bfloat16*)up, ld_up, (__nv_bfloat16*)out, N, C);
+  QPAM_LAUNCH_CHECK("k_cgu_gate_fwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_cgu_gate_bwd(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up,
+                                 const void* dout, int32_t dtype, void* dgate, int64_t ld_dgate, void* dup,
+                                 int64_t ld_dup, int64_t N, int32_t C, void* stream) {
+  QPAM_REQUIRE(gate && up && dout && dgate && dup, "cgu_gate_bwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && N > 0 && C > 0 && C % 4 == 0, "cgu_gate_bwd: C must be a multiple of 4 (got %d)", C);
+  const int64_t al = dtype == QPAM_F32 ? 4 : 8;
+  QPAM_REQUIRE(ld_gate >= 2 * C && ld_up >= 2 * C && ld_dgate >= 2 * C && ld_dup >= 2 * C && ld_gate % al == 0 &&
+                   ld_up % al == 0 && ld_dgate % al == 0 && ld_dup % al == 0,
+               "cgu_gate_bwd: row strides must cover 2*C scalars and keep rows 16-byte aligned");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, 0));
+  if (dtype == QPAM_F32)
+    k_cgu_gate_bwd<float><<<grid, threads, 0, st>>>((const float*)gate, ld_gate, (const float*)up, ld_up, (const float*)dout,
+                                                    (float*)dgate, ld_dgate, (float*)dup, ld_dup, N, C);
+  else
+    k_cgu_gate_bwd<__nv_bfloat16><<<grid, threads, 0, st>>>((const __nv_bfloat16*)gate, ld_gate, (const __nv_bfloat16*)up, ld_up,
+                                                            (const __nv_bfloat16*)dout, (__nv_bfloat16*)dgate, ld_dgate,
+                                                            (__nv_bfloat16*)dup, ld_dup, N, C);
+  QPAM_LAUNCH_CHECK("k_cgu_gate_bwd");
+  return QPAM_OK;
+}
+
+static int pam_prep(bool bwd, const void* qkv, int32_t dtype, const float* rope, int64_t rope_len,
+                    const int64_t* positions, int64_t offset, const float* omp, void* q, void* k, void* v,
+                    void* dqkv, float* domp, int32_t B, int32_t T, int32_t H, int32_t d, void* stream) {
+  QPAM_REQUIRE(qkv && q && k && v && (!bwd || dqkv), "pam_prep: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && B > 0 && T > 0 && H > 0, "pam_prep: bad dtype or empty shape");
+  QPAM_REQUIRE(d >= 4 && d <= 128 && (d & (d - 1)) == 0, "pam_prep: head_dim must be a power of two in [4,128] (got %d)", d);
+  QPAM_REQUIRE(!rope || rope_len > 0, "pam_prep: empty rotary table");
+  QPAM_REQUIRE(!rope || positions || offset + T <= rope_len, "pam_prep: rotary table shorter than offset + T");
+  cudaStream_t st = (cudaStream_t)stream;
+  PrepParams p{qkv, rope, positions, omp, q, k, v, dqkv, (bwd && omp) ? domp : nullptr, offset, rope_len, B, T, H, d};
+  const int per_tok = 3 * H * (d / 4);
+  const int threads = std::min(256, (per_tok + 31) / 32 * 32);
+  const int grid = (int)std::min<int64_t>((int64_t)B * T, 148 * 16);
+  if (dtype == QPAM_F32) {
+    if (bwd) k_pam_prep<float, true><<<grid, threads, 0, st>>>(p);
+    else k_pam_prep<float, false><<<grid, threads, 0, st>>>(p);
+  } else {
+    if (bwd) k_pam_prep<__nv_bfloat16, true><<<grid, threads, 0, st>>>(p);
+    else k_pam_prep<__nv_bfloat16, false><<<grid, threads, 0, st>>>(p);
+  }
+  if (bwd) { QPAM_LAUNCH_CHECK("k_pam_prep_bwd"); } else { QPAM_LAUNCH_CHECK("k_pam_prep_fwd"); }
+  return QPAM_OK;
+}
+
+extern "C" int qpam_pam_prep_fwd(const void* qkv, int32_t dtype, const float* rope, int64_t rope_len,
+                                 const int64_t* positions, int64_t offset, const float* omp, void* q, void* k,
+                                 void* v, int32_t B, int32_t T, int32_t H, int32_t d, void* stream) {
+  return pam_prep(false, qkv, dtype, rope, rope_len, positions, offset, omp, q, k, v, nullptr, nullptr, B, T, H, d, stream);
+}
+
+extern "C" int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* rope, int64_t rope_len,
+                                 const int64_t* positions, int64_t offset, const float* omp, const void* dq,
+                                 const void* dk, const void* dv, void* dqkv, float* domp, int32_t B, int32_t T,
+                                 int32_t H, int32_t d, void* stream) {
+  return pam_prep(true, qkv, dtype, rope, rope_len, positions, offset, omp, const_cast<void*>(dq),
+                  const_cast<void*>(dk), const_cast<void*>(dv), dqkv, domp, B, T, H, d, stream);
+}

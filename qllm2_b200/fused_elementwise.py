@@ -1,0 +1,292 @@
+"""Fused element-wise complex operators (forward and backward in one kernel pass each).
+
+Same names, arguments and arithmetic as the reference's `v11/triton_kernels.py`
+(`fused_complex_norm` :546, `fused_mod_swish` :552, `fused_mod_relu` :558, `fused_cgu_gate` :564; the
+plain arithmetic they must match is `_pt_*` :489-519), on tensors laid out [..., C, 2].  `pam_prep`
+covers the head split + rotary rotation + protect-gate scaling of the PAM layer's input stage
+(`v11/model.py:271-350`).  CUDA tensors only: there is no PyTorch fallback in these functions.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import check, dtype_code, ptr, stream_ptr
+
+
+def _autocast_dtype(t: torch.Tensor) -> torch.dtype:
+    if t.is_cuda and torch.is_autocast_enabled("cuda"):
+        return torch.get_autocast_dtype("cuda")
+    return t.dtype
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.QPamError("the fused complex operators run on CUDA tensors only")
+
+
+def _rows(t: torch.Tensor):
+    """(tensor, N, C, row stride in scalars) of a [..., C, 2] tensor; copies only if rows are not uniform."""
+    if t.dim() < 2 or t.shape[-1] != 2:
+        raise _lib.QPamError(f"expected a [..., C, 2] tensor, got {tuple(t.shape)}")
+    C = t.shape[-2]
+    if C % 4:
+        raise _lib.QPamError(f"the channel count must be a multiple of 4 (got {C})")
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"unsupported dtype {t.dtype}")
+    ok = t.stride(-1) == 1 and t.stride(-2) == 2 and t.data_ptr() % 16 == 0
+    if ok and t.dim() > 2:
+        ld = t.stride(-3)
+        ok = ld >= 2 * C and ld % (16 // t.element_size()) == 0
+        for i in range(t.dim() - 4, -1, -1):
+            ok = ok and (t.shape[i] == 1 or t.stride(i) == t.stride(i + 1) * t.shape[i + 1])
+    elif ok:
+        ld = 2 * C
+    if not ok:
+        t = t.contiguous()
+        ld = 2 * C
+    N = t.numel() // (2 * C)
+    return t, N, C, ld
+
+
+def _param(p: torch.Tensor, C: int, name: str) -> torch.Tensor:
+    if p.numel() != C:
+        raise _lib.QPamError(f"{name} must have {C} entries, got {p.numel()}")
+    return p.detach().float().contiguous()
+
+
+# ------------------------------------------------------------------------------------ norm
+class _ComplexNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, scale, eps, out_dtype):
+        z = z.contiguous()
+        D = z.shape[-2]
+        N = z.numel() // (2 * D)
+        sc = _param(scale, D, "scale")
+        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+        check(_lib.lib().qpam_cnorm_fwd(ptr(z), dtype_code(z.dtype), ptr(sc), ptr(out), dtype_code(out_dtype),
+                                        N, D, float(eps), stream_ptr()), "qpam_cnorm_fwd")
+        ctx.save_for_backward(z, scale)
+        ctx.eps, ctx.out_dtype = eps, out_dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        z, scale = ctx.saved_tensors
+        D = z.shape[-2]
+        N = z.numel() // (2 * D)
+        dout = dout.to(ctx.out_dtype).contiguous()
+        P = max(4, min((N + 3) // 4 * 4, 148 * 16))
+        part = torch.empty(P, D, dtype=torch.float32, device=z.device)
+        dz = torch.empty_like(z)
+        check(_lib.lib().qpam_cnorm_bwd(ptr(z), dtype_code(z.dtype), ptr(_param(scale, D, "scale")), ptr(dout),
+                                        dtype_code(ctx.out_dtype), ptr(dz), ptr(part), P, N, D, float(ctx.eps),
+                                        stream_ptr()), "qpam_cnorm_bwd")
+        return dz, part.sum(0).to(scale.dtype).view_as(scale), None, None
+
+
+def fused_complex_norm(z: torch.Tensor, scale: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """z / (|z|+1e-8) * (|z| / rms) * scale over the channel axis of [..., D, 2]
+    (v11/triton_kernels.py:489-494).  Under bf16 autocast the result is bf16 (the next operator is a
+    projection that would cast it anyway); otherwise it has z's dtype."""
+    _require_cuda(z, scale)
+    if z.dim() < 2 or z.shape[-1] != 2 or z.shape[-2] % 4 or z.shape[-2] > 3072:
+        raise _lib.QPamError(f"fused_complex_norm: expected [..., D, 2] with D a multiple of 4 up to 3072, got {tuple(z.shape)}")
+    if z.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"unsupported dtype {z.dtype}")
+    out_dtype = _autocast_dtype(z)
+    if out_dtype not in (torch.float32, torch.bfloat16) or (z.dtype == torch.bfloat16 and out_dtype == torch.float32):
+        out_dtype = z.dtype
+    return _ComplexNormFn.apply(z, scale, eps, out_dtype)
+
+
+# ------------------------------------------------------------------------------------ activations
+class _ModActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z, bias, beta):
+        z = z.contiguous()
+        C = z.shape[-2]
+        N = z.numel() // (2 * C)
+        out = torch.empty_like(z)
+        b = _param(bias, C, "bias")
+        be = None if beta is None else _param(beta, C, "beta")
+        check(_lib.lib().qpam_modact_fwd(ptr(z), dtype_code(z.dtype), ptr(b), ptr(be), ptr(out), N, C, stream_ptr()),
+              "qpam_modact_fwd")
+        ctx.save_for_backward(z, bias, beta)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        z, bias, beta = ctx.saved_tensors
+        C = z.shape[-2]
+        N = z.numel() // (2 * C)
+        dout = dout.to(z.dtype).contiguous()
+        xb = (C // 4 + 255) // 256
+        P = max(1, min(N, (148 * 8) // xb))
+        pb = torch.empty(P, C, dtype=torch.float32, device=z.device)
+        pe = None if beta is None else torch.empty(P, C, dtype=torch.float32, device=z.device)
+        dz = torch.empty_like(z)
+        check(_lib.lib().qpam_modact_bwd(ptr(z), dtype_code(z.dtype), ptr(_param(bias, C, "bias")),
+                                         None if beta is None else ptr(_param(beta, C, "beta")), ptr(dout), ptr(dz),
+                                         ptr(pb), ptr(pe), P, N, C, stream_ptr()), "qpam_modact_bwd")
+        dbias = pb.sum(0).to(bias.dtype).view_as(bias)
+        dbeta = None if beta is None else pe.sum(0).to(beta.dtype).view_as(beta)
+        return dz, dbias, dbeta
+
+
+def _check_act_input(z, name):
+    _require_cuda(z)
+    if z.dim() < 2 or z.shape[-1] != 2 or z.shape[-2] % 4:
+        raise _lib.QPamError(f"{name}: expected [..., C, 2] with C a multiple of 4, got {tuple(z.shape)}")
+    if z.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"unsupported dtype {z.dtype}")
+
+
+def fused_mod_swish(z: torch.Tensor, bias: torch.Tensor, beta: torch.Tensor) -> torch.Tensor:
+    """z/(|z|+1e-8) * |z| sigmoid(beta |z| + bias)   (v11/triton_kernels.py:497-501)."""
+    _check_act_input(z, "fused_mod_swish")
+    _require_cuda(bias, beta)
+    return _ModActFn.apply(z, bias, beta)
+
+
+def fused_mod_relu(z: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """z/(|z|+1e-8) * relu(|z| + bias)   (v11/triton_kernels.py:504-508)."""
+    _check_act_input(z, "fused_mod_relu")
+    _require_cuda(bias)
+    return _ModActFn.apply(z, bias, None)
+
+
+# ------------------------------------------------------------------------------------ gated unit
+class _CguGateFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        gate, N, C, ldg = _rows(gate)
+        up, Nu, Cu, ldu = _rows(up)
+        out = torch.empty(*gate.shape[:-2], C, 2, dtype=gate.dtype, device=gate.device)
+        check(_lib.lib().qpam_cgu_gate_fwd(ptr(gate), ldg, ptr(up), ldu, dtype_code(gate.dtype), ptr(out), N, C,
+                                           stream_ptr()), "qpam_cgu_gate_fwd")
+        ctx.save_for_backward(gate, up)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        gate, up = ctx.saved_tensors
+        gate, N, C, ldg = _rows(gate)
+        up, _, _, ldu = _rows(up)
+        dout = dout.to(gate.dtype).contiguous()
+        # one buffer [..., 2C, 2]: when gate and up are the two halves of one projection output, autograd
+        # can hand the buffer on without re-assembling it
+        both = torch.empty(*gate.shape[:-2], 2 * C, 2, dtype=gate.dtype, device=gate.device)
+        dgate, dup = both[..., :C, :], both[..., C:, :]
+        check(_lib.lib().qpam_cgu_gate_bwd(ptr(gate), ldg, ptr(up), ldu, ptr(dout), dtype_code(gate.dtype),
+                                           ptr(dgate), 4 * C, dup.data_ptr(), 4 * C, N, C, stream_ptr()),
+              "qpam_cgu_gate_bwd")
+        return dgate, dup
+
+
+class _CguGatePackedFn(torch.autograd.Function):
+    """gate and up as the two channel halves of one [..., 2C, 2] tensor; the gradient comes back packed."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        gu = gu.contiguous()
+        C = gu.shape[-2] // 2
+        N = gu.numel() // (4 * C)
+        out = torch.empty(*gu.shape[:-2], C, 2, dtype=gu.dtype, device=gu.device)
+        base = gu.data_ptr()
+        check(_lib.lib().qpam_cgu_gate_fwd(base, 4 * C, base + 2 * C * gu.element_size(), 4 * C, dtype_code(gu.dtype),
+                                           ptr(out), N, C, stream_ptr()), "qpam_cgu_gate_fwd")
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        C = gu.shape[-2] // 2
+        N = gu.numel() // (4 * C)
+        dout = dout.to(gu.dtype).contiguous()
+        dgu = torch.empty_like(gu)
+        base, dbase, off = gu.data_ptr(), dgu.data_ptr(), 2 * C * gu.element_size()
+        check(_lib.lib().qpam_cgu_gate_bwd(base, 4 * C, base + off, 4 * C, ptr(dout), dtype_code(gu.dtype), dbase, 4 * C,
+                                           dbase + off, 4 * C, N, C, stream_ptr()), "qpam_cgu_gate_bwd")
+        return dgu
+
+
+def fused_cgu_gate(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """gate/(|gate|+1e-8) * up * sigmoid(|gate|), complex product   (v11/triton_kernels.py:511-519)."""
+    _require_cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise _lib.QPamError(f"fused_cgu_gate: gate {tuple(gate.shape)} {gate.dtype} and up {tuple(up.shape)} {up.dtype} differ")
+    _check_act_input(gate, "fused_cgu_gate")
+    return _CguGateFn.apply(gate, up)
+
+
+def fused_cgu_gate_packed(gate_up: torch.Tensor) -> torch.Tensor:
+    """`fused_cgu_gate(gate_up[..., :C, :], gate_up[..., C:, :])` for one projection output [..., 2C, 2]."""
+    _check_act_input(gate_up, "fused_cgu_gate_packed")
+    if gate_up.shape[-2] % 8:
+        raise _lib.QPamError("fused_cgu_gate_packed: the packed channel count must be a multiple of 8")
+    return _CguGatePackedFn.apply(gate_up)
+
+
+# ------------------------------------------------------------------------------------ PAM input stage
+class _PamPrepFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, rope, omp, positions, offset, H, d):
+        qkv = qkv.contiguous()
+        B, T = qkv.shape[0], qkv.shape[1]
+        q, k, v = (torch.empty(B, H, T, d, 2, dtype=qkv.dtype, device=qkv.device) for _ in range(3))
+        ompf = None if omp is None else omp.detach().float().contiguous()
+        check(_lib.lib().qpam_pam_prep_fwd(ptr(qkv), dtype_code(qkv.dtype), ptr(rope), 0 if rope is None else rope.shape[0],
+                                           ptr(positions), int(offset), ptr(ompf), ptr(q), ptr(k), ptr(v), B, T, H, d,
+                                           stream_ptr()), "qpam_pam_prep_fwd")
+        ctx.save_for_backward(qkv, rope, ompf, positions)
+        ctx.meta = (offset, H, d, None if omp is None else omp.dtype)
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv, rope, ompf, positions = ctx.saved_tensors
+        offset, H, d, omp_dtype = ctx.meta
+        B, T = qkv.shape[0], qkv.shape[1]
+        dq, dk, dv = (g.to(qkv.dtype).contiguous() for g in (dq, dk, dv))
+        dqkv = torch.empty_like(qkv)
+        domp = None if ompf is None else torch.empty(B, T, H, dtype=torch.float32, device=qkv.device)
+        check(_lib.lib().qpam_pam_prep_bwd(ptr(qkv), dtype_code(qkv.dtype), ptr(rope), 0 if rope is None else rope.shape[0],
+                                           ptr(positions), int(offset), ptr(ompf), ptr(dq), ptr(dk), ptr(dv), ptr(dqkv),
+                                           ptr(domp), B, T, H, d, stream_ptr()), "qpam_pam_prep_bwd")
+        return dqkv, None, None if domp is None else domp.to(omp_dtype), None, None, None, None
+
+
+def pam_prep(qkv: torch.Tensor, rope: Optional[torch.Tensor], omp: Optional[torch.Tensor], *, n_heads: int,
+             head_dim: int, positions: Optional[torch.Tensor] = None, offset: int = 0):
+    """Split a fused projection `qkv` [B, T, 3*H*d, 2] into q, k, v' [B, H, T, d, 2]: q and k rotated by
+    `rope[pos]` ([P, d, 2] = (cos, sin), float32; None = no rotation), v' = omp * v with omp [B, T, H]
+    (the complement of the protect gate; None = 1).  pos = positions[b, t] (int64) or offset + t.
+    One pass instead of the reference's view/transpose/contiguous, two complex products and the gate
+    product (v11/model.py:279-306, 340-349)."""
+    _require_cuda(qkv, rope, omp, positions)
+    B, T = qkv.shape[0], qkv.shape[1]
+    H, d = n_heads, head_dim
+    if qkv.numel() != B * T * 3 * H * d * 2 or qkv.shape[-1] != 2:
+        raise _lib.QPamError(f"pam_prep: qkv {tuple(qkv.shape)} is not [B, T, 3*{H}*{d}, 2]")
+    if qkv.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"unsupported dtype {qkv.dtype}")
+    if d < 4 or d > 128 or d & (d - 1):
+        raise _lib.QPamError(f"pam_prep: head_dim must be a power of two in [4, 128], got {d}")
+    if rope is not None:
+        if rope.dim() != 3 or rope.shape[1:] != (d, 2):
+            raise _lib.QPamError(f"pam_prep: rope must be [P, {d}, 2], got {tuple(rope.shape)}")
+        rope = rope.detach().float().contiguous()
+        if positions is None and offset + T > rope.shape[0]:
+            raise _lib.QPamError("pam_prep: the rotary table is shorter than offset + T")
+    if omp is not None and tuple(omp.shape) != (B, T, H):
+        raise _lib.QPamError(f"pam_prep: omp must be [B, T, H] = {(B, T, H)}, got {tuple(omp.shape)}")
+    if positions is not None:
+        if positions.numel() != B * T:
+            raise _lib.QPamError("pam_prep: positions must have one entry per token")
+        positions = positions.to(torch.int64).contiguous()
+    return _PamPrepFn.apply(qkv, rope, omp, positions, offset, H, d)

@@ -25,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import fused_elementwise as FE
 from . import ops
 from .fused_ce import fused_linear_cross_entropy
 
@@ -107,13 +108,28 @@ class ComplexLinear(nn.Module):
             self.register_parameter("bias_real", None)
             self.register_parameter("bias_imag", None)
 
+    def block_weight(self) -> torch.Tensor:
+        """[2*out, 2*in] real matrix acting on interleaved (re, im) columns: rows (o, re) = (Wr, -Wi),
+        rows (o, im) = (Wi, Wr).  With it the complex product is ONE GEMM whose output is already
+        interleaved.  Cached while no gradient is needed and the parameters are unchanged."""
+        wr, wi = self.weight_real, self.weight_imag
+        live = torch.is_grad_enabled() and (wr.requires_grad or wi.requires_grad)
+        key = (wr._version, wi._version, wr.data_ptr(), wi.data_ptr(), wr.dtype)
+        if not live and getattr(self, "_bw_key", None) == key:
+            return self._bw
+        w = torch.stack([torch.stack([wr, -wi], dim=-1), torch.stack([wi, wr], dim=-1)], dim=1)
+        w = w.view(2 * self.out_dim, 2 * self.in_dim)
+        if not live:
+            self._bw, self._bw_key = w.detach(), key
+        return w
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        xr, xi = x[..., 0], x[..., 1]
-        yr = F.linear(xr, self.weight_real) - F.linear(xi, self.weight_imag)
-        yi = F.linear(xr, self.weight_imag) + F.linear(xi, self.weight_real)
+        lead = x.shape[:-2]
+        bias = None
         if self.bias_real is not None:
-            yr, yi = yr + self.bias_real, yi + self.bias_imag
-        return torch.stack([yr, yi], dim=-1)
+            bias = torch.stack([self.bias_real, self.bias_imag], dim=-1).view(-1)
+        y = F.linear(x.reshape(*lead, 2 * self.in_dim), self.block_weight(), bias)
+        return y.view(*lead, self.out_dim, 2)
 
 
 class ComplexNorm(nn.Module):
@@ -125,6 +141,8 @@ class ComplexNorm(nn.Module):
         self.eps = eps
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
+        if z.is_cuda:
+            return FE.fused_complex_norm(z, self.scale, self.eps)
         mag = _magnitude(z)
         rms = torch.sqrt((mag ** 2).mean(dim=-1, keepdim=True) + self.eps)
         unit = z / (mag.unsqueeze(-1) + 1e-8)
@@ -138,6 +156,8 @@ class ModSwish(nn.Module):
         self.beta = nn.Parameter(torch.ones(dim))
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
+        if z.is_cuda:
+            return FE.fused_mod_swish(z, self.bias, self.beta)
         mag = _magnitude(z)
         act = mag * torch.sigmoid(self.beta * mag + self.bias)
         return z / (mag.unsqueeze(-1) + 1e-8) * act.unsqueeze(-1)
@@ -149,6 +169,8 @@ class ModReLU(nn.Module):
         self.bias = nn.Parameter(torch.full((dim,), -0.1))
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
+        if z.is_cuda:
+            return FE.fused_mod_relu(z, self.bias)
         mag = _magnitude(z)
         return z / (mag.unsqueeze(-1) + 1e-8) * F.relu(mag + self.bias).unsqueeze(-1)
 
@@ -170,6 +192,8 @@ class ComplexGatedUnit(nn.Module):
     def forward(self, z: torch.Tensor) -> torch.Tensor:
         gate = self.gate_proj(z)
         up = self.act(self.up_proj(z))
+        if z.is_cuda:
+            return self.down_proj(FE.fused_cgu_gate(gate, up))
         gmag = _magnitude(gate)
         phase = gate / (gmag.unsqueeze(-1) + 1e-8)
         gated = _complex_mul(phase, up) * torch.sigmoid(gmag).unsqueeze(-1)
@@ -302,8 +326,9 @@ class V11PAMLayer(nn.Module):
         ent = -(mean_p * (mean_p + 1e-8).log()).sum(dim=-1)
         return -self.route_balance_lambda * ent.mean()
 
-    def _gamma_all_and_vprime(self, x: torch.Tensor, values: torch.Tensor):
-        """gamma [K,B,H,T] for every state and the protected value v' (v11/model.py:630-655)."""
+    def _gates(self, x: torch.Tensor):
+        """gamma [K,B,H,T] for every state and omp = 1 - p [B,T,H] (None without the protect gate)
+        (v11/model.py:630-655)."""
         K = self.n_states
         flat = _concat_planes(x)
         dt = self.dt_proj(flat) + self.dt_bias                                    # [B,T,H]
@@ -315,13 +340,45 @@ class V11PAMLayer(nn.Module):
         if self.gamma_floor and self.gamma_floor > 0.0:
             base = self.gamma_floor + (1.0 - self.gamma_floor) * base
         if not self.use_gsp:
-            return base.contiguous(), values
+            return base.contiguous(), None
         gate_in = flat if self.gate_content_aware else _magnitude(x)
-        protect = torch.sigmoid(self.protect_gate(gate_in)).transpose(1, 2)      # [B,H,T]
+        p_bth = torch.sigmoid(self.protect_gate(gate_in))                         # [B,T,H]
+        protect = p_bth.transpose(1, 2)                                           # [B,H,T]
         if self.gate_surprisal_lambda > 0 and self.training:
             self._gate_prob_bt = protect.mean(dim=1)
         gamma = base * (1 - protect) + protect
-        return gamma.contiguous(), values * (1 - protect)[..., None, None]
+        return gamma.contiguous(), 1 - p_bth
+
+    def _gamma_all_and_vprime(self, x: torch.Tensor, values: torch.Tensor):
+        """gamma [K,B,H,T] and the protected value v' = (1 - p) v for values [B,H,T,d,2]."""
+        gamma, omp = self._gates(x)
+        if omp is None:
+            return gamma, values
+        return gamma, values * omp.transpose(1, 2)[..., None, None]
+
+    def _fused_prep_ok(self, x: torch.Tensor) -> bool:
+        d = self.head_dim
+        return x.is_cuda and self.fused_qkv and not self.qk_norm and 4 <= d <= 128 and d & (d - 1) == 0
+
+    def project_gated(self, x: torch.Tensor, step_offset: int = 0, positions: Optional[torch.Tensor] = None):
+        """q, k, v' [B,H,T,d,2] and gamma [K,B,H,T] of one layer input x [B,T,D,2].  `positions` [B,T]
+        gives every token its own rotary position (continuous batching); otherwise step_offset + t."""
+        if not self._fused_prep_ok(x):
+            if positions is not None:
+                raise ValueError("per-token positions need the fused projection path (fused_qkv, no qk_norm, CUDA)")
+            q, k, v = self._project(x, step_offset)
+            gamma, vprime = self._gamma_all_and_vprime(x, v)
+            return q, k, vprime, gamma
+        gamma, omp = self._gates(x)
+        rope = None
+        if self.use_rope:
+            if positions is None and step_offset + x.shape[1] > self.rope_cache.shape[0]:
+                self.register_buffer("rope_cache", build_rope_cache((step_offset + x.shape[1]) * 2, self.head_dim).to(x.device),
+                                     persistent=False)
+            rope = self.rope_cache
+        q, k, vprime = FE.pam_prep(self.qkv_proj(x), rope, omp, n_heads=self.num_heads, head_dim=self.head_dim,
+                                   positions=positions, offset=step_offset)
+        return q, k, vprime, gamma
 
     def _gamma_and_vprime(self, x, values, state_offset: float = 0.0):
         """Single-state form kept for callers of the reference API (v11/model.py:308-350)."""
@@ -361,8 +418,7 @@ class V11PAMLayer(nn.Module):
     def forward(self, x: torch.Tensor, state=None, step_offset: int = 0):
         B, T = x.shape[0], x.shape[1]
         H, d, K = self.num_heads, self.head_dim, self.n_states
-        q, k, v = self._project(x, step_offset)
-        gamma, vprime = self._gamma_all_and_vprime(x, v)
+        q, k, vprime, gamma = self.project_gated(x, step_offset)
         coef = self._coef(x)
         if state is None and T > 1:
             y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, head_dim=d, chunk=self.chunk_size)
@@ -519,6 +575,9 @@ class V11LM(nn.Module):
 
     def ce_from_lm(self, lm, labels, loss_mask=None, ignore_index=-100, chunk: int = 4096):
         H, W = self.tied_head_matrices(lm)
+        if H.is_cuda and torch.is_autocast_enabled("cuda"):
+            # the reference's head matmuls run in the autocast dtype; here that selects the tensor-core kernels
+            H = H.to(torch.get_autocast_dtype("cuda"))
         if H.dtype != W.dtype:
             W = W.to(H.dtype)
         mask = loss_mask.reshape(-1) if loss_mask is not None else None

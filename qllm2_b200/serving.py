@@ -18,7 +18,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 import torch
 
 from . import ops
-from .model import V11LM, _complex_mul, _concat_planes, _magnitude
+from .model import V11LM
 
 
 # ------------------------------------------------------------------------------------ scheduler
@@ -97,7 +97,10 @@ class ContinuousBatcher:
     """Greedy decode of many sequences through a V11LM with continuous batching."""
 
     def __init__(self, model: V11LM, n_slots: int, state_dtype: Optional[torch.dtype] = None,
-                 max_prefill_tokens: int = 1 << 17):
+                 max_prefill_tokens: int = 1 << 17, cuda_graph: bool = False, max_position: int = 8192):
+        """cuda_graph=True captures the decode step once for a full batch of n_slots rows (idle rows carry
+        slot id -1, which the step kernel skips) and replays it every step: the per-token cost is then the
+        kernels', not the ~10^3 launches' of the Python layer loop."""
         self.model = model.eval()
         cfg = model.config
         p = next(model.parameters())
@@ -108,30 +111,34 @@ class ContinuousBatcher:
         self.sched = SlotScheduler(n_slots, max_prefill_tokens)
         self.steps = 0
         self.decoded_tokens = 0
+        self.n_slots = n_slots
+        self.cuda_graph = cuda_graph
+        self._graph = None
+        self._ensure_rope(max_position)    # tables must not grow while a captured graph reads them
+        if cuda_graph:
+            self._g_ids = torch.zeros(n_slots, 1, dtype=torch.long, device=self.device)
+            self._g_pos = torch.zeros(n_slots, 1, dtype=torch.long, device=self.device)
+            self._g_slots = torch.full((n_slots,), -1, dtype=torch.int32, device=self.device)
+            self._g_out = None
 
     def submit(self, prompt, max_new_tokens):
         return self.sched.submit([int(t) for t in prompt], max_new_tokens)
 
-    # -- layer pieces with explicit per-token positions ------------------------------------
-    def _qkv(self, pam, x, positions):
-        """x [B,T,D,2], positions [B,T] -> q,k,v [B,H,T,d,2] with per-token RoPE."""
-        B, T = x.shape[0], x.shape[1]
-        H, d = pam.num_heads, pam.head_dim
-        qkv = pam.qkv_proj(x).view(B, T, 3, H, d, 2)
-        q, k, v = (qkv[:, :, i].transpose(1, 2).contiguous() for i in range(3))
-        if pam.use_rope:
-            need = int(positions.max()) + 1
-            if need > pam.rope_cache.shape[0]:
-                from .model import build_rope_cache
-                pam.register_buffer("rope_cache", build_rope_cache(need * 2, d).to(x.device), persistent=False)
-            rot = pam.rope_cache[positions].to(x.dtype).unsqueeze(1)       # [B,1,T,d,2]
-            q, k = _complex_mul(q, rot), _complex_mul(k, rot)
-        return q, k, v
+    def _ensure_rope(self, need: int):
+        """Rotary tables must cover every position before a step that cannot look at its positions on the host."""
+        from .model import build_rope_cache
+        for blk in self.model.blocks:
+            if blk.pam.use_rope and blk.pam.rope_cache.shape[0] < need:
+                if self._graph is not None:
+                    raise RuntimeError(f"position {need - 1} is beyond max_position of the captured decode step")
+                blk.pam.register_buffer("rope_cache", build_rope_cache(max(need, 2 * blk.pam.rope_cache.shape[0]), blk.pam.head_dim).to(self.device),
+                                        persistent=False)
 
     @torch.no_grad()
     def _prefill(self, batch: List[Request]):
         m = self.model
         lens = [len(r.prompt) for r in batch]
+        self._ensure_rope(max(lens))
         ids = torch.tensor([t for r in batch for t in r.prompt], dtype=torch.long, device=self.device)[None]
         positions = torch.cat([torch.arange(n, device=self.device) for n in lens])[None]
         cu = torch.zeros(len(batch) + 1, dtype=torch.int32)
@@ -143,8 +150,7 @@ class ContinuousBatcher:
             z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
             xn = blk.norm2(z)
             pam = blk.pam
-            q, k, v = self._qkv(pam, xn, positions)
-            gamma, vprime = pam._gamma_all_and_vprime(xn, v)
+            q, k, vprime, gamma = pam.project_gated(xn, positions=positions)
             coef = pam._coef(xn)
             y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, cu_seqlens=cu, head_dim=pam.head_dim)
             ops.pam_pool_store(self.pool, slots, s, layer=li)
@@ -158,18 +164,48 @@ class ContinuousBatcher:
 
     @torch.no_grad()
     def _decode(self, live: List[Request]):
-        m = self.model
         n = len(live)
-        ids = torch.tensor([r.generated[-1] for r in live], dtype=torch.long, device=self.device)[:, None]
-        positions = torch.tensor([r.position for r in live], dtype=torch.long, device=self.device)[:, None]
-        slots = torch.tensor([r.slot for r in live], dtype=torch.int32, device=self.device)
+        self._ensure_rope(max(r.position for r in live) + 1)
+        ids = torch.tensor([r.generated[-1] for r in live], dtype=torch.long)
+        positions = torch.tensor([r.position for r in live], dtype=torch.long)
+        slots = torch.tensor([r.slot for r in live], dtype=torch.int32)
+        if self.cuda_graph:
+            self._g_ids.zero_()
+            self._g_pos.zero_()
+            self._g_slots.fill_(-1)
+            self._g_ids[:n, 0] = ids.to(self.device)
+            self._g_pos[:n, 0] = positions.to(self.device)
+            self._g_slots[:n] = slots.to(self.device)
+            if self._graph is None:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):   # warm-up outside the capture, on idle rows only (no slot changes)
+                    self._decode_tensors(self._g_ids, self._g_pos, torch.full_like(self._g_slots, -1))
+                torch.cuda.current_stream().wait_stream(side)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._g_out = self._decode_tensors(self._g_ids, self._g_pos, self._g_slots)
+                self._graph = graph
+            self._graph.replay()
+            nxt = self._g_out[:n]
+        else:
+            nxt = self._decode_tensors(ids.to(self.device)[:, None], positions.to(self.device)[:, None],
+                                       slots.to(self.device))
+        for r, t in zip(live, nxt.tolist()):
+            r.generated.append(int(t))
+        self.decoded_tokens += n
+
+    @torch.no_grad()
+    def _decode_tensors(self, ids, positions, slots):
+        """One decode step for rows (ids [n,1], positions [n,1], slots [n]); returns next ids [n]."""
+        m = self.model
+        n = ids.shape[0]
         z = m.embed_norm(m.embed(ids))                                      # [n,1,D,2]
         for li, blk in enumerate(m.blocks):
             z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
             xn = blk.norm2(z)
             pam = blk.pam
-            q, k, v = self._qkv(pam, xn, positions)
-            gamma, vprime = pam._gamma_all_and_vprime(xn, v)                # [K,n,H,1]
+            q, k, vprime, gamma = pam.project_gated(xn, positions=positions)   # gamma [K,n,H,1]
             coef = pam._coef(xn)
             y = ops.pam_decode_step(self.pool, slots, (q[:, :, 0] * pam.head_dim ** -0.5).contiguous(),
                                     k[:, :, 0].contiguous(), vprime[:, :, 0].contiguous(),
@@ -177,10 +213,7 @@ class ContinuousBatcher:
                                     layer=li)
             out = pam.o_proj(y.reshape(n, 1, pam.inner_dim, 2))
             z = z + out * blk.pam_scale
-        nxt = m.greedy_next(m._head_hidden(z)[:, 0])
-        for r, t in zip(live, nxt.tolist()):
-            r.generated.append(int(t))
-        self.decoded_tokens += n
+        return m.greedy_next(m._head_hidden(z)[:, 0])
 
     def step(self) -> int:
         """Admit + prefill waiting sequences, then advance every live sequence by one token."""

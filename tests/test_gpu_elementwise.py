@@ -1,0 +1,188 @@
+"""Fused element-wise complex operators against the reference's plain arithmetic.
+
+Golden vectors (tests/golden/elementwise.npz) come from the reference's `_pt_*` functions in float64;
+fp32 kernels must match to 1e-4 relative, bf16 to 2e-2.  Larger seeded cases compare with the same
+arithmetic written in torch (fp32) on the device.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from qllm2_b200 import fused_elementwise as FE
+from qllm2_b200._lib import QPamError
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.detach().double().flatten(), b.detach().double().flatten()
+    return float((a - b).norm() / (b.norm() + 1e-30))
+
+
+@pytest.fixture(scope="module")
+def gold(golden_dir):
+    return dict(np.load(os.path.join(golden_dir, "elementwise.npz")))
+
+
+def _t(g, key, dtype=torch.float32, grad=False):
+    return torch.from_numpy(g[key]).to(DEV).to(dtype).requires_grad_(grad)
+
+
+CASES = {
+    "norm": (lambda z, p: FE.fused_complex_norm(z, p["scale"], 1e-6), ["scale"]),
+    "swish": (lambda z, p: FE.fused_mod_swish(z, p["bias"], p["beta"]), ["bias", "beta"]),
+    "relu": (lambda z, p: FE.fused_mod_relu(z, p["bias"]), ["bias"]),
+    "gate": (lambda z, p: FE.fused_cgu_gate(z, p["up"]), ["up"]),
+}
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("name", list(CASES))
+def test_against_reference_golden(gold, tag, name):
+    fn, wrt = CASES[name]
+    z = _t(gold, f"{tag}_z", grad=True)
+    p = {k: _t(gold, f"{tag}_{k}", grad=True) for k in wrt}
+    dout = _t(gold, f"{tag}_dout")
+    y = fn(z, p)
+    assert y.dtype == torch.float32 and y.shape == z.shape
+    grads = torch.autograd.grad((y * dout).sum(), [z] + [p[k] for k in wrt])
+    assert rel(y, _t(gold, f"{tag}_{name}_out")) < 1e-4
+    for i, g in enumerate(grads):
+        assert rel(g, _t(gold, f"{tag}_{name}_grad{i}")) < 1e-4, (name, i)
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("name", list(CASES))
+def test_bf16_io_matches_fp32_on_the_same_rounded_inputs(gold, tag, name):
+    """bf16 tensors in and out, fp32 arithmetic inside: against the fp32 kernels fed the bf16-rounded
+    values, only the rounding of the results differs (2e-2 is the bf16 bar; parameters stay fp32)."""
+    fn, wrt = CASES[name]
+    outs = []
+    for dtype in (torch.bfloat16, torch.float32):
+        z = _t(gold, f"{tag}_z", torch.bfloat16).to(dtype).requires_grad_(True)
+        p = {k: (_t(gold, f"{tag}_{k}", torch.bfloat16).to(dtype) if k == "up" else _t(gold, f"{tag}_{k}")).requires_grad_(True)
+             for k in wrt}
+        dout = _t(gold, f"{tag}_dout", torch.bfloat16).to(dtype)
+        y = fn(z, p)
+        assert y.dtype == dtype
+        outs.append([y] + list(torch.autograd.grad((y.float() * dout.float()).sum(), [z] + [p[k] for k in wrt])))
+    for a, b in zip(*outs):
+        assert rel(a, b) < 2e-2
+
+
+def _pt_norm(z, scale, eps=1e-6):
+    mag = torch.sqrt(z[..., 0] ** 2 + z[..., 1] ** 2 + 1e-8)
+    rms = torch.sqrt((mag ** 2).mean(-1, keepdim=True) + eps)
+    return z / (mag.unsqueeze(-1) + 1e-8) * ((mag / rms) * scale).unsqueeze(-1)
+
+
+def _pt_swish(z, bias, beta):
+    mag = torch.sqrt(z[..., 0] ** 2 + z[..., 1] ** 2 + 1e-8)
+    return z / (mag.unsqueeze(-1) + 1e-8) * (mag * torch.sigmoid(beta * mag + bias)).unsqueeze(-1)
+
+
+def _pt_gate(gate, up):
+    mag = torch.sqrt(gate[..., 0] ** 2 + gate[..., 1] ** 2 + 1e-8)
+    ph = gate / (mag.unsqueeze(-1) + 1e-8)
+    pr = ph[..., 0] * up[..., 0] - ph[..., 1] * up[..., 1]
+    pi = ph[..., 0] * up[..., 1] + ph[..., 1] * up[..., 0]
+    return torch.stack([pr, pi], -1) * torch.sigmoid(mag)[..., None]
+
+
+@pytest.mark.parametrize("N,C", [(1, 384), (4099, 384), (777, 1152), (130, 2304)])
+def test_large_rows_match_torch_arithmetic(N, C):
+    g = torch.Generator().manual_seed(N + C)
+    z = torch.randn(N, C, 2, generator=g).to(DEV).requires_grad_(True)
+    up = torch.randn(N, C, 2, generator=g).to(DEV).requires_grad_(True)
+    dout = torch.randn(N, C, 2, generator=g).to(DEV)
+    scale = (1 + 0.2 * torch.randn(C, generator=g)).to(DEV).requires_grad_(True)
+    bias = (0.5 * torch.randn(C, generator=g)).to(DEV).requires_grad_(True)
+    beta = (1 + 0.2 * torch.randn(C, generator=g)).to(DEV).requires_grad_(True)
+    pairs = [
+        (lambda: FE.fused_complex_norm(z, scale), lambda: _pt_norm(z, scale), [z, scale]),
+        (lambda: FE.fused_mod_swish(z, bias, beta), lambda: _pt_swish(z, bias, beta), [z, bias, beta]),
+        (lambda: FE.fused_cgu_gate(z, up), lambda: _pt_gate(z, up), [z, up]),
+    ]
+    for ours, theirs, wrt in pairs:
+        y, yr = ours(), theirs()
+        assert rel(y, yr) < 1e-5
+        ga = torch.autograd.grad((y * dout).sum(), wrt)
+        gb = torch.autograd.grad((yr * dout).sum(), wrt)
+        for a, b in zip(ga, gb):
+            assert rel(a, b) < 1e-4
+
+
+def test_norm_under_autocast_returns_bf16_and_matches():
+    g = torch.Generator().manual_seed(5)
+    z = torch.randn(3, 50, 384, 2, generator=g).to(DEV).requires_grad_(True)
+    scale = torch.ones(384, device=DEV, requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = FE.fused_complex_norm(z, scale)
+    assert y.dtype == torch.bfloat16
+    yr = _pt_norm(z, scale)
+    assert rel(y, yr) < 1e-2
+    dout = torch.randn_like(yr)
+    ga = torch.autograd.grad((y.float() * dout).sum(), [z, scale])
+    gb = torch.autograd.grad((yr * dout).sum(), [z, scale])
+    assert ga[0].dtype == torch.float32
+    assert rel(ga[0], gb[0]) < 2e-2 and rel(ga[1], gb[1]) < 2e-2
+
+
+def test_packed_gate_equals_two_tensor_gate_and_strided_views():
+    g = torch.Generator().manual_seed(9)
+    gu = torch.randn(5, 11, 2 * 96, 2, generator=g).to(DEV).requires_grad_(True)
+    dout = torch.randn(5, 11, 96, 2, generator=g).to(DEV)
+    y1 = FE.fused_cgu_gate_packed(gu)
+    (g1,) = torch.autograd.grad((y1 * dout).sum(), [gu])
+    y2 = FE.fused_cgu_gate(gu[..., :96, :], gu[..., 96:, :])     # strided views, no copies
+    (g2,) = torch.autograd.grad((y2 * dout).sum(), [gu])
+    y3 = _pt_gate(gu[..., :96, :], gu[..., 96:, :])
+    (g3,) = torch.autograd.grad((y3 * dout).sum(), [gu])
+    assert torch.equal(y1, y2) and torch.equal(g1, g2)
+    assert rel(y1, y3) < 1e-5 and rel(g1, g3) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("H,d", [(6, 64), (3, 32), (2, 128)])
+def test_pam_prep_matches_torch_path(dtype, tol, H, d):
+    from qllm2_b200.model import _complex_mul, build_rope_cache
+    B, T = 2, 37
+    g = torch.Generator().manual_seed(H * d)
+    qkv32 = torch.randn(B, T, 3 * H * d, 2, generator=g).to(DEV)
+    omp32 = torch.rand(B, T, H, generator=g).to(DEV)
+    rope = build_rope_cache(128, d).to(DEV)
+    douts = [torch.randn(B, H, T, d, 2, generator=g).to(DEV) for _ in range(3)]
+    for positions, offset in ((None, 5), (torch.randint(0, 128, (B, T), generator=g).to(DEV), 0)):
+        qkv = qkv32.to(dtype).requires_grad_(True)
+        omp = omp32.clone().requires_grad_(True)
+        q, k, v = FE.pam_prep(qkv, rope, omp, n_heads=H, head_dim=d, positions=positions, offset=offset)
+        ga = torch.autograd.grad(sum((a.float() * b).sum() for a, b in zip((q, k, v), douts)), [qkv, omp])
+        # the same stage with torch operators in fp32 (the module's own path)
+        x = qkv32.clone().requires_grad_(True)
+        o2 = omp32.clone().requires_grad_(True)
+        parts = x.view(B, T, 3, H, d, 2)
+        qr, kr, vr = (parts[:, :, i].transpose(1, 2) for i in range(3))
+        rot = (rope[offset:offset + T] if positions is None else rope[positions].unsqueeze(1))
+        qr, kr = _complex_mul(qr, rot), _complex_mul(kr, rot)
+        vr = vr * o2.transpose(1, 2)[..., None, None]
+        gb = torch.autograd.grad(sum((a * b).sum() for a, b in zip((qr, kr, vr), douts)), [x, o2])
+        for a, b in zip((q, k, v), (qr, kr, vr)):
+            assert a.shape == b.shape and rel(a, b) < tol
+        assert rel(ga[0], gb[0]) < tol and rel(ga[1], gb[1]) < tol
+
+
+def test_wrappers_refuse_bad_input_before_any_launch():
+    z = torch.randn(4, 6, 2, device=DEV)          # 6 channels: not a multiple of 4
+    with pytest.raises(QPamError):
+        FE.fused_complex_norm(z, torch.ones(6, device=DEV))
+    with pytest.raises(QPamError):
+        FE.fused_mod_relu(torch.randn(4, 8, 2), torch.zeros(8))           # CPU tensor
+    with pytest.raises(QPamError):
+        FE.fused_cgu_gate(torch.randn(4, 8, 2, device=DEV), torch.randn(4, 12, 2, device=DEV))
+    with pytest.raises(QPamError):
+        FE.pam_prep(torch.randn(1, 4, 3 * 2 * 24, 2, device=DEV), None, None, n_heads=2, head_dim=24)
+    with pytest.raises(QPamError):
+        FE.fused_mod_swish(torch.randn(4, 8, 2, device=DEV), torch.zeros(8, device=DEV), torch.zeros(4, device=DEV))

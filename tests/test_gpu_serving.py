@@ -30,13 +30,15 @@ def test_batcher_matches_reference_greedy(golden_dir, name):
     assert len(out) == 6 and all(len(v) > 0 for v in out.values())
 
 
-def test_batcher_equals_sequential_generate(golden_dir):
-    """Every sequence decoded in the batch equals the same sequence decoded alone by V11LM.generate."""
+@pytest.mark.parametrize("graph", [False, True])
+def test_batcher_equals_sequential_generate(golden_dir, graph):
+    """Every sequence decoded in the batch equals the same sequence decoded alone by V11LM.generate
+    (graph=True: the decode step is replayed from one captured CUDA graph)."""
     g, net = _load(golden_dir, "k3")
     V = net.config.vocab_size
     gen = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, V, (int(n),), generator=gen) for n in (3, 40, 25, 1, 70, 12, 31)]
-    eng = ContinuousBatcher(net, n_slots=4)
+    eng = ContinuousBatcher(net, n_slots=4, cuda_graph=graph)
     rids = [eng.submit(p.tolist(), 6) for p in prompts]
     out = eng.run()
     mism = 0
