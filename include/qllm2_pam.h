@@ -233,6 +233,15 @@ int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* rope, int64_t
                       const void* dk, const void* dv, void* dqkv, float* domp, int32_t B, int32_t T,
                       int32_t H, int32_t d, void* stream);
 
+/* Read-out of K phase-routed states (v11/model.py:766-781: the sum over states weighted by
+ * alpha_k e^{i phi_k}):  y[r,:] = sum_k coef[k,r] * yk[k][r,:] over R rows of d complex channels;
+ * yk / dyk are HOST arrays of K device pointers, coef / dcoef fp32 [K,R,2].
+ * Backward: dyk[k] = conj(coef[k]) dy,  dcoef[k,r] = sum_j dy[r,j] conj(yk[k][r,j]). */
+int qpam_state_combine_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype, int32_t K,
+                           int64_t R, int32_t d, void* stream);
+int qpam_state_combine_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
+                           float* dcoef, int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Launch accounting and per-kernel timing.  The reference times whole calls with
  * time.perf_counter around torch.cuda.synchronize (v11/bench_flash_pam.py:73-84); these entry

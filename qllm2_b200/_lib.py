@@ -70,6 +70,9 @@ SIGNATURES = {
                                     c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_pam_prep_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "qpam_state_combine_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_void_p]),
+    "qpam_state_combine_bwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, C.POINTER(c_void_p), c_void_p, c_int32,
+                                         c_int32, c_int64, c_int32, c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

@@ -438,6 +438,67 @@ __global__ void __launch_bounds__(256) k_pam_prep(PrepParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Read-out of K phase-routed states:  y[r, :] = sum_k c_k[r] * y_k[r, :]  (complex), rows r = (b,h,t),
+// coef fp32 [K, R, 2].  Backward: dy_k = conj(c_k) dy,  dc_k[r] = sum_j dy[r,j] conj(y_k[r,j]).
+// d/4 consecutive lanes share a row (d a power of two <= 128).
+// ------------------------------------------------------------------------------------------------
+struct CombineParams {
+  const void* yk[QPAM_MAX_STATES];
+  void* dyk[QPAM_MAX_STATES];
+  const float* coef;
+  void* y;        // fwd: output; bwd: incoming gradient
+  float* dcoef;   // bwd
+  int64_t R;
+  int d, K;
+};
+
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
+  const int gpr = p.d >> 2;  // vector groups per row
+  const int64_t total = p.R * gpr;
+  const int64_t total_pad = (total + 31) & ~(int64_t)31;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_pad;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const bool on = idx < total;
+    const int64_t r = on ? idx / gpr : 0;
+    const int g = on ? (int)(idx - r * gpr) : 0;
+    const int64_t off = (r * p.d + g * 4) * 2;
+    float ar[4] = {0.f, 0.f, 0.f, 0.f}, ai[4] = {0.f, 0.f, 0.f, 0.f};
+    if (BWD && on) V4<T>::ld(reinterpret_cast<const T*>(p.y) + off, ar, ai);
+    for (int k = 0; k < p.K; ++k) {
+      const float2 c = on ? *reinterpret_cast<const float2*>(p.coef + ((int64_t)k * p.R + r) * 2) : make_float2(0.f, 0.f);
+      float yr[4] = {0.f, 0.f, 0.f, 0.f}, yi[4] = {0.f, 0.f, 0.f, 0.f};
+      if (on) V4<T>::ld(reinterpret_cast<const T*>(p.yk[k]) + off, yr, yi);
+      if (!BWD) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          ar[j] += c.x * yr[j] - c.y * yi[j];
+          ai[j] += c.x * yi[j] + c.y * yr[j];
+        }
+      } else {
+        float dr = 0.f, di = 0.f, gr[4], gi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dr += ar[j] * yr[j] + ai[j] * yi[j];
+          di += ai[j] * yr[j] - ar[j] * yi[j];
+          gr[j] = c.x * ar[j] + c.y * ai[j];
+          gi[j] = c.x * ai[j] - c.y * ar[j];
+        }
+        for (int o = gpr >> 1; o; o >>= 1) {
+          dr += __shfl_xor_sync(0xffffffffu, dr, o);
+          di += __shfl_xor_sync(0xffffffffu, di, o);
+        }
+        if (on) {
+          V4<T>::st(reinterpret_cast<T*>(p.dyk[k]) + off, gr, gi);
+          if (g == 0) *reinterpret_cast<float2*>(p.dcoef + ((int64_t)k * p.R + r) * 2) = make_float2(dr, di);
+        }
+      }
+    }
+    if (!BWD && on) V4<T>::st(reinterpret_cast<T*>(p.y) + off, ar, ai);
+  }
+}
+
 inline bool is_dtype(int32_t d) { return d == QPAM_F32 || d == QPAM_BF16; }
 inline int act_grid_y(int64_t N, int xblocks, int P) {
   int64_t y = P > 0 ? P : std::max<int64_t>(1, (148 * 8) / xblocks);
@@ -590,4 +651,41 @@ extern "C" int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* ro
                                  int32_t H, int32_t d, void* stream) {
   return pam_prep(true, qkv, dtype, rope, rope_len, positions, offset, omp, const_cast<void*>(dq),
                   const_cast<void*>(dk), const_cast<void*>(dv), dqkv, domp, B, T, H, d, stream);
+}
+
+static int state_combine(bool bwd, const void* const* yk, void* const* dyk, const float* coef, void* y, float* dcoef,
+                         int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream) {
+  QPAM_REQUIRE(yk && coef && y && (!bwd || (dyk && dcoef)), "state_combine: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && K >= 1 && K <= QPAM_MAX_STATES && R >= 0, "state_combine: bad dtype, K or row count");
+  QPAM_REQUIRE(d >= 4 && d <= 128 && (d & (d - 1)) == 0, "state_combine: d must be a power of two in [4,128] (got %d)", d);
+  if (R == 0) return QPAM_OK;
+  CombineParams p{};
+  for (int k = 0; k < K; ++k) {
+    QPAM_REQUIRE(yk[k] && (!bwd || dyk[k]), "state_combine: NULL state tensor");
+    p.yk[k] = yk[k];
+    p.dyk[k] = bwd ? dyk[k] : nullptr;
+  }
+  p.coef = coef; p.y = y; p.dcoef = dcoef; p.R = R; p.d = d; p.K = K;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = R * (d / 4);
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  if (dtype == QPAM_F32) {
+    if (bwd) k_state_combine<float, true><<<grid, 256, 0, st>>>(p);
+    else k_state_combine<float, false><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (bwd) k_state_combine<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
+    else k_state_combine<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+  }
+  if (bwd) { QPAM_LAUNCH_CHECK("k_state_combine_bwd"); } else { QPAM_LAUNCH_CHECK("k_state_combine_fwd"); }
+  return QPAM_OK;
+}
+
+extern "C" int qpam_state_combine_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype, int32_t K,
+                                      int64_t R, int32_t d, void* stream) {
+  return state_combine(false, yk, nullptr, coef, y, nullptr, dtype, K, R, d, stream);
+}
+
+extern "C" int qpam_state_combine_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
+                                      float* dcoef, int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream) {
+  return state_combine(true, yk, dyk, coef, const_cast<void*>(dy), dcoef, dtype, K, R, d, stream);
 }

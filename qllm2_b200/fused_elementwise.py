@@ -290,3 +290,55 @@ def pam_prep(qkv: torch.Tensor, rope: Optional[torch.Tensor], omp: Optional[torc
             raise _lib.QPamError("pam_prep: positions must have one entry per token")
         positions = positions.to(torch.int64).contiguous()
     return _PamPrepFn.apply(qkv, rope, omp, positions, offset, H, d)
+
+
+# ------------------------------------------------------------------------------------ K-state read-out
+class _StateCombineFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, coef, *yks):
+        K = len(yks)
+        yks = tuple(t.contiguous() for t in yks)
+        d = yks[0].shape[-2]
+        R = yks[0].numel() // (2 * d)
+        cf = coef.detach().float().contiguous()
+        y = torch.empty_like(yks[0])
+        arr = (_lib.c_void_p * K)(*[t.data_ptr() for t in yks])
+        check(_lib.lib().qpam_state_combine_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, R, d, stream_ptr()),
+              "qpam_state_combine_fwd")
+        ctx.save_for_backward(cf, *yks)
+        ctx.coef_dtype = coef.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cf, *yks = ctx.saved_tensors
+        K = len(yks)
+        d = yks[0].shape[-2]
+        R = yks[0].numel() // (2 * d)
+        dy = dy.to(yks[0].dtype).contiguous()
+        dyks = [torch.empty_like(t) for t in yks]
+        dcoef = torch.empty_like(cf)
+        arr = (_lib.c_void_p * K)(*[t.data_ptr() for t in yks])
+        darr = (_lib.c_void_p * K)(*[t.data_ptr() for t in dyks])
+        check(_lib.lib().qpam_state_combine_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K, R, d,
+                                                stream_ptr()), "qpam_state_combine_bwd")
+        return (dcoef.to(ctx.coef_dtype), *dyks)
+
+
+def state_combine(coef: torch.Tensor, yks) -> torch.Tensor:
+    """y = sum_k coef[k] * yks[k] (complex): coef [K, ..., 2] over the leading axes of yks[k] [..., d, 2]
+    (the K-state read-out of v11/model.py:766-781), forward and backward in one pass each."""
+    yks = list(yks)
+    _require_cuda(coef, *yks)
+    K = len(yks)
+    if not 1 <= K <= 4:
+        raise _lib.QPamError(f"state_combine: 1..4 states, got {K}")
+    shape, dt = yks[0].shape, yks[0].dtype
+    d = shape[-2]
+    if any(t.shape != shape or t.dtype != dt for t in yks) or shape[-1] != 2:
+        raise _lib.QPamError("state_combine: the state outputs must share one [..., d, 2] shape and dtype")
+    if dt not in (torch.float32, torch.bfloat16) or d < 4 or d > 128 or d & (d - 1):
+        raise _lib.QPamError(f"state_combine: bf16/f32 and d a power of two in [4,128]; got {dt}, d={d}")
+    if tuple(coef.shape) != (K, *shape[:-2], 2):
+        raise _lib.QPamError(f"state_combine: coef must be {(K, *shape[:-2], 2)}, got {tuple(coef.shape)}")
+    return _StateCombineFn.apply(coef, *yks)

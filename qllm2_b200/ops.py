@@ -143,16 +143,19 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
         # single-state scan with decay gamma^(k) on the same q, k, v (the fused K-state form of the
         # reference, v11/model.py:657-781, is algebraically this sum).  autograd composes the backward:
         # K single-state backward scans with upstream conj(c_k) dy, and dc_k = <dy, y^(k)>.
-        y, finals = None, []
+        ys, finals = [], []
         for kk in range(K):
             yk, sk = _PamScanFn.apply(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1],
                                       cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
-            if coef is not None:
-                c = coef[kk].to(yk.dtype).unsqueeze(-2)                      # [B,H,T,1,2]
-                yk = torch.stack([yk[..., 0] * c[..., 0] - yk[..., 1] * c[..., 1],
-                                  yk[..., 0] * c[..., 1] + yk[..., 1] * c[..., 0]], dim=-1)
-            y = yk if y is None else y + yk
+            ys.append(yk)
             finals.append(sk)
+        if coef is None:
+            y = ys[0]
+            for yk in ys[1:]:
+                y = y + yk
+        else:
+            from .fused_elementwise import state_combine
+            y = state_combine(coef, ys)
         return y, torch.cat(finals, dim=0)
     return _PamScanFn.apply(q, k, v, gamma, coef, s0, cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
 

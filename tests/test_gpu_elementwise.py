@@ -186,3 +186,25 @@ def test_wrappers_refuse_bad_input_before_any_launch():
         FE.pam_prep(torch.randn(1, 4, 3 * 2 * 24, 2, device=DEV), None, None, n_heads=2, head_dim=24)
     with pytest.raises(QPamError):
         FE.fused_mod_swish(torch.randn(4, 8, 2, device=DEV), torch.zeros(8, device=DEV), torch.zeros(4, device=DEV))
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("K,d", [(3, 64), (2, 32), (4, 128), (1, 16)])
+def test_state_combine_matches_complex_sum(dtype, tol, K, d):
+    g = torch.Generator().manual_seed(K * d)
+    shape = (2, 3, 29)
+    yks32 = [torch.randn(*shape, d, 2, generator=g).to(DEV) for _ in range(K)]
+    coef32 = torch.randn(K, *shape, 2, generator=g).to(DEV)
+    dy = torch.randn(*shape, d, 2, generator=g).to(DEV)
+    yks = [t.to(dtype).requires_grad_(True) for t in yks32]
+    coef = coef32.clone().requires_grad_(True)
+    y = FE.state_combine(coef, yks)
+    ga = torch.autograd.grad((y.float() * dy).sum(), [coef] + yks)
+    ref_in = [t.clone().requires_grad_(True) for t in yks32]
+    cr = coef32.clone().requires_grad_(True)
+    yr = sum(torch.view_as_real(torch.view_as_complex(cr[k]).unsqueeze(-1) * torch.view_as_complex(ref_in[k]))
+             for k in range(K))
+    gb = torch.autograd.grad((yr * dy).sum(), [cr] + ref_in)
+    assert y.dtype == dtype and rel(y, yr) < tol
+    for a, b in zip(ga, gb):
+        assert rel(a, b) < tol
