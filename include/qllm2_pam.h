@@ -233,6 +233,47 @@ int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* rope, int64_t
                       const void* dk, const void* dv, void* dqkv, float* domp, int32_t B, int32_t T,
                       int32_t H, int32_t d, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Forward-only block fusions for inference (prefill and the per-token decode step driven by
+ * V11LM.generate, v11/model.py:1206-1245), where nothing is kept for a backward pass.
+ * ------------------------------------------------------------------------------------------ */
+/* gate_up [N, ld]: columns [0,2C) = gate, [2C,4C) = up (interleaved complex), one projection output.
+ * out [N,C,2] = gate/(|gate|+1e-8) * act(up) * sigmoid(|gate|), act = modSwish (beta != NULL) or
+ * modReLU (ComplexGatedUnit.forward, v11/complex_ops.py:175-220). */
+int qpam_act_gate_packed_fwd(const void* gate_up, int64_t ld, int32_t dtype, const float* bias,
+                             const float* beta, void* out, int64_t N, int32_t C, void* stream);
+/* z [N,D,2] += res_scale[0] * delta (delta NULL: unchanged; res_scale NULL: 1), then
+ * xn = ComplexNorm(z; norm_scale) (xn NULL: skipped) and mag [N,D] = |xn| (NULL: skipped).
+ * The residual add and the pre-norm of V11Block.forward (v11/model.py block forward). */
+int qpam_residual_cnorm_fwd(void* z, const void* delta, const float* res_scale, const float* norm_scale,
+                            void* xn, void* mag, int32_t dtype, int64_t N, int32_t D, float eps,
+                            void* stream);
+/* Input stage of the PAM layer from projection outputs (row strides ld_* in scalars):
+ *   qkv   [B*T, ld_qkv]  first 3*H*d*2 columns = (q|k|v, head, channel, re/im)
+ *   dt    [B*T, ld_dt]   H decay logits            (dt_proj output incl. its bias)
+ *   pg    [B*T, ld_pg]   H protect-gate logits     (NULL: no protect gate)
+ *   phase [B*T, ld_phase] H*K routing phases, (h,k) order (NULL: 0)
+ *   score [B*T, ld_score] H*K routing scores       (NULL: uniform weights 1)
+ * Outputs: q (times q_scale), k rotated by rope[pos]; v' = (1-p) v, all [B,H,T,d,2];
+ *   gamma [K,B,H,T] fp32 = base (1-p) + p, base = exp(-softplus(dt + dt_bias[h] + state_dt_offset[k]))
+ *   (gamma_floor applied to base); coef [K,B,H,T,2] fp32 = K softmax_k(score) e^{i phase} (NULL when K == 1).
+ * (PhaseAssociativeLayer._project, _gamma_and_vprime and the phase routing, v11/model.py:271-350, 630-655.) */
+typedef struct qpam_front_args {
+  const void *qkv, *dt, *pg, *phase, *score;
+  int64_t ld_qkv, ld_dt, ld_pg, ld_phase, ld_score;
+  const float* dt_bias;          /* [H] */
+  const float* state_dt_offset;  /* [K] or NULL */
+  const float* rope;             /* [rope_len, d, 2] (cos, sin) or NULL */
+  const int64_t* positions;      /* [B*T] or NULL: offset + t */
+  int64_t rope_len, offset;
+  void *q, *k, *v;
+  float* gamma;
+  float* coef;
+  float gamma_floor, q_scale;
+  int32_t B, T, H, d, K, io_dtype;
+} qpam_front_args;
+int qpam_pam_front_fwd(const qpam_front_args* args, void* stream);
+
 /* Read-out of K phase-routed states (v11/model.py:766-781: the sum over states weighted by
  * alpha_k e^{i phi_k}):  y[r,:] = sum_k coef[k,r] * yk[k][r,:] over R rows of d complex channels;
  * yk / dyk are HOST arrays of K device pointers, coef / dcoef fp32 [K,R,2].

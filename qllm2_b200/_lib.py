@@ -40,6 +40,18 @@ class CEArgs(C.Structure):
 
 
 # name -> (restype, argtypes); every symbol declared in include/qllm2_pam.h
+class FrontArgs(C.Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("dt", c_void_p), ("pg", c_void_p), ("phase", c_void_p), ("score", c_void_p),
+        ("ld_qkv", c_int64), ("ld_dt", c_int64), ("ld_pg", c_int64), ("ld_phase", c_int64), ("ld_score", c_int64),
+        ("dt_bias", c_void_p), ("state_dt_offset", c_void_p), ("rope", c_void_p), ("positions", c_void_p),
+        ("rope_len", c_int64), ("offset", c_int64),
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("gamma", c_void_p), ("coef", c_void_p),
+        ("gamma_floor", c_float), ("q_scale", c_float),
+        ("B", c_int32), ("T", c_int32), ("H", c_int32), ("d", c_int32), ("K", c_int32), ("io_dtype", c_int32),
+    ]
+
+
 SIGNATURES = {
     "qpam_scan_workspace_bytes": (c_size_t, [C.POINTER(ScanArgs), c_int32]),
     "qpam_scan_fwd": (c_int32, [C.POINTER(ScanArgs), c_void_p]),
@@ -73,6 +85,10 @@ SIGNATURES = {
     "qpam_state_combine_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_void_p]),
     "qpam_state_combine_bwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, C.POINTER(c_void_p), c_void_p, c_int32,
                                          c_int32, c_int64, c_int32, c_void_p]),
+    "qpam_act_gate_packed_fwd": (c_int32, [c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
+    "qpam_residual_cnorm_fwd": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64,
+                                          c_int32, C.c_float, c_void_p]),
+    "qpam_pam_front_fwd": (c_int32, [C.POINTER(FrontArgs), c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

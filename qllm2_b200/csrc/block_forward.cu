@@ -1,0 +1,280 @@
+// Forward-only fusions of a V11 block for inference (prefill and the per-token decode step), where
+// no activation has to be kept for a backward pass:
+//   k_act_gate_packed   modSwish/modReLU of the `up` half + the gated-unit product, from ONE
+//                       projection output [N, gate | up]                (v11/model.py CGU forward)
+//   k_residual_cnorm    z += s * delta  and  xn = ComplexNorm(z) (+ |xn|) in one sweep over the row
+//   k_pam_front         decay / protect gate / phase-routing read-out weights AND the head split +
+//                       rotary rotation + protect scaling, from the fused projection output
+//                       (PhaseAssociativeLayer._project, _gamma_and_vprime, phase routing:
+//                       v11/model.py:271-350, 630-655)
+// The reference runs each of these as 10-30 separate torch operators per layer and token
+// (v11/model.py:1206-1245 drives them once per generated token).
+#include <algorithm>
+
+#include "common.cuh"
+#include "elementwise.cuh"
+
+namespace qpam {
+namespace {
+using namespace ew;
+
+template <typename T>
+__device__ __forceinline__ float rnd(float x);
+template <>
+__device__ __forceinline__ float rnd<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float rnd<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <typename T, bool SWISH>
+__global__ void __launch_bounds__(256) k_act_gate_packed(const T* __restrict__ gu, int64_t ld,
+                                                         const float* __restrict__ bias,
+                                                         const float* __restrict__ beta, T* __restrict__ out,
+                                                         int64_t N, int C) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= (C >> 2)) return;
+  float b4[4], be4[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b4[j] = bias[g * 4 + j];
+    be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
+  }
+  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
+    float ar[4], ai[4], ur[4], ui[4];
+    V4<T>::ld(gu + row * ld + g * 8, ar, ai);
+    V4<T>::ld(gu + row * ld + 2 * C + g * 8, ur, ui);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float um = sqrtf(ur[j] * ur[j] + ui[j] * ui[j] + MAG_EPS);
+      const float act = SWISH ? um * sigmoidf_(be4[j] * um + b4[j]) : fmaxf(um + b4[j], 0.f);
+      const float f = act / (um + MAG_EPS);
+      const float gm = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float h = sigmoidf_(gm) / (gm + MAG_EPS) * f;
+      const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
+      ar[j] = pr * h;
+      ai[j] = pi * h;
+    }
+    V4<T>::st(out + (row * C + g * 4) * 2, ar, ai);
+  }
+}
+
+// One warp per row.  The updated row is written first and read back for the second sweep (same
+// thread, L1/L2 hits), so any width works without a register cache.
+template <typename T>
+__global__ void __launch_bounds__(128) k_residual_cnorm(T* __restrict__ z, const T* __restrict__ delta,
+                                                        const float* __restrict__ res_scale,
+                                                        const float* __restrict__ norm_scale, T* __restrict__ xn,
+                                                        T* __restrict__ mag_out, int64_t N, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int groups = D >> 2;
+  const float s = res_scale ? *res_scale : 1.f;
+  for (int64_t row = warp; row < N; row += nwarps) {
+    T* zr = z + row * (int64_t)D * 2;
+    float ss = 0.f;
+    for (int g = lane; g < groups; g += 32) {
+      float re[4], im[4];
+      V4<T>::ld(zr + g * 8, re, im);
+      if (delta) {
+        float dr[4], di[4];
+        V4<T>::ld(delta + row * (int64_t)D * 2 + g * 8, dr, di);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          re[j] = fmaf(s, dr[j], re[j]);
+          im[j] = fmaf(s, di[j], im[j]);
+        }
+        V4<T>::st(zr + g * 8, re, im);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // the norm sees the stored (rounded) residual stream, as the modules do
+          re[j] = rnd<T>(re[j]);
+          im[j] = rnd<T>(im[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ss += re[j] * re[j] + im[j] * im[j] + MAG_EPS;
+    }
+    ss = warp_sum(ss);
+    if (!xn) continue;
+    const float rrms = rsqrtf(ss / (float)D + eps);
+    for (int g = lane; g < groups; g += 32) {
+      float re[4], im[4], mg[4];
+      V4<T>::ld(zr + g * 8, re, im);
+      const float4 sc = *reinterpret_cast<const float4*>(norm_scale + g * 4);
+      const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float m = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+        const float w = m / (m + MAG_EPS) * rrms * s4[j];
+        re[j] *= w;
+        im[j] *= w;
+      }
+      V4<T>::st(xn + row * (int64_t)D * 2 + g * 8, re, im);
+      if (mag_out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // magnitude of the stored (rounded) values
+          const float r0 = rnd<T>(re[j]), i0 = rnd<T>(im[j]);
+          mg[j] = sqrtf(r0 * r0 + i0 * i0 + MAG_EPS);
+        }
+        T* mp = mag_out + row * (int64_t)D + g * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) IO<T>::st(mp + j, mg[j]);
+      }
+    }
+  }
+}
+
+struct FrontParams {
+  qpam_front_args a;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_pam_front(FrontParams fp) {
+  const qpam_front_args& a = fp.a;
+  __shared__ float s_keep[64];
+  const int H = a.H, K = a.K, d = a.d;
+  const int gph = d >> 2;
+  const int per_tok = 3 * H * gph;
+  const int64_t ntok = (int64_t)a.B * a.T;
+  for (int64_t tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
+    const int b = (int)(tok / a.T), t = (int)(tok - (int64_t)b * a.T);
+    // ---- per-head scalars: decay per state, protect gate, read-out weights
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+      const float dt = IO<T>::ld(reinterpret_cast<const T*>(a.dt) + tok * a.ld_dt + h) + a.dt_bias[h];
+      float p = 0.f;
+      if (a.pg) p = sigmoidf_(IO<T>::ld(reinterpret_cast<const T*>(a.pg) + tok * a.ld_pg + h));
+      s_keep[h] = 1.f - p;
+      float wsum = 0.f, wmax = -INFINITY;
+      if (a.score) {
+        for (int k = 0; k < K; ++k) wmax = fmaxf(wmax, IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k));
+        for (int k = 0; k < K; ++k) wsum += __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax);
+      }
+      for (int k = 0; k < K; ++k) {
+        const float x = dt + (a.state_dt_offset ? a.state_dt_offset[k] : 0.f);
+        const float sp = x > 20.f ? x : log1pf(__expf(x));  // softplus
+        float base = __expf(-sp);
+        if (a.gamma_floor > 0.f) base = a.gamma_floor + (1.f - a.gamma_floor) * base;
+        const int64_t gi = (((int64_t)k * a.B + b) * H + h) * a.T + t;
+        a.gamma[gi] = base * (1.f - p) + p;
+        if (a.coef) {
+          float w = 1.f, ph = 0.f;
+          if (a.score) w = __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax) / wsum * (float)K;
+          if (a.phase) ph = IO<T>::ld(reinterpret_cast<const T*>(a.phase) + tok * a.ld_phase + h * K + k);
+          float sn, cs;
+          sincosf(ph, &sn, &cs);
+          *reinterpret_cast<float2*>(a.coef + gi * 2) = make_float2(w * cs, w * sn);
+        }
+      }
+    }
+    __syncthreads();
+    // ---- head split, rotation, protect scaling
+    int64_t pos = a.positions ? a.positions[tok] : a.offset + t;
+    pos = pos < 0 ? 0 : (pos >= a.rope_len ? a.rope_len - 1 : pos);
+    for (int idx = threadIdx.x; idx < per_tok; idx += blockDim.x) {
+      const int which = idx / (H * gph);
+      const int rem = idx - which * H * gph;
+      const int h = rem / gph, g = rem - h * gph;
+      const int64_t src = tok * a.ld_qkv + ((int64_t)which * H + h) * d * 2 + g * 8;
+      const int64_t dst = (((int64_t)b * H + h) * a.T + t) * (int64_t)d * 2 + g * 8;
+      T* side = reinterpret_cast<T*>(which == 0 ? a.q : which == 1 ? a.k : a.v);
+      float re[4], im[4];
+      V4<T>::ld(reinterpret_cast<const T*>(a.qkv) + src, re, im);
+      if (which < 2) {
+        const float mul = which == 0 ? a.q_scale : 1.f;
+        if (a.rope) {
+          const float4 c0 = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2);
+          const float4 c1 = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2 + 4);
+          const float cs[4] = {c0.x, c0.z, c1.x, c1.z};
+          const float sn[4] = {c0.y, c0.w, c1.y, c1.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float r0 = re[j], i0 = im[j];
+            re[j] = (r0 * cs[j] - i0 * sn[j]) * mul;
+            im[j] = (r0 * sn[j] + i0 * cs[j]) * mul;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            re[j] *= mul;
+            im[j] *= mul;
+          }
+        }
+      } else {
+        const float keep = s_keep[h];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          re[j] *= keep;
+          im[j] *= keep;
+        }
+      }
+      V4<T>::st(side + dst, re, im);
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+}  // namespace qpam
+
+using namespace qpam;
+using namespace qpam::ew;
+
+extern "C" int qpam_act_gate_packed_fwd(const void* gate_up, int64_t ld, int32_t dtype, const float* bias,
+                                        const float* beta, void* out, int64_t N, int32_t C, void* stream) {
+  QPAM_REQUIRE(gate_up && bias && out, "act_gate_packed: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && C > 0 && C % 4 == 0, "act_gate_packed: C must be a multiple of 4 (got %d)", C);
+  QPAM_REQUIRE(ld >= 4 * (int64_t)C && ld % (dtype == QPAM_F32 ? 4 : 8) == 0,
+               "act_gate_packed: the row stride must cover 4*C scalars and keep rows 16-byte aligned");
+  if (N == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, (unsigned)std::min<int64_t>(N, std::max(1, (148 * 8) / xb)));
+#define QPAM_AG(T)                                                                                                  \
+  if (beta) k_act_gate_packed<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C); \
+  else k_act_gate_packed<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C);
+  if (dtype == QPAM_F32) { QPAM_AG(float) } else { QPAM_AG(__nv_bfloat16) }
+#undef QPAM_AG
+  QPAM_LAUNCH_CHECK("k_act_gate_packed");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_residual_cnorm_fwd(void* z, const void* delta, const float* res_scale, const float* norm_scale,
+                                       void* xn, void* mag, int32_t dtype, int64_t N, int32_t D, float eps,
+                                       void* stream) {
+  QPAM_REQUIRE(z && (delta || xn), "residual_cnorm: NULL pointer argument");
+  QPAM_REQUIRE(!xn || norm_scale, "residual_cnorm: the norm needs its scale vector");
+  QPAM_REQUIRE(!mag || xn, "residual_cnorm: magnitudes are those of the normalised rows");
+  QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && D > 0 && D % 4 == 0, "residual_cnorm: D must be a multiple of 4 (got %d)", D);
+  if (N == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int blocks = (int)std::min<int64_t>((N + 3) / 4, 148 * 8);
+  if (dtype == QPAM_F32)
+    k_residual_cnorm<float><<<blocks, 128, 0, st>>>((float*)z, (const float*)delta, res_scale, norm_scale, (float*)xn, (float*)mag, N, D, eps);
+  else
+    k_residual_cnorm<__nv_bfloat16><<<blocks, 128, 0, st>>>((__nv_bfloat16*)z, (const __nv_bfloat16*)delta, res_scale, norm_scale,
+                                                            (__nv_bfloat16*)xn, (__nv_bfloat16*)mag, N, D, eps);
+  QPAM_LAUNCH_CHECK("k_residual_cnorm");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_pam_front_fwd(const qpam_front_args* a, void* stream) {
+  QPAM_REQUIRE(a, "pam_front: NULL args");
+  QPAM_REQUIRE(a->qkv && a->dt && a->dt_bias && a->q && a->k && a->v && a->gamma, "pam_front: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(a->io_dtype) && a->B > 0 && a->T > 0 && a->H > 0 && a->H <= 64, "pam_front: bad dtype or shape (H <= 64)");
+  QPAM_REQUIRE(a->K >= 1 && a->K <= QPAM_MAX_STATES, "pam_front: K must be in [1,%d]", QPAM_MAX_STATES);
+  QPAM_REQUIRE(a->d >= 4 && a->d <= 128 && (a->d & (a->d - 1)) == 0, "pam_front: head_dim must be a power of two in [4,128]");
+  const int64_t al = a->io_dtype == QPAM_F32 ? 4 : 8;
+  QPAM_REQUIRE(a->ld_qkv >= 6 * (int64_t)a->H * a->d && a->ld_qkv % al == 0, "pam_front: qkv row stride too small or rows not 16-byte aligned");
+  QPAM_REQUIRE(!a->rope || a->rope_len > 0, "pam_front: empty rotary table");
+  QPAM_REQUIRE(!a->rope || a->positions || a->offset + a->T <= a->rope_len, "pam_front: rotary table shorter than offset + T");
+  QPAM_REQUIRE(a->K == 1 || a->coef, "pam_front: K > 1 needs the read-out weight output");
+  QPAM_REQUIRE(!a->score || a->coef, "pam_front: scores without read-out weights");
+  cudaStream_t st = (cudaStream_t)stream;
+  FrontParams fp{*a};
+  const int per_tok = 3 * a->H * (a->d / 4);
+  const int threads = std::min(256, (per_tok + 31) / 32 * 32);
+  const int grid = (int)std::min<int64_t>((int64_t)a->B * a->T, 148 * 16);
+  if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp);
+  else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp);
+  QPAM_LAUNCH_CHECK("k_pam_front");
+  return QPAM_OK;
+}

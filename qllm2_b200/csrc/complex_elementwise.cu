@@ -10,54 +10,11 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "elementwise.cuh"
 
 namespace qpam {
 namespace {
-
-constexpr float MAG_EPS = 1e-8f;  // inside the square root and beside the magnitude, as the reference
-
-// 4 complex channels (re,im interleaved) <-> registers
-template <typename T>
-struct V4;
-template <>
-struct V4<float> {
-  static __device__ __forceinline__ void ld(const float* p, float (&r)[4], float (&i)[4]) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    r[0] = a.x; i[0] = a.y; r[1] = a.z; i[1] = a.w; r[2] = b.x; i[2] = b.y; r[3] = b.z; i[3] = b.w;
-  }
-  static __device__ __forceinline__ void st(float* p, const float (&r)[4], const float (&i)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(r[0], i[0], r[1], i[1]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(r[2], i[2], r[3], i[3]);
-  }
-};
-template <>
-struct V4<__nv_bfloat16> {
-  static __device__ __forceinline__ void ld(const __nv_bfloat16* p, float (&r)[4], float (&i)[4]) {
-    const uint4 u = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      r[j] = __uint_as_float(w[j] << 16);
-      i[j] = __uint_as_float(w[j] & 0xffff0000u);
-    }
-  }
-  static __device__ __forceinline__ void st(__nv_bfloat16* p, const float (&r)[4], const float (&i)[4]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(r[j], i[j]);
-      w[j] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
-  }
-};
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+using namespace ew;
 
 // ------------------------------------------------------------------------------------------------
 // Magnitude-RMS norm.  out = z / (|z| + e) * (|z| / rms) * scale,  |z| = sqrt(re^2 + im^2 + e),
@@ -499,7 +456,6 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
   }
 }
 
-inline bool is_dtype(int32_t d) { return d == QPAM_F32 || d == QPAM_BF16; }
 inline int act_grid_y(int64_t N, int xblocks, int P) {
   int64_t y = P > 0 ? P : std::max<int64_t>(1, (148 * 8) / xblocks);
   return (int)std::min<int64_t>(std::min<int64_t>(y, N), 65535);

@@ -18,6 +18,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 import torch
 
 from . import ops
+from .fused_forward import FusedForward
 from .model import V11LM
 
 
@@ -93,14 +94,45 @@ class SlotScheduler:
 
 
 # ------------------------------------------------------------------------------------ engine
+class _PrefillMix:
+    """Sequence mixing at prefill: the packed ragged scan; final states go to the sequences' slots."""
+    q_scale = 1.0     # the scan applies head_dim^-0.5 itself
+
+    def __init__(self, eng, cu, slots):
+        self.eng, self.cu, self.slots = eng, cu, slots
+
+    def __call__(self, layer, q, k, v, gamma, coef):
+        y, s = ops.pam_scan(q, k, v, gamma, coef=coef, cu_seqlens=self.cu, head_dim=q.shape[3])
+        ops.pam_pool_store(self.eng.pool, self.slots, s, layer=layer)
+        return y.transpose(1, 2).reshape(q.shape[2], -1)
+
+
+class _DecodeMix:
+    """Sequence mixing at decode: one recurrent step in place on the slots of the live sequences."""
+
+    def __init__(self, eng, slots):
+        self.eng, self.slots = eng, slots
+        self.q_scale = eng.model.config.head_dim ** -0.5
+
+    def __call__(self, layer, q, k, v, gamma, coef):
+        n, H, _, d, _ = q.shape
+        K = gamma.shape[0]
+        y = ops.pam_decode_step(self.eng.pool, self.slots, q.view(n, H, d, 2), k.view(n, H, d, 2), v.view(n, H, d, 2),
+                                gamma.view(K, n, H), None if coef is None else coef.view(K, n, H, 2), layer=layer)
+        return y.view(n, -1)
+
+
 class ContinuousBatcher:
     """Greedy decode of many sequences through a V11LM with continuous batching."""
 
     def __init__(self, model: V11LM, n_slots: int, state_dtype: Optional[torch.dtype] = None,
-                 max_prefill_tokens: int = 1 << 17, cuda_graph: bool = False, max_position: int = 8192):
+                 max_prefill_tokens: int = 1 << 17, cuda_graph: bool = False, max_position: int = 8192,
+                 fused: bool = True):
         """cuda_graph=True captures the decode step once for a full batch of n_slots rows (idle rows carry
         slot id -1, which the step kernel skips) and replays it every step: the per-token cost is then the
-        kernels', not the ~10^3 launches' of the Python layer loop."""
+        kernels', not the launches' of the Python layer loop.  fused=True runs the blocks through
+        `FusedForward` (packed weights, ~10 launches per layer) when the configuration allows it;
+        fused=False keeps the module path (`V11Block` operators)."""
         self.model = model.eval()
         cfg = model.config
         p = next(model.parameters())
@@ -114,6 +146,8 @@ class ContinuousBatcher:
         self.n_slots = n_slots
         self.cuda_graph = cuda_graph
         self._graph = None
+        self.max_position = max_position
+        self.ff = FusedForward(model, max_position) if fused and FusedForward.unsupported_reason(model) is None else None
         self._ensure_rope(max_position)    # tables must not grow while a captured graph reads them
         if cuda_graph:
             self._g_ids = torch.zeros(n_slots, 1, dtype=torch.long, device=self.device)
@@ -126,6 +160,10 @@ class ContinuousBatcher:
 
     def _ensure_rope(self, need: int):
         """Rotary tables must cover every position before a step that cannot look at its positions on the host."""
+        if self.ff is not None:
+            if need > self.max_position:
+                raise RuntimeError(f"position {need - 1} is beyond max_position={self.max_position} of this batcher")
+            return
         from .model import build_rope_cache
         for blk in self.model.blocks:
             if blk.pam.use_rope and blk.pam.rope_cache.shape[0] < need:
@@ -145,6 +183,16 @@ class ContinuousBatcher:
         cu[1:] = torch.tensor(lens).cumsum(0).int()
         cu = cu.to(self.device)
         slots = torch.tensor([r.slot for r in batch], dtype=torch.int32, device=self.device)
+        if self.ff is not None:
+            xn = self.ff.hidden(ids, _PrefillMix(self, cu, slots), positions=positions)
+            nxt = self.ff.greedy_next(self.ff.head_hidden(xn[(cu[1:] - 1).long()]))
+        else:
+            nxt = self._prefill_modules(ids, positions, cu, slots)
+        for r, t in zip(batch, nxt.tolist()):
+            r.generated.append(int(t))
+
+    def _prefill_modules(self, ids, positions, cu, slots):
+        m = self.model
         z = m.embed_norm(m.embed(ids))
         for li, blk in enumerate(m.blocks):
             z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
@@ -158,9 +206,7 @@ class ContinuousBatcher:
             z = z + out * blk.pam_scale
         last = (cu[1:] - 1).long()
         lm = m._head_hidden(z[:, last])                                     # [1, n, D, 2]
-        nxt = m.greedy_next(lm[0])
-        for r, t in zip(batch, nxt.tolist()):
-            r.generated.append(int(t))
+        return m.greedy_next(lm[0])
 
     @torch.no_grad()
     def _decode(self, live: List[Request]):
@@ -198,6 +244,9 @@ class ContinuousBatcher:
     @torch.no_grad()
     def _decode_tensors(self, ids, positions, slots):
         """One decode step for rows (ids [n,1], positions [n,1], slots [n]); returns next ids [n]."""
+        if self.ff is not None:
+            xn = self.ff.hidden(ids, _DecodeMix(self, slots), positions=positions)
+            return self.ff.greedy_next(self.ff.head_hidden(xn))
         m = self.model
         n = ids.shape[0]
         z = m.embed_norm(m.embed(ids))                                      # [n,1,D,2]

@@ -1,0 +1,108 @@
+"""Inference forward through packed weights and the fused block kernels vs the module path.
+
+The module path (V11Block operators) is pinned to the reference by tests/test_gpu_model.py; here the
+packed forward must reproduce its hidden states (fp32: 1e-4 relative; bf16: 2e-2) and greedy ids.
+"""
+import pytest
+import torch
+
+from qllm2_b200 import model as M, ops
+from qllm2_b200.fused_forward import FusedForward
+from qllm2_b200.serving import ContinuousBatcher
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+class _ScanMix:
+    q_scale = 1.0
+
+    def __call__(self, layer, q, k, v, gamma, coef):
+        y, _ = ops.pam_scan(q, k, v, gamma, coef=coef, head_dim=q.shape[3])
+        return y.transpose(1, 2).reshape(q.shape[2], -1)
+
+
+def rel(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a - b).norm() / b.norm())
+
+
+VARIANTS = {
+    "k1_swish": dict(n_states=1),
+    "k3_content_gate": dict(n_states=3, gate_content_aware=True),
+    "k3_compete_routed": dict(n_states=3, gate_content_aware=True, routing_content_aware=True, state_compete=True,
+                              phase_init="spread"),
+    "k2_compete_magnitude_routing": dict(n_states=2, state_compete=True, phase_init="ortho"),
+    "k1_modrelu_no_gsp_floor": dict(n_states=1, activation="modrelu", use_gsp=False, gamma_floor=0.05),
+    "k3_no_rope_d32": dict(n_states=3, use_rope=False, head_dim=32, n_heads=4),
+}
+
+
+def _net(over, dtype=torch.float32):
+    torch.manual_seed(0)
+    kw = dict(vocab_size=257, dim=64, n_heads=2, head_dim=32, n_layers=3, expand=2, dropout=0.0, max_seq_len=256,
+              gradient_checkpointing=False, chunk_size=64)
+    kw.update(over)
+    net = M.V11LM(M.V11Config(**kw)).to(DEV).eval()
+    with torch.no_grad():                      # move every gate and routing weight off its zero/constant init
+        for p in net.parameters():
+            if p.dim() <= 1:
+                p.add_(0.2 * torch.randn_like(p))
+        for blk in net.blocks:
+            if hasattr(blk.pam, "score_proj"):
+                blk.pam.score_proj.weight.normal_(std=0.3)
+    return net.to(dtype)
+
+
+@pytest.mark.parametrize("variant", list(VARIANTS))
+def test_hidden_and_head_match_module_path_fp32(variant):
+    net = _net(VARIANTS[variant])
+    ids = torch.randint(0, 257, (1, 150), generator=torch.Generator().manual_seed(1)).to(DEV)
+    ff = FusedForward(net, max_position=512)
+    xn = ff.hidden(ids, _ScanMix())
+    with torch.no_grad():
+        z = net._embed(ids, 0)
+        z, _ = net._run_blocks(z, None, 0, False)
+        ref = net.output_norm(z)[0]
+        ref_lm = net._head_hidden(z)[0]
+    assert rel(xn, ref) < 1e-4
+    lm = ff.head_hidden(xn)
+    assert rel(lm, ref_lm) < 1e-4
+    assert torch.equal(ff.greedy_next(lm), net.greedy_next(ref_lm))
+
+
+def test_hidden_matches_module_path_bf16():
+    net = _net(VARIANTS["k3_content_gate"], torch.bfloat16)
+    ids = torch.randint(0, 257, (1, 130), generator=torch.Generator().manual_seed(2)).to(DEV)
+    xn = FusedForward(net, max_position=512).hidden(ids, _ScanMix())
+    with torch.no_grad():
+        z = net._embed(ids, 0)
+        z, _ = net._run_blocks(z, None, 0, False)
+        ref = net.output_norm(z)[0]
+    assert rel(xn, ref) < 2e-2
+
+
+@pytest.mark.parametrize("graph", [False, True])
+@pytest.mark.parametrize("variant", ["k3_compete_routed", "k2_compete_magnitude_routing", "k1_modrelu_no_gsp_floor"])
+def test_batcher_fused_equals_module_path(variant, graph):
+    """Continuous batching through the packed forward (optionally replayed from a CUDA graph) yields the
+    same token ids as the module path, sequence by sequence (fp32)."""
+    net = _net(VARIANTS[variant])
+    gen = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, 257, (int(n),), generator=gen).tolist() for n in (3, 40, 25, 1, 70, 12)]
+    outs = []
+    for fused in (True, False):
+        eng = ContinuousBatcher(net, n_slots=4, cuda_graph=graph and fused, fused=fused, max_position=512)
+        assert (eng.ff is not None) == fused
+        rids = [eng.submit(p, 6) for p in prompts]
+        res = eng.run()
+        outs.append([res[r] for r in rids])
+    assert outs[0] == outs[1]
+
+
+def test_positions_beyond_the_table_are_refused():
+    net = _net(VARIANTS["k1_swish"])
+    eng = ContinuousBatcher(net, n_slots=2, max_position=16)
+    eng.submit(list(range(1, 30)), 2)
+    with pytest.raises(RuntimeError):
+        eng.run()

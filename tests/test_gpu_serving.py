@@ -12,12 +12,14 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("name", ["k1", "k3", "d64"])
-def test_batcher_matches_reference_greedy(golden_dir, name):
+def test_batcher_matches_reference_greedy(golden_dir, name, fused):
     """The golden prompt decoded inside a busy batch (other sequences joining and leaving around it)."""
     g, net = _load(golden_dir, name)
     V = net.config.vocab_size
-    eng = ContinuousBatcher(net, n_slots=3)
+    eng = ContinuousBatcher(net, n_slots=3, fused=fused)
+    assert (eng.ff is not None) == fused
     gen = torch.Generator().manual_seed(0)
     others = [torch.randint(0, V, (n,), generator=gen).tolist() for n in (5, 33, 64, 9, 17)]
     eng.submit(others[0], 3)
