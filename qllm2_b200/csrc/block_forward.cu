@@ -123,6 +123,67 @@ __global__ void __launch_bounds__(128) k_residual_cnorm(T* __restrict__ z, const
   }
 }
 
+// Few rows (a decode step): one CTA per row, one vector of 4 channels per thread, a single sweep.
+template <typename T>
+__global__ void __launch_bounds__(1024) k_residual_cnorm_row(T* __restrict__ z, const T* __restrict__ delta,
+                                                             const float* __restrict__ res_scale,
+                                                             const float* __restrict__ norm_scale,
+                                                             T* __restrict__ xn, T* __restrict__ mag_out, int D,
+                                                             float eps) {
+  __shared__ float s_part[32];
+  const int64_t row = blockIdx.x;
+  const int g = threadIdx.x, groups = D >> 2;
+  const bool on = g < groups;
+  float re[4] = {0.f, 0.f, 0.f, 0.f}, im[4] = {0.f, 0.f, 0.f, 0.f}, ss = 0.f;
+  if (on) {
+    V4<T>::ld(z + row * (int64_t)D * 2 + g * 8, re, im);
+    if (delta) {
+      const float s = res_scale ? *res_scale : 1.f;
+      float dr[4], di[4];
+      V4<T>::ld(delta + row * (int64_t)D * 2 + g * 8, dr, di);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        re[j] = fmaf(s, dr[j], re[j]);
+        im[j] = fmaf(s, di[j], im[j]);
+      }
+      V4<T>::st(z + row * (int64_t)D * 2 + g * 8, re, im);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        re[j] = rnd<T>(re[j]);
+        im[j] = rnd<T>(im[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += re[j] * re[j] + im[j] * im[j] + MAG_EPS;
+  }
+  if (!xn) return;
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += s_part[w];
+  if (!on) return;
+  const float rrms = rsqrtf(tot / (float)D + eps);
+  const float4 sc = *reinterpret_cast<const float4*>(norm_scale + g * 4);
+  const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float m = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+    const float w = m / (m + MAG_EPS) * rrms * s4[j];
+    re[j] *= w;
+    im[j] *= w;
+  }
+  V4<T>::st(xn + row * (int64_t)D * 2 + g * 8, re, im);
+  if (mag_out) {
+    T* mp = mag_out + row * (int64_t)D + g * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float r0 = rnd<T>(re[j]), i0 = rnd<T>(im[j]);
+      IO<T>::st(mp + j, sqrtf(r0 * r0 + i0 * i0 + MAG_EPS));
+    }
+  }
+}
+
 struct FrontParams {
   qpam_front_args a;
 };
@@ -246,6 +307,16 @@ extern "C" int qpam_residual_cnorm_fwd(void* z, const void* delta, const float* 
   QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && D > 0 && D % 4 == 0, "residual_cnorm: D must be a multiple of 4 (got %d)", D);
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  if (N <= 148 * 8 && D <= 4096) {  // few rows: a CTA per row keeps every SM busy
+    const int threads = (D / 4 + 31) / 32 * 32;
+    if (dtype == QPAM_F32)
+      k_residual_cnorm_row<float><<<(unsigned)N, threads, 0, st>>>((float*)z, (const float*)delta, res_scale, norm_scale, (float*)xn, (float*)mag, D, eps);
+    else
+      k_residual_cnorm_row<__nv_bfloat16><<<(unsigned)N, threads, 0, st>>>((__nv_bfloat16*)z, (const __nv_bfloat16*)delta, res_scale, norm_scale,
+                                                                            (__nv_bfloat16*)xn, (__nv_bfloat16*)mag, D, eps);
+    QPAM_LAUNCH_CHECK("k_residual_cnorm_row");
+    return QPAM_OK;
+  }
   const int blocks = (int)std::min<int64_t>((N + 3) / 4, 148 * 8);
   if (dtype == QPAM_F32)
     k_residual_cnorm<float><<<blocks, 128, 0, st>>>((float*)z, (const float*)delta, res_scale, norm_scale, (float*)xn, (float*)mag, N, D, eps);

@@ -71,6 +71,18 @@ def test_hidden_and_head_match_module_path_fp32(variant):
     assert torch.equal(ff.greedy_next(lm), net.greedy_next(ref_lm))
 
 
+def test_long_prefill_uses_the_many_row_kernels():
+    """More rows than one CTA per row covers (the warp-per-row sweep of the residual+norm kernel)."""
+    net = _net(dict(VARIANTS["k3_compete_routed"], max_seq_len=2048))
+    ids = torch.randint(0, 257, (1, 1500), generator=torch.Generator().manual_seed(3)).to(DEV)
+    xn = FusedForward(net, max_position=2048).hidden(ids, _ScanMix())
+    with torch.no_grad():
+        z = net._embed(ids, 0)
+        z, _ = net._run_blocks(z, None, 0, False)
+        ref = net.output_norm(z)[0]
+    assert rel(xn, ref) < 1e-4
+
+
 def test_hidden_matches_module_path_bf16():
     net = _net(VARIANTS["k3_content_gate"], torch.bfloat16)
     ids = torch.randint(0, 257, (1, 130), generator=torch.Generator().manual_seed(2)).to(DEV)
