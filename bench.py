@@ -407,7 +407,7 @@ def side_measurements(dev, peaks):
     del h, w, t
     torch.cuda.empty_cache()
     out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
-    out["continuous_decode"] = continuous_decode(dev)
+    out["continuous_decode"] = continuous_decode(dev, peaks)
     torch.cuda.empty_cache()
     out["train_step_config3"] = train_step(dev, time_ms)
     return out
@@ -465,8 +465,13 @@ def packed_prefill(dev, peaks, time_ms):
                       "inputs drawn on the device"}
 
 
-def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=1024):
-    """Continuous-batching greedy decode through the 12-block model of config 5 (bounded sample)."""
+def continuous_decode(dev, peaks, n_seq=512, n_slots=256, new_tokens=32, max_prompt=1024):
+    """Continuous-batching greedy decode through the 12-block model of config 5: 256 state slots, a bounded
+    sample of the 2048-prompt job (512 prompts of 32..1024 tokens, 32 new tokens each).  Three engines:
+    packed weights + fused block kernels replayed from one CUDA graph (the product path), the same without
+    the graph, and the module path (`V11Block` operators).  `steady_decode_tokens_per_s` is the decode step
+    alone with every slot busy; its roofline counts the state pool read+written once per layer and every
+    weight read once per step."""
     from qllm2_b200 import model as M, synthetic
     from qllm2_b200.serving import ContinuousBatcher
     torch.manual_seed(0)
@@ -475,8 +480,9 @@ def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=102
     net = M.V11LM(cfg).to(dev).bfloat16().eval()
     prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
     out = {}
-    for mode in ("graph", "eager"):
-        eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, cuda_graph=(mode == "graph"))
+    for mode, kw in (("fused_graph", dict(cuda_graph=True, fused=True)), ("fused", dict(cuda_graph=False, fused=True)),
+                     ("modules", dict(cuda_graph=False, fused=False))):
+        eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, **kw)
         for p_ in prompts:
             eng.submit(p_.tolist(), new_tokens)
         torch.cuda.synchronize()
@@ -485,10 +491,10 @@ def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=102
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         gen_tokens = sum(len(v_) for v_ in res.values())
-        out[mode] = {"generated_tokens": gen_tokens, "seconds": dt, "decode_tokens_per_s": gen_tokens / dt,
+        out[mode] = {"generated_tokens": gen_tokens, "seconds": dt, "tokens_per_s_incl_prefill": gen_tokens / dt,
                      "engine_steps": eng.steps}
-        if mode == "graph" and eng._graph is not None:
-            # the decode step alone, every slot busy: replay the captured step on idle rows re-pointed at slots
+        if eng._graph is not None:
+            # the decode step alone, every slot busy: replay the captured step with all rows pointed at slots
             eng._g_slots.copy_(torch.arange(n_slots, dtype=torch.int32, device=dev))
             for _ in range(3):
                 eng._graph.replay()
@@ -499,12 +505,18 @@ def continuous_decode(dev, n_seq=256, n_slots=128, new_tokens=32, max_prompt=102
             e1.record()
             torch.cuda.synchronize()
             ms = e0.elapsed_time(e1) / 20
-            out[mode]["decode_step_ms"] = ms
-            out[mode]["steady_decode_tokens_per_s"] = n_slots / ms * 1e3
+            state_bytes = 2 * eng.pool.numel() * eng.pool.element_size()
+            weight_bytes = sum(t.numel() * t.element_size() for L_ in eng.ff.layers
+                               for t in (L_.w_gu, L_.w_down, L_.w_front, L_.w_o)) + eng.ff.w_vocab.numel() * 2
+            out[mode].update({"decode_step_ms": ms, "steady_decode_tokens_per_s": n_slots / ms * 1e3,
+                              "state_bytes_per_step": state_bytes, "weight_bytes_per_step": weight_bytes,
+                              "achieved_gbs": (state_bytes + weight_bytes) / ms / 1e6,
+                              "frac_of_hbm_peak": (state_bytes + weight_bytes) / ms / 1e6 / peaks["hbm"]})
+        del eng
+        torch.cuda.empty_cache()
     out["prompt_tokens"] = int(sum(len(p_) for p_ in prompts))
     out["config"] = (f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
-                     f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init; wall time includes the packed prefills; "
-                     f"graph = decode step replayed from one CUDA graph, eager = the Python layer loop")
+                     f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init")
     return out
 
 
