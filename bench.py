@@ -170,8 +170,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / CE side measurements")
+    ap.add_argument("--only-elementwise", action="store_true",
+                    help="run only the element-wise block kernels at the config-3 layer shape and print their line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.only_elementwise:
+        torch.cuda.set_device(0)
+        print(json.dumps({"elementwise_kernels": elementwise_kernels(torch.device("cuda:0"), load_peaks())}))
+        return
     if args.impl == "reference":
         run_reference(args)
         return
@@ -407,6 +413,7 @@ def side_measurements(dev, peaks):
     del h, w, t
     torch.cuda.empty_cache()
     out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
+    out["elementwise_kernels"] = elementwise_kernels(dev, peaks)
     out["continuous_decode"] = continuous_decode(dev, peaks)
     torch.cuda.empty_cache()
     out["train_step_config3"] = train_step(dev, time_ms)
@@ -438,6 +445,99 @@ def train_step(dev, time_ms, B=8, T=2048):
     return {"ms_per_step": ms, "tokens_per_s": B * T / ms * 1e3, "loss": float(last[0].detach()),
             "params": sum(p_.numel() for p_ in net.parameters()),
             "config": f"B={B} T={T}, 8 blocks, dim 384, H6 d64 K3, vocab 50261, bf16 autocast, fwd+loss+bwd, no optimizer step"}
+
+
+def elementwise_kernels(dev, peaks, N=16384, D=384, expand=3, H=6, d=64, K=3):
+    """The element-wise block kernels at the layer shape of config 3 (B*T = 16384 rows, dim 384, hidden 1152,
+    bf16 activations): one launch each, CUDA events, against the HBM roofline with algorithmic bytes =
+    every input row read once + every output row written once.  Inputs rotate over 3 sets (> L2 together)."""
+    from qllm2_b200 import fused_elementwise as FE
+    from qllm2_b200.model import build_rope_cache
+    g = torch.Generator().manual_seed(0)
+    C = D * expand
+    bf = torch.bfloat16
+
+    def rnd(*shape, dtype=bf):
+        return torch.randn(*shape, generator=g).to(dev).to(dtype)
+
+    sets = []
+    for _ in range(3):
+        sets.append(dict(z=rnd(N, D, 2, dtype=torch.float32), zc=rnd(N, C, 2), up=rnd(N, C, 2), dz=rnd(N, D, 2),
+                         dc=rnd(N, C, 2), qkv=rnd(8, N // 8, 3 * H * d, 2), omp=torch.rand(8, N // 8, H, generator=g).to(dev),
+                         ys=[rnd(8, H, N // 8, d, 2) for _ in range(K)], coef=rnd(K, 8, H, N // 8, 2, dtype=torch.float32),
+                         dq=[rnd(8, H, N // 8, d, 2) for _ in range(3)]))
+    scale = torch.ones(D, device=dev, requires_grad=True)
+    bias = torch.zeros(C, device=dev, requires_grad=True)
+    beta = torch.ones(C, device=dev, requires_grad=True)
+    rope = build_rope_cache(N // 8, d).to(dev)
+    TD, TC = N * D * 2, N * C * 2          # scalars per [N,D,2] / [N,C,2] tensor
+    TQ = N * H * d * 2
+    def leaf(t):
+        return t.detach().requires_grad_(True)
+
+    def c_norm(s_):
+        z = leaf(s_["z"])
+        return FE._ComplexNormFn.apply(z, scale, 1e-6, bf), [z, scale]
+
+    def c_swish(s_):
+        z = leaf(s_["zc"])
+        return FE.fused_mod_swish(z, bias, beta), [z, bias, beta]
+
+    def c_gate(s_):
+        a_, b_ = leaf(s_["zc"]), leaf(s_["up"])
+        return FE.fused_cgu_gate(a_, b_), [a_, b_]
+
+    def c_prep(s_):
+        a_, b_ = leaf(s_["qkv"]), leaf(s_["omp"])
+        return FE.pam_prep(a_, rope, b_, n_heads=H, head_dim=d), [a_, b_]
+
+    def c_comb(s_):
+        c_, ys_ = leaf(s_["coef"]), [leaf(y) for y in s_["ys"]]
+        return FE.state_combine(c_, ys_), [c_] + ys_
+
+    cases = {
+        # name: (forward(set) -> (outputs, inputs), upstream grads(set), forward bytes, backward bytes)
+        "cnorm(f32->bf16)": (c_norm, lambda s_: s_["dz"], TD * 4 + TD * 2, TD * 4 + TD * 2 + TD * 4),
+        "mod_swish": (c_swish, lambda s_: s_["dc"], 2 * TC * 2, 3 * TC * 2),
+        "cgu_gate": (c_gate, lambda s_: s_["dc"], 3 * TC * 2, 5 * TC * 2),
+        "pam_prep": (c_prep, lambda s_: s_["dq"], 6 * TQ * 2, 9 * TQ * 2),
+        "state_combine(K=3)": (c_comb, lambda s_: s_["dq"][0], (K + 1) * TQ * 2, (2 * K + 1) * TQ * 2),
+    }
+    out = {}
+    for name, (fwd, up, fbytes, bbytes) in cases.items():
+        def run_f(i):
+            return fwd(sets[i % 3])
+        for i in range(3):
+            run_f(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.no_grad():
+            torch.cuda._sleep(20_000_000)     # the host queues the launches behind this, so they run back to back
+            e0.record()
+            for i in range(12):
+                run_f(i)
+            e1.record()
+        torch.cuda.synchronize()
+        fms = e0.elapsed_time(e1) / 12
+        # backward: build the graphs first (one more for a warm-up), then time only the backward calls
+        y0, ins0 = run_f(0)
+        g0 = up(sets[0])
+        torch.autograd.grad(list(y0) if isinstance(y0, tuple) else [y0], ins0, list(g0) if isinstance(g0, list) else [g0])
+        built = [run_f(i) for i in range(12)]
+        torch.cuda.synchronize()
+        torch.cuda._sleep(40_000_000)
+        e0.record()
+        for i, (y, ins) in enumerate(built):
+            gsrc = up(sets[i % 3])
+            torch.autograd.grad(list(y) if isinstance(y, tuple) else [y], ins,
+                                list(gsrc) if isinstance(gsrc, list) else [gsrc])
+        e1.record()
+        torch.cuda.synchronize()
+        bms = e0.elapsed_time(e1) / 12
+        out[name] = {"fwd_ms": fms, "fwd_gbs": fbytes / fms / 1e6, "fwd_frac_of_hbm_peak": fbytes / fms / 1e6 / peaks["hbm"],
+                     "bwd_ms": bms, "bwd_gbs": bbytes / bms / 1e6, "bwd_frac_of_hbm_peak": bbytes / bms / 1e6 / peaks["hbm"]}
+    out["config"] = f"N={N} rows, dim {D}, hidden {C}, H={H} d={d} K={K}, bf16 activations; backward time includes the small torch sums of parameter-gradient partials"
+    return out
 
 
 def packed_prefill(dev, peaks, time_ms):

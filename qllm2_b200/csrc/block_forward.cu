@@ -26,7 +26,7 @@ template <>
 __device__ __forceinline__ float rnd<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 template <typename T, bool SWISH>
-__global__ void __launch_bounds__(256) k_act_gate_packed(const T* __restrict__ gu, int64_t ld,
+__global__ void __launch_bounds__(512) k_act_gate_packed(const T* __restrict__ gu, int64_t ld,
                                                          const float* __restrict__ bias,
                                                          const float* __restrict__ beta, T* __restrict__ out,
                                                          int64_t N, int C) {
@@ -38,17 +38,18 @@ __global__ void __launch_bounds__(256) k_act_gate_packed(const T* __restrict__ g
     b4[j] = bias[g * 4 + j];
     be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
   }
+#pragma unroll 2
   for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
     float ar[4], ai[4], ur[4], ui[4];
     V4<T>::ld(gu + row * ld + g * 8, ar, ai);
     V4<T>::ld(gu + row * ld + 2 * C + g * 8, ur, ui);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float um = sqrtf(ur[j] * ur[j] + ui[j] * ui[j] + MAG_EPS);
+      const float um = fsqrt_(ur[j] * ur[j] + ui[j] * ui[j] + MAG_EPS);
       const float act = SWISH ? um * sigmoidf_(be4[j] * um + b4[j]) : fmaxf(um + b4[j], 0.f);
-      const float f = act / (um + MAG_EPS);
-      const float gm = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float h = sigmoidf_(gm) / (gm + MAG_EPS) * f;
+      const float f = act * frcp_(um + MAG_EPS);
+      const float gm = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float h = sigmoidf_(gm) * frcp_(gm + MAG_EPS) * f;
       const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
       ar[j] = pr * h;
       ai[j] = pi * h;
@@ -103,8 +104,8 @@ __global__ void __launch_bounds__(128) k_residual_cnorm(T* __restrict__ z, const
       const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float m = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-        const float w = m / (m + MAG_EPS) * rrms * s4[j];
+        const float m = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+        const float w = m * frcp_(m + MAG_EPS) * rrms * s4[j];
         re[j] *= w;
         im[j] *= w;
       }
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(128) k_residual_cnorm(T* __restrict__ z, const
 #pragma unroll
         for (int j = 0; j < 4; ++j) {  // magnitude of the stored (rounded) values
           const float r0 = rnd<T>(re[j]), i0 = rnd<T>(im[j]);
-          mg[j] = sqrtf(r0 * r0 + i0 * i0 + MAG_EPS);
+          mg[j] = fsqrt_(r0 * r0 + i0 * i0 + MAG_EPS);
         }
         T* mp = mag_out + row * (int64_t)D + g * 4;
 #pragma unroll
@@ -168,8 +169,8 @@ __global__ void __launch_bounds__(1024) k_residual_cnorm_row(T* __restrict__ z, 
   const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float m = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-    const float w = m / (m + MAG_EPS) * rrms * s4[j];
+    const float m = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+    const float w = m * frcp_(m + MAG_EPS) * rrms * s4[j];
     re[j] *= w;
     im[j] *= w;
   }
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(1024) k_residual_cnorm_row(T* __restrict__ z, 
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float r0 = rnd<T>(re[j]), i0 = rnd<T>(im[j]);
-      IO<T>::st(mp + j, sqrtf(r0 * r0 + i0 * i0 + MAG_EPS));
+      IO<T>::st(mp + j, fsqrt_(r0 * r0 + i0 * i0 + MAG_EPS));
     }
   }
 }
@@ -189,7 +190,7 @@ struct FrontParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256) k_pam_front(FrontParams fp) {
+__global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
   const qpam_front_args& a = fp.a;
   __shared__ float s_keep[64];
   const int H = a.H, K = a.K, d = a.d;
@@ -287,8 +288,8 @@ extern "C" int qpam_act_gate_packed_fwd(const void* gate_up, int64_t ld, int32_t
                "act_gate_packed: the row stride must cover 4*C scalars and keep rows 16-byte aligned");
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, (unsigned)std::min<int64_t>(N, std::max(1, (148 * 8) / xb)));
+  const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, (unsigned)std::min<int64_t>(N, std::max(1, (148 * 2048) / (xb * threads))));
 #define QPAM_AG(T)                                                                                                  \
   if (beta) k_act_gate_packed<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C); \
   else k_act_gate_packed<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C);
@@ -342,7 +343,7 @@ extern "C" int qpam_pam_front_fwd(const qpam_front_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   FrontParams fp{*a};
   const int per_tok = 3 * a->H * (a->d / 4);
-  const int threads = std::min(256, (per_tok + 31) / 32 * 32);
+  const int threads = pick_threads(per_tok);
   const int grid = (int)std::min<int64_t>((int64_t)a->B * a->T, 148 * 16);
   if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp);
   else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp);

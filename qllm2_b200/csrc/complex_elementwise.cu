@@ -54,8 +54,8 @@ __global__ void __launch_bounds__(128) k_cnorm_fwd(const TI* __restrict__ z, con
         float orr[4], oi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mag = sqrtf(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
-          const float w = mag / (mag + MAG_EPS) * rrms * s4[j];
+          const float mag = fsqrt_(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
+          const float w = mag * frcp_(mag + MAG_EPS) * rrms * s4[j];
           orr[j] = re[cv][j] * w;
           oi[j] = im[cv][j] * w;
         }
@@ -97,9 +97,9 @@ __global__ void __launch_bounds__(128) k_cnorm_bwd(const TI* __restrict__ z, con
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float m2 = re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS;
-          const float mag = sqrtf(m2);
+          const float mag = fsqrt_(m2);
           ss += m2;
-          cs += (gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j]) * s4[j] * (mag / (mag + MAG_EPS));
+          cs += (gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j]) * s4[j] * (mag * frcp_(mag + MAG_EPS));
         }
       }
     }
@@ -121,12 +121,12 @@ __global__ void __launch_bounds__(128) k_cnorm_bwd(const TI* __restrict__ z, con
         float orr[4], oi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mag = sqrtf(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
-          const float inv = 1.f / (mag + MAG_EPS);
+          const float mag = fsqrt_(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
+          const float inv = frcp_(mag + MAG_EPS);
           const float m = mag * inv;
           const float s = gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j];
           const float w = m * rrms * s4[j];
-          const float k = s * s4[j] * MAG_EPS * rrms * inv * inv / mag - common;
+          const float k = s * s4[j] * MAG_EPS * rrms * inv * inv * frcp_(mag) - common;
           orr[j] = gr[cv][j] * w + re[cv][j] * k;
           oi[j] = gi[cv][j] * w + im[cv][j] * k;
           acc[v][j] += s * m * rrms;
@@ -172,7 +172,7 @@ int cnorm_launch(bool bwd, const void* z, const float* scale, const void* dout_o
 // A thread owns one group of 4 channels and walks rows blockIdx.y, blockIdx.y + gridDim.y, ...
 // ------------------------------------------------------------------------------------------------
 template <typename T, bool SWISH>
-__global__ void __launch_bounds__(256) k_modact_fwd(const T* __restrict__ z, const float* __restrict__ bias,
+__global__ void __launch_bounds__(512) k_modact_fwd(const T* __restrict__ z, const float* __restrict__ bias,
                                                     const float* __restrict__ beta, T* __restrict__ out,
                                                     int64_t N, int C) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
@@ -183,14 +183,15 @@ __global__ void __launch_bounds__(256) k_modact_fwd(const T* __restrict__ z, con
     b4[j] = bias[g * 4 + j];
     be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
   }
+#pragma unroll 2
   for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
     float re[4], im[4];
     V4<T>::ld(z + (row * C + g * 4) * 2, re, im);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+      const float mag = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
       const float act = SWISH ? mag * sigmoidf_(be4[j] * mag + b4[j]) : fmaxf(mag + b4[j], 0.f);
-      const float f = act / (mag + MAG_EPS);
+      const float f = act * frcp_(mag + MAG_EPS);
       re[j] *= f;
       im[j] *= f;
     }
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(256) k_modact_fwd(const T* __restrict__ z, con
 
 // out = z f(|z|):  dz = dout f + z s f'(|z|) / |z|,  s = Re(conj(z) dout).
 template <typename T, bool SWISH>
-__global__ void __launch_bounds__(256) k_modact_bwd(const T* __restrict__ z, const float* __restrict__ bias,
+__global__ void __launch_bounds__(512) k_modact_bwd(const T* __restrict__ z, const float* __restrict__ bias,
                                                     const float* __restrict__ beta, const T* __restrict__ dout,
                                                     T* __restrict__ dz, float* __restrict__ dbias_part,
                                                     float* __restrict__ dbeta_part, int64_t N, int C) {
@@ -212,14 +213,15 @@ __global__ void __launch_bounds__(256) k_modact_bwd(const T* __restrict__ z, con
     b4[j] = bias[g * 4 + j];
     be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
   }
+#pragma unroll 2
   for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
     float re[4], im[4], gr[4], gi[4];
     V4<T>::ld(z + (row * C + g * 4) * 2, re, im);
     V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = sqrtf(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-      const float inv = 1.f / (mag + MAG_EPS);
+      const float mag = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+      const float inv = frcp_(mag + MAG_EPS);
       const float s = gr[j] * re[j] + gi[j] * im[j];
       float act, dact;  // act(|z|) and its derivative
       if (SWISH) {
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(256) k_modact_bwd(const T* __restrict__ z, con
         ab[j] += on ? s * inv : 0.f;
       }
       const float f = act * inv;
-      const float k = s * (dact * inv - act * inv * inv) / mag;
+      const float k = s * (dact * inv - act * inv * inv) * frcp_(mag);
       const float r0 = re[j], i0 = im[j];
       re[j] = gr[j] * f + r0 * k;
       im[j] = gi[j] * f + i0 * k;
@@ -256,19 +258,20 @@ __global__ void __launch_bounds__(256) k_modact_bwd(const T* __restrict__ z, con
 // gate / up / dgate / dup rows may sit inside wider matrices: ld_* are row strides in scalars.
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) k_cgu_gate_fwd(const T* __restrict__ gate, int64_t ld_gate,
+__global__ void __launch_bounds__(512) k_cgu_gate_fwd(const T* __restrict__ gate, int64_t ld_gate,
                                                       const T* __restrict__ up, int64_t ld_up,
                                                       T* __restrict__ out, int64_t N, int C) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= (C >> 2)) return;
+#pragma unroll 2
   for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
     float ar[4], ai[4], ur[4], ui[4];
     V4<T>::ld(gate + row * ld_gate + g * 8, ar, ai);
     V4<T>::ld(up + row * ld_up + g * 8, ur, ui);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float h = sigmoidf_(mag) / (mag + MAG_EPS);
+      const float mag = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float h = sigmoidf_(mag) * frcp_(mag + MAG_EPS);
       const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
       ar[j] = pr * h;
       ai[j] = pi * h;
@@ -278,13 +281,14 @@ __global__ void __launch_bounds__(256) k_cgu_gate_fwd(const T* __restrict__ gate
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) k_cgu_gate_bwd(const T* __restrict__ gate, int64_t ld_gate,
+__global__ void __launch_bounds__(512) k_cgu_gate_bwd(const T* __restrict__ gate, int64_t ld_gate,
                                                       const T* __restrict__ up, int64_t ld_up,
                                                       const T* __restrict__ dout, T* __restrict__ dgate,
                                                       int64_t ld_dgate, T* __restrict__ dup, int64_t ld_dup,
                                                       int64_t N, int C) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= (C >> 2)) return;
+#pragma unroll 2
   for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
     float ar[4], ai[4], ur[4], ui[4], gr[4], gi[4], dur[4], dui[4];
     V4<T>::ld(gate + row * ld_gate + g * 8, ar, ai);
@@ -292,8 +296,8 @@ __global__ void __launch_bounds__(256) k_cgu_gate_bwd(const T* __restrict__ gate
     V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = sqrtf(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float inv = 1.f / (mag + MAG_EPS);
+      const float mag = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
+      const float inv = frcp_(mag + MAG_EPS);
       const float sg = sigmoidf_(mag);
       const float h = sg * inv;
       const float dh = sg * (1.f - sg) * inv - sg * inv * inv;
@@ -302,7 +306,7 @@ __global__ void __launch_bounds__(256) k_cgu_gate_bwd(const T* __restrict__ gate
       // d(up) = conj(gate) dout h ;  d(gate) = conj(up) dout h + gate s h'(|gate|) / |gate|
       dur[j] = h * (ar[j] * gr[j] + ai[j] * gi[j]);
       dui[j] = h * (ar[j] * gi[j] - ai[j] * gr[j]);
-      const float k = s * dh / mag;
+      const float k = s * dh * frcp_(mag);
       const float dgr = h * (ur[j] * gr[j] + ui[j] * gi[j]) + ar[j] * k;
       const float dgi = h * (ur[j] * gi[j] - ui[j] * gr[j]) + ai[j] * k;
       ar[j] = dgr;
@@ -332,64 +336,95 @@ struct PrepParams {
   int B, T, H, d;
 };
 
+constexpr int PREP_U = 2;  // tokens in flight per thread: all their loads are issued before any arithmetic or store
+
+// A thread owns one (head, group of 4 channels) and moves q, k and v of it (the rotary factors are shared by
+// q and k); d/4 consecutive lanes cover a head, so d(omp) is a shuffle sum.
 template <typename T, bool BWD>
-__global__ void __launch_bounds__(256) k_pam_prep(PrepParams p) {
+__global__ void __launch_bounds__(512) k_pam_prep(PrepParams p) {
   const int gph = p.d >> 2;
-  const int per_tok = 3 * p.H * gph;
+  const int per_tok = p.H * gph;
   const int per_tok_pad = (per_tok + 31) & ~31;
   const int64_t ntok = (int64_t)p.B * p.T;
-  for (int64_t tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
-    const int b = (int)(tok / p.T), t = (int)(tok - (int64_t)b * p.T);
-    int64_t pos = p.positions ? p.positions[tok] : p.offset + t;
-    pos = pos < 0 ? 0 : (pos >= p.rope_len ? p.rope_len - 1 : pos);
+  const int64_t ntile = (ntok + PREP_U - 1) / PREP_U;
+  const int64_t side_stride = (int64_t)p.H * p.d * 2;  // q -> k -> v inside one token of qkv
+  for (int64_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
     for (int idx = threadIdx.x; idx < per_tok_pad; idx += blockDim.x) {
-      const bool on = idx < per_tok;
-      const int which = on ? idx / (p.H * gph) : 0;
-      const int rem = on ? idx - which * p.H * gph : 0;
-      const int h = rem / gph, g = rem - h * gph;
-      const int64_t src = ((tok * 3 + which) * p.H + h) * (int64_t)p.d * 2 + g * 8;
-      const int64_t dst = (((int64_t)b * p.H + h) * p.T + t) * (int64_t)p.d * 2 + g * 8;
-      T* side = reinterpret_cast<T*>(which == 0 ? p.q : which == 1 ? p.k : p.v);
-      float re[4] = {0.f, 0.f, 0.f, 0.f}, im[4] = {0.f, 0.f, 0.f, 0.f};
-      const float keep = (which == 2 && p.omp) ? p.omp[tok * p.H + h] : 1.f;
-      float dot = 0.f;
-      if (on) {
-        if (!BWD) {
-          V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src, re, im);
-        } else {
-          V4<T>::ld(side + dst, re, im);
-          if (which == 2 && p.domp) {
-            float vr[4], vi[4];
-            V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src, vr, vi);
+      const bool lane_on = idx < per_tok;
+      const int h = lane_on ? idx / gph : 0, g = lane_on ? idx - h * gph : 0;
+      float re[PREP_U][3][4], im[PREP_U][3][4], vr[PREP_U][4], vi[PREP_U][4], keep[PREP_U];
+      float4 c0[PREP_U], c1[PREP_U];
+      int64_t src[PREP_U], dst[PREP_U];
+      bool on[PREP_U];
+      // ---- all loads first
 #pragma unroll
-            for (int j = 0; j < 4; ++j) dot += vr[j] * re[j] + vi[j] * im[j];
+      for (int u = 0; u < PREP_U; ++u) {
+        const int64_t tok = tile * PREP_U + u;
+        on[u] = lane_on && tok < ntok;
+        const int64_t tk = on[u] ? tok : 0;
+        const int b = (int)(tk / p.T), t = (int)(tk - (int64_t)b * p.T);
+        src[u] = (tk * 3 * p.H + h) * (int64_t)p.d * 2 + g * 8;
+        dst[u] = (((int64_t)b * p.H + h) * p.T + t) * (int64_t)p.d * 2 + g * 8;
+        keep[u] = 1.f;
+        c0[u] = c1[u] = make_float4(1.f, 0.f, 1.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          vr[u][j] = vi[u][j] = 0.f;
+#pragma unroll
+          for (int w = 0; w < 3; ++w) re[u][w][j] = im[u][w][j] = 0.f;
+        }
+        if (on[u]) {
+          if (!BWD) {
+#pragma unroll
+            for (int w = 0; w < 3; ++w) V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src[u] + w * side_stride, re[u][w], im[u][w]);
+          } else {
+            V4<T>::ld(reinterpret_cast<const T*>(p.q) + dst[u], re[u][0], im[u][0]);
+            V4<T>::ld(reinterpret_cast<const T*>(p.k) + dst[u], re[u][1], im[u][1]);
+            V4<T>::ld(reinterpret_cast<const T*>(p.v) + dst[u], re[u][2], im[u][2]);
+            if (p.domp) V4<T>::ld(reinterpret_cast<const T*>(p.qkv) + src[u] + 2 * side_stride, vr[u], vi[u]);
+          }
+          if (p.omp) keep[u] = p.omp[tk * p.H + h];
+          if (p.rope) {
+            int64_t pos = p.positions ? p.positions[tk] : p.offset + t;
+            pos = pos < 0 ? 0 : (pos >= p.rope_len ? p.rope_len - 1 : pos);
+            c0[u] = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2);
+            c1[u] = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2 + 4);
           }
         }
-        if (which < 2 && p.rope) {
-          const float4 c0 = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2);
-          const float4 c1 = *reinterpret_cast<const float4*>(p.rope + (pos * p.d + g * 4) * 2 + 4);
-          const float cs[4] = {c0.x, c0.z, c1.x, c1.z};
-          const float sn[4] = {c0.y, c0.w, c1.y, c1.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float s_ = BWD ? -sn[j] : sn[j];  // the gradient rotates back
-            const float r0 = re[j], i0 = im[j];
-            re[j] = r0 * cs[j] - i0 * s_;
-            im[j] = r0 * s_ + i0 * cs[j];
-          }
-        } else if (which == 2) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            re[j] *= keep;
-            im[j] *= keep;
-          }
-        }
-        if (!BWD) V4<T>::st(side + dst, re, im);
-        else V4<T>::st(reinterpret_cast<T*>(p.dqkv) + src, re, im);
       }
-      if (BWD && p.domp) {  // sum over the head's channels: gph consecutive lanes (gph divides 32)
-        for (int o = gph >> 1; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (on && which == 2 && g == 0) p.domp[tok * p.H + h] = dot;
+      // ---- arithmetic and stores
+#pragma unroll
+      for (int u = 0; u < PREP_U; ++u) {
+        float dot = 0.f;
+        if (on[u]) {
+          const float cs[4] = {c0[u].x, c0[u].z, c1[u].x, c1[u].z};
+          const float sn[4] = {c0[u].y, c0[u].w, c1[u].y, c1[u].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            dot += vr[u][j] * re[u][2][j] + vi[u][j] * im[u][2][j];
+            const float s_ = BWD ? -sn[j] : sn[j];  // the gradient rotates back
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+              const float r0 = re[u][w][j], i0 = im[u][w][j];
+              re[u][w][j] = r0 * cs[j] - i0 * s_;
+              im[u][w][j] = r0 * s_ + i0 * cs[j];
+            }
+            re[u][2][j] *= keep[u];
+            im[u][2][j] *= keep[u];
+          }
+          if (!BWD) {
+            V4<T>::st(reinterpret_cast<T*>(p.q) + dst[u], re[u][0], im[u][0]);
+            V4<T>::st(reinterpret_cast<T*>(p.k) + dst[u], re[u][1], im[u][1]);
+            V4<T>::st(reinterpret_cast<T*>(p.v) + dst[u], re[u][2], im[u][2]);
+          } else {
+#pragma unroll
+            for (int w = 0; w < 3; ++w) V4<T>::st(reinterpret_cast<T*>(p.dqkv) + src[u] + w * side_stride, re[u][w], im[u][w]);
+          }
+        }
+        if (BWD && p.domp) {  // sum over the head's channels: gph consecutive lanes (gph divides 32)
+          for (int o = gph >> 1; o; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+          if (on[u] && g == 0) p.domp[(tile * PREP_U + u) * p.H + h] = dot;
+        }
       }
     }
   }
@@ -456,8 +491,8 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
   }
 }
 
-inline int act_grid_y(int64_t N, int xblocks, int P) {
-  int64_t y = P > 0 ? P : std::max<int64_t>(1, (148 * 8) / xblocks);
+inline int act_grid_y(int64_t N, int xblocks, int threads) {  // enough rows in flight to fill every SM's thread slots
+  const int64_t y = std::max<int64_t>(1, (148 * 2048) / ((int64_t)xblocks * threads));
   return (int)std::min<int64_t>(std::min<int64_t>(y, N), 65535);
 }
 
@@ -500,8 +535,8 @@ extern "C" int qpam_modact_fwd(const void* z, int32_t dtype, const float* bias, 
   QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && C > 0 && C % 4 == 0, "modact_fwd: C must be a multiple of 4 (got %d)", C);
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, act_grid_y(N, xb, 0));
+  const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, threads));
 #define QPAM_ACT(T)                                                                                      \
   if (beta) k_modact_fwd<T, true><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (T*)out, N, C);     \
   else k_modact_fwd<T, false><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (T*)out, N, C);
@@ -518,7 +553,7 @@ extern "C" int qpam_modact_bwd(const void* z, int32_t dtype, const float* bias, 
   QPAM_REQUIRE(is_dtype(dtype) && N > 0 && C > 0 && C % 4 == 0, "modact_bwd: C must be a multiple of 4 (got %d)", C);
   QPAM_REQUIRE(P > 0 && P <= N && P <= 65535, "modact_bwd: partial rows must be in [1, min(N, 65535)]");
   cudaStream_t st = (cudaStream_t)stream;
-  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
+  const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
   dim3 grid(xb, P);
 #define QPAM_ACT(T)                                                                                              \
   if (beta) k_modact_bwd<T, true><<<grid, threads, 0, st>>>((const T*)z, bias, beta, (const T*)dout, (T*)dz,      \
@@ -540,8 +575,8 @@ extern "C" int qpam_cgu_gate_fwd(const void* gate, int64_t ld_gate, const void* 
                "cgu_gate_fwd: row strides must cover 2*C scalars and keep rows 16-byte aligned");
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, act_grid_y(N, xb, 0));
+  const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, threads));
   if (dtype == QPAM_F32) k_cgu_gate_fwd<float><<<grid, threads, 0, st>>>((const float*)gate, ld_gate, (const float*)up, ld_up, (float*)out, N, C);
   else k_cgu_gate_fwd<__nv_bfloat16><<<grid, threads, 0, st>>>((const __nv_bfloat16*)gate, ld_gate, (const __nv_bfloat16*)up, ld_up, (__nv_bfloat16*)out, N, C);
   QPAM_LAUNCH_CHECK("k_cgu_gate_fwd");
@@ -558,8 +593,8 @@ extern "C" int qpam_cgu_gate_bwd(const void* gate, int64_t ld_gate, const void* 
                    ld_up % al == 0 && ld_dgate % al == 0 && ld_dup % al == 0,
                "cgu_gate_bwd: row strides must cover 2*C scalars and keep rows 16-byte aligned");
   cudaStream_t st = (cudaStream_t)stream;
-  const int groups = C / 4, threads = std::min(256, (groups + 31) / 32 * 32), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, act_grid_y(N, xb, 0));
+  const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
+  dim3 grid(xb, act_grid_y(N, xb, threads));
   if (dtype == QPAM_F32)
     k_cgu_gate_bwd<float><<<grid, threads, 0, st>>>((const float*)gate, ld_gate, (const float*)up, ld_up, (const float*)dout,
                                                     (float*)dgate, ld_dgate, (float*)dup, ld_dup, N, C);
@@ -581,9 +616,9 @@ static int pam_prep(bool bwd, const void* qkv, int32_t dtype, const float* rope,
   QPAM_REQUIRE(!rope || positions || offset + T <= rope_len, "pam_prep: rotary table shorter than offset + T");
   cudaStream_t st = (cudaStream_t)stream;
   PrepParams p{qkv, rope, positions, omp, q, k, v, dqkv, (bwd && omp) ? domp : nullptr, offset, rope_len, B, T, H, d};
-  const int per_tok = 3 * H * (d / 4);
-  const int threads = std::min(256, (per_tok + 31) / 32 * 32);
-  const int grid = (int)std::min<int64_t>((int64_t)B * T, 148 * 16);
+  const int per_tok = H * (d / 4);
+  const int threads = pick_threads(per_tok);
+  const int grid = (int)std::min<int64_t>(((int64_t)B * T + PREP_U - 1) / PREP_U, (148 * 2048) / threads);
   if (dtype == QPAM_F32) {
     if (bwd) k_pam_prep<float, true><<<grid, threads, 0, st>>>(p);
     else k_pam_prep<float, false><<<grid, threads, 0, st>>>(p);

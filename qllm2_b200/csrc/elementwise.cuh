@@ -49,8 +49,21 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+// Approximate reciprocal / square root (about 2 ulp): the IEEE forms cost several times more issue slots, and
+// these kernels do ~10 of them per 8 bytes moved.
+__device__ __forceinline__ float frcp_(float x) { return __fdividef(1.f, x); }
+__device__ __forceinline__ float fsqrt_(float x) { return x * rsqrtf(x); }  // x >= 1e-8 here, never 0
+__device__ __forceinline__ float sigmoidf_(float x) { return frcp_(1.f + __expf(-x)); }
 
+// Threads per CTA for kernels whose threads each own one group of 4 channels: the largest multiple of 32
+// (up to 256) that divides the group count, so that no CTA runs mostly idle; 256 when none does.  Up to
+// 512 groups get one thread each.  Kernels launched with it declare __launch_bounds__(512).
+inline int pick_threads(int groups) {
+  if (groups <= 512) return (groups + 31) / 32 * 32;
+  for (int t = 256; t >= 64; t -= 32)
+    if (groups % t == 0) return t;
+  return 256;
+}
 inline bool is_dtype(int32_t d) { return d == QPAM_F32 || d == QPAM_BF16; }
 
 }  // namespace ew

@@ -124,8 +124,7 @@ class _ModActFn(torch.autograd.Function):
         C = z.shape[-2]
         N = z.numel() // (2 * C)
         dout = dout.to(z.dtype).contiguous()
-        xb = (C // 4 + 255) // 256
-        P = max(1, min(N, (148 * 8) // xb))
+        P = max(1, min(N, 1024))        # rows of partial parameter gradients = row partitions of the launch
         pb = torch.empty(P, C, dtype=torch.float32, device=z.device)
         pe = None if beta is None else torch.empty(P, C, dtype=torch.float32, device=z.device)
         dz = torch.empty_like(z)
