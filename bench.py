@@ -440,9 +440,30 @@ def train_step(dev, time_ms, B=8, T=2048):
             lm, aux, _ = net._hidden_to_lm(x)
         loss = net.ce_from_lm(lm.bfloat16(), y)
         loss.backward()
-        last[0] = loss
+        last[0] = loss.detach()      # keep no autograd graph alive between steps (a graph capture below needs that)
     ms = time_ms(step, 3, warm=2)
-    return {"ms_per_step": ms, "tokens_per_s": B * T / ms * 1e3, "loss": float(last[0].detach()),
+    graphed = {}
+    try:
+        # the same step captured once into a CUDA graph and replayed: what is left when the host's ~1500
+        # launches per step are taken out (gradients land in static buffers owned by the graph)
+        net.zero_grad(set_to_none=True)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        net.zero_grad(set_to_none=True)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                lm, aux, _ = net._hidden_to_lm(x)
+            gloss = net.ce_from_lm(lm.bfloat16(), y)
+            gloss.backward()
+        gms = time_ms(graph.replay, 5, warm=2)
+        graphed = {"ms_per_step_graph": gms, "tokens_per_s_graph": B * T / gms * 1e3, "loss_graph": float(gloss.detach())}
+    except Exception as exc:  # noqa: BLE001 - the eager number above stands on its own
+        graphed = {"graph_error": f"{type(exc).__name__}: {exc}"[:300]}
+    return {"ms_per_step": ms, "tokens_per_s": B * T / ms * 1e3, "loss": float(last[0]), **graphed,
             "params": sum(p_.numel() for p_ in net.parameters()),
             "config": f"B={B} T={T}, 8 blocks, dim 384, H6 d64 K3, vocab 50261, bf16 autocast, fwd+loss+bwd, no optimizer step"}
 

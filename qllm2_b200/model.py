@@ -534,7 +534,7 @@ class V11LM(nn.Module):
             a = getattr(blk.pam, "_route_aux", None)
             if a is not None:
                 total = a if total is None else total + a
-        return total if total is not None else torch.tensor(0.0, device=device)
+        return total if total is not None else torch.zeros((), device=device)
 
     def _run_blocks(self, z, states, step_offset, checkpoint):
         new_states = []
