@@ -370,7 +370,7 @@ def main():
                     "unit": r["unit"], "frac": r["frac"], "traffic": traffic, "peak_source": peaks["src"] + " burst"}
 
     extra = {}
-    if not args.no_extras and rank == 0:
+    if not args.no_extras and rank == 0 and world == 1:   # side measurements are single-GPU
         extra = side_measurements(dev, peaks)
 
     cpu = cpu_scan_baseline() if (rank == 0 and world == 1) else None
