@@ -274,6 +274,22 @@ typedef struct qpam_front_args {
 } qpam_front_args;
 int qpam_pam_front_fwd(const qpam_front_args* args, void* stream);
 
+/* Residual with a learnable scalar (V11Block.forward: x + mixed * cgu_scale, x + pam_out * pam_scale):
+ * out[i] = x[i] + scale[0] * delta[i] over n scalars (n a multiple of 4; x/out and delta may differ in
+ * dtype).  Backward: ddelta = scale[0] * dout, dscale = sum of the P partials, d(x) = dout. */
+int qpam_scaled_residual_fwd(const void* x, int32_t x_dtype, const void* delta, int32_t d_dtype,
+                             const float* scale, void* out, int64_t n, void* stream);
+int qpam_scaled_residual_bwd(const void* dout, int32_t x_dtype, const void* delta, int32_t d_dtype,
+                             const float* scale, void* ddelta, float* dscale_partials, int32_t P,
+                             int64_t n, void* stream);
+/* Real block form of a complex weight (ComplexLinear.forward, v11/complex_ops.py): w [2*out, 2*in] with
+ * rows (o,re) = (Wr, -Wi) and (o,im) = (Wi, Wr) over interleaved (j,re),(j,im) columns, so that one real GEMM
+ * on interleaved activations is the complex product.  Backward folds dw into dWr, dWi. */
+int qpam_block_weight_fwd(const void* wr, const void* wi, int32_t w_dtype, void* w, int32_t out_dtype,
+                          int32_t out_dim, int32_t in_dim, void* stream);
+int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dwr, void* dwi, int32_t w_dtype,
+                          int32_t out_dim, int32_t in_dim, void* stream);
+
 /* Read-out of K phase-routed states (v11/model.py:766-781: the sum over states weighted by
  * alpha_k e^{i phi_k}):  y[r,:] = sum_k coef[k,r] * yk[k][r,:] over R rows of d complex channels;
  * yk / dyk are HOST arrays of K device pointers, coef / dcoef fp32 [K,R,2].

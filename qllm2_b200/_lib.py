@@ -89,6 +89,11 @@ SIGNATURES = {
     "qpam_residual_cnorm_fwd": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64,
                                           c_int32, C.c_float, c_void_p]),
     "qpam_pam_front_fwd": (c_int32, [C.POINTER(FrontArgs), c_void_p]),
+    "qpam_scaled_residual_fwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_int64, c_void_p]),
+    "qpam_scaled_residual_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int32,
+                                           c_int64, c_void_p]),
+    "qpam_block_weight_fwd": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "qpam_block_weight_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

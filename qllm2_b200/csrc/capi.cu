@@ -93,14 +93,22 @@ extern "C" int qpam_profile_end(char* buf, size_t buf_bytes) {
 }
 
 namespace qpam {
+// one device status word per translation unit that waits on the device
 int ce_tc_device_status(int* value, bool clear);
+int scan_tc_device_status(int* value, bool clear);
+int decode_device_status(int* value, bool clear);
 }
 
 extern "C" int qpam_device_status(int32_t* status, int32_t clear) {
-  int v = 0;
-  int rc = qpam::ce_tc_device_status(&v, clear != 0);
-  if (rc) return rc;
-  if (status) *status = v;
+  int first = 0;
+  int (*readers[])(int*, bool) = {qpam::ce_tc_device_status, qpam::scan_tc_device_status, qpam::decode_device_status};
+  for (auto rd : readers) {
+    int v = 0;
+    const int rc = rd(&v, clear != 0);
+    if (rc) return rc;
+    if (first == 0) first = v;
+  }
+  if (status) *status = first;
   return QPAM_OK;
 }
 

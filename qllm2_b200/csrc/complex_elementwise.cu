@@ -644,6 +644,89 @@ extern "C" int qpam_pam_prep_bwd(const void* qkv, int32_t dtype, const float* ro
                   const_cast<void*>(dk), const_cast<void*>(dv), dqkv, domp, B, T, H, d, stream);
 }
 
+namespace qpam {
+namespace {
+using namespace ew;
+// ------------------------------------------------------------------------------------------------
+// Residual with a learnable scalar:  out = x + s * delta  (x, out: TX; delta: TD), backward
+// d(delta) = s * dout, d(s) = sum dout * delta (per-CTA partial sums), d(x) = dout.
+// Block weight of a complex projection:  W[(o,c),(j,c')] with (c,c') = (re,re): Wr, (re,im): -Wi,
+// (im,re): Wi, (im,im): Wr, so that interleaved y = x W^T is the complex product; and its transpose
+// map for the gradient  dWr = dW[re,re] + dW[im,im],  dWi = dW[im,re] - dW[re,im].
+// ------------------------------------------------------------------------------------------------
+template <typename TX, typename TD>
+__global__ void __launch_bounds__(256) k_scaled_residual_fwd(const TX* __restrict__ x, const TD* __restrict__ delta,
+                                                             const float* __restrict__ s, TX* __restrict__ out,
+                                                             int64_t n) {
+  const float sv = *s;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float xv[4], dv[4];
+    E4<TX>::ld(x + i, xv);
+    E4<TD>::ld(delta + i, dv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) xv[j] = fmaf(sv, dv[j], xv[j]);
+    E4<TX>::st(out + i, xv);
+  }
+}
+
+template <typename TX, typename TD>
+__global__ void __launch_bounds__(256) k_scaled_residual_bwd(const TX* __restrict__ dout, const TD* __restrict__ delta,
+                                                             const float* __restrict__ s, TD* __restrict__ ddelta,
+                                                             float* __restrict__ ds_part, int64_t n) {
+  __shared__ float red[8];
+  const float sv = *s;
+  float acc = 0.f;
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float gv[4], dv[4];
+    E4<TX>::ld(dout + i, gv);
+    E4<TD>::ld(delta + i, dv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc = fmaf(gv[j], dv[j], acc);
+      dv[j] = sv * gv[j];
+    }
+    E4<TD>::st(ddelta + i, dv);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+    ds_part[blockIdx.x] = t;
+  }
+}
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) k_block_weight_fwd(const TW* __restrict__ wr, const TW* __restrict__ wi,
+                                                          TO* __restrict__ w, int out_dim, int in_dim) {
+  const int64_t n = (int64_t)out_dim * in_dim;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t o = i / in_dim, j = i - o * in_dim;
+    const float a = IO<TW>::ld(wr + i), b = IO<TW>::ld(wi + i);
+    TO* r0 = w + (2 * o) * (int64_t)(2 * in_dim) + 2 * j;       // row (o, re)
+    TO* r1 = r0 + 2 * in_dim;                                   // row (o, im)
+    IO<TO>::st2(r0, make_float2(a, -b));
+    IO<TO>::st2(r1, make_float2(b, a));
+  }
+}
+
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) k_block_weight_bwd(const TO* __restrict__ dw, TW* __restrict__ dwr,
+                                                          TW* __restrict__ dwi, int out_dim, int in_dim) {
+  const int64_t n = (int64_t)out_dim * in_dim;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t o = i / in_dim, j = i - o * in_dim;
+    const TO* r0 = dw + (2 * o) * (int64_t)(2 * in_dim) + 2 * j;
+    const float2 a = IO<TO>::ld2(r0), b = IO<TO>::ld2(r0 + 2 * in_dim);
+    IO<TW>::st(dwr + i, a.x + b.y);
+    IO<TW>::st(dwi + i, b.x - a.y);
+  }
+}
+
+}  // namespace
+}  // namespace qpam
+
 static int state_combine(bool bwd, const void* const* yk, void* const* dyk, const float* coef, void* y, float* dcoef,
                          int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream) {
   QPAM_REQUIRE(yk && coef && y && (!bwd || (dyk && dcoef)), "state_combine: NULL pointer argument");
@@ -679,4 +762,78 @@ extern "C" int qpam_state_combine_fwd(const void* const* yk, const float* coef, 
 extern "C" int qpam_state_combine_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
                                       float* dcoef, int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream) {
   return state_combine(true, yk, dyk, coef, const_cast<void*>(dy), dcoef, dtype, K, R, d, stream);
+}
+
+template <typename TX, typename TD>
+static int scaled_residual(bool bwd, const void* x_or_dout, const void* delta, const float* s, void* out_or_ddelta,
+                           float* ds_part, int32_t P, int64_t n, cudaStream_t st) {
+  if (!bwd) {
+    const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256 + 1, 148 * 8);
+    k_scaled_residual_fwd<TX, TD><<<grid, 256, 0, st>>>((const TX*)x_or_dout, (const TD*)delta, s, (TX*)out_or_ddelta, n);
+    QPAM_LAUNCH_CHECK("k_scaled_residual_fwd");
+  } else {
+    k_scaled_residual_bwd<TX, TD><<<P, 256, 0, st>>>((const TX*)x_or_dout, (const TD*)delta, s, (TD*)out_or_ddelta, ds_part, n);
+    QPAM_LAUNCH_CHECK("k_scaled_residual_bwd");
+  }
+  return QPAM_OK;
+}
+
+extern "C" int qpam_scaled_residual_fwd(const void* x, int32_t x_dtype, const void* delta, int32_t d_dtype,
+                                        const float* scale, void* out, int64_t n, void* stream) {
+  QPAM_REQUIRE(x && delta && scale && out, "scaled_residual_fwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(x_dtype) && is_dtype(d_dtype) && n >= 0 && n % 4 == 0, "scaled_residual_fwd: bad dtype, or a size that is not a multiple of 4");
+  if (n == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+#define QPAM_SR_F(TX, TD) scaled_residual<TX, TD>(false, x, delta, scale, out, nullptr, 0, n, st)
+  if (x_dtype == QPAM_F32 && d_dtype == QPAM_F32) return QPAM_SR_F(float, float);
+  if (x_dtype == QPAM_F32) return QPAM_SR_F(float, __nv_bfloat16);
+  if (d_dtype == QPAM_BF16) return QPAM_SR_F(__nv_bfloat16, __nv_bfloat16);
+  return QPAM_SR_F(__nv_bfloat16, float);
+#undef QPAM_SR_F
+}
+
+extern "C" int qpam_scaled_residual_bwd(const void* dout, int32_t x_dtype, const void* delta, int32_t d_dtype,
+                                        const float* scale, void* ddelta, float* dscale_partials, int32_t P,
+                                        int64_t n, void* stream) {
+  QPAM_REQUIRE(dout && delta && scale && ddelta && dscale_partials, "scaled_residual_bwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(x_dtype) && is_dtype(d_dtype) && n > 0 && n % 4 == 0 && P > 0 && P <= 65535, "scaled_residual_bwd: bad dtype, size (multiple of 4) or partial count");
+  cudaStream_t st = (cudaStream_t)stream;
+#define QPAM_SR_B(TX, TD) scaled_residual<TX, TD>(true, dout, delta, scale, ddelta, dscale_partials, P, n, st)
+  if (x_dtype == QPAM_F32 && d_dtype == QPAM_F32) return QPAM_SR_B(float, float);
+  if (x_dtype == QPAM_F32) return QPAM_SR_B(float, __nv_bfloat16);
+  if (d_dtype == QPAM_BF16) return QPAM_SR_B(__nv_bfloat16, __nv_bfloat16);
+  return QPAM_SR_B(__nv_bfloat16, float);
+#undef QPAM_SR_B
+}
+
+extern "C" int qpam_block_weight_fwd(const void* wr, const void* wi, int32_t w_dtype, void* w, int32_t out_dtype,
+                                     int32_t out_dim, int32_t in_dim, void* stream) {
+  QPAM_REQUIRE(wr && wi && w, "block_weight_fwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(w_dtype) && is_dtype(out_dtype) && out_dim > 0 && in_dim > 0, "block_weight_fwd: bad dtype or shape");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, 148 * 8);
+#define QPAM_BW(TW, TO) k_block_weight_fwd<TW, TO><<<grid, 256, 0, st>>>((const TW*)wr, (const TW*)wi, (TO*)w, out_dim, in_dim)
+  if (w_dtype == QPAM_F32 && out_dtype == QPAM_F32) QPAM_BW(float, float);
+  else if (w_dtype == QPAM_F32) QPAM_BW(float, __nv_bfloat16);
+  else if (out_dtype == QPAM_BF16) QPAM_BW(__nv_bfloat16, __nv_bfloat16);
+  else QPAM_BW(__nv_bfloat16, float);
+#undef QPAM_BW
+  QPAM_LAUNCH_CHECK("k_block_weight_fwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dwr, void* dwi, int32_t w_dtype,
+                                     int32_t out_dim, int32_t in_dim, void* stream) {
+  QPAM_REQUIRE(dw && dwr && dwi, "block_weight_bwd: NULL pointer argument");
+  QPAM_REQUIRE(is_dtype(w_dtype) && is_dtype(out_dtype) && out_dim > 0 && in_dim > 0, "block_weight_bwd: bad dtype or shape");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, 148 * 8);
+#define QPAM_BW(TW, TO) k_block_weight_bwd<TW, TO><<<grid, 256, 0, st>>>((const TO*)dw, (TW*)dwr, (TW*)dwi, out_dim, in_dim)
+  if (w_dtype == QPAM_F32 && out_dtype == QPAM_F32) QPAM_BW(float, float);
+  else if (w_dtype == QPAM_F32) QPAM_BW(float, __nv_bfloat16);
+  else if (out_dtype == QPAM_BF16) QPAM_BW(__nv_bfloat16, __nv_bfloat16);
+  else QPAM_BW(__nv_bfloat16, float);
+#undef QPAM_BW
+  QPAM_LAUNCH_CHECK("k_block_weight_bwd");
+  return QPAM_OK;
 }

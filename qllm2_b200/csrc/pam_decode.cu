@@ -7,6 +7,7 @@
 // shuffles.  Continuous batching: `slot_ids` picks the slot of every live sequence, so sequences
 // join and leave by editing that index vector only.
 #include "common.cuh"
+#include "umma.cuh"
 
 namespace qpam {
 
@@ -122,6 +123,135 @@ __global__ void __launch_bounds__(256) k_decode_step(DecodeParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// bf16 state, d = 64: the K states of one (sequence, head) are 16 KB each.  They are brought into
+// shared memory by bulk copies issued up front by one thread (all K in flight at once, independent of
+// the register file), updated in place there, and written back by bulk copies.  With ~50 KB per CTA
+// four CTAs fit on an SM, i.e. ~190 KB of loads in flight per SM.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(umma::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(umma::smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :
+               : "l"(reinterpret_cast<uint64_t>(gdst)), "r"(umma::smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_and_wait_read() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+constexpr int DEC_BULK_STATE_BYTES = 64 * 64 * 2 * 2;  // one bf16 state
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
+  constexpr int D = 64, NC = 4, LPR = D / NC, RPP = 256 / LPR, PASSES = D / RPP;
+  extern __shared__ __align__(128) unsigned char dec_smem[];
+  __shared__ float2 sq[D], sk[D], sv[D];
+  __shared__ __align__(8) uint64_t bar;
+  const int tid = threadIdx.x;
+  const int seq = blockIdx.x / p.H, h = blockIdx.x - seq * p.H;
+  const int slot = p.slot_ids[seq];
+  if (slot < 0 || slot >= p.n_slots) return;  // padded / retired entry: nothing to do (whole CTA)
+  __nv_bfloat16* pool = reinterpret_cast<__nv_bfloat16*>(p.pool);
+  const size_t state_elems = (size_t)D * D * 2;
+  const size_t base = (((size_t)slot * p.L + p.layer) * p.K) * p.H + h;  // + k * H per state
+  if (tid == 0) {
+    umma::mbar_init(&bar, 1);
+    umma::fence_barrier_init();
+    umma::mbar_arrive_expect_tx(&bar, (uint32_t)(p.K * DEC_BULK_STATE_BYTES));
+    for (int k = 0; k < p.K; ++k)
+      bulk_load(dec_smem + (size_t)k * DEC_BULK_STATE_BYTES, pool + (base + (size_t)k * p.H) * state_elems,
+                DEC_BULK_STATE_BYTES, &bar);
+  }
+  const size_t vb = ((size_t)seq * p.H + h) * D * 2;
+  if (tid < D) {
+    sq[tid] = IO<T>::ld2(reinterpret_cast<const T*>(p.q) + vb + 2 * tid);
+    sk[tid] = IO<T>::ld2(reinterpret_cast<const T*>(p.k) + vb + 2 * tid);
+    sv[tid] = IO<T>::ld2(reinterpret_cast<const T*>(p.v) + vb + 2 * tid);
+  }
+  __syncthreads();  // also publishes the barrier's initialisation to the waiters
+  const bool arrived = umma::mbar_wait(&bar, 0, 31);
+  const int row0 = tid / LPR, j0 = (tid % LPR) * NC;
+  float2 kq[NC], qq[NC], yacc[PASSES];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) {
+    kq[c] = sk[j0 + c];
+    qq[c] = sq[j0 + c];
+  }
+#pragma unroll
+  for (int r = 0; r < PASSES; ++r) yacc[r] = make_float2(0.f, 0.f);
+  if (arrived) {
+    for (int k = 0; k < p.K; ++k) {
+      __nv_bfloat16* S = reinterpret_cast<__nv_bfloat16*>(dec_smem + (size_t)k * DEC_BULK_STATE_BYTES);
+      const size_t gi = ((size_t)k * p.n + seq) * p.H + h;
+      const float g = p.gamma[gi];
+      float2 cf = make_float2(1.f, 0.f);
+      if (p.coef != nullptr) cf = *reinterpret_cast<const float2*>(p.coef + gi * 2);
+#pragma unroll
+      for (int r = 0; r < PASSES; ++r) {
+        const int row = row0 + r * RPP;
+        uint4* cell = reinterpret_cast<uint4*>(S + ((size_t)row * D + j0) * 2);
+        uint4 raw = *cell;
+        __nv_bfloat162* b = reinterpret_cast<__nv_bfloat162*>(&raw);
+        const float2 vi = sv[row];
+        float2 part = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          float2 e = __bfloat1622float2(b[c]);
+          const float2 o = cmulc(vi, kq[c]);  // v_i conj(k_j)
+          e.x = fmaf(g, e.x, o.x);
+          e.y = fmaf(g, e.y, o.y);
+          cfma<false, false>(part, e, qq[c]);
+          b[c] = __float22bfloat162_rn(e);
+        }
+        *cell = raw;
+        const float2 m = cmul(cf, part);
+        yacc[r].x += m.x;
+        yacc[r].y += m.y;
+      }
+    }
+  }
+  umma::fence_proxy_async();  // the bulk stores below read what the generic proxy just wrote
+  __syncthreads();
+  if (tid == 0 && arrived) {
+    for (int k = 0; k < p.K; ++k)
+      bulk_store(pool + (base + (size_t)k * p.H) * state_elems, dec_smem + (size_t)k * DEC_BULK_STATE_BYTES,
+                 DEC_BULK_STATE_BYTES);
+    bulk_commit_and_wait_read();  // shared memory must outlive the copies that read it
+  }
+#pragma unroll
+  for (int r = 0; r < PASSES; ++r) {
+    float2 a = yacc[r];
+#pragma unroll
+    for (int o = LPR / 2; o > 0; o >>= 1) {
+      a.x += __shfl_xor_sync(0xffffffffu, a.x, o);
+      a.y += __shfl_xor_sync(0xffffffffu, a.y, o);
+    }
+    if ((tid % LPR) == 0) IO<T>::st2(reinterpret_cast<T*>(p.y) + vb + 2 * (row0 + r * RPP), a);
+  }
+}
+
+template <typename T>
+static int launch_decode_bulk(const DecodeParams& p, cudaStream_t st) {
+  const size_t smem = (size_t)p.K * DEC_BULK_STATE_BYTES;
+  auto kern = k_decode_step_bulk<T>;
+  QPAM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<p.n * p.H, 256, smem, st>>>(p);
+  QPAM_LAUNCH_CHECK("k_decode_step_bulk");
+  return QPAM_OK;
+}
+
+int decode_device_status(int* value, bool clear) {
+  QPAM_CUDA(umma::read_device_error(value, clear));
+  return QPAM_OK;
+}
+
 template <int D, typename ST, typename T>
 static int launch_decode(const DecodeParams& p, cudaStream_t st) {
   constexpr int NC = StateVec<ST>::NC;
@@ -161,6 +291,8 @@ extern "C" int qpam_decode_step(void* state_pool, int32_t state_dtype, int64_t n
   if (n == 0) return QPAM_OK;
   DecodeParams p{state_pool, slot_ids, q, k, v, gamma, coef, y, n_slots, L, layer, n, H, K};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (d == 64 && state_dtype == QPAM_BF16)   // shared-memory staged variant (bulk copies)
+    return io_dtype == QPAM_F32 ? launch_decode_bulk<float>(p, st) : launch_decode_bulk<__nv_bfloat16>(p, st);
 #define QPAM_DEC(DD)                                                                          \
   if (state_dtype == QPAM_F32)                                                                \
     return io_dtype == QPAM_F32 ? launch_decode<DD, float, float>(p, st)                      \

@@ -262,6 +262,13 @@ static int scan_bwd_t(const qpam_scan_args* a, const ScanLayout& L, const void* 
 
 }  // namespace qpam
 
+namespace qpam {
+int scan_tc_device_status(int* value, bool clear) {
+  QPAM_CUDA(umma::read_device_error(value, clear));
+  return QPAM_OK;
+}
+}  // namespace qpam
+
 using namespace qpam;
 
 extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t with_backward) {

@@ -341,3 +341,78 @@ def state_combine(coef: torch.Tensor, yks) -> torch.Tensor:
     if tuple(coef.shape) != (K, *shape[:-2], 2):
         raise _lib.QPamError(f"state_combine: coef must be {(K, *shape[:-2], 2)}, got {tuple(coef.shape)}")
     return _StateCombineFn.apply(coef, *yks)
+
+
+# ------------------------------------------------------------------------------------ residual, block weight
+class _ScaledResidualFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, delta, scale):
+        x, delta = x.contiguous(), delta.contiguous()
+        sc = scale.detach().float().reshape(1)
+        out = torch.empty_like(x)
+        check(_lib.lib().qpam_scaled_residual_fwd(ptr(x), dtype_code(x.dtype), ptr(delta), dtype_code(delta.dtype), ptr(sc),
+                                                  ptr(out), x.numel(), stream_ptr()), "qpam_scaled_residual_fwd")
+        ctx.save_for_backward(delta, sc)
+        ctx.meta = (scale.dtype, scale.shape, x.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        delta, sc = ctx.saved_tensors
+        s_dtype, s_shape, x_dtype = ctx.meta
+        dout = dout.to(x_dtype).contiguous()
+        P = max(1, min(148 * 8, delta.numel() // 4096 + 1))
+        part = torch.empty(P, dtype=torch.float32, device=delta.device)
+        ddelta = torch.empty_like(delta)
+        check(_lib.lib().qpam_scaled_residual_bwd(ptr(dout), dtype_code(x_dtype), ptr(delta), dtype_code(delta.dtype), ptr(sc),
+                                                  ptr(ddelta), ptr(part), P, delta.numel(), stream_ptr()),
+              "qpam_scaled_residual_bwd")
+        return dout, ddelta, part.sum().to(s_dtype).reshape(s_shape)
+
+
+def scaled_residual(x: torch.Tensor, delta: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """x + scale * delta with a learnable scalar `scale` (the two residual adds of V11Block.forward); the
+    result has x's dtype, delta may be bf16 beside an fp32 residual stream."""
+    _require_cuda(x, delta, scale)
+    if x.shape != delta.shape or scale.numel() != 1 or x.numel() % 4:
+        raise _lib.QPamError(f"scaled_residual: x {tuple(x.shape)} / delta {tuple(delta.shape)} must match (size a multiple "
+                             f"of 4) and scale must be a scalar")
+    for t in (x, delta):
+        if t.dtype not in (torch.float32, torch.bfloat16):
+            raise _lib.QPamError(f"unsupported dtype {t.dtype}")
+    return _ScaledResidualFn.apply(x, delta, scale)
+
+
+class _BlockWeightFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, wr, wi, out_dtype):
+        wr, wi = wr.contiguous(), wi.contiguous()
+        out_dim, in_dim = wr.shape
+        w = torch.empty(2 * out_dim, 2 * in_dim, dtype=out_dtype, device=wr.device)
+        check(_lib.lib().qpam_block_weight_fwd(ptr(wr), ptr(wi), dtype_code(wr.dtype), ptr(w), dtype_code(out_dtype), out_dim,
+                                               in_dim, stream_ptr()), "qpam_block_weight_fwd")
+        ctx.meta = (wr.dtype, out_dtype, out_dim, in_dim)
+        return w
+
+    @staticmethod
+    def backward(ctx, dw):
+        w_dtype, out_dtype, out_dim, in_dim = ctx.meta
+        dw = dw.to(out_dtype).contiguous()
+        dwr = torch.empty(out_dim, in_dim, dtype=w_dtype, device=dw.device)
+        dwi = torch.empty_like(dwr)
+        check(_lib.lib().qpam_block_weight_bwd(ptr(dw), dtype_code(out_dtype), ptr(dwr), ptr(dwi), dtype_code(w_dtype), out_dim,
+                                               in_dim, stream_ptr()), "qpam_block_weight_bwd")
+        return dwr, dwi, None
+
+
+def block_weight(weight_real: torch.Tensor, weight_imag: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """[2*out, 2*in] real matrix with rows (o,re) = (Wr, -Wi), (o,im) = (Wi, Wr) over interleaved (re, im)
+    columns: `F.linear(x.view(..., 2*in), block_weight(Wr, Wi))` is the complex projection of
+    `ComplexLinear` (v11/complex_ops.py) with an interleaved result."""
+    _require_cuda(weight_real, weight_imag)
+    if weight_real.shape != weight_imag.shape or weight_real.dim() != 2 or weight_real.dtype != weight_imag.dtype:
+        raise _lib.QPamError("block_weight: Wr and Wi must be two [out, in] matrices of one dtype")
+    if weight_real.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"unsupported dtype {weight_real.dtype}")
+    out_dtype = out_dtype or weight_real.dtype
+    return _BlockWeightFn.apply(weight_real, weight_imag, out_dtype)

@@ -114,11 +114,17 @@ class ComplexLinear(nn.Module):
         interleaved.  Cached while no gradient is needed and the parameters are unchanged."""
         wr, wi = self.weight_real, self.weight_imag
         live = torch.is_grad_enabled() and (wr.requires_grad or wi.requires_grad)
-        key = (wr._version, wi._version, wr.data_ptr(), wi.data_ptr(), wr.dtype)
+        out_dtype = wr.dtype
+        if wr.is_cuda and torch.is_autocast_enabled("cuda") and torch.get_autocast_dtype("cuda") == torch.bfloat16:
+            out_dtype = torch.bfloat16          # written in the GEMM's dtype: no separate cast of the weight
+        key = (wr._version, wi._version, wr.data_ptr(), wi.data_ptr(), wr.dtype, out_dtype)
         if not live and getattr(self, "_bw_key", None) == key:
             return self._bw
-        w = torch.stack([torch.stack([wr, -wi], dim=-1), torch.stack([wi, wr], dim=-1)], dim=1)
-        w = w.view(2 * self.out_dim, 2 * self.in_dim)
+        if wr.is_cuda and wr.dtype in (torch.float32, torch.bfloat16):
+            w = FE.block_weight(wr, wi, out_dtype)
+        else:
+            w = torch.stack([torch.stack([wr, -wi], dim=-1), torch.stack([wi, wr], dim=-1)], dim=1)
+            w = w.view(2 * self.out_dim, 2 * self.in_dim)
         if not live:
             self._bw, self._bw_key = w.detach(), key
         return w
@@ -426,7 +432,7 @@ class V11PAMLayer(nn.Module):
         else:
             y, new_state = self._recurrent(q, k, vprime, gamma, coef, state)
         out = self.o_proj(y.transpose(1, 2).contiguous().view(B, T, self.inner_dim, 2))
-        if self.training:
+        if self.training and self.dropout.p > 0:
             out = out * _dropout_mask(self.dropout, out)
         return out, new_state
 
@@ -469,11 +475,18 @@ class V11Block(nn.Module):
 
     def forward(self, x, pam_state=None, step_offset: int = 0):
         mixed = self.cgu(self.norm1(x))
-        if self.training:
+        if self.training and self.cgu_dropout.p > 0:
             mixed = mixed * _dropout_mask(self.cgu_dropout, mixed)
-        x = x + mixed * self.cgu_scale
+        x = self._residual(x, mixed, self.cgu_scale)
         pam_out, new_state = self.pam(self.norm2(x), state=pam_state, step_offset=step_offset)
-        return x + pam_out * self.pam_scale, new_state
+        return self._residual(x, pam_out, self.pam_scale), new_state
+
+    @staticmethod
+    def _residual(x, delta, scale):
+        if x.is_cuda and x.numel() % 4 == 0 and x.dtype in (torch.float32, torch.bfloat16) \
+                and delta.dtype in (torch.float32, torch.bfloat16):
+            return FE.scaled_residual(x, delta, scale)
+        return x + delta * scale
 
 
 class ComplexPosEmbed(nn.Module):

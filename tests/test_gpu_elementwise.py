@@ -208,3 +208,47 @@ def test_state_combine_matches_complex_sum(dtype, tol, K, d):
     assert y.dtype == dtype and rel(y, yr) < tol
     for a, b in zip(ga, gb):
         assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("xd,dd", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                   (torch.bfloat16, torch.bfloat16)])
+def test_scaled_residual_matches_torch(xd, dd):
+    g = torch.Generator().manual_seed(11)
+    x32 = torch.randn(37, 52, 2, generator=g).to(DEV)
+    d32 = torch.randn(37, 52, 2, generator=g).to(DEV)
+    dout = torch.randn(37, 52, 2, generator=g).to(DEV)
+    s = torch.tensor(0.37, device=DEV, requires_grad=True)
+    x = x32.to(xd).requires_grad_(True)
+    d = d32.to(dd).requires_grad_(True)
+    y = FE.scaled_residual(x, d, s)
+    assert y.dtype == xd
+    ga = torch.autograd.grad((y.float() * dout).sum(), [x, d, s])
+    xr, dr, sr = x.detach().float().requires_grad_(True), d.detach().float().requires_grad_(True), s.detach().clone().requires_grad_(True)
+    yr = xr + dr * sr
+    gb = torch.autograd.grad((yr * dout).sum(), [xr, dr, sr])
+    tol = 1e-6 if xd == torch.float32 and dd == torch.float32 else 1e-2
+    assert rel(y, yr) < tol
+    for a, b in zip(ga, gb):
+        assert rel(a, b) < tol
+
+
+@pytest.mark.parametrize("wd,od", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                   (torch.bfloat16, torch.bfloat16)])
+def test_block_weight_is_the_complex_product(wd, od):
+    g = torch.Generator().manual_seed(12)
+    out_dim, in_dim = 24, 40
+    wr = torch.randn(out_dim, in_dim, generator=g).to(DEV).to(wd).requires_grad_(True)
+    wi = torch.randn(out_dim, in_dim, generator=g).to(DEV).to(wd).requires_grad_(True)
+    x = torch.randn(9, in_dim, 2, generator=g).to(DEV)
+    dy = torch.randn(9, out_dim, 2, generator=g).to(DEV)
+    w = FE.block_weight(wr, wi, od)
+    assert w.dtype == od and w.shape == (2 * out_dim, 2 * in_dim)
+    y = (x.reshape(9, 2 * in_dim) @ w.float().T).view(9, out_dim, 2)
+    ga = torch.autograd.grad((y * dy).sum(), [wr, wi])
+    wr2, wi2 = wr.detach().float().requires_grad_(True), wi.detach().float().requires_grad_(True)
+    yc = torch.view_as_complex(x) @ torch.complex(wr2, wi2).T
+    gb = torch.autograd.grad((torch.view_as_real(yc) * dy).sum(), [wr2, wi2])
+    tol = 1e-5 if od == torch.float32 else 1e-2
+    assert rel(y, torch.view_as_real(yc)) < tol
+    for a, b in zip(ga, gb):
+        assert rel(a, b) < tol
