@@ -296,6 +296,10 @@ int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dwr, void* dw
  * Backward: dyk[k] = conj(coef[k]) dy,  dcoef[k,r] = sum_j dy[r,j] conj(yk[k][r,j]). */
 int qpam_state_combine_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype, int32_t K,
                            int64_t R, int32_t d, void* stream);
+/* Forward only, inputs [B,H,T,d,2], output token-major [B,T,H,d,2]: the head merge before o_proj
+ * (v11/model.py:835-836) folded into the read-out. */
+int qpam_state_combine_tokens_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype,
+                                  int32_t K, int32_t B, int32_t H, int32_t T, int32_t d, void* stream);
 int qpam_state_combine_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
                            float* dcoef, int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream);
 

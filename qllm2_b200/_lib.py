@@ -83,6 +83,8 @@ SIGNATURES = {
     "qpam_pam_prep_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_state_combine_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_void_p]),
+    "qpam_state_combine_tokens_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                                c_int32, c_int32, c_void_p]),
     "qpam_state_combine_bwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, C.POINTER(c_void_p), c_void_p, c_int32,
                                          c_int32, c_int64, c_int32, c_void_p]),
     "qpam_act_gate_packed_fwd": (c_int32, [c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),

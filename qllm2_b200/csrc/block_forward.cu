@@ -189,88 +189,98 @@ struct FrontParams {
   qpam_front_args a;
 };
 
+constexpr int FRONT_U = 2;  // tokens in flight per thread
+
+// A thread owns one (head, group of 4 channels) of FRONT_U consecutive tokens and moves q, k and v of it
+// (all loads first); the first lane of every head also writes that head's decays and read-out weights.
 template <typename T>
 __global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
   const qpam_front_args& a = fp.a;
-  __shared__ float s_keep[64];
   const int H = a.H, K = a.K, d = a.d;
   const int gph = d >> 2;
-  const int per_tok = 3 * H * gph;
+  const int per_tok = H * gph;
   const int64_t ntok = (int64_t)a.B * a.T;
-  for (int64_t tok = blockIdx.x; tok < ntok; tok += gridDim.x) {
-    const int b = (int)(tok / a.T), t = (int)(tok - (int64_t)b * a.T);
-    // ---- per-head scalars: decay per state, protect gate, read-out weights
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-      const float dt = IO<T>::ld(reinterpret_cast<const T*>(a.dt) + tok * a.ld_dt + h) + a.dt_bias[h];
-      float p = 0.f;
-      if (a.pg) p = sigmoidf_(IO<T>::ld(reinterpret_cast<const T*>(a.pg) + tok * a.ld_pg + h));
-      s_keep[h] = 1.f - p;
-      float wsum = 0.f, wmax = -INFINITY;
-      if (a.score) {
-        for (int k = 0; k < K; ++k) wmax = fmaxf(wmax, IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k));
-        for (int k = 0; k < K; ++k) wsum += __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax);
-      }
-      for (int k = 0; k < K; ++k) {
-        const float x = dt + (a.state_dt_offset ? a.state_dt_offset[k] : 0.f);
-        const float sp = x > 20.f ? x : log1pf(__expf(x));  // softplus
-        float base = __expf(-sp);
-        if (a.gamma_floor > 0.f) base = a.gamma_floor + (1.f - a.gamma_floor) * base;
-        const int64_t gi = (((int64_t)k * a.B + b) * H + h) * a.T + t;
-        a.gamma[gi] = base * (1.f - p) + p;
-        if (a.coef) {
-          float w = 1.f, ph = 0.f;
-          if (a.score) w = __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax) / wsum * (float)K;
-          if (a.phase) ph = IO<T>::ld(reinterpret_cast<const T*>(a.phase) + tok * a.ld_phase + h * K + k);
-          float sn, cs;
-          sincosf(ph, &sn, &cs);
-          *reinterpret_cast<float2*>(a.coef + gi * 2) = make_float2(w * cs, w * sn);
-        }
-      }
-    }
-    __syncthreads();
-    // ---- head split, rotation, protect scaling
-    int64_t pos = a.positions ? a.positions[tok] : a.offset + t;
-    pos = pos < 0 ? 0 : (pos >= a.rope_len ? a.rope_len - 1 : pos);
+  const int64_t ntile = (ntok + FRONT_U - 1) / FRONT_U;
+  const int64_t side_stride = (int64_t)H * d * 2;
+  for (int64_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
     for (int idx = threadIdx.x; idx < per_tok; idx += blockDim.x) {
-      const int which = idx / (H * gph);
-      const int rem = idx - which * H * gph;
-      const int h = rem / gph, g = rem - h * gph;
-      const int64_t src = tok * a.ld_qkv + ((int64_t)which * H + h) * d * 2 + g * 8;
-      const int64_t dst = (((int64_t)b * H + h) * a.T + t) * (int64_t)d * 2 + g * 8;
-      T* side = reinterpret_cast<T*>(which == 0 ? a.q : which == 1 ? a.k : a.v);
-      float re[4], im[4];
-      V4<T>::ld(reinterpret_cast<const T*>(a.qkv) + src, re, im);
-      if (which < 2) {
-        const float mul = which == 0 ? a.q_scale : 1.f;
-        if (a.rope) {
-          const float4 c0 = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2);
-          const float4 c1 = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2 + 4);
-          const float cs[4] = {c0.x, c0.z, c1.x, c1.z};
-          const float sn[4] = {c0.y, c0.w, c1.y, c1.w};
+      const int h = idx / gph, g = idx - h * gph;
+      float re[FRONT_U][3][4], im[FRONT_U][3][4], pgv[FRONT_U];
+      float4 c0[FRONT_U], c1[FRONT_U];
+      int64_t dst[FRONT_U];
+      bool on[FRONT_U];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float r0 = re[j], i0 = im[j];
-            re[j] = (r0 * cs[j] - i0 * sn[j]) * mul;
-            im[j] = (r0 * sn[j] + i0 * cs[j]) * mul;
-          }
-        } else {
+      for (int u = 0; u < FRONT_U; ++u) {
+        const int64_t tok = tile * FRONT_U + u;
+        on[u] = tok < ntok;
+        const int64_t tk = on[u] ? tok : 0;
+        const int b = (int)(tk / a.T), t = (int)(tk - (int64_t)b * a.T);
+        const int64_t src = tk * a.ld_qkv + (int64_t)h * d * 2 + g * 8;
+        dst[u] = (((int64_t)b * H + h) * a.T + t) * (int64_t)d * 2 + g * 8;
+        c0[u] = c1[u] = make_float4(1.f, 0.f, 1.f, 0.f);
+        pgv[u] = 0.f;
+        if (on[u]) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            re[j] *= mul;
-            im[j] *= mul;
+          for (int w = 0; w < 3; ++w) V4<T>::ld(reinterpret_cast<const T*>(a.qkv) + src + w * side_stride, re[u][w], im[u][w]);
+          if (a.pg) pgv[u] = IO<T>::ld(reinterpret_cast<const T*>(a.pg) + tk * a.ld_pg + h);
+          if (a.rope) {
+            int64_t pos = a.positions ? a.positions[tk] : a.offset + t;
+            pos = pos < 0 ? 0 : (pos >= a.rope_len ? a.rope_len - 1 : pos);
+            c0[u] = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2);
+            c1[u] = *reinterpret_cast<const float4*>(a.rope + (pos * d + g * 4) * 2 + 4);
           }
         }
-      } else {
-        const float keep = s_keep[h];
+      }
+#pragma unroll
+      for (int u = 0; u < FRONT_U; ++u) {
+        if (!on[u]) continue;
+        const float p = a.pg ? sigmoidf_(pgv[u]) : 0.f;
+        const float keep = 1.f - p;
+        const float cs[4] = {c0[u].x, c0[u].z, c1[u].x, c1[u].z};
+        const float sn[4] = {c0[u].y, c0[u].w, c1[u].y, c1[u].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          re[j] *= keep;
-          im[j] *= keep;
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            const float mul = w == 0 ? a.q_scale : 1.f;
+            const float r0 = re[u][w][j], i0 = im[u][w][j];
+            re[u][w][j] = (r0 * cs[j] - i0 * sn[j]) * mul;
+            im[u][w][j] = (r0 * sn[j] + i0 * cs[j]) * mul;
+          }
+          re[u][2][j] *= keep;
+          im[u][2][j] *= keep;
+        }
+        V4<T>::st(reinterpret_cast<T*>(a.q) + dst[u], re[u][0], im[u][0]);
+        V4<T>::st(reinterpret_cast<T*>(a.k) + dst[u], re[u][1], im[u][1]);
+        V4<T>::st(reinterpret_cast<T*>(a.v) + dst[u], re[u][2], im[u][2]);
+        if (g == 0) {  // per-head scalars of this token: decay per state, read-out weights
+          const int64_t tok = tile * FRONT_U + u;
+          const int b = (int)(tok / a.T), t = (int)(tok - (int64_t)b * a.T);
+          const float dt = IO<T>::ld(reinterpret_cast<const T*>(a.dt) + tok * a.ld_dt + h) + a.dt_bias[h];
+          float wsum = 0.f, wmax = -INFINITY;
+          if (a.score) {
+            for (int k = 0; k < K; ++k) wmax = fmaxf(wmax, IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k));
+            for (int k = 0; k < K; ++k) wsum += __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax);
+          }
+          for (int k = 0; k < K; ++k) {
+            const float x = dt + (a.state_dt_offset ? a.state_dt_offset[k] : 0.f);
+            const float sp = x > 20.f ? x : log1pf(__expf(x));  // softplus
+            float base = __expf(-sp);
+            if (a.gamma_floor > 0.f) base = a.gamma_floor + (1.f - a.gamma_floor) * base;
+            const int64_t gi = (((int64_t)k * a.B + b) * H + h) * a.T + t;
+            a.gamma[gi] = base * (1.f - p) + p;
+            if (a.coef) {
+              float w = 1.f, ph = 0.f;
+              if (a.score) w = __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax) / wsum * (float)K;
+              if (a.phase) ph = IO<T>::ld(reinterpret_cast<const T*>(a.phase) + tok * a.ld_phase + h * K + k);
+              float sn_, cs_;
+              sincosf(ph, &sn_, &cs_);
+              *reinterpret_cast<float2*>(a.coef + gi * 2) = make_float2(w * cs_, w * sn_);
+            }
+          }
         }
       }
-      V4<T>::st(side + dst, re, im);
     }
-    __syncthreads();
   }
 }
 
@@ -342,9 +352,9 @@ extern "C" int qpam_pam_front_fwd(const qpam_front_args* a, void* stream) {
   QPAM_REQUIRE(!a->score || a->coef, "pam_front: scores without read-out weights");
   cudaStream_t st = (cudaStream_t)stream;
   FrontParams fp{*a};
-  const int per_tok = 3 * a->H * (a->d / 4);
+  const int per_tok = a->H * (a->d / 4);
   const int threads = pick_threads(per_tok);
-  const int grid = (int)std::min<int64_t>((int64_t)a->B * a->T, 148 * 16);
+  const int grid = (int)std::min<int64_t>(((int64_t)a->B * a->T + FRONT_U - 1) / FRONT_U, (148 * 2048) / threads);
   if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp);
   else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp);
   QPAM_LAUNCH_CHECK("k_pam_front");

@@ -443,6 +443,7 @@ struct CombineParams {
   float* dcoef;   // bwd
   int64_t R;
   int d, K;
+  int H, T;       // > 0: the forward output is written token-major, y[b, t, h, :] for row r = (b, h, t)
 };
 
 template <typename T, bool BWD>
@@ -487,7 +488,14 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
         }
       }
     }
-    if (!BWD && on) V4<T>::st(reinterpret_cast<T*>(p.y) + off, ar, ai);
+    if (!BWD && on) {
+      int64_t o2 = off;
+      if (p.H > 0) {
+        const int64_t bh = r / p.T, t = r - bh * p.T, b = bh / p.H, h = bh - b * p.H;
+        o2 = (((b * p.T + t) * p.H + h) * p.d + g * 4) * 2;
+      }
+      V4<T>::st(reinterpret_cast<T*>(p.y) + o2, ar, ai);
+    }
   }
 }
 
@@ -728,7 +736,7 @@ __global__ void __launch_bounds__(256) k_block_weight_bwd(const TO* __restrict__
 }  // namespace qpam
 
 static int state_combine(bool bwd, const void* const* yk, void* const* dyk, const float* coef, void* y, float* dcoef,
-                         int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream) {
+                         int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream, int32_t H = 0, int32_t T = 0) {
   QPAM_REQUIRE(yk && coef && y && (!bwd || (dyk && dcoef)), "state_combine: NULL pointer argument");
   QPAM_REQUIRE(is_dtype(dtype) && K >= 1 && K <= QPAM_MAX_STATES && R >= 0, "state_combine: bad dtype, K or row count");
   QPAM_REQUIRE(d >= 4 && d <= 128 && (d & (d - 1)) == 0, "state_combine: d must be a power of two in [4,128] (got %d)", d);
@@ -739,7 +747,7 @@ static int state_combine(bool bwd, const void* const* yk, void* const* dyk, cons
     p.yk[k] = yk[k];
     p.dyk[k] = bwd ? dyk[k] : nullptr;
   }
-  p.coef = coef; p.y = y; p.dcoef = dcoef; p.R = R; p.d = d; p.K = K;
+  p.coef = coef; p.y = y; p.dcoef = dcoef; p.R = R; p.d = d; p.K = K; p.H = H; p.T = T;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = R * (d / 4);
   const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
@@ -836,4 +844,10 @@ extern "C" int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dw
 #undef QPAM_BW
   QPAM_LAUNCH_CHECK("k_block_weight_bwd");
   return QPAM_OK;
+}
+
+extern "C" int qpam_state_combine_tokens_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype, int32_t K,
+                                             int32_t B, int32_t H, int32_t T, int32_t d, void* stream) {
+  QPAM_REQUIRE(B > 0 && H > 0 && T > 0, "state_combine_tokens: empty shape");
+  return state_combine(false, yk, nullptr, coef, y, nullptr, dtype, K, (int64_t)B * H * T, d, stream, H, T);
 }

@@ -324,6 +324,28 @@ class _StateCombineFn(torch.autograd.Function):
         return (dcoef.to(ctx.coef_dtype), *dyks)
 
 
+@torch.no_grad()
+def state_combine_tokens(coef: torch.Tensor, yks) -> torch.Tensor:
+    """Inference form of `state_combine` for yks[k] [B, H, T, d, 2]: the result is written token-major,
+    [B, T, H*d, 2], which is the layout the output projection reads (no transpose copy)."""
+    yks = [t.contiguous() for t in yks]
+    _require_cuda(coef, *yks)
+    K = len(yks)
+    B, H, T, d, two = yks[0].shape
+    if not 1 <= K <= 4 or two != 2 or any(t.shape != yks[0].shape or t.dtype != yks[0].dtype for t in yks):
+        raise _lib.QPamError("state_combine_tokens: 1..4 state outputs of one [B,H,T,d,2] shape and dtype")
+    if yks[0].dtype not in (torch.float32, torch.bfloat16) or d < 4 or d > 128 or d & (d - 1):
+        raise _lib.QPamError(f"state_combine_tokens: bf16/f32 and d a power of two in [4,128]; got {yks[0].dtype}, d={d}")
+    if tuple(coef.shape) != (K, B, H, T, 2):
+        raise _lib.QPamError(f"state_combine_tokens: coef must be {(K, B, H, T, 2)}, got {tuple(coef.shape)}")
+    cf = coef.float().contiguous()
+    y = torch.empty(B, T, H * d, 2, dtype=yks[0].dtype, device=yks[0].device)
+    arr = (_lib.c_void_p * K)(*[t.data_ptr() for t in yks])
+    check(_lib.lib().qpam_state_combine_tokens_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, B, H, T, d, stream_ptr()),
+          "qpam_state_combine_tokens_fwd")
+    return y
+
+
 def state_combine(coef: torch.Tensor, yks) -> torch.Tensor:
     """y = sum_k coef[k] * yks[k] (complex): coef [K, ..., 2] over the leading axes of yks[k] [..., d, 2]
     (the K-state read-out of v11/model.py:766-781), forward and backward in one pass each."""

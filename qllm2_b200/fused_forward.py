@@ -51,7 +51,7 @@ class FusedForward:
         self.b_head_proj = (None if hp.bias_real is None else
                             torch.stack([hp.bias_real, hp.bias_imag], -1).reshape(-1).detach().to(self.dtype))
         self.w_vocab = torch.cat([model.embed.embed_real.weight, model.embed.embed_imag.weight], -1).detach().to(self.dtype).contiguous()
-        self.layers = [self._pack(blk) for blk in model.blocks]
+        self.layers = [self.pack_block(blk, self.dtype) for blk in model.blocks]
 
     @staticmethod
     def unsupported_reason(model: V11LM) -> Optional[str]:
@@ -71,10 +71,16 @@ class FusedForward:
         return None
 
     # ---------------------------------------------------------------------------------- packing
-    def _pack(self, blk) -> SimpleNamespace:
-        D, H, K, T = self.D, self.H, self.K, self.dtype
-        L = SimpleNamespace()
+    @staticmethod
+    def pack_block(blk, dtype) -> SimpleNamespace:
+        """Packed weights of one V11Block (any device): `w_gu` [4*hidden, 2D] = gate | up block matrices,
+        `w_down`, `w_front` = qkv block matrix followed by the gate / routing Linears that read the layer
+        input (columns permuted from [re | im] planes to interleaved order; `cols[name]` = ("a", column)),
+        `w_mag` = the Linears that read |x| (`cols[name]` = ("m", column)), `w_o`, and fp32 parameters."""
         cgu, pam = blk.cgu, blk.pam
+        D, H, K, T = pam.dim, pam.num_heads, pam.n_states, dtype
+        inner, device = pam.inner_dim, blk.norm1.scale.device
+        L = SimpleNamespace()
         L.n1, L.n2 = _f32(blk.norm1.scale), _f32(blk.norm2.scale)
         L.hidden = cgu.gate_proj.out_dim
         L.w_gu = torch.cat([cgu.gate_proj.block_weight(), cgu.up_proj.block_weight()], 0).detach().to(T).contiguous()
@@ -91,7 +97,7 @@ class FusedForward:
             w = lin.weight.detach()
             return w.view(w.shape[0], 2, D).transpose(1, 2).reshape(w.shape[0], 2 * D)
 
-        rows_a, bias_a, rows_m, bias_m = [pam.qkv_proj.block_weight().detach()], [torch.zeros(6 * self.inner, device=self.device)], [], []
+        rows_a, bias_a, rows_m, bias_m = [pam.qkv_proj.block_weight().detach()], [torch.zeros(6 * inner, device=device)], [], []
         L.cols = {}
 
         def add(name, lin, content_aware):
@@ -114,8 +120,8 @@ class FusedForward:
         n_a = sum(r.shape[0] for r in rows_a)
         pad = (-n_a) % 8            # rows of the projection output stay 16-byte aligned
         if pad:
-            rows_a.append(torch.zeros(pad, 2 * D, device=self.device))
-            bias_a.append(torch.zeros(pad, device=self.device))
+            rows_a.append(torch.zeros(pad, 2 * D, device=device))
+            bias_a.append(torch.zeros(pad, device=device))
         L.w_front = torch.cat([r.float() for r in rows_a], 0).to(T).contiguous()
         L.b_front = torch.cat([b.float() for b in bias_a], 0).to(T).contiguous()
         L.w_mag = torch.cat([r.float() for r in rows_m], 0).to(T).contiguous() if rows_m else None

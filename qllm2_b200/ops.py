@@ -160,6 +160,27 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
     return _PamScanFn.apply(q, k, v, gamma, coef, s0, cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
 
 
+@torch.no_grad()
+def pam_scan_tokens(q, k, v, gamma, coef=None, s0=None, cu_seqlens=None, *, head_dim=None, eps: float = 1e-6,
+                    chunk: int = 64):
+    """Inference form of `pam_scan`: same arguments, but Y comes back token-major, [B, T, H*d, 2] -- the layout
+    the output projection reads (the head merge of v11/model.py:835-836) -- and nothing is kept for a backward
+    pass.  With K phase-routed states in bf16 at d = 64 the merge is folded into the read-out kernel."""
+    K = gamma.shape[0] if gamma.dim() == 4 else 1
+    B, H, T, d = q.shape[:4]
+    if K > 1 and coef is not None and q.dtype == torch.bfloat16 and d == 64 and q.is_cuda:
+        from .fused_elementwise import state_combine_tokens
+        ys, finals = [], []
+        for kk in range(K):
+            yk, sk = pam_scan(q, k, v, gamma[kk:kk + 1], s0=None if s0 is None else s0[kk:kk + 1], cu_seqlens=cu_seqlens,
+                              head_dim=head_dim, eps=eps, chunk=chunk)
+            ys.append(yk)
+            finals.append(sk)
+        return state_combine_tokens(coef, ys), torch.cat(finals, dim=0)
+    y, s = pam_scan(q, k, v, gamma, coef=coef, s0=s0, cu_seqlens=cu_seqlens, head_dim=head_dim, eps=eps, chunk=chunk)
+    return y.transpose(1, 2).reshape(B, T, H * d, 2), s
+
+
 # --------------------------------------------------------------------------------------- decode
 def pam_decode_step(state_pool, slot_ids, q_scaled, k, v, gamma, coef=None, *, layer: int = 0):
     """One recurrent step, in place on ``state_pool`` [n_slots, L, K, H, d, d, 2].

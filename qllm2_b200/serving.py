@@ -102,9 +102,9 @@ class _PrefillMix:
         self.eng, self.cu, self.slots = eng, cu, slots
 
     def __call__(self, layer, q, k, v, gamma, coef):
-        y, s = ops.pam_scan(q, k, v, gamma, coef=coef, cu_seqlens=self.cu, head_dim=q.shape[3])
+        y, s = ops.pam_scan_tokens(q, k, v, gamma, coef=coef, cu_seqlens=self.cu, head_dim=q.shape[3])
         ops.pam_pool_store(self.eng.pool, self.slots, s, layer=layer)
-        return y.transpose(1, 2).reshape(q.shape[2], -1)
+        return y.view(q.shape[2], -1)
 
 
 class _DecodeMix:

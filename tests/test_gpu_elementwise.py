@@ -252,3 +252,23 @@ def test_block_weight_is_the_complex_product(wd, od):
     assert rel(y, torch.view_as_real(yc)) < tol
     for a, b in zip(ga, gb):
         assert rel(a, b) < tol
+
+
+def test_token_major_scan_equals_scan_then_head_merge():
+    """`pam_scan_tokens` (inference: K bf16 scans + read-out written token-major) against `pam_scan` + transpose."""
+    from qllm2_b200 import ops
+    g = torch.Generator().manual_seed(21)
+    B, H, T, d, K = 2, 3, 200, 64, 3
+    q, k, v = (torch.randn(B, H, T, d, 2, generator=g).mul(0.125).to(DEV).bfloat16() for _ in range(3))
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=g) + 3).to(DEV)
+    coef = torch.randn(K, B, H, T, 2, generator=g).to(DEV)
+    with torch.no_grad():
+        y_ref, s_ref = ops.pam_scan(q, k, v, gamma, coef=coef)
+        y_tok, s_tok = ops.pam_scan_tokens(q, k, v, gamma, coef=coef)
+    assert y_tok.shape == (B, T, H * d, 2)
+    assert torch.equal(y_tok, y_ref.transpose(1, 2).reshape(B, T, H * d, 2))
+    assert torch.equal(s_tok, s_ref)
+    # fp32 (no fused read-out): same contract
+    y32, _ = ops.pam_scan_tokens(q.float(), k.float(), v.float(), gamma, coef=coef)
+    r32, _ = ops.pam_scan(q.float(), k.float(), v.float(), gamma, coef=coef)
+    assert torch.equal(y32, r32.transpose(1, 2).reshape(B, T, H * d, 2))
