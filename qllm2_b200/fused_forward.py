@@ -209,6 +209,13 @@ class FusedForward:
         return h
 
     @torch.no_grad()
+    def logits(self, lm: torch.Tensor) -> torch.Tensor:
+        """Tied-head logits [n, V] (float32) of rows lm [n, D, 2]: Re(lm . conj(E)) as one real GEMM
+        (v11/model.py:1136-1139); only the sampling path needs them."""
+        Hm = torch.cat([lm[..., 0], lm[..., 1]], dim=-1)
+        return F.linear(Hm, self.w_vocab).float()
+
+    @torch.no_grad()
     def greedy_next(self, lm: torch.Tensor) -> torch.Tensor:
         """argmax over the tied head for rows lm [n, D, 2] (no logits are formed)."""
         Hm = torch.cat([lm[..., 0], lm[..., 1]], dim=-1).contiguous()

@@ -609,32 +609,42 @@ class V11LM(nn.Module):
 
     @torch.no_grad()
     def generate(self, input_ids, max_new_tokens=100, temperature=1.0, top_k=50, top_p=0.0,
-                 repetition_penalty=1.0, eos_token_id=None):
+                 repetition_penalty=1.0, eos_token_id=None, fused: bool = True):
         """Prefill once (parallel scan), then one O(1) recurrent step per token.  temperature <= 0
-        selects greedy decoding (arg-max of the logits)."""
+        selects greedy decoding (arg-max of the logits).  On CUDA the loop runs on the packed forward with
+        the decode step replayed from a CUDA graph (`fused=False` keeps the module-by-module loop)."""
         self.eval()
+        greedy = temperature is None or temperature <= 0
+
+        def sample(nl, out):
+            if greedy:
+                return nl.argmax(dim=-1, keepdim=True)
+            nl = nl / temperature
+            if repetition_penalty != 1.0:
+                sc = torch.gather(nl, 1, out)
+                nl.scatter_(1, out, torch.where(sc > 0, sc / repetition_penalty, sc * repetition_penalty))
+            if top_k > 0:
+                kth = nl.topk(min(top_k, nl.size(-1))).values[:, -1:]
+                nl[nl < kth] = float("-inf")
+            if top_p > 0:
+                sl, si = nl.sort(descending=True)
+                pr = sl.softmax(dim=-1)
+                sl[(pr.cumsum(dim=-1) - pr) >= top_p] = float("-inf")
+                nl = sl.scatter(1, si, sl)
+            return torch.multinomial(nl.softmax(dim=-1), 1)
+
+        if fused and input_ids.is_cuda and max_new_tokens > 0:
+            from .fused_forward import FusedForward
+            if FusedForward.unsupported_reason(self) is None:
+                from .serving import generate_fused
+                sample.greedy = greedy
+                return generate_fused(self, input_ids, max_new_tokens, sample, eos_token_id=eos_token_id)
         out = input_ids.clone()
         logits, states, _ = self.forward(out)
         step = out.shape[1]
         done = torch.zeros(out.shape[0], dtype=torch.bool, device=out.device)
         for _ in range(max_new_tokens):
-            nl = logits[:, -1].float()
-            if temperature is None or temperature <= 0:
-                nxt = nl.argmax(dim=-1, keepdim=True)
-            else:
-                nl = nl / temperature
-                if repetition_penalty != 1.0:
-                    sc = torch.gather(nl, 1, out)
-                    nl.scatter_(1, out, torch.where(sc > 0, sc / repetition_penalty, sc * repetition_penalty))
-                if top_k > 0:
-                    kth = nl.topk(min(top_k, nl.size(-1))).values[:, -1:]
-                    nl[nl < kth] = float("-inf")
-                if top_p > 0:
-                    sl, si = nl.sort(descending=True)
-                    pr = sl.softmax(dim=-1)
-                    sl[(pr.cumsum(dim=-1) - pr) >= top_p] = float("-inf")
-                    nl = sl.scatter(1, si, sl)
-                nxt = torch.multinomial(nl.softmax(dim=-1), 1)
+            nxt = sample(logits[:, -1].float(), out)
             out = torch.cat([out, nxt], dim=1)
             if eos_token_id is not None:
                 done |= nxt.squeeze(1) == eos_token_id

@@ -281,3 +281,91 @@ class ContinuousBatcher:
         while not self.sched.idle:
             self.step()
         return {r.rid: r.generated for r in self.sched.finished}
+
+
+# ------------------------------------------------------------------------------------ V11LM.generate
+class _BatchPrefillMix:
+    """Sequence mixing at the prefill of `generate`: B equal-length rows, final states into slots 0..B-1."""
+    q_scale = 1.0
+
+    def __init__(self, pool, slots):
+        self.pool, self.slots = pool, slots
+
+    def __call__(self, layer, q, k, v, gamma, coef):
+        y, s = ops.pam_scan_tokens(q, k, v, gamma, coef=coef, head_dim=q.shape[3])
+        ops.pam_pool_store(self.pool, self.slots, s, layer=layer)
+        return y.view(q.shape[0] * q.shape[2], -1)
+
+
+class _PoolDecodeMix:
+    def __init__(self, pool, slots, head_dim):
+        self.pool, self.slots, self.q_scale = pool, slots, head_dim ** -0.5
+
+    def __call__(self, layer, q, k, v, gamma, coef):
+        n, H, _, d, _ = q.shape
+        K = gamma.shape[0]
+        y = ops.pam_decode_step(self.pool, self.slots, q.view(n, H, d, 2), k.view(n, H, d, 2), v.view(n, H, d, 2),
+                                gamma.view(K, n, H), None if coef is None else coef.view(K, n, H, 2), layer=layer)
+        return y.view(n, -1)
+
+
+def _fused_forward_of(model: V11LM, need_positions: int) -> FusedForward:
+    """The model's packed forward, rebuilt when a parameter changed or longer positions are needed."""
+    key = (tuple(p._version for p in model.parameters()), next(model.parameters()).dtype, next(model.parameters()).device)
+    cached = getattr(model, "_fused_forward_cache", None)
+    if cached is not None and cached[0] == key and (cached[1].rope is None or cached[1].rope.shape[0] >= need_positions):
+        return cached[1]
+    ff = FusedForward(model, max_position=max(need_positions, 2 * model.config.max_seq_len))
+    model._fused_forward_cache = (key, ff)
+    return ff
+
+
+@torch.no_grad()
+def generate_fused(model: V11LM, input_ids, max_new_tokens, sample, eos_token_id=None):
+    """`V11LM.generate` on the packed forward: one parallel prefill, then per token one decode step replayed
+    from a CUDA graph (layer loop of v11/model.py:1206-1245).  `sample(logits [B,V] float32 or None, out) -> next
+    ids [B,1]` picks the tokens; it gets None when it declared `sample.greedy` (arg-max without logits)."""
+    cfg = model.config
+    B, T0 = input_ids.shape
+    ff = _fused_forward_of(model, T0 + max_new_tokens + 1)
+    dev = input_ids.device
+    state_dtype = torch.float32 if ff.dtype == torch.float32 else torch.bfloat16
+    pool = torch.zeros(B, cfg.n_layers, cfg.n_states, cfg.n_heads, cfg.head_dim, cfg.head_dim, 2, dtype=state_dtype, device=dev)
+    slots = torch.arange(B, dtype=torch.int32, device=dev)
+    greedy = getattr(sample, "greedy", False)
+
+    def head(xn_rows):
+        lm = ff.head_hidden(xn_rows)
+        return ff.greedy_next(lm)[:, None] if greedy else ff.logits(lm)
+
+    out = input_ids.clone()
+    xn = ff.hidden(out, _BatchPrefillMix(pool, slots))
+    res = head(xn.view(B, T0, cfg.dim, 2)[:, -1])
+    ids_buf = torch.zeros(B, 1, dtype=torch.long, device=dev)
+    pos_buf = torch.zeros(B, 1, dtype=torch.long, device=dev)
+    mix = _PoolDecodeMix(pool, slots, cfg.head_dim)
+    graph, g_res = None, None
+    done = torch.zeros(B, dtype=torch.bool, device=dev)
+    for i in range(max_new_tokens):
+        nxt = res if greedy else sample(res, out)
+        out = torch.cat([out, nxt], dim=1)
+        if eos_token_id is not None:
+            done |= nxt.squeeze(1) == eos_token_id
+            if bool(done.all()):
+                break
+        if i + 1 == max_new_tokens:
+            break
+        ids_buf.copy_(nxt)
+        pos_buf.fill_(T0 + i)
+        if graph is None and i == 0:
+            res = head(ff.hidden(ids_buf, mix, positions=pos_buf))          # first step eagerly (warms every kernel up)
+        elif graph is None:
+            graph = torch.cuda.CUDAGraph()                                  # capture records the step, it does not run it
+            with torch.cuda.graph(graph):
+                g_res = head(ff.hidden(ids_buf, mix, positions=pos_buf))
+            graph.replay()
+            res = g_res.clone()
+        else:
+            graph.replay()
+            res = g_res.clone()
+    return out

@@ -118,3 +118,24 @@ def test_positions_beyond_the_table_are_refused():
     eng.submit(list(range(1, 30)), 2)
     with pytest.raises(RuntimeError):
         eng.run()
+
+
+@pytest.mark.parametrize("variant", ["k3_compete_routed", "k1_swish"])
+def test_generate_on_the_packed_forward_equals_the_module_loop(variant):
+    net = _net(VARIANTS[variant])
+    ids = torch.randint(0, 257, (3, 21), generator=torch.Generator().manual_seed(6)).to(DEV)
+    fast = net.generate(ids, max_new_tokens=9, temperature=0.0)
+    slow = net.generate(ids, max_new_tokens=9, temperature=0.0, fused=False)
+    assert fast.shape == (3, 30) and torch.equal(fast, slow)
+    one = net.generate(ids, max_new_tokens=1, temperature=0.0)
+    assert torch.equal(one, slow[:, :22])
+    # sampling path: logits come from the packed head; same seed, same path -> same tokens, all in range
+    torch.manual_seed(3)
+    a = net.generate(ids, max_new_tokens=6, temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.1)
+    torch.manual_seed(3)
+    b = net.generate(ids, max_new_tokens=6, temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.1)
+    assert torch.equal(a, b) and int(a.max()) < 257 and torch.equal(a[:, :21], ids)
+    # an end-of-sequence id stops the loop early
+    eos = int(slow[0, 21])
+    stopped = net.generate(ids[:1], max_new_tokens=9, temperature=0.0, eos_token_id=eos)
+    assert stopped.shape[1] == 22
