@@ -25,6 +25,14 @@ __device__ __forceinline__ float rnd<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ float rnd<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// sigmoid in the precision the result is stored in
+template <typename T>
+__device__ __forceinline__ float sig(float x);
+template <>
+__device__ __forceinline__ float sig<float>(float x) { return sigmoidf_(x); }
+template <>
+__device__ __forceinline__ float sig<__nv_bfloat16>(float x) { return sigmoid_approx(x); }
+
 template <typename T, bool SWISH>
 __global__ void __launch_bounds__(512) k_act_gate_packed(const T* __restrict__ gu, int64_t ld,
                                                          const float* __restrict__ bias,
@@ -38,23 +46,31 @@ __global__ void __launch_bounds__(512) k_act_gate_packed(const T* __restrict__ g
     b4[j] = bias[g * 4 + j];
     be4[j] = SWISH ? beta[g * 4 + j] : 0.f;
   }
-#pragma unroll 2
-  for (int64_t row = blockIdx.y; row < N; row += gridDim.y) {
-    float ar[4], ai[4], ur[4], ui[4];
-    V4<T>::ld(gu + row * ld + g * 8, ar, ai);
-    V4<T>::ld(gu + row * ld + 2 * C + g * 8, ur, ui);
+  constexpr int U = 2;  // rows in flight per thread: their four loads are issued before any arithmetic
+  for (int64_t row0 = (int64_t)blockIdx.y * U; row0 < N; row0 += (int64_t)gridDim.y * U) {
+    float ar[U][4], ai[U][4], ur[U][4], ui[U][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float um = fsqrt_(ur[j] * ur[j] + ui[j] * ui[j] + MAG_EPS);
-      const float act = SWISH ? um * sigmoidf_(be4[j] * um + b4[j]) : fmaxf(um + b4[j], 0.f);
-      const float f = act * frcp_(um + MAG_EPS);
-      const float gm = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float h = sigmoidf_(gm) * frcp_(gm + MAG_EPS) * f;
-      const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
-      ar[j] = pr * h;
-      ai[j] = pi * h;
+    for (int u = 0; u < U; ++u) {
+      const int64_t row = row0 + u < N ? row0 + u : N - 1;
+      V4<T>::ld(gu + row * ld + g * 8, ar[u], ai[u]);
+      V4<T>::ld(gu + row * ld + 2 * C + g * 8, ur[u], ui[u]);
     }
-    V4<T>::st(out + (row * C + g * 4) * 2, ar, ai);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (row0 + u >= N) break;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const MagInv um_ = mag_inv(ur[u][j] * ur[u][j] + ui[u][j] * ui[u][j] + MAG_EPS); const float um = um_.mag;
+        const float act = SWISH ? um * sig<T>(be4[j] * um + b4[j]) : fmaxf(um + b4[j], 0.f);
+        const float f = act * um_.inv;
+        const MagInv gm_ = mag_inv(ar[u][j] * ar[u][j] + ai[u][j] * ai[u][j] + MAG_EPS); const float gm = gm_.mag;
+        const float h = sig<T>(gm) * gm_.inv * f;
+        const float pr = ar[u][j] * ur[u][j] - ai[u][j] * ui[u][j], pi = ar[u][j] * ui[u][j] + ai[u][j] * ur[u][j];
+        ar[u][j] = pr * h;
+        ai[u][j] = pi * h;
+      }
+      V4<T>::st(out + ((row0 + u) * C + g * 4) * 2, ar[u], ai[u]);
+    }
   }
 }
 
@@ -104,8 +120,8 @@ __global__ void __launch_bounds__(128) k_residual_cnorm(T* __restrict__ z, const
       const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float m = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-        const float w = m * frcp_(m + MAG_EPS) * rrms * s4[j];
+        const MagInv m_ = mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS); const float m = m_.mag;
+        const float w = m * m_.inv * rrms * s4[j];
         re[j] *= w;
         im[j] *= w;
       }
@@ -169,8 +185,8 @@ __global__ void __launch_bounds__(1024) k_residual_cnorm_row(T* __restrict__ z, 
   const float s4[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    const float m = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-    const float w = m * frcp_(m + MAG_EPS) * rrms * s4[j];
+    const MagInv m_ = mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS); const float m = m_.mag;
+    const float w = m * m_.inv * rrms * s4[j];
     re[j] *= w;
     im[j] *= w;
   }
@@ -189,12 +205,14 @@ struct FrontParams {
   qpam_front_args a;
 };
 
-constexpr int FRONT_U = 2;  // tokens in flight per thread
+constexpr int FRONT_U = 1;  // tokens per tile (one keeps the streaming warps at ~64 registers, 4+ CTAs per SM)
 
-// A thread owns one (head, group of 4 channels) of FRONT_U consecutive tokens and moves q, k and v of it
-// (all loads first); the first lane of every head also writes that head's decays and read-out weights.
+// Threads [0, main_threads): one (head, group of 4 channels) of FRONT_U consecutive tokens each, moving q, k
+// and v of it (all loads first).  Threads [main_threads, blockDim): one (head, state) pair each, writing the
+// decay and the read-out weight of those tokens -- a chain of small dependent loads and transcendentals that
+// runs beside the streaming warps instead of at their tail.
 template <typename T>
-__global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
+__global__ void __launch_bounds__(512) k_pam_front(FrontParams fp, int main_threads) {
   const qpam_front_args& a = fp.a;
   const int H = a.H, K = a.K, d = a.d;
   const int gph = d >> 2;
@@ -202,8 +220,43 @@ __global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
   const int64_t ntok = (int64_t)a.B * a.T;
   const int64_t ntile = (ntok + FRONT_U - 1) / FRONT_U;
   const int64_t side_stride = (int64_t)H * d * 2;
+  if ((int)threadIdx.x >= main_threads) {
+    const int gate_threads = blockDim.x - main_threads;
+    for (int64_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
+      for (int e = threadIdx.x - main_threads; e < FRONT_U * H * K; e += gate_threads) {
+        const int u = e / (H * K), hk = e - u * H * K, h = hk / K, k = hk - h * K;
+        const int64_t tok = tile * FRONT_U + u;
+        if (tok >= ntok) continue;
+        const int b = (int)(tok / a.T), t = (int)(tok - (int64_t)b * a.T);
+        const float x = IO<T>::ld(reinterpret_cast<const T*>(a.dt) + tok * a.ld_dt + h) + a.dt_bias[h] +
+                        (a.state_dt_offset ? a.state_dt_offset[k] : 0.f);
+        const float p = a.pg ? sigmoidf_(IO<T>::ld(reinterpret_cast<const T*>(a.pg) + tok * a.ld_pg + h)) : 0.f;
+        float w = 1.f, ph = 0.f;
+        if (a.coef) {
+          if (a.phase) ph = IO<T>::ld(reinterpret_cast<const T*>(a.phase) + tok * a.ld_phase + h * K + k);
+          if (a.score) {
+            const T* sc = reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K;
+            float wmax = -INFINITY, wsum = 0.f;
+            for (int kk = 0; kk < K; ++kk) wmax = fmaxf(wmax, IO<T>::ld(sc + kk));
+            for (int kk = 0; kk < K; ++kk) wsum += __expf(IO<T>::ld(sc + kk) - wmax);
+            w = __expf(IO<T>::ld(sc + k) - wmax) / wsum * (float)K;
+          }
+        }
+        float base = sigmoidf_(-x);   // exp(-softplus(x)) = 1 / (1 + e^x)
+        if (a.gamma_floor > 0.f) base = a.gamma_floor + (1.f - a.gamma_floor) * base;
+        const int64_t gi = (((int64_t)k * a.B + b) * H + h) * a.T + t;
+        a.gamma[gi] = base * (1.f - p) + p;
+        if (a.coef) {
+          float sn_, cs_;
+          sincosf(ph, &sn_, &cs_);
+          *reinterpret_cast<float2*>(a.coef + gi * 2) = make_float2(w * cs_, w * sn_);
+        }
+      }
+    }
+    return;
+  }
   for (int64_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
-    for (int idx = threadIdx.x; idx < per_tok; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < per_tok; idx += main_threads) {
       const int h = idx / gph, g = idx - h * gph;
       float re[FRONT_U][3][4], im[FRONT_U][3][4], pgv[FRONT_U];
       float4 c0[FRONT_U], c1[FRONT_U];
@@ -234,8 +287,7 @@ __global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
 #pragma unroll
       for (int u = 0; u < FRONT_U; ++u) {
         if (!on[u]) continue;
-        const float p = a.pg ? sigmoidf_(pgv[u]) : 0.f;
-        const float keep = 1.f - p;
+        const float keep = a.pg ? 1.f - sigmoidf_(pgv[u]) : 1.f;
         const float cs[4] = {c0[u].x, c0[u].z, c1[u].x, c1[u].z};
         const float sn[4] = {c0[u].y, c0[u].w, c1[u].y, c1[u].w};
 #pragma unroll
@@ -253,32 +305,6 @@ __global__ void __launch_bounds__(512) k_pam_front(FrontParams fp) {
         V4<T>::st(reinterpret_cast<T*>(a.q) + dst[u], re[u][0], im[u][0]);
         V4<T>::st(reinterpret_cast<T*>(a.k) + dst[u], re[u][1], im[u][1]);
         V4<T>::st(reinterpret_cast<T*>(a.v) + dst[u], re[u][2], im[u][2]);
-        if (g == 0) {  // per-head scalars of this token: decay per state, read-out weights
-          const int64_t tok = tile * FRONT_U + u;
-          const int b = (int)(tok / a.T), t = (int)(tok - (int64_t)b * a.T);
-          const float dt = IO<T>::ld(reinterpret_cast<const T*>(a.dt) + tok * a.ld_dt + h) + a.dt_bias[h];
-          float wsum = 0.f, wmax = -INFINITY;
-          if (a.score) {
-            for (int k = 0; k < K; ++k) wmax = fmaxf(wmax, IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k));
-            for (int k = 0; k < K; ++k) wsum += __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax);
-          }
-          for (int k = 0; k < K; ++k) {
-            const float x = dt + (a.state_dt_offset ? a.state_dt_offset[k] : 0.f);
-            const float sp = x > 20.f ? x : log1pf(__expf(x));  // softplus
-            float base = __expf(-sp);
-            if (a.gamma_floor > 0.f) base = a.gamma_floor + (1.f - a.gamma_floor) * base;
-            const int64_t gi = (((int64_t)k * a.B + b) * H + h) * a.T + t;
-            a.gamma[gi] = base * (1.f - p) + p;
-            if (a.coef) {
-              float w = 1.f, ph = 0.f;
-              if (a.score) w = __expf(IO<T>::ld(reinterpret_cast<const T*>(a.score) + tok * a.ld_score + h * K + k) - wmax) / wsum * (float)K;
-              if (a.phase) ph = IO<T>::ld(reinterpret_cast<const T*>(a.phase) + tok * a.ld_phase + h * K + k);
-              float sn_, cs_;
-              sincosf(ph, &sn_, &cs_);
-              *reinterpret_cast<float2*>(a.coef + gi * 2) = make_float2(w * cs_, w * sn_);
-            }
-          }
-        }
       }
     }
   }
@@ -299,7 +325,7 @@ extern "C" int qpam_act_gate_packed_fwd(const void* gate_up, int64_t ld, int32_t
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, (unsigned)std::min<int64_t>(N, std::max(1, (148 * 2048) / (xb * threads))));
+  dim3 grid(xb, (unsigned)std::min<int64_t>((N + 1) / 2, std::max(1, (148 * 2048) / (xb * threads))));
 #define QPAM_AG(T)                                                                                                  \
   if (beta) k_act_gate_packed<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C); \
   else k_act_gate_packed<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C);
@@ -353,10 +379,12 @@ extern "C" int qpam_pam_front_fwd(const qpam_front_args* a, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   FrontParams fp{*a};
   const int per_tok = a->H * (a->d / 4);
-  const int threads = pick_threads(per_tok);
+  const int main_threads = std::min(pick_threads(per_tok), 384);
+  const int gate_threads = std::min((FRONT_U * a->H * a->K + 31) / 32 * 32, 128);
+  const int threads = main_threads + gate_threads;
   const int grid = (int)std::min<int64_t>(((int64_t)a->B * a->T + FRONT_U - 1) / FRONT_U, (148 * 2048) / threads);
-  if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp);
-  else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp);
+  if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp, main_threads);
+  else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp, main_threads);
   QPAM_LAUNCH_CHECK("k_pam_front");
   return QPAM_OK;
 }

@@ -54,8 +54,8 @@ __global__ void __launch_bounds__(128) k_cnorm_fwd(const TI* __restrict__ z, con
         float orr[4], oi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mag = fsqrt_(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
-          const float w = mag * frcp_(mag + MAG_EPS) * rrms * s4[j];
+          const MagInv mag_ = mag_inv(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS); const float mag = mag_.mag;
+          const float w = mag * mag_.inv * rrms * s4[j];
           orr[j] = re[cv][j] * w;
           oi[j] = im[cv][j] * w;
         }
@@ -97,9 +97,9 @@ __global__ void __launch_bounds__(128) k_cnorm_bwd(const TI* __restrict__ z, con
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const float m2 = re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS;
-          const float mag = fsqrt_(m2);
+          const MagInv mag_ = mag_inv(m2); const float mag = mag_.mag;
           ss += m2;
-          cs += (gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j]) * s4[j] * (mag * frcp_(mag + MAG_EPS));
+          cs += (gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j]) * s4[j] * (mag * mag_.inv);
         }
       }
     }
@@ -121,12 +121,12 @@ __global__ void __launch_bounds__(128) k_cnorm_bwd(const TI* __restrict__ z, con
         float orr[4], oi[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float mag = fsqrt_(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS);
-          const float inv = frcp_(mag + MAG_EPS);
+          const MagInv mag_ = mag_inv(re[cv][j] * re[cv][j] + im[cv][j] * im[cv][j] + MAG_EPS); const float mag = mag_.mag;
+          const float inv = mag_.inv;
           const float m = mag * inv;
           const float s = gr[cv][j] * re[cv][j] + gi[cv][j] * im[cv][j];
           const float w = m * rrms * s4[j];
-          const float k = s * s4[j] * MAG_EPS * rrms * inv * inv * frcp_(mag) - common;
+          const float k = s * s4[j] * MAG_EPS * rrms * inv * inv * mag_.rmag - common;
           orr[j] = gr[cv][j] * w + re[cv][j] * k;
           oi[j] = gi[cv][j] * w + im[cv][j] * k;
           acc[v][j] += s * m * rrms;
@@ -189,9 +189,9 @@ __global__ void __launch_bounds__(512) k_modact_fwd(const T* __restrict__ z, con
     V4<T>::ld(z + (row * C + g * 4) * 2, re, im);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
+      const MagInv mag_ = mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS); const float mag = mag_.mag;
       const float act = SWISH ? mag * sigmoidf_(be4[j] * mag + b4[j]) : fmaxf(mag + b4[j], 0.f);
-      const float f = act * frcp_(mag + MAG_EPS);
+      const float f = act * mag_.inv;
       re[j] *= f;
       im[j] *= f;
     }
@@ -220,8 +220,8 @@ __global__ void __launch_bounds__(512) k_modact_bwd(const T* __restrict__ z, con
     V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = fsqrt_(re[j] * re[j] + im[j] * im[j] + MAG_EPS);
-      const float inv = frcp_(mag + MAG_EPS);
+      const MagInv mag_ = mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS); const float mag = mag_.mag;
+      const float inv = mag_.inv;
       const float s = gr[j] * re[j] + gi[j] * im[j];
       float act, dact;  // act(|z|) and its derivative
       if (SWISH) {
@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(512) k_modact_bwd(const T* __restrict__ z, con
         ab[j] += on ? s * inv : 0.f;
       }
       const float f = act * inv;
-      const float k = s * (dact * inv - act * inv * inv) * frcp_(mag);
+      const float k = s * (dact * inv - act * inv * inv) * mag_.rmag;
       const float r0 = re[j], i0 = im[j];
       re[j] = gr[j] * f + r0 * k;
       im[j] = gi[j] * f + i0 * k;
@@ -270,8 +270,8 @@ __global__ void __launch_bounds__(512) k_cgu_gate_fwd(const T* __restrict__ gate
     V4<T>::ld(up + row * ld_up + g * 8, ur, ui);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float h = sigmoidf_(mag) * frcp_(mag + MAG_EPS);
+      const MagInv mag_ = mag_inv(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS); const float mag = mag_.mag;
+      const float h = sigmoidf_(mag) * mag_.inv;
       const float pr = ar[j] * ur[j] - ai[j] * ui[j], pi = ar[j] * ui[j] + ai[j] * ur[j];
       ar[j] = pr * h;
       ai[j] = pi * h;
@@ -296,8 +296,8 @@ __global__ void __launch_bounds__(512) k_cgu_gate_bwd(const T* __restrict__ gate
     V4<T>::ld(dout + (row * C + g * 4) * 2, gr, gi);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float mag = fsqrt_(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS);
-      const float inv = frcp_(mag + MAG_EPS);
+      const MagInv mag_ = mag_inv(ar[j] * ar[j] + ai[j] * ai[j] + MAG_EPS); const float mag = mag_.mag;
+      const float inv = mag_.inv;
       const float sg = sigmoidf_(mag);
       const float h = sg * inv;
       const float dh = sg * (1.f - sg) * inv - sg * inv * inv;
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(512) k_cgu_gate_bwd(const T* __restrict__ gate
       // d(up) = conj(gate) dout h ;  d(gate) = conj(up) dout h + gate s h'(|gate|) / |gate|
       dur[j] = h * (ar[j] * gr[j] + ai[j] * gi[j]);
       dui[j] = h * (ar[j] * gi[j] - ai[j] * gr[j]);
-      const float k = s * dh * frcp_(mag);
+      const float k = s * dh * mag_.rmag;
       const float dgr = h * (ur[j] * gr[j] + ui[j] * gi[j]) + ar[j] * k;
       const float dgi = h * (ur[j] * gi[j] - ui[j] * gr[j]) + ai[j] * k;
       ar[j] = dgr;

@@ -79,6 +79,24 @@ __device__ __forceinline__ float warp_sum(float v) {
 // these kernels do ~10 of them per 8 bytes moved.
 __device__ __forceinline__ float frcp_(float x) { return __fdividef(1.f, x); }
 __device__ __forceinline__ float fsqrt_(float x) { return x * rsqrtf(x); }  // x >= 1e-8 here, never 0
+// |z|, 1/(|z| + 1e-8) and 1/|z| of m2 = re^2 + im^2 + 1e-8 from ONE special-function instruction:
+// with rs = rsqrt(m2):  |z| = m2 rs,  1/(|z| + e) = rs / (1 + e rs) = rs (1 - t + t^2 - ...), t = e rs <= 1e-4
+// (m2 >= 1e-8), so the two kept terms leave an error below 1e-12.  These kernels are otherwise bound by the
+// special-function unit (16 results per clock per SM), not by HBM.
+struct MagInv {
+  float mag, inv, rmag;
+};
+__device__ __forceinline__ MagInv mag_inv(float m2) {
+  const float rs = rsqrtf(m2);
+  const float t = MAG_EPS * rs;
+  return {m2 * rs, rs * (1.f - t + t * t), rs};
+}
+// sigmoid from one special-function instruction (tanh.approx, abs. error ~5e-4): for results stored as bf16
+__device__ __forceinline__ float sigmoid_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(0.5f * x));
+  return fmaf(0.5f, y, 0.5f);
+}
 __device__ __forceinline__ float sigmoidf_(float x) { return frcp_(1.f + __expf(-x)); }
 
 // Threads per CTA for kernels whose threads each own one group of 4 channels: the largest multiple of 32
