@@ -83,12 +83,23 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
   if (!L.valid) return;
   const int h = blockIdx.y;
   const bool has_state = LOWER ? ((L.c > 0) || (p.s0 != nullptr)) : ((L.c < L.nc - 1) || (p.ds_final != nullptr));
+  const int row0 = (L.b * p.H + h) * p.T + L.t0;
   if (tid == 0) {
     mbar_init(&bars[0], 1);
     mbar_init(&bars[1], 1);
     mbar_init(&bars[2], 1);
     fence_barrier_init();
+    // the token tiles are requested first: the prologue below (TMEM allocation, cumulative decay, factors,
+    // carried-state prefetch) runs while they are in flight
+    mbar_arrive_expect_tx(&bars[0], 6 * 16384);
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      tma_load_2d(RA + kb * 16384, &maps.a1, &bars[0], kb * 64, row0);
+      tma_load_2d(RB + kb * 16384, &maps.b1, &bars[0], kb * 64, row0);
+      tma_load_2d(RC + kb * 16384, &maps.x2, &bars[0], kb * 64, row0);
+    }
   }
+  __syncwarp();
   if (warp == 0) tmem_alloc<256>(tmem_slot);
   if (warp == 1) warp_cumsum128(Acum, p.gamma + gamma_base(p, 0, L.b, h, L.t0), L.len, p.eps, lane);
   tc_fence_before();
@@ -108,16 +119,6 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
     }
   }
   const float st_cst = LOWER ? cexp(a_mid) : cexp(a_last - a_mid);
-  const int row0 = (L.b * p.H + h) * p.T + L.t0;
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&bars[0], 6 * 16384);
-#pragma unroll
-    for (int kb = 0; kb < 2; ++kb) {
-      tma_load_2d(RA + kb * 16384, &maps.a1, &bars[0], kb * 64, row0);
-      tma_load_2d(RB + kb * 16384, &maps.b1, &bars[0], kb * 64, row0);
-      tma_load_2d(RC + kb * 16384, &maps.x2, &bars[0], kb * 64, row0);
-    }
-  }
   // carried state, fetched early and kept as packed bf16 (4 complex per item, 4 items per thread)
   uint32_t st_r[4][2], st_i[4][2];
   if (has_state) {
