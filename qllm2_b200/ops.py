@@ -161,6 +161,42 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
 
 
 @torch.no_grad()
+def pam_scan_states(k, v, gamma, s0=None, cu_seqlens=None, *, eps: float = GAMMA_EPS, chunk: int = 64):
+    """Final state(s) of the scan only -- S after the last token, float32 [K,S,H,d,d,2] -- without forming Y:
+    the chunk-local sums and the inter-chunk carry run, the output kernel does not (about a third of a forward
+    scan).  k, v [B,H,T,d,2]; gamma [B,H,T] or [K,B,H,T]; s0 / cu_seqlens as in `pam_scan`."""
+    L = _lib.lib()
+    _require_cuda(k, v, gamma)
+    if gamma.dim() == 3:
+        gamma = gamma.unsqueeze(0)
+    if k.dtype != v.dtype:
+        dt = torch.promote_types(k.dtype, v.dtype)
+        k, v = k.to(dt), v.to(dt)
+    k, v = k.contiguous(), v.contiguous()
+    gamma = gamma.float().contiguous()
+    B, H, T, d = k.shape[:4]
+    K = gamma.shape[0]
+    if k.shape != v.shape or k.dim() != 5 or k.shape[-1] != 2 or tuple(gamma.shape) != (K, B, H, T):
+        raise _lib.QPamError(f"pam_scan_states: k/v must be one [B,H,T,d,2] shape and gamma [K,B,H,T]; got {tuple(k.shape)}, "
+                             f"{tuple(v.shape)}, {tuple(gamma.shape)}")
+    if cu_seqlens is not None:
+        if B != 1:
+            raise _lib.QPamError("packed mode (cu_seqlens) needs B == 1")
+        cu_seqlens = cu_seqlens.to(device=k.device, dtype=torch.int32).contiguous()
+    S = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    if s0 is not None:
+        if s0.numel() != K * S * H * d * d * 2:
+            raise _lib.QPamError(f"s0 must be [K,S,H,d,d,2] = {(K, S, H, d, d, 2)}, got {tuple(s0.shape)}")
+        s0 = s0.float().contiguous()
+    s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=k.device)
+    a = _scan_args(k, k, v, gamma, None, s0, cu_seqlens, None, s_final, d ** -0.5, eps, chunk)   # q is not read
+    ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 0), k.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(L.qpam_scan_fwd(C.byref(a), stream_ptr()), "qpam_scan_fwd")
+    return s_final
+
+
+@torch.no_grad()
 def pam_scan_tokens(q, k, v, gamma, coef=None, s0=None, cu_seqlens=None, *, head_dim=None, eps: float = 1e-6,
                     chunk: int = 64):
     """Inference form of `pam_scan`: same arguments, but Y comes back token-major, [B, T, H*d, 2] -- the layout

@@ -198,3 +198,19 @@ def test_large_property_linearity_in_v():
     y3, s3 = ops.pam_scan(q.float(), k.float(), (v.float() + 2 * v2.float()), gam)
     assert_close(y3.cpu().numpy(), (y1 + 2 * y2).cpu().numpy(), 1e-4, "linearity Y")
     assert_close(s3.cpu().numpy(), (s1 + 2 * s2).cpu().numpy(), 1e-4, "linearity S")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_states_only_scan_equals_the_full_scan_state(dtype):
+    """`pam_scan_states` (no output kernel) returns the state `pam_scan` returns, batch and packed."""
+    from qllm2_b200 import ops
+    g = torch.Generator().manual_seed(17)
+    B, H, T, d, K = 2, 2, 300, 64, 2
+    k, v, q = (torch.randn(B, H, T, d, 2, generator=g).mul(0.125).to("cuda").to(dtype) for _ in range(3))
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=g) + 3).to("cuda")
+    s0 = (torch.randn(K, B, H, d, d, 2, generator=g) * 0.1).to("cuda")
+    _, s_ref = ops.pam_scan(q, k, v, gamma, s0=s0)
+    assert torch.equal(ops.pam_scan_states(k, v, gamma, s0=s0), s_ref)
+    cu = torch.tensor([0, 120, 120, 300], dtype=torch.int32)
+    _, s_ref = ops.pam_scan(q[:1], k[:1], v[:1], gamma[:, :1], cu_seqlens=cu)
+    assert torch.equal(ops.pam_scan_states(k[:1], v[:1], gamma[:, :1], cu_seqlens=cu), s_ref)

@@ -84,3 +84,61 @@ def test_vocab_parallel_stats_two_ranks():
     ret = mgr.dict()
     mp.spawn(_rank_main, args=(2, port, 101, ret), nprocs=2, join=True)
     assert ret["lse_err"] < 1e-12 and ret["loss_err"] < 1e-12 and ret["argmax_ok"]
+
+
+# ------------------------------------------------------------------ sequence-parallel prefill (2 gloo ranks)
+def _oracle_scan(q, k, v, gamma, coef=None, s0=None, head_dim=None, eps=1e-6, chunk=64):
+    from oracle import pam_oracle as po
+    cz = None if coef is None else po.to_complex(coef.numpy())
+    sz = None if s0 is None else po.to_complex(s0.double().numpy())
+    Y, S = po.scan_recurrence(po.to_complex(q.numpy()), po.to_complex(k.numpy()), po.to_complex(v.numpy()), gamma.numpy(),
+                              head_dim=head_dim, eps=eps, s0=sz, coef=cz)
+    return torch.from_numpy(po.to_split(Y)), torch.from_numpy(po.to_split(S))
+
+
+def _oracle_states(k, v, gamma, eps=1e-6, chunk=64):
+    return _oracle_scan(torch.zeros_like(k), k, v, gamma, eps=eps)[1]
+
+
+def _seqpar_rank(rank, world, port, ret):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from qllm2_b200.seq_parallel import pam_scan_sequence_parallel
+    gen = torch.Generator().manual_seed(0)
+    B, H, T, d, K = 2, 2, 23, 4, 3
+    q, k, v = (torch.randn(B, H, T, d, 2, generator=gen, dtype=torch.float64) * 0.5 for _ in range(3))
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=gen, dtype=torch.float64) + 2)
+    coef = torch.randn(K, B, H, T, 2, generator=gen, dtype=torch.float64)
+    s0 = torch.randn(K, B, H, d, d, 2, generator=gen, dtype=torch.float64) * 0.1
+    cut = [0, 9, T]                                                   # ragged split: 9 and 14 tokens
+    sl = slice(cut[rank], cut[rank + 1])
+    y, s = pam_scan_sequence_parallel(q[:, :, sl], k[:, :, sl], v[:, :, sl], gamma[..., sl], coef=coef[:, :, :, sl], s0=s0,
+                                      scan=_oracle_scan, scan_states=_oracle_states)
+    y_full, s_full = _oracle_scan(q, k, v, gamma, coef=coef, s0=s0)
+    ret[f"y{rank}"] = float((y - y_full[:, :, sl]).abs().max())
+    if rank == world - 1:
+        ret["s"] = float((s.double() - s_full).abs().max())
+    dist.destroy_process_group()
+
+
+def test_sequence_parallel_prefill_two_ranks():
+    """Two segments of one sequence, (decay, state) exchanged once: outputs and final state equal the
+    unsplit scan (oracle arithmetic, float64)."""
+    ret = mp.Manager().dict()
+    mp.spawn(_seqpar_rank, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["y0"] < 1e-6 and ret["y1"] < 1e-6 and ret["s"] < 1e-6, dict(ret)
+
+
+def test_fold_segment_states_is_the_linear_recurrence():
+    from qllm2_b200.seq_parallel import fold_segment_states, segment_decay
+    gen = torch.Generator().manual_seed(1)
+    W = 4
+    states = torch.randn(W, 2, 1, 3, 2, 2, 2, generator=gen, dtype=torch.float64)
+    decays = torch.rand(W, 2, 1, 3, generator=gen, dtype=torch.float64)
+    s0 = torch.randn(2, 1, 3, 2, 2, 2, generator=gen, dtype=torch.float64)
+    cur = s0.clone()
+    for r in range(W):
+        assert torch.allclose(fold_segment_states(states, decays, r, s0), cur)
+        cur = cur * decays[r][..., None, None, None] + states[r]
+    g = torch.rand(2, 1, 3, 50, generator=gen) * 0.5 + 0.5
+    assert torch.allclose(segment_decay(g, 1e-6), (g.double() + 1e-6).prod(-1).float(), rtol=1e-5)
