@@ -188,6 +188,10 @@ def pam_scan_states(k, v, gamma, s0=None, cu_seqlens=None, *, eps: float = GAMMA
         if s0.numel() != K * S * H * d * d * 2:
             raise _lib.QPamError(f"s0 must be [K,S,H,d,d,2] = {(K, S, H, d, d, 2)}, got {tuple(s0.shape)}")
         s0 = s0.float().contiguous()
+    if K > 1 and k.dtype == torch.bfloat16 and d == 64:
+        # one state at a time, as `pam_scan` does for this case: the tensor-core kernels take a single state
+        return torch.cat([pam_scan_states(k, v, gamma[kk:kk + 1], None if s0 is None else s0.reshape(K, S, H, d, d, 2)[kk:kk + 1],
+                                          cu_seqlens, eps=eps, chunk=chunk) for kk in range(K)], dim=0)
     s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=k.device)
     a = _scan_args(k, k, v, gamma, None, s0, cu_seqlens, None, s_final, d ** -0.5, eps, chunk)   # q is not read
     ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 0), k.device)

@@ -30,6 +30,11 @@ class Request:
     max_new_tokens: int
     generated: List[int] = field(default_factory=list)
     slot: int = -1
+    prefilled: int = 0          # prompt tokens already absorbed into the slot's state
+
+    @property
+    def prefilling(self) -> bool:
+        return self.prefilled < len(self.prompt)
 
     @property
     def position(self) -> int:
@@ -44,11 +49,17 @@ class Request:
 class SlotScheduler:
     """Admission and retirement of sequences over a fixed number of state slots."""
 
-    def __init__(self, n_slots: int, max_prefill_tokens: int = 1 << 17):
+    def __init__(self, n_slots: int, max_prefill_tokens: int = 1 << 17, chunked_prefill: bool = False):
+        """chunked_prefill=True lets a prompt be absorbed in pieces of at most `max_prefill_tokens` per engine
+        step (the next piece starts from the state the previous one left in the slot), so one long prompt
+        cannot stall the decode steps of the other sequences; False admits whole prompts only."""
         if n_slots <= 0:
             raise ValueError("n_slots must be positive")
+        if max_prefill_tokens <= 0:
+            raise ValueError("max_prefill_tokens must be positive")
         self.n_slots = n_slots
         self.max_prefill_tokens = max_prefill_tokens
+        self.chunked_prefill = chunked_prefill
         self.free: Deque[int] = deque(range(n_slots))
         self.waiting: Deque[Request] = deque()
         self.live: Dict[int, Request] = {}       # slot -> request
@@ -77,6 +88,27 @@ class SlotScheduler:
             tokens += len(nxt.prompt)
         return batch
 
+    def plan_prefill(self):
+        """Prefill work of one engine step as (request, first prompt token, token count) items.  Whole prompts
+        when `chunked_prefill` is off; otherwise sequences already in a slot continue first, then waiting ones
+        are admitted, all within the token budget (a piece may end mid-prompt)."""
+        if not self.chunked_prefill:
+            return [(r, 0, len(r.prompt)) for r in self.admit()]
+        items, budget = [], self.max_prefill_tokens
+        for r in self.live_requests():
+            if r.prefilling and budget > 0:
+                take = min(len(r.prompt) - r.prefilled, budget)
+                items.append((r, r.prefilled, take))
+                budget -= take
+        while self.waiting and self.free and budget > 0:
+            r = self.waiting.popleft()
+            r.slot = self.free.popleft()
+            self.live[r.slot] = r
+            take = min(len(r.prompt), budget)
+            items.append((r, 0, take))
+            budget -= take
+        return items
+
     def retire_finished(self) -> List[Request]:
         out = [r for r in self.live.values() if r.done]
         for r in out:
@@ -98,11 +130,12 @@ class _PrefillMix:
     """Sequence mixing at prefill: the packed ragged scan; final states go to the sequences' slots."""
     q_scale = 1.0     # the scan applies head_dim^-0.5 itself
 
-    def __init__(self, eng, cu, slots):
-        self.eng, self.cu, self.slots = eng, cu, slots
+    def __init__(self, eng, cu, slots, s0_of=None):
+        self.eng, self.cu, self.slots, self.s0_of = eng, cu, slots, s0_of
 
     def __call__(self, layer, q, k, v, gamma, coef):
-        y, s = ops.pam_scan_tokens(q, k, v, gamma, coef=coef, cu_seqlens=self.cu, head_dim=q.shape[3])
+        y, s = ops.pam_scan_tokens(q, k, v, gamma, coef=coef, cu_seqlens=self.cu, head_dim=q.shape[3],
+                                   s0=None if self.s0_of is None else self.s0_of(layer))
         ops.pam_pool_store(self.eng.pool, self.slots, s, layer=layer)
         return y.view(q.shape[2], -1)
 
@@ -127,12 +160,14 @@ class ContinuousBatcher:
 
     def __init__(self, model: V11LM, n_slots: int, state_dtype: Optional[torch.dtype] = None,
                  max_prefill_tokens: int = 1 << 17, cuda_graph: bool = False, max_position: int = 8192,
-                 fused: bool = True):
+                 fused: bool = True, chunked_prefill: bool = False):
         """cuda_graph=True captures the decode step once for a full batch of n_slots rows (idle rows carry
         slot id -1, which the step kernel skips) and replays it every step: the per-token cost is then the
         kernels', not the launches' of the Python layer loop.  fused=True runs the blocks through
         `FusedForward` (packed weights, ~10 launches per layer) when the configuration allows it;
-        fused=False keeps the module path (`V11Block` operators)."""
+        fused=False keeps the module path (`V11Block` operators).  chunked_prefill=True absorbs prompts in
+        pieces of at most max_prefill_tokens per step, each piece scanned from the state its predecessor left in
+        the slot (the streaming use of the reference's stateful forward, v11/duplex/infer_stream.py:101-102)."""
         self.model = model.eval()
         cfg = model.config
         p = next(model.parameters())
@@ -140,7 +175,7 @@ class ContinuousBatcher:
         self.state_dtype = state_dtype or (torch.float32 if p.dtype == torch.float32 else torch.bfloat16)
         self.pool = torch.zeros(n_slots, cfg.n_layers, cfg.n_states, cfg.n_heads, cfg.head_dim, cfg.head_dim, 2,
                                 dtype=self.state_dtype, device=self.device)
-        self.sched = SlotScheduler(n_slots, max_prefill_tokens)
+        self.sched = SlotScheduler(n_slots, max_prefill_tokens, chunked_prefill=chunked_prefill)
         self.steps = 0
         self.decoded_tokens = 0
         self.n_slots = n_slots
@@ -173,25 +208,35 @@ class ContinuousBatcher:
                                         persistent=False)
 
     @torch.no_grad()
-    def _prefill(self, batch: List[Request]):
-        m = self.model
-        lens = [len(r.prompt) for r in batch]
-        self._ensure_rope(max(lens))
-        ids = torch.tensor([t for r in batch for t in r.prompt], dtype=torch.long, device=self.device)[None]
-        positions = torch.cat([torch.arange(n, device=self.device) for n in lens])[None]
-        cu = torch.zeros(len(batch) + 1, dtype=torch.int32)
+    def _prefill(self, items):
+        """items: (request, first prompt token, token count).  A piece that starts mid-prompt is scanned from the
+        state its predecessor left in the slot; a request emits its first token when its last piece is done."""
+        lens = [take for _, _, take in items]
+        self._ensure_rope(max(st + take for _, st, take in items))
+        ids = torch.tensor([t for r, st, take in items for t in r.prompt[st:st + take]], dtype=torch.long, device=self.device)[None]
+        positions = torch.cat([torch.arange(st, st + take, device=self.device) for _, st, take in items])[None]
+        cu = torch.zeros(len(items) + 1, dtype=torch.int32)
         cu[1:] = torch.tensor(lens).cumsum(0).int()
         cu = cu.to(self.device)
-        slots = torch.tensor([r.slot for r in batch], dtype=torch.int32, device=self.device)
+        slots = torch.tensor([r.slot for r, _, _ in items], dtype=torch.int32, device=self.device)
+        s0_of = None
+        if any(st > 0 for _, st, _ in items):
+            resumed = torch.tensor([1.0 if st > 0 else 0.0 for _, st, _ in items], device=self.device)
+
+            def s0_of(layer):      # [K,S,H,d,d,2] float32; fresh sequences start from zero whatever the slot held
+                s = self.pool[slots.long(), layer].float() * resumed[:, None, None, None, None, None]
+                return s.permute(1, 0, 2, 3, 4, 5).contiguous()
         if self.ff is not None:
-            xn = self.ff.hidden(ids, _PrefillMix(self, cu, slots), positions=positions)
+            xn = self.ff.hidden(ids, _PrefillMix(self, cu, slots, s0_of), positions=positions)
             nxt = self.ff.greedy_next(self.ff.head_hidden(xn[(cu[1:] - 1).long()]))
         else:
-            nxt = self._prefill_modules(ids, positions, cu, slots)
-        for r, t in zip(batch, nxt.tolist()):
-            r.generated.append(int(t))
+            nxt = self._prefill_modules(ids, positions, cu, slots, s0_of)
+        for (r, st, take), t in zip(items, nxt.tolist()):
+            r.prefilled = st + take
+            if not r.prefilling:
+                r.generated.append(int(t))
 
-    def _prefill_modules(self, ids, positions, cu, slots):
+    def _prefill_modules(self, ids, positions, cu, slots, s0_of=None):
         m = self.model
         z = m.embed_norm(m.embed(ids))
         for li, blk in enumerate(m.blocks):
@@ -200,7 +245,8 @@ class ContinuousBatcher:
             pam = blk.pam
             q, k, vprime, gamma = pam.project_gated(xn, positions=positions)
             coef = pam._coef(xn)
-            y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, cu_seqlens=cu, head_dim=pam.head_dim)
+            y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, cu_seqlens=cu, head_dim=pam.head_dim,
+                                s0=None if s0_of is None else s0_of(li))
             ops.pam_pool_store(self.pool, slots, s, layer=li)
             out = pam.o_proj(y.transpose(1, 2).contiguous().view(1, ids.shape[1], pam.inner_dim, 2))
             z = z + out * blk.pam_scale
@@ -267,8 +313,8 @@ class ContinuousBatcher:
     def step(self) -> int:
         """Admit + prefill waiting sequences, then advance every live sequence by one token."""
         self.sched.retire_finished()
-        live_before = [r for r in self.sched.live_requests() if not r.done]
-        batch = self.sched.admit()
+        live_before = [r for r in self.sched.live_requests() if not r.done and not r.prefilling]
+        batch = self.sched.plan_prefill()
         if batch:
             self._prefill(batch)
         if live_before:

@@ -139,3 +139,22 @@ def test_generate_on_the_packed_forward_equals_the_module_loop(variant):
     eos = int(slow[0, 21])
     stopped = net.generate(ids[:1], max_new_tokens=9, temperature=0.0, eos_token_id=eos)
     assert stopped.shape[1] == 22
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_chunked_prefill_equals_whole_prefill(fused):
+    """Prompts absorbed in pieces of at most 16 tokens per step (each piece scanned from the state its
+    predecessor left in the slot) decode to the same ids as whole-prompt prefill."""
+    net = _net(VARIANTS["k3_compete_routed"])
+    gen = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, 257, (int(n),), generator=gen).tolist() for n in (70, 5, 33, 16, 41)]
+    outs = []
+    for chunked in (True, False):
+        eng = ContinuousBatcher(net, n_slots=3, fused=fused, max_position=512, chunked_prefill=chunked,
+                                max_prefill_tokens=16 if chunked else 1 << 16)
+        rids = [eng.submit(p, 5) for p in prompts]
+        res = eng.run()
+        outs.append([res[r] for r in rids])
+        if chunked:
+            assert eng.steps > 10           # 165 prompt tokens at 16 per step
+    assert outs[0] == outs[1]

@@ -142,3 +142,31 @@ def test_fold_segment_states_is_the_linear_recurrence():
         cur = cur * decays[r][..., None, None, None] + states[r]
     g = torch.rand(2, 1, 3, 50, generator=gen) * 0.5 + 0.5
     assert torch.allclose(segment_decay(g, 1e-6), (g.double() + 1e-6).prod(-1).float(), rtol=1e-5)
+
+
+def test_scheduler_chunked_prefill_plan():
+    """With chunked prefill a prompt longer than the budget is absorbed over several steps, resumed pieces
+    first, and the budget is never exceeded."""
+    s = SlotScheduler(n_slots=2, max_prefill_tokens=25, chunked_prefill=True)
+    a, b, c = s.submit([0] * 40, 1), s.submit([0] * 10, 1), s.submit([0] * 7, 1)
+    plan = s.plan_prefill()
+    assert [(r.rid, st, n) for r, st, n in plan] == [(a, 0, 25)]          # budget spent on the first piece
+    for r, st, n in plan:
+        r.prefilled = st + n
+    plan = s.plan_prefill()
+    assert [(r.rid, st, n) for r, st, n in plan] == [(a, 25, 15), (b, 0, 10)]
+    for r, st, n in plan:
+        r.prefilled = st + n
+    assert s.plan_prefill() == []                                          # both slots taken, nothing left to prefill
+    assert not s.live[0].prefilling and not s.live[1].prefilling and len(s.waiting) == 1
+    for r in s.live_requests():
+        r.generated.append(1)
+    s.retire_finished()
+    assert [(r.rid, st, n) for r, st, n in s.plan_prefill()] == [(c, 0, 7)]
+    # whole-prompt mode keeps the old contract
+    w = SlotScheduler(n_slots=4, max_prefill_tokens=25)
+    for n in (10, 10, 10):
+        w.submit([0] * n, 1)
+    assert [(st, n) for _, st, n in w.plan_prefill()] == [(0, 10), (0, 10)]
+    with pytest.raises(ValueError):
+        SlotScheduler(1, max_prefill_tokens=0)
