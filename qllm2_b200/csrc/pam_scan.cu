@@ -4,6 +4,7 @@
 #include "pam_scan_chunk.cuh"
 #include "pam_scan_tc.cuh"
 #include "pam_scan_tc2.cuh"
+#include "pam_scan_tc3.cuh"
 #include "tma_host.cuh"
 
 namespace qpam {
@@ -25,7 +26,13 @@ static bool tc_fwd_eligible(const qpam_scan_args* a) {
          (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->y) & 15) == 0 &&
          (int64_t)a->B * a->H * a->T < ((int64_t)1 << 31);
 }
-static int fwd_chunk_len(const qpam_scan_args* a) { return tc_fwd_eligible(a) ? tcs::TC : CH; }
+// bf16 / d = 64 / 2..4 phase-routed states: forward on the fused K-state tensor-core kernel
+static bool tc_fwdK_eligible(const qpam_scan_args* a) {
+  return a->io_dtype == QPAM_BF16 && a->d == 64 && a->K >= 2 && a->K <= QPAM_MAX_STATES &&
+         (((uintptr_t)a->q | (uintptr_t)a->k | (uintptr_t)a->v | (uintptr_t)a->y) & 15) == 0 &&
+         (int64_t)a->B * a->H * a->T < ((int64_t)1 << 31);
+}
+static int fwd_chunk_len(const qpam_scan_args* a) { return (tc_fwd_eligible(a) || tc_fwdK_eligible(a)) ? tcs::TC : CH; }
 
 static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   ScanLayout L{};
@@ -145,10 +152,10 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   if (L.grid_chunks > 0) {
     int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
+    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H, a->K), 256, tcs::OUTER_SMEM, st>>>(p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
   }
-  k_state_scan<false><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
+  k_state_scan<false><<<dim3(a->S, a->H * a->K, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
   QPAM_LAUNCH_CHECK("k_state_scan<fwd>");
   return QPAM_OK;
 }
@@ -183,6 +190,28 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
   if (L.grid_chunks > 0 && a->y != nullptr) {
     rc = tc_chunk2_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
     if (rc) return rc;
+  }
+  return QPAM_OK;
+}
+
+// bf16 / d = 64 / K = 2..4 states: state sums and carry per state, then ONE fused output kernel
+static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  if (a->cu_seqlens != nullptr) {
+    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+    QPAM_LAUNCH_CHECK("k_chunk_prefix");
+  }
+  int rc = tc_states(p, L, a, st);
+  if (rc) return rc;
+  if (L.grid_chunks > 0 && a->y != nullptr) {
+    tcs::ChunkMaps maps;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = set_smem(tcs::k_tc_chunk_fwdK, tcs::CHUNKK_SMEM))) return rc;
+    tcs::k_tc_chunk_fwdK<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNKK_SMEM, st>>>(maps, p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_fwdK");
   }
   return QPAM_OK;
 }
@@ -297,7 +326,7 @@ extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) {
   }
   QPAM_REQUIRE(a->y != nullptr || a->s_final != nullptr, "scan fwd: both y and s_final are NULL");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (L.ch == tcs::TC) return scan_fwd_tc(a, L, st);
+  if (L.ch == tcs::TC) return tc_fwdK_eligible(a) ? scan_fwd_tcK(a, L, st) : scan_fwd_tc(a, L, st);
   QPAM_DISPATCH_SCAN(scan_fwd_t, a, L, st);
 }
 

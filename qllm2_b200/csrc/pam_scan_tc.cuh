@@ -74,6 +74,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
   const int h = blockIdx.y;
+  const int kst = blockIdx.z;                 // state (its decay weights the rows); grid z = K
   const size_t tb = token_base(p, L.b, h, L.t0, TD);
   const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.q : p.k) + tb);
   const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.dy : p.v) + tb);
@@ -94,7 +95,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
     fence_barrier_init();
   }
   if (warp == 0) tmem_alloc<64>(tmem_slot);
-  if (warp == 1) warp_cumsum128(Acum, p.gamma + gamma_base(p, 0, L.b, h, L.t0), L.len, p.eps, lane);
+  if (warp == 1) warp_cumsum128(Acum, p.gamma + gamma_base(p, kst, L.b, h, L.t0), L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -142,15 +143,15 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
   tc_fence_after();
   if (ok) {
     // lane n' = 2j+c of the tile holds column i: state[i][j][c] sits at float offset i*128 + n'
-    float2* slot = DSTATE ? p.dstates + state_base(p, 0, h, L.slot0 + L.c, TD)
-                          : p.states + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    float2* slot = DSTATE ? p.dstates + state_base(p, kst, h, L.slot0 + L.c, TD)
+                          : p.states + state_base(p, kst, h, L.slot0 + L.c + 1, TD);
     const int q4 = warp & 3, cc = warp >> 2;   // TMEM lane quarter, column half
     float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
     float v[32];
     tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + cc * 32, v);
 #pragma unroll
     for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
-    if (!DSTATE && tid == 0) p.chunk_decay[(size_t)h * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
+    if (!DSTATE && tid == 0) p.chunk_decay[((size_t)kst * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
   }
   tc_fence_before();
   __syncthreads();

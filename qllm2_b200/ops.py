@@ -138,7 +138,8 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
     if cu_seqlens is not None:
         cu_seqlens = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
     K = gamma.shape[0]
-    if K > 1 and q.dtype == torch.bfloat16 and d == 64:
+    needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, gamma, coef, s0))
+    if K > 1 and q.dtype == torch.bfloat16 and d == 64 and needs_grad:
         # Phase-routed K-state scan on the tensor-core kernels: y = sum_k c_k y^(k), where y^(k) is the
         # single-state scan with decay gamma^(k) on the same q, k, v (the fused K-state form of the
         # reference, v11/model.py:657-781, is algebraically this sum).  autograd composes the backward:
@@ -188,10 +189,6 @@ def pam_scan_states(k, v, gamma, s0=None, cu_seqlens=None, *, eps: float = GAMMA
         if s0.numel() != K * S * H * d * d * 2:
             raise _lib.QPamError(f"s0 must be [K,S,H,d,d,2] = {(K, S, H, d, d, 2)}, got {tuple(s0.shape)}")
         s0 = s0.float().contiguous()
-    if K > 1 and k.dtype == torch.bfloat16 and d == 64:
-        # one state at a time, as `pam_scan` does for this case: the tensor-core kernels take a single state
-        return torch.cat([pam_scan_states(k, v, gamma[kk:kk + 1], None if s0 is None else s0.reshape(K, S, H, d, d, 2)[kk:kk + 1],
-                                          cu_seqlens, eps=eps, chunk=chunk) for kk in range(K)], dim=0)
     s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=k.device)
     a = _scan_args(k, k, v, gamma, None, s0, cu_seqlens, None, s_final, d ** -0.5, eps, chunk)   # q is not read
     ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 0), k.device)
@@ -205,18 +202,8 @@ def pam_scan_tokens(q, k, v, gamma, coef=None, s0=None, cu_seqlens=None, *, head
                     chunk: int = 64):
     """Inference form of `pam_scan`: same arguments, but Y comes back token-major, [B, T, H*d, 2] -- the layout
     the output projection reads (the head merge of v11/model.py:835-836) -- and nothing is kept for a backward
-    pass.  With K phase-routed states in bf16 at d = 64 the merge is folded into the read-out kernel."""
-    K = gamma.shape[0] if gamma.dim() == 4 else 1
+    pass (K phase-routed states in bf16 at d = 64 then run the fused K-state output kernel)."""
     B, H, T, d = q.shape[:4]
-    if K > 1 and coef is not None and q.dtype == torch.bfloat16 and d == 64 and q.is_cuda:
-        from .fused_elementwise import state_combine_tokens
-        ys, finals = [], []
-        for kk in range(K):
-            yk, sk = pam_scan(q, k, v, gamma[kk:kk + 1], s0=None if s0 is None else s0[kk:kk + 1], cu_seqlens=cu_seqlens,
-                              head_dim=head_dim, eps=eps, chunk=chunk)
-            ys.append(yk)
-            finals.append(sk)
-        return state_combine_tokens(coef, ys), torch.cat(finals, dim=0)
     y, s = pam_scan(q, k, v, gamma, coef=coef, s0=s0, cu_seqlens=cu_seqlens, head_dim=head_dim, eps=eps, chunk=chunk)
     return y.transpose(1, 2).reshape(B, T, H * d, 2), s
 

@@ -133,3 +133,57 @@ def test_multistate_bf16_on_tensor_cores(golden_dir):
     assert_close(dv.float().cpu().numpy(), po.to_split(b["dv"]), TOL, "dv")
     assert_close(dgam.cpu().numpy(), b["dgamma"], TOL, "dgamma")
     assert_close(dcoef.cpu().numpy(), po.to_split(b["dcoef"]), TOL, "dcoef")
+
+
+def _k_state_inputs(B, H, T, K, seed):
+    inp = synthetic.scan_inputs(B, H, T, 64, seed=seed, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(seed + 1)
+    shift = torch.tensor([1.0, 3.0, 5.0, 2.0])[:K].view(K, 1, 1, 1)
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=gen) + shift)
+    phase = torch.randn(K, B, H, T, generator=gen)
+    alpha = 0.5 + torch.rand(K, B, H, T, generator=gen)
+    coef = torch.stack([alpha * torch.cos(phase), alpha * torch.sin(phase)], dim=-1)
+    return inp, gamma, coef
+
+
+@pytest.mark.parametrize("K,B,H,T", [(3, 1, 2, 300), (2, 2, 1, 128), (4, 1, 1, 515), (3, 2, 3, 1), (2, 1, 2, 77)])
+def test_fused_k_state_forward(K, B, H, T):
+    """Inference (no gradient needed): K states in ONE output kernel against the fp64 oracle, with and without
+    read-out weights and an initial state."""
+    inp, gamma, coef = _k_state_inputs(B, H, T, K, seed=70 + T)
+    gen = torch.Generator().manual_seed(5)
+    s0 = torch.randn(K, B, H, 64, 64, 2, generator=gen) * 0.05
+    qc, kc, vc = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v))
+    for use_coef, use_s0 in ((True, False), (True, True), (False, False)):
+        with torch.no_grad():
+            y, s = ops.pam_scan(inp.q.to(DEV), inp.k.to(DEV), inp.v.to(DEV), gamma.to(DEV),
+                                coef=coef.to(DEV) if use_coef else None, s0=s0.to(DEV) if use_s0 else None)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        y_ref, s_ref = po.scan_recurrence(qc, kc, vc, gamma.double().numpy(),
+                                          coef=po.to_complex(coef.numpy()) if use_coef else None,
+                                          s0=po.to_complex(s0.numpy()) if use_s0 else None)
+        assert_close(y.float().cpu().numpy(), po.to_split(y_ref), TOL, f"Y coef={use_coef} s0={use_s0}")
+        assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S")
+        assert rel_err(y.float().cpu().numpy(), po.to_split(y_ref)) < 8e-3
+
+
+def test_fused_k_state_forward_packed_and_launch_count():
+    """Packed ragged sequences through the fused K-state kernel; the output pass is ONE launch for all states."""
+    K = 3
+    p = synthetic.packed_inputs(4, 60, 500, 2, 64, seed=19, dtype=torch.bfloat16)
+    total = p.q.shape[1]
+    gen = torch.Generator().manual_seed(6)
+    gamma = torch.sigmoid(torch.randn(K, 2, total, generator=gen) + torch.tensor([1.0, 3.0, 5.0]).view(K, 1, 1))
+    coef = torch.randn(K, 2, total, 2, generator=gen)
+    q, k, v = (t.unsqueeze(0).to(DEV) for t in (p.q, p.k, p.v))
+    with torch.no_grad():
+        n0 = _lib.launch_count()
+        y, s = ops.pam_scan(q, k, v, gamma.unsqueeze(1).to(DEV), coef=coef.unsqueeze(1).to(DEV), cu_seqlens=p.cu_seqlens)
+        launches = _lib.launch_count() - n0
+    assert _lib.device_status() == 0
+    assert launches == 4              # chunk prefix, state sums (grid z = K), carry, fused output
+    qc, kc, vc = (po.to_complex(t.float().numpy()) for t in (p.q, p.k, p.v))
+    y_ref, s_ref = po.scan_varlen(qc, kc, vc, gamma.double().numpy(), p.cu_seqlens.numpy(), coef=po.to_complex(coef.numpy()))
+    assert_close(y[0].float().cpu().numpy(), po.to_split(y_ref), TOL, "Y packed")
+    assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S packed")
