@@ -86,6 +86,11 @@ size_t qpam_scan_workspace_bytes(const qpam_scan_args* args, int32_t with_backwa
  * qpam_scan_bwd with the SAME workspace contents may pass states_valid=1 to reuse them. */
 int qpam_scan_fwd(const qpam_scan_args* args, void* stream);
 
+/* qpam_scan_fwd with y written token-major, [B,T,H,d,2] (packed mode: [T_total,H,d,2]): the head merge
+ * that precedes the output projection (v11/model.py:835-836) without a transpose pass.  Forward only;
+ * available where the tensor-core kernels run (bf16, d = 64), QPAM_EUNSUPPORTED otherwise. */
+int qpam_scan_fwd_tokens(const qpam_scan_args* args, void* stream);
+
 /* Forward scan with no workspace argument, for hosts that are not allowed to allocate device
  * memory: a server whose memory pool took the whole GPU at start-up, a sandboxed plugin, or a
  * latency-critical loop where cudaMalloc (which may synchronise the device) is forbidden.  The

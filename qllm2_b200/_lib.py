@@ -55,6 +55,7 @@ class FrontArgs(C.Structure):
 SIGNATURES = {
     "qpam_scan_workspace_bytes": (c_size_t, [C.POINTER(ScanArgs), c_int32]),
     "qpam_scan_fwd": (c_int32, [C.POINTER(ScanArgs), c_void_p]),
+    "qpam_scan_fwd_tokens": (c_int32, [C.POINTER(ScanArgs), c_void_p]),
     "qpam_scan_fwd_static": (c_int32, [C.POINTER(ScanArgs), c_void_p]),
     "qpam_scan_bwd": (c_int32, [C.POINTER(ScanArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),

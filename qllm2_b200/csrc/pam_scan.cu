@@ -178,8 +178,9 @@ static int tc_chunk2_launch(const qpam_scan_args* a, const ScanLayout& L, const 
   return QPAM_OK;
 }
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
-static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
+static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st, bool token_major = false) {
   ScanParams p = make_params(a, L);
+  p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
     k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
@@ -195,8 +196,9 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
 }
 
 // bf16 / d = 64 / K = 2..4 states: state sums and carry per state, then ONE fused output kernel
-static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st) {
+static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st, bool token_major = false) {
   ScanParams p = make_params(a, L);
+  p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
     k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
@@ -316,7 +318,7 @@ extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t wit
     }                                                                                    \
   } while (0)
 
-extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) {
+static int scan_fwd_any(const qpam_scan_args* a, void* stream, bool token_major) {
   int rc = check_scan_args(a);
   if (rc) return rc;
   const ScanLayout L = scan_layout(a, fwd_chunk_len(a));
@@ -326,9 +328,17 @@ extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) {
   }
   QPAM_REQUIRE(a->y != nullptr || a->s_final != nullptr, "scan fwd: both y and s_final are NULL");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (L.ch == tcs::TC) return tc_fwdK_eligible(a) ? scan_fwd_tcK(a, L, st) : scan_fwd_tc(a, L, st);
+  if (L.ch == tcs::TC) return tc_fwdK_eligible(a) ? scan_fwd_tcK(a, L, st, token_major) : scan_fwd_tc(a, L, st, token_major);
+  if (token_major) {
+    set_error("scan fwd: the token-major output exists on the tensor-core path only (bf16, d = 64)");
+    return QPAM_EUNSUPPORTED;
+  }
   QPAM_DISPATCH_SCAN(scan_fwd_t, a, L, st);
 }
+
+extern "C" int qpam_scan_fwd(const qpam_scan_args* a, void* stream) { return scan_fwd_any(a, stream, false); }
+
+extern "C" int qpam_scan_fwd_tokens(const qpam_scan_args* a, void* stream) { return scan_fwd_any(a, stream, true); }
 
 extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, void* dk, void* dv,
                              float* dgamma, float* dcoef, const float* ds_final, float* ds0,

@@ -107,6 +107,7 @@ struct ScanParams {
   int64_t nslots;
   int32_t B, H, T, K;
   float q_scale, eps;
+  int32_t y_token_major;   // tensor-core forward kernels only: y laid out [B,T,H,d,2] instead of [B,H,T,d,2]
 };
 
 __device__ __forceinline__ size_t token_base(const ScanParams& p, int b, int h, int t, int D) {

@@ -285,7 +285,9 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
   {
     void* outp = MODE == M_FWD ? p.y : MODE == M_DQ ? p.dq : MODE == M_DV ? p.dv : p.dk;
     const size_t rbase = token_base(p, L.b, h, L.t0 + r, TD) + hf * 64;   // channels [32 hf, 32 hf + 32)
-    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(outp) + rbase;
+    const size_t obase = (MODE == M_FWD && p.y_token_major)
+                             ? (((size_t)L.b * p.T + L.t0 + r) * p.H + h) * (size_t)(TD * 2) + hf * 64 : rbase;
+    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(outp) + obase;
     const __nv_bfloat16* drow = reinterpret_cast<const __nv_bfloat16*>(MODE == M_DQ ? p.q : p.k) + rbase;
     uint4 dpre[8];
     if ((MODE == M_DQ || MODE == M_DK) && r < L.len) {

@@ -280,7 +280,8 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
     }
   }
   {
-    const size_t rbase = token_base(p, L.b, h, L.t0 + r, TD) + hf * 64;   // channels [32 hf, 32 hf + 32)
+    const size_t rbase = (p.y_token_major ? (((size_t)L.b * p.T + L.t0 + r) * p.H + h) * (size_t)(TD * 2)
+                                          : token_base(p, L.b, h, L.t0 + r, TD)) + hf * 64;   // channels [32 hf, 32 hf + 32)
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.y) + rbase;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {

@@ -204,8 +204,36 @@ def pam_scan_tokens(q, k, v, gamma, coef=None, s0=None, cu_seqlens=None, *, head
     the output projection reads (the head merge of v11/model.py:835-836) -- and nothing is kept for a backward
     pass (K phase-routed states in bf16 at d = 64 then run the fused K-state output kernel)."""
     B, H, T, d = q.shape[:4]
-    y, s = pam_scan(q, k, v, gamma, coef=coef, s0=s0, cu_seqlens=cu_seqlens, head_dim=head_dim, eps=eps, chunk=chunk)
-    return y.transpose(1, 2).reshape(B, T, H * d, 2), s
+    gamma4 = gamma if gamma.dim() == 4 else gamma.unsqueeze(0)
+    K = gamma4.shape[0]
+    direct = (q.is_cuda and d == 64 and q.dtype == k.dtype == v.dtype == torch.bfloat16 and T > 0
+              and (K > 1 or coef is None) and tuple(gamma4.shape) == (K, B, H, T)
+              and q.shape == k.shape == v.shape and (cu_seqlens is None or B == 1))
+    if not direct:
+        y, s = pam_scan(q, k, v, gamma, coef=coef, s0=s0, cu_seqlens=cu_seqlens, head_dim=head_dim, eps=eps, chunk=chunk)
+        return y.transpose(1, 2).reshape(B, T, H * d, 2), s
+    # tensor-core path: the output kernel writes [B,T,H,d,2] itself
+    L = _lib.lib()
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    gamma4 = gamma4.float().contiguous()
+    if coef is not None:
+        if tuple(coef.shape) != (K, B, H, T, 2):
+            raise _lib.QPamError(f"coef must be [K,B,H,T,2] = {(K, B, H, T, 2)}, got {tuple(coef.shape)}")
+        coef = coef.float().contiguous()
+    if cu_seqlens is not None:
+        cu_seqlens = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
+    S = B if cu_seqlens is None else cu_seqlens.numel() - 1
+    if s0 is not None:
+        if s0.numel() != K * S * H * d * d * 2:
+            raise _lib.QPamError(f"s0 must be [K,S,H,d,d,2] = {(K, S, H, d, d, 2)}, got {tuple(s0.shape)}")
+        s0 = s0.float().contiguous()
+    y = torch.empty(B, T, H * d, 2, dtype=q.dtype, device=q.device)
+    s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=q.device)
+    a = _scan_args(q, k, v, gamma4, coef, s0, cu_seqlens, y, s_final, (d if head_dim is None else head_dim) ** -0.5, eps, chunk)
+    ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 0), q.device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    check(L.qpam_scan_fwd_tokens(C.byref(a), stream_ptr()), "qpam_scan_fwd_tokens")
+    return y, s_final
 
 
 # --------------------------------------------------------------------------------------- decode

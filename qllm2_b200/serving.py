@@ -213,7 +213,7 @@ class ContinuousBatcher:
         state its predecessor left in the slot; a request emits its first token when its last piece is done."""
         lens = [take for _, _, take in items]
         self._ensure_rope(max(st + take for _, st, take in items))
-        ids = torch.tensor([t for r, st, take in items for t in r.prompt[st:st + take]], dtype=torch.long, device=self.device)[None]
+        ids = torch.cat([torch.as_tensor(r.prompt[st:st + take], dtype=torch.long) for r, st, take in items]).to(self.device)[None]
         positions = torch.cat([torch.arange(st, st + take, device=self.device) for _, st, take in items])[None]
         cu = torch.zeros(len(items) + 1, dtype=torch.int32)
         cu[1:] = torch.tensor(lens).cumsum(0).int()

@@ -268,6 +268,15 @@ def test_token_major_scan_equals_scan_then_head_merge():
     assert y_tok.shape == (B, T, H * d, 2)
     assert torch.equal(y_tok, y_ref.transpose(1, 2).reshape(B, T, H * d, 2))
     assert torch.equal(s_tok, s_ref)
+    # one state (single-state tensor-core kernel, token-major store) and packed sequences
+    with torch.no_grad():
+        y1, s1 = ops.pam_scan_tokens(q, k, v, gamma[0])
+        r1, t1 = ops.pam_scan(q, k, v, gamma[0])
+        cu = torch.tensor([0, 70, 70, 200], dtype=torch.int32)
+        y2, s2 = ops.pam_scan_tokens(q[:1], k[:1], v[:1], gamma[:, :1], coef=coef[:, :1], cu_seqlens=cu)
+        r2, t2 = ops.pam_scan(q[:1], k[:1], v[:1], gamma[:, :1], coef=coef[:, :1], cu_seqlens=cu)
+    assert torch.equal(y1, r1.transpose(1, 2).reshape(B, T, H * d, 2)) and torch.equal(s1, t1)
+    assert torch.equal(y2, r2.transpose(1, 2).reshape(1, T, H * d, 2)) and torch.equal(s2, t2)
     # fp32 (no fused read-out): same contract
     y32, _ = ops.pam_scan_tokens(q.float(), k.float(), v.float(), gamma, coef=coef)
     r32, _ = ops.pam_scan(q.float(), k.float(), v.float(), gamma, coef=coef)
