@@ -170,10 +170,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / CE side measurements")
+    ap.add_argument("--only-inference", action="store_true",
+                    help="run only a small packed prefill + decode of the config-5 model (a profiling target)")
     ap.add_argument("--only-elementwise", action="store_true",
                     help="run only the element-wise block kernels at the config-3 layer shape and print their line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.only_inference:
+        torch.cuda.set_device(0)
+        print(json.dumps({"inference_small": inference_small(torch.device("cuda:0"))}))
+        return
     if args.only_elementwise:
         torch.cuda.set_device(0)
         print(json.dumps({"elementwise_kernels": elementwise_kernels(torch.device("cuda:0"), load_peaks())}))
@@ -614,6 +620,27 @@ def packed_prefill(dev, peaks, time_ms):
             "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm"],
             "config": "32 sequences, lengths U[512,16384] (seed 0), H=16 d=64 K=1 bf16, forward (Y + per-sequence states); "
                       "inputs drawn on the device"}
+
+
+def inference_small(dev, n_seq=48, n_slots=48, new_tokens=3, max_prompt=1024):
+    """A small run of the config-5 model through the packed forward without a CUDA graph: one packed prefill of
+    ~25 k tokens and a few decode steps, so that a profiler sees each kernel as its own launch."""
+    from qllm2_b200 import model as M, synthetic
+    from qllm2_b200.serving import ContinuousBatcher
+    torch.manual_seed(0)
+    cfg = M.V11Config(vocab_size=50261, dim=768, n_heads=12, head_dim=64, n_layers=12, n_states=3,
+                      gate_content_aware=True, dropout=0.0, gradient_checkpointing=False, max_seq_len=8192)
+    net = M.V11LM(cfg).to(dev).bfloat16().eval()
+    prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
+    eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, cuda_graph=False, fused=True)
+    for p_ in prompts:
+        eng.submit(p_.tolist(), new_tokens)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = eng.run()
+    torch.cuda.synchronize()
+    return {"seconds": time.perf_counter() - t0, "prompt_tokens": int(sum(len(p_) for p_ in prompts)),
+            "generated_tokens": sum(len(v_) for v_ in res.values()), "engine_steps": eng.steps}
 
 
 def continuous_decode(dev, peaks, n_seq=512, n_slots=256, new_tokens=32, max_prompt=1024):
