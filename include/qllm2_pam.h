@@ -295,6 +295,23 @@ int qpam_block_weight_fwd(const void* wr, const void* wi, int32_t w_dtype, void*
 int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dwr, void* dwi, int32_t w_dtype,
                           int32_t out_dim, int32_t in_dim, void* stream);
 
+/* Gate arithmetic of the PAM layer from the outputs of its small Linears, all fp32 (v11/model.py:308-350,
+ * 630-655, 685-720): dt, pg [B,T,H]; phase, score [B,T,H,K]; pg / phase / score / state_dt_offset may be NULL.
+ *   gamma[k,b,h,t] = base'_k (1-p) + p,  base_k = exp(-softplus(dt + dt_bias[h] + state_dt_offset[k])),
+ *   base' = gamma_floor + (1-gamma_floor) base,  p = sigmoid(pg);  omp[b,t,h] = 1-p;
+ *   coef[k,b,h,t] = K softmax_k(score) e^{i phase_k}   (coef NULL: not produced).
+ * Backward: d(dt), d(pg), d(phase), d(score) and P rows of partial sums of d(x_k) [P,H,K], whose sum over P
+ * and K is d(dt_bias) and over P and H is d(state_dt_offset). */
+int qpam_pam_gates_fwd(const float* dt, const float* pg, const float* phase, const float* score,
+                       const float* dt_bias, const float* state_dt_offset, float gamma_floor,
+                       float* gamma, float* omp, float* coef, int32_t B, int32_t T, int32_t H, int32_t K,
+                       void* stream);
+int qpam_pam_gates_bwd(const float* dt, const float* pg, const float* phase, const float* score,
+                       const float* dt_bias, const float* state_dt_offset, float gamma_floor,
+                       const float* dgamma, const float* domp, const float* dcoef, float* ddt, float* dpg,
+                       float* dphase, float* dscore, float* dx_partials, int32_t P, int32_t B, int32_t T,
+                       int32_t H, int32_t K, void* stream);
+
 /* Read-out of K phase-routed states (v11/model.py:766-781: the sum over states weighted by
  * alpha_k e^{i phi_k}):  y[r,:] = sum_k coef[k,r] * yk[k][r,:] over R rows of d complex channels;
  * yk / dyk are HOST arrays of K device pointers, coef / dcoef fp32 [K,R,2].

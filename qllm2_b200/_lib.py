@@ -97,6 +97,8 @@ SIGNATURES = {
                                            c_int64, c_void_p]),
     "qpam_block_weight_fwd": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_block_weight_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "qpam_pam_gates_fwd": (c_int32, [c_void_p] * 6 + [C.c_float] + [c_void_p] * 3 + [c_int32] * 4 + [c_void_p]),
+    "qpam_pam_gates_bwd": (c_int32, [c_void_p] * 6 + [C.c_float] + [c_void_p] * 8 + [c_int32] * 5 + [c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

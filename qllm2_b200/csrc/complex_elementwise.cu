@@ -735,6 +735,100 @@ __global__ void __launch_bounds__(256) k_block_weight_bwd(const TO* __restrict__
 }  // namespace
 }  // namespace qpam
 
+namespace qpam {
+namespace {
+using namespace ew;
+// ------------------------------------------------------------------------------------------------
+// Gate arithmetic of the PAM layer on [B,T,H] logits (v11/model.py:308-350, 630-655, 685-720):
+//   x_k = dt + dt_bias[h] + off[k];  base_k = 1/(1+e^{x_k}) (= exp(-softplus(x_k)));  base'_k = floor + (1-floor) base_k
+//   p = sigmoid(pg) (0 without the protect gate);  gamma[k,b,h,t] = base'_k (1-p) + p;  omp[b,t,h] = 1 - p
+//   w = K softmax_k(score) (1 without scores);  coef[k,b,h,t] = w_k e^{i phase_k}
+// One thread per (b,t,h); the backward writes d(dt), d(pg), d(phase), d(score) and per-CTA partial sums
+// of d(x_k) over its tokens, [P, H, K], from which d(dt_bias) and d(off) follow.
+// ------------------------------------------------------------------------------------------------
+struct GateParams {
+  const float *dt, *pg, *phase, *score;      // [B,T,H], [B,T,H], [B,T,H,K], [B,T,H,K] (pg/phase/score may be null)
+  const float *dt_bias, *off;                // [H], [K] (off may be null)
+  float *gamma, *omp, *coef;                 // fwd out: [K,B,H,T], [B,T,H] (null without pg), [K,B,H,T,2] (null if K == 1 and no phase)
+  const float *dgamma, *domp, *dcoef;        // bwd in
+  float *ddt, *dpg, *dphase, *dscore, *dx_part;   // bwd out; dx_part [P,H,K]
+  float floor_;
+  int B, T, H, K;
+};
+
+template <bool BWD>
+__global__ void __launch_bounds__(256) k_pam_gates(GateParams p) {
+  extern __shared__ float s_part[];          // [H*K] (backward)
+  const int HK = p.H * p.K;
+  if (BWD) {
+    for (int i = threadIdx.x; i < HK; i += blockDim.x) s_part[i] = 0.f;
+    __syncthreads();
+  }
+  const int64_t n = (int64_t)p.B * p.T * p.H;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int h = (int)(e % p.H);
+    const int64_t bt = e / p.H;
+    const int b = (int)(bt / p.T), t = (int)(bt - (int64_t)b * p.T);
+    const float dtv = p.dt[e] + p.dt_bias[h];
+    const float pr = p.pg ? sigmoidf_(p.pg[e]) : 0.f;
+    float sc[QPAM_MAX_STATES], w[QPAM_MAX_STATES];
+    float wmax = -INFINITY, wsum = 0.f;
+    if (p.score) {
+      for (int k = 0; k < p.K; ++k) { sc[k] = p.score[e * p.K + k]; wmax = fmaxf(wmax, sc[k]); }
+      for (int k = 0; k < p.K; ++k) { w[k] = __expf(sc[k] - wmax); wsum += w[k]; }
+      for (int k = 0; k < p.K; ++k) w[k] = w[k] / wsum * (float)p.K;
+    } else {
+      for (int k = 0; k < p.K; ++k) w[k] = 1.f;
+    }
+    float dp = 0.f, ddt = 0.f, wdw = 0.f, dw[QPAM_MAX_STATES];
+    for (int k = 0; k < p.K; ++k) {
+      const float x = dtv + (p.off ? p.off[k] : 0.f);
+      const float base = sigmoidf_(-x);
+      const float basef = p.floor_ > 0.f ? p.floor_ + (1.f - p.floor_) * base : base;
+      const int64_t gi = (((int64_t)k * p.B + b) * p.H + h) * p.T + t;
+      float sn = 0.f, cs = 1.f;
+      const bool has_coef = p.coef != nullptr || p.dcoef != nullptr;
+      if (has_coef && p.phase) sincosf(p.phase[e * p.K + k], &sn, &cs);
+      if (!BWD) {
+        p.gamma[gi] = basef * (1.f - pr) + pr;
+        if (p.coef) *reinterpret_cast<float2*>(p.coef + gi * 2) = make_float2(w[k] * cs, w[k] * sn);
+      } else {
+        const float dg = p.dgamma[gi];
+        dp += dg * (1.f - basef);
+        const float dx = -(1.f - (p.floor_ > 0.f ? p.floor_ : 0.f)) * dg * (1.f - pr) * base * (1.f - base);
+        ddt += dx;
+        atomicAdd(&s_part[h * p.K + k], dx);
+        dw[k] = 0.f;
+        if (p.dcoef) {
+          const float2 dc = *reinterpret_cast<const float2*>(p.dcoef + gi * 2);
+          dw[k] = cs * dc.x + sn * dc.y;
+          if (p.dphase) p.dphase[e * p.K + k] = w[k] * (cs * dc.y - sn * dc.x);
+          wdw += w[k] * dw[k];
+        } else if (p.dphase) {
+          p.dphase[e * p.K + k] = 0.f;
+        }
+      }
+    }
+    if (!BWD) {
+      if (p.omp) p.omp[e] = 1.f - pr;
+    } else {
+      p.ddt[e] = ddt;
+      if (p.dpg) {
+        if (p.domp) dp -= p.domp[e];
+        p.dpg[e] = dp * pr * (1.f - pr);
+      }
+      if (p.dscore)
+        for (int k = 0; k < p.K; ++k) p.dscore[e * p.K + k] = w[k] * (dw[k] - wdw / (float)p.K);
+    }
+  }
+  if (BWD) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < HK; i += blockDim.x) p.dx_part[(int64_t)blockIdx.x * HK + i] = s_part[i];
+  }
+}
+}  // namespace
+}  // namespace qpam
+
 static int state_combine(bool bwd, const void* const* yk, void* const* dyk, const float* coef, void* y, float* dcoef,
                          int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream, int32_t H = 0, int32_t T = 0) {
   QPAM_REQUIRE(yk && coef && y && (!bwd || (dyk && dcoef)), "state_combine: NULL pointer argument");
@@ -850,4 +944,46 @@ extern "C" int qpam_state_combine_tokens_fwd(const void* const* yk, const float*
                                              int32_t B, int32_t H, int32_t T, int32_t d, void* stream) {
   QPAM_REQUIRE(B > 0 && H > 0 && T > 0, "state_combine_tokens: empty shape");
   return state_combine(false, yk, nullptr, coef, y, nullptr, dtype, K, (int64_t)B * H * T, d, stream, H, T);
+}
+
+static int pam_gates(bool bwd, GateParams& p, int32_t P, void* stream) {
+  QPAM_REQUIRE(p.dt && p.dt_bias, "pam_gates: NULL pointer argument");
+  QPAM_REQUIRE(p.B > 0 && p.T > 0 && p.H > 0 && p.K >= 1 && p.K <= QPAM_MAX_STATES, "pam_gates: bad shape (K in [1,%d])", QPAM_MAX_STATES);
+  QPAM_REQUIRE(!p.score || p.K > 1, "pam_gates: routing scores need K > 1");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t n = (int64_t)p.B * p.T * p.H;
+  if (!bwd) {
+    QPAM_REQUIRE(p.gamma && (!p.pg || p.omp), "pam_gates_fwd: NULL output");
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
+    k_pam_gates<false><<<grid, 256, 0, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_pam_gates_fwd");
+  } else {
+    QPAM_REQUIRE(p.dgamma && p.ddt && p.dx_part && (!p.pg || p.dpg), "pam_gates_bwd: NULL pointer argument");
+    QPAM_REQUIRE(P > 0 && P <= 148 * 8, "pam_gates_bwd: partial rows must be in [1, %d]", 148 * 8);
+    k_pam_gates<true><<<P, 256, sizeof(float) * p.H * p.K, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_pam_gates_bwd");
+  }
+  return QPAM_OK;
+}
+
+extern "C" int qpam_pam_gates_fwd(const float* dt, const float* pg, const float* phase, const float* score,
+                                  const float* dt_bias, const float* state_dt_offset, float gamma_floor,
+                                  float* gamma, float* omp, float* coef, int32_t B, int32_t T, int32_t H, int32_t K,
+                                  void* stream) {
+  GateParams p{};
+  p.dt = dt; p.pg = pg; p.phase = phase; p.score = score; p.dt_bias = dt_bias; p.off = state_dt_offset;
+  p.gamma = gamma; p.omp = omp; p.coef = coef; p.floor_ = gamma_floor; p.B = B; p.T = T; p.H = H; p.K = K;
+  return pam_gates(false, p, 0, stream);
+}
+
+extern "C" int qpam_pam_gates_bwd(const float* dt, const float* pg, const float* phase, const float* score,
+                                  const float* dt_bias, const float* state_dt_offset, float gamma_floor,
+                                  const float* dgamma, const float* domp, const float* dcoef, float* ddt, float* dpg,
+                                  float* dphase, float* dscore, float* dx_partials, int32_t P, int32_t B, int32_t T,
+                                  int32_t H, int32_t K, void* stream) {
+  GateParams p{};
+  p.dt = dt; p.pg = pg; p.phase = phase; p.score = score; p.dt_bias = dt_bias; p.off = state_dt_offset;
+  p.dgamma = dgamma; p.domp = domp; p.dcoef = dcoef; p.ddt = ddt; p.dpg = dpg; p.dphase = dphase; p.dscore = dscore;
+  p.dx_part = dx_partials; p.floor_ = gamma_floor; p.B = B; p.T = T; p.H = H; p.K = K;
+  return pam_gates(true, p, P, stream);
 }

@@ -438,3 +438,68 @@ def block_weight(weight_real: torch.Tensor, weight_imag: torch.Tensor, out_dtype
         raise _lib.QPamError(f"unsupported dtype {weight_real.dtype}")
     out_dtype = out_dtype or weight_real.dtype
     return _BlockWeightFn.apply(weight_real, weight_imag, out_dtype)
+
+
+# ------------------------------------------------------------------------------------ PAM gate arithmetic
+class _PamGatesFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, dt, pg, phase, score, dt_bias, dt_off, gamma_floor, K, want_coef):
+        B, T, H = dt.shape
+        f = lambda t: None if t is None else t.detach().float().contiguous()
+        dtf, pgf, phf, scf, bf, of = f(dt), f(pg), f(phase), f(score), f(dt_bias), f(dt_off)
+        dev = dt.device
+        gamma = torch.empty(K, B, H, T, dtype=torch.float32, device=dev)
+        omp = None if pg is None else torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        coef = torch.empty(K, B, H, T, 2, dtype=torch.float32, device=dev) if want_coef else None
+        check(_lib.lib().qpam_pam_gates_fwd(ptr(dtf), ptr(pgf), ptr(phf), ptr(scf), ptr(bf), ptr(of), float(gamma_floor),
+                                            ptr(gamma), ptr(omp), ptr(coef), B, T, H, K, stream_ptr()), "qpam_pam_gates_fwd")
+        ctx.save_for_backward(dtf, pgf, phf, scf, bf, of)
+        ctx.meta = (gamma_floor, K, tuple(None if t is None else t.dtype for t in (dt, pg, phase, score, dt_bias, dt_off)))
+        outs = (gamma, omp if omp is not None else gamma.new_empty(0), coef if coef is not None else gamma.new_empty(0))
+        return outs
+
+    @staticmethod
+    def backward(ctx, dgamma, domp, dcoef):
+        dtf, pgf, phf, scf, bf, of = ctx.saved_tensors
+        gamma_floor, K, dtypes = ctx.meta
+        B, T, H = dtf.shape
+        dev = dtf.device
+        g = lambda t, ok: None if (t is None or not ok or t.numel() == 0) else t.float().contiguous()
+        dgamma = torch.zeros(K, B, H, T, dtype=torch.float32, device=dev) if dgamma is None else dgamma.float().contiguous()
+        domp, dcoef = g(domp, pgf is not None), g(dcoef, True)
+        ddt = torch.empty_like(dtf)
+        dpg = None if pgf is None else torch.empty_like(pgf)
+        dph = None if phf is None else torch.empty_like(phf)
+        dsc = None if scf is None else torch.empty_like(scf)
+        P = max(1, min(148 * 4, (dtf.numel() + 255) // 256))
+        part = torch.empty(P, H, K, dtype=torch.float32, device=dev)
+        check(_lib.lib().qpam_pam_gates_bwd(ptr(dtf), ptr(pgf), ptr(phf), ptr(scf), ptr(bf), ptr(of), float(gamma_floor),
+                                            ptr(dgamma), ptr(domp), ptr(dcoef), ptr(ddt), ptr(dpg), ptr(dph), ptr(dsc),
+                                            ptr(part), P, B, T, H, K, stream_ptr()), "qpam_pam_gates_bwd")
+        hk = part.sum(0)                                                   # [H,K]
+        cast = lambda t, i: None if t is None else t.to(dtypes[i])
+        return (cast(ddt, 0), cast(dpg, 1), cast(dph, 2), cast(dsc, 3), cast(hk.sum(1), 4),
+                None if of is None else cast(hk.sum(0), 5), None, None, None)
+
+
+def pam_gates(dt, pg, phase, score, dt_bias, state_dt_offset, gamma_floor: float, n_states: int):
+    """Decay, protect gate and phase-routing read-out weights of the PAM layer from the outputs of its small
+    Linears (v11/model.py:308-350, 630-655, 685-720), forward and backward in one kernel each:
+    dt, pg [B,T,H]; phase, score [B,T,H,K] (pg / phase / score / state_dt_offset may be None).
+    Returns gamma [K,B,H,T], omp = 1 - p [B,T,H] (None without pg), coef [K,B,H,T,2] (None without phase)."""
+    _require_cuda(dt, pg, phase, score, dt_bias, state_dt_offset)
+    B, T, H = dt.shape
+    K = n_states
+    if not 1 <= K <= 4:
+        raise _lib.QPamError(f"pam_gates: 1..4 states, got {K}")
+    if pg is not None and pg.shape != dt.shape:
+        raise _lib.QPamError("pam_gates: pg must have dt's shape [B,T,H]")
+    for t, name in ((phase, "phase"), (score, "score")):
+        if t is not None and tuple(t.shape) != (B, T, H, K):
+            raise _lib.QPamError(f"pam_gates: {name} must be [B,T,H,K] = {(B, T, H, K)}, got {tuple(t.shape)}")
+    if dt_bias.numel() != H or (state_dt_offset is not None and state_dt_offset.numel() != K):
+        raise _lib.QPamError("pam_gates: dt_bias must have H entries and state_dt_offset K")
+    if score is not None and (K == 1 or phase is None):
+        raise _lib.QPamError("pam_gates: routing scores need K > 1 and phases")
+    gamma, omp, coef = _PamGatesFn.apply(dt, pg, phase, score, dt_bias, state_dt_offset, gamma_floor, K, phase is not None)
+    return gamma, (omp if pg is not None else None), (coef if phase is not None else None)

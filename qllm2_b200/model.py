@@ -355,6 +355,38 @@ class V11PAMLayer(nn.Module):
         gamma = base * (1 - protect) + protect
         return gamma.contiguous(), 1 - p_bth
 
+    def _fused_gates_ok(self, x: torch.Tensor) -> bool:
+        """One kernel for the decay / protect / routing arithmetic unless a training-time auxiliary loss needs
+        the intermediate tensors."""
+        aux = self.training and ((self.route_balance_lambda > 0 and self.state_compete) or self.gate_surprisal_lambda > 0)
+        return x.is_cuda and not aux and 1 <= self.n_states <= 4
+
+    def gates_and_coef(self, x: torch.Tensor):
+        """gamma [K,B,H,T], omp [B,T,H] or None, coef [K,B,H,T,2] or None for one layer input x [B,T,D,2]."""
+        if not self._fused_gates_ok(x):
+            gamma, omp = self._gates(x)
+            return gamma, omp, self._coef(x)
+        B, T = x.shape[0], x.shape[1]
+        H, K = self.num_heads, self.n_states
+        flat = _concat_planes(x)
+        mag = None
+        dt = self.dt_proj(flat)
+        pg = phase = score = None
+        if self.use_gsp:
+            if not self.gate_content_aware:
+                mag = _magnitude(x)
+            pg = self.protect_gate(flat if self.gate_content_aware else mag)
+        if K > 1:
+            if not self.routing_content_aware and mag is None:
+                mag = _magnitude(x)
+            r = flat if self.routing_content_aware else mag
+            phase = self.phase_proj(r).view(B, T, H, K)
+            if self.state_compete:
+                score = self.score_proj(r).view(B, T, H, K)
+        self._route_aux = None
+        return FE.pam_gates(dt, pg, phase, score, self.dt_bias, self.state_dt_offset if K > 1 else None,
+                            float(self.gamma_floor or 0.0), K)
+
     def _gamma_all_and_vprime(self, x: torch.Tensor, values: torch.Tensor):
         """gamma [K,B,H,T] and the protected value v' = (1 - p) v for values [B,H,T,d,2]."""
         gamma, omp = self._gates(x)
@@ -367,15 +399,16 @@ class V11PAMLayer(nn.Module):
         return x.is_cuda and self.fused_qkv and not self.qk_norm and 4 <= d <= 128 and d & (d - 1) == 0
 
     def project_gated(self, x: torch.Tensor, step_offset: int = 0, positions: Optional[torch.Tensor] = None):
-        """q, k, v' [B,H,T,d,2] and gamma [K,B,H,T] of one layer input x [B,T,D,2].  `positions` [B,T]
+        """q, k, v' [B,H,T,d,2], gamma [K,B,H,T] and the read-out weights coef [K,B,H,T,2] (None when K == 1) of
+        one layer input x [B,T,D,2].  `positions` [B,T]
         gives every token its own rotary position (continuous batching); otherwise step_offset + t."""
         if not self._fused_prep_ok(x):
             if positions is not None:
                 raise ValueError("per-token positions need the fused projection path (fused_qkv, no qk_norm, CUDA)")
             q, k, v = self._project(x, step_offset)
             gamma, vprime = self._gamma_all_and_vprime(x, v)
-            return q, k, vprime, gamma
-        gamma, omp = self._gates(x)
+            return q, k, vprime, gamma, self._coef(x)
+        gamma, omp, coef = self.gates_and_coef(x)
         rope = None
         if self.use_rope:
             if positions is None and step_offset + x.shape[1] > self.rope_cache.shape[0]:
@@ -384,7 +417,7 @@ class V11PAMLayer(nn.Module):
             rope = self.rope_cache
         q, k, vprime = FE.pam_prep(self.qkv_proj(x), rope, omp, n_heads=self.num_heads, head_dim=self.head_dim,
                                    positions=positions, offset=step_offset)
-        return q, k, vprime, gamma
+        return q, k, vprime, gamma, coef
 
     def _gamma_and_vprime(self, x, values, state_offset: float = 0.0):
         """Single-state form kept for callers of the reference API (v11/model.py:308-350)."""
@@ -424,8 +457,7 @@ class V11PAMLayer(nn.Module):
     def forward(self, x: torch.Tensor, state=None, step_offset: int = 0):
         B, T = x.shape[0], x.shape[1]
         H, d, K = self.num_heads, self.head_dim, self.n_states
-        q, k, vprime, gamma = self.project_gated(x, step_offset)
-        coef = self._coef(x)
+        q, k, vprime, gamma, coef = self.project_gated(x, step_offset)
         if state is None and T > 1:
             y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, head_dim=d, chunk=self.chunk_size)
             new_state = (s[0] if K == 1 else s).to(x.dtype)

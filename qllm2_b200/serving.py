@@ -243,8 +243,7 @@ class ContinuousBatcher:
             z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
             xn = blk.norm2(z)
             pam = blk.pam
-            q, k, vprime, gamma = pam.project_gated(xn, positions=positions)
-            coef = pam._coef(xn)
+            q, k, vprime, gamma, coef = pam.project_gated(xn, positions=positions)
             y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, cu_seqlens=cu, head_dim=pam.head_dim,
                                 s0=None if s0_of is None else s0_of(li))
             ops.pam_pool_store(self.pool, slots, s, layer=li)
@@ -300,8 +299,7 @@ class ContinuousBatcher:
             z = z + blk.cgu(blk.norm1(z)) * blk.cgu_scale
             xn = blk.norm2(z)
             pam = blk.pam
-            q, k, vprime, gamma = pam.project_gated(xn, positions=positions)   # gamma [K,n,H,1]
-            coef = pam._coef(xn)
+            q, k, vprime, gamma, coef = pam.project_gated(xn, positions=positions)   # gamma [K,n,H,1]
             y = ops.pam_decode_step(self.pool, slots, (q[:, :, 0] * pam.head_dim ** -0.5).contiguous(),
                                     k[:, :, 0].contiguous(), vprime[:, :, 0].contiguous(),
                                     gamma[..., 0].contiguous(), None if coef is None else coef[:, :, :, 0].contiguous(),

@@ -281,3 +281,49 @@ def test_token_major_scan_equals_scan_then_head_merge():
     y32, _ = ops.pam_scan_tokens(q.float(), k.float(), v.float(), gamma, coef=coef)
     r32, _ = ops.pam_scan(q.float(), k.float(), v.float(), gamma, coef=coef)
     assert torch.equal(y32, r32.transpose(1, 2).reshape(B, T, H * d, 2))
+
+
+@pytest.mark.parametrize("K,use_pg,use_score,floor", [(3, True, True, 0.0), (3, True, False, 0.05), (1, True, False, 0.0),
+                                                      (2, False, True, 0.0), (1, False, False, 0.1), (4, True, True, 0.0)])
+def test_pam_gates_match_torch_arithmetic(K, use_pg, use_score, floor):
+    import torch.nn.functional as F
+    g = torch.Generator().manual_seed(K * 7 + int(use_pg))
+    B, T, H = 2, 19, 3
+    mk = lambda *s: torch.randn(*s, generator=g).to(DEV).requires_grad_(True)
+    dt, bias = mk(B, T, H), mk(H)
+    pg = mk(B, T, H) if use_pg else None
+    phase = mk(B, T, H, K) if K > 1 else None
+    score = mk(B, T, H, K) if (use_score and K > 1) else None
+    off = mk(K) if K > 1 else None
+    gamma, omp, coef = FE.pam_gates(dt, pg, phase, score, bias, off, floor, K)
+    # the module's arithmetic (v11/model.py:630-655, 685-720) with torch operators
+    x = (dt + bias).unsqueeze(0) + (off.view(K, 1, 1, 1) if off is not None else 0)
+    base = torch.exp(-F.softplus(x)).permute(0, 1, 3, 2)                       # [K,B,H,T]
+    if floor > 0:
+        base = floor + (1 - floor) * base
+    if use_pg:
+        p = torch.sigmoid(pg)
+        gamma_ref = base * (1 - p.transpose(1, 2)) + p.transpose(1, 2)
+        omp_ref = 1 - p
+    else:
+        gamma_ref, omp_ref = base, None
+    coef_ref = None
+    if K > 1:
+        w = F.softmax(score, dim=-1) * K if score is not None else torch.ones_like(phase)
+        ph, w = phase.permute(3, 0, 2, 1), w.permute(3, 0, 2, 1)
+        coef_ref = torch.stack([w * torch.cos(ph), w * torch.sin(ph)], dim=-1)
+    assert gamma.shape == (K, B, H, T) and rel(gamma, gamma_ref) < 1e-5
+    assert (omp is None) == (omp_ref is None) and (coef is None) == (coef_ref is None)
+    outs, refs = [gamma], [gamma_ref]
+    if omp is not None:
+        assert rel(omp, omp_ref) < 1e-5
+        outs.append(omp); refs.append(omp_ref)
+    if coef is not None:
+        assert rel(coef, coef_ref) < 1e-5
+        outs.append(coef); refs.append(coef_ref)
+    ups = [torch.randn(o.shape, generator=g).to(DEV) for o in outs]
+    wrt = [t for t in (dt, pg, phase, score, bias, off) if t is not None]
+    ga = torch.autograd.grad(sum((o * u).sum() for o, u in zip(outs, ups)), wrt)
+    gb = torch.autograd.grad(sum((o * u).sum() for o, u in zip(refs, ups)), wrt)
+    for a, b in zip(ga, gb):
+        assert a.shape == b.shape and rel(a, b) < 1e-4
