@@ -312,6 +312,11 @@ int qpam_pam_gates_bwd(const float* dt, const float* pg, const float* phase, con
                        float* dphase, float* dscore, float* dx_partials, int32_t P, int32_t B, int32_t T,
                        int32_t H, int32_t K, void* stream);
 
+/* mag[i] = sqrt(re_i^2 + im_i^2 + 1e-8) over n complex values (n a multiple of 4), the input of the
+ * magnitude-driven gate and routing Linears (v11/model.py:330-349, 640-655); backward dz = dmag z / |z|. */
+int qpam_cmagnitude_fwd(const void* z, int32_t dtype, void* mag, int64_t n, void* stream);
+int qpam_cmagnitude_bwd(const void* z, const void* dmag, int32_t dtype, void* dz, int64_t n, void* stream);
+
 /* Read-out of K phase-routed states (v11/model.py:766-781: the sum over states weighted by
  * alpha_k e^{i phi_k}):  y[r,:] = sum_k coef[k,r] * yk[k][r,:] over R rows of d complex channels;
  * yk / dyk are HOST arrays of K device pointers, coef / dcoef fp32 [K,R,2].
@@ -322,6 +327,9 @@ int qpam_state_combine_fwd(const void* const* yk, const float* coef, void* y, in
  * (v11/model.py:835-836) folded into the read-out. */
 int qpam_state_combine_tokens_fwd(const void* const* yk, const float* coef, void* y, int32_t dtype,
                                   int32_t K, int32_t B, int32_t H, int32_t T, int32_t d, void* stream);
+int qpam_state_combine_tokens_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
+                                  float* dcoef, int32_t dtype, int32_t K, int32_t B, int32_t H, int32_t T,
+                                  int32_t d, void* stream);   /* dy token-major, dyk [B,H,T,d,2] */
 int qpam_state_combine_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
                            float* dcoef, int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream);
 

@@ -86,6 +86,8 @@ SIGNATURES = {
     "qpam_state_combine_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32, c_void_p]),
     "qpam_state_combine_tokens_fwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                                 c_int32, c_int32, c_void_p]),
+    "qpam_state_combine_tokens_bwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, C.POINTER(c_void_p), c_void_p, c_int32,
+                                                c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_state_combine_bwd": (c_int32, [C.POINTER(c_void_p), c_void_p, c_void_p, C.POINTER(c_void_p), c_void_p, c_int32,
                                          c_int32, c_int64, c_int32, c_void_p]),
     "qpam_act_gate_packed_fwd": (c_int32, [c_void_p, c_int64, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_void_p]),
@@ -99,6 +101,8 @@ SIGNATURES = {
     "qpam_block_weight_bwd": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
     "qpam_pam_gates_fwd": (c_int32, [c_void_p] * 6 + [C.c_float] + [c_void_p] * 3 + [c_int32] * 4 + [c_void_p]),
     "qpam_pam_gates_bwd": (c_int32, [c_void_p] * 6 + [C.c_float] + [c_void_p] * 8 + [c_int32] * 5 + [c_void_p]),
+    "qpam_cmagnitude_fwd": (c_int32, [c_void_p, c_int32, c_void_p, c_int64, c_void_p]),
+    "qpam_cmagnitude_bwd": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p]),
     "qpam_launch_count": (C.c_longlong, []),
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),

@@ -443,7 +443,7 @@ struct CombineParams {
   float* dcoef;   // bwd
   int64_t R;
   int d, K;
-  int H, T;       // > 0: the forward output is written token-major, y[b, t, h, :] for row r = (b, h, t)
+  int H, T;       // > 0: y (forward) and dy (backward) are token-major, [b, t, h, :] for row r = (b, h, t)
 };
 
 template <typename T, bool BWD>
@@ -458,7 +458,12 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
     const int g = on ? (int)(idx - r * gpr) : 0;
     const int64_t off = (r * p.d + g * 4) * 2;
     float ar[4] = {0.f, 0.f, 0.f, 0.f}, ai[4] = {0.f, 0.f, 0.f, 0.f};
-    if (BWD && on) V4<T>::ld(reinterpret_cast<const T*>(p.y) + off, ar, ai);
+    int64_t yo = off;                                   // where this group sits in y (forward) / dy (backward)
+    if (p.H > 0) {
+      const int64_t bh = r / p.T, t = r - bh * p.T, b = bh / p.H, h = bh - b * p.H;
+      yo = (((b * p.T + t) * p.H + h) * p.d + g * 4) * 2;
+    }
+    if (BWD && on) V4<T>::ld(reinterpret_cast<const T*>(p.y) + yo, ar, ai);
     for (int k = 0; k < p.K; ++k) {
       const float2 c = on ? *reinterpret_cast<const float2*>(p.coef + ((int64_t)k * p.R + r) * 2) : make_float2(0.f, 0.f);
       float yr[4] = {0.f, 0.f, 0.f, 0.f}, yi[4] = {0.f, 0.f, 0.f, 0.f};
@@ -488,14 +493,7 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
         }
       }
     }
-    if (!BWD && on) {
-      int64_t o2 = off;
-      if (p.H > 0) {
-        const int64_t bh = r / p.T, t = r - bh * p.T, b = bh / p.H, h = bh - b * p.H;
-        o2 = (((b * p.T + t) * p.H + h) * p.d + g * 4) * 2;
-      }
-      V4<T>::st(reinterpret_cast<T*>(p.y) + o2, ar, ai);
-    }
+    if (!BWD && on) V4<T>::st(reinterpret_cast<T*>(p.y) + yo, ar, ai);
   }
 }
 
@@ -829,6 +827,36 @@ __global__ void __launch_bounds__(256) k_pam_gates(GateParams p) {
 }  // namespace
 }  // namespace qpam
 
+namespace qpam {
+namespace {
+using namespace ew;
+// |z| = sqrt(re^2 + im^2 + 1e-8) of [n] complex values -> [n];  backward dz = dm z / |z|.
+template <typename T, bool BWD>
+__global__ void __launch_bounds__(256) k_cmagnitude(const T* __restrict__ z, const T* __restrict__ dm, T* __restrict__ out, int64_t n) {
+  for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (int64_t)gridDim.x * blockDim.x * 4) {
+    float re[4], im[4];
+    V4<T>::ld(z + i * 2, re, im);
+    if (!BWD) {
+      float m[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) m[j] = mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS).mag;
+      E4<T>::st(out + i, m);
+    } else {
+      float g[4];
+      E4<T>::ld(dm + i, g);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float s = g[j] * mag_inv(re[j] * re[j] + im[j] * im[j] + MAG_EPS).rmag;
+        re[j] *= s;
+        im[j] *= s;
+      }
+      V4<T>::st(out + i * 2, re, im);
+    }
+  }
+}
+}  // namespace
+}  // namespace qpam
+
 static int state_combine(bool bwd, const void* const* yk, void* const* dyk, const float* coef, void* y, float* dcoef,
                          int32_t dtype, int32_t K, int64_t R, int32_t d, void* stream, int32_t H = 0, int32_t T = 0) {
   QPAM_REQUIRE(yk && coef && y && (!bwd || (dyk && dcoef)), "state_combine: NULL pointer argument");
@@ -986,4 +1014,32 @@ extern "C" int qpam_pam_gates_bwd(const float* dt, const float* pg, const float*
   p.dgamma = dgamma; p.domp = domp; p.dcoef = dcoef; p.ddt = ddt; p.dpg = dpg; p.dphase = dphase; p.dscore = dscore;
   p.dx_part = dx_partials; p.floor_ = gamma_floor; p.B = B; p.T = T; p.H = H; p.K = K;
   return pam_gates(true, p, P, stream);
+}
+
+extern "C" int qpam_cmagnitude_fwd(const void* z, int32_t dtype, void* mag, int64_t n, void* stream) {
+  QPAM_REQUIRE(z && mag && is_dtype(dtype) && n >= 0 && n % 4 == 0, "cmagnitude_fwd: NULL pointer, bad dtype or n not a multiple of 4");
+  if (n == 0) return QPAM_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 8);
+  if (dtype == QPAM_F32) k_cmagnitude<float, false><<<grid, 256, 0, st>>>((const float*)z, nullptr, (float*)mag, n);
+  else k_cmagnitude<__nv_bfloat16, false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, nullptr, (__nv_bfloat16*)mag, n);
+  QPAM_LAUNCH_CHECK("k_cmagnitude_fwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_cmagnitude_bwd(const void* z, const void* dmag, int32_t dtype, void* dz, int64_t n, void* stream) {
+  QPAM_REQUIRE(z && dmag && dz && is_dtype(dtype) && n > 0 && n % 4 == 0, "cmagnitude_bwd: NULL pointer, bad dtype or n not a multiple of 4");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 8);
+  if (dtype == QPAM_F32) k_cmagnitude<float, true><<<grid, 256, 0, st>>>((const float*)z, (const float*)dmag, (float*)dz, n);
+  else k_cmagnitude<__nv_bfloat16, true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)dmag, (__nv_bfloat16*)dz, n);
+  QPAM_LAUNCH_CHECK("k_cmagnitude_bwd");
+  return QPAM_OK;
+}
+
+extern "C" int qpam_state_combine_tokens_bwd(const void* const* yk, const float* coef, const void* dy, void* const* dyk,
+                                             float* dcoef, int32_t dtype, int32_t K, int32_t B, int32_t H, int32_t T,
+                                             int32_t d, void* stream) {
+  QPAM_REQUIRE(B > 0 && H > 0 && T > 0, "state_combine_tokens: empty shape");
+  return state_combine(true, yk, dyk, coef, const_cast<void*>(dy), dcoef, dtype, K, (int64_t)B * H * T, d, stream, H, T);
 }

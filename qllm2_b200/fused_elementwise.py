@@ -294,23 +294,30 @@ def pam_prep(qkv: torch.Tensor, rope: Optional[torch.Tensor], omp: Optional[torc
 # ------------------------------------------------------------------------------------ K-state read-out
 class _StateCombineFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, coef, *yks):
+    def forward(ctx, coef, token_major, *yks):
         K = len(yks)
         yks = tuple(t.contiguous() for t in yks)
         d = yks[0].shape[-2]
         R = yks[0].numel() // (2 * d)
         cf = coef.detach().float().contiguous()
-        y = torch.empty_like(yks[0])
         arr = (_lib.c_void_p * K)(*[t.data_ptr() for t in yks])
-        check(_lib.lib().qpam_state_combine_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, R, d, stream_ptr()),
-              "qpam_state_combine_fwd")
+        if token_major:
+            B, H, T = yks[0].shape[:3]
+            y = torch.empty(B, T, H * d, 2, dtype=yks[0].dtype, device=yks[0].device)
+            check(_lib.lib().qpam_state_combine_tokens_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, B, H, T, d,
+                                                           stream_ptr()), "qpam_state_combine_tokens_fwd")
+        else:
+            y = torch.empty_like(yks[0])
+            check(_lib.lib().qpam_state_combine_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, R, d, stream_ptr()),
+                  "qpam_state_combine_fwd")
         ctx.save_for_backward(cf, *yks)
-        ctx.coef_dtype = coef.dtype
+        ctx.meta = (coef.dtype, token_major)
         return y
 
     @staticmethod
     def backward(ctx, dy):
         cf, *yks = ctx.saved_tensors
+        coef_dtype, token_major = ctx.meta
         K = len(yks)
         d = yks[0].shape[-2]
         R = yks[0].numel() // (2 * d)
@@ -319,9 +326,14 @@ class _StateCombineFn(torch.autograd.Function):
         dcoef = torch.empty_like(cf)
         arr = (_lib.c_void_p * K)(*[t.data_ptr() for t in yks])
         darr = (_lib.c_void_p * K)(*[t.data_ptr() for t in dyks])
-        check(_lib.lib().qpam_state_combine_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K, R, d,
-                                                stream_ptr()), "qpam_state_combine_bwd")
-        return (dcoef.to(ctx.coef_dtype), *dyks)
+        if token_major:
+            B, H, T = yks[0].shape[:3]
+            check(_lib.lib().qpam_state_combine_tokens_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K,
+                                                           B, H, T, d, stream_ptr()), "qpam_state_combine_tokens_bwd")
+        else:
+            check(_lib.lib().qpam_state_combine_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K, R, d,
+                                                    stream_ptr()), "qpam_state_combine_bwd")
+        return (dcoef.to(coef_dtype), None, *dyks)
 
 
 @torch.no_grad()
@@ -346,9 +358,10 @@ def state_combine_tokens(coef: torch.Tensor, yks) -> torch.Tensor:
     return y
 
 
-def state_combine(coef: torch.Tensor, yks) -> torch.Tensor:
+def state_combine(coef: torch.Tensor, yks, token_major: bool = False) -> torch.Tensor:
     """y = sum_k coef[k] * yks[k] (complex): coef [K, ..., 2] over the leading axes of yks[k] [..., d, 2]
-    (the K-state read-out of v11/model.py:766-781), forward and backward in one pass each."""
+    (the K-state read-out of v11/model.py:766-781), forward and backward in one pass each.  token_major=True
+    (yks[k] [B,H,T,d,2]) returns y as [B, T, H*d, 2], the layout the output projection reads."""
     yks = list(yks)
     _require_cuda(coef, *yks)
     K = len(yks)
@@ -362,7 +375,9 @@ def state_combine(coef: torch.Tensor, yks) -> torch.Tensor:
         raise _lib.QPamError(f"state_combine: bf16/f32 and d a power of two in [4,128]; got {dt}, d={d}")
     if tuple(coef.shape) != (K, *shape[:-2], 2):
         raise _lib.QPamError(f"state_combine: coef must be {(K, *shape[:-2], 2)}, got {tuple(coef.shape)}")
-    return _StateCombineFn.apply(coef, *yks)
+    if token_major and len(shape) != 5:
+        raise _lib.QPamError("state_combine: token_major needs [B,H,T,d,2] state outputs")
+    return _StateCombineFn.apply(coef, token_major, *yks)
 
 
 # ------------------------------------------------------------------------------------ residual, block weight
@@ -503,3 +518,32 @@ def pam_gates(dt, pg, phase, score, dt_bias, state_dt_offset, gamma_floor: float
         raise _lib.QPamError("pam_gates: routing scores need K > 1 and phases")
     gamma, omp, coef = _PamGatesFn.apply(dt, pg, phase, score, dt_bias, state_dt_offset, gamma_floor, K, phase is not None)
     return gamma, (omp if pg is not None else None), (coef if phase is not None else None)
+
+
+# ------------------------------------------------------------------------------------ magnitude
+class _MagnitudeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, z):
+        z = z.contiguous()
+        out = torch.empty(z.shape[:-1], dtype=z.dtype, device=z.device)
+        check(_lib.lib().qpam_cmagnitude_fwd(ptr(z), dtype_code(z.dtype), ptr(out), out.numel(), stream_ptr()), "qpam_cmagnitude_fwd")
+        ctx.save_for_backward(z)
+        return out
+
+    @staticmethod
+    def backward(ctx, dm):
+        (z,) = ctx.saved_tensors
+        dm = dm.to(z.dtype).contiguous()
+        dz = torch.empty_like(z)
+        check(_lib.lib().qpam_cmagnitude_bwd(ptr(z), ptr(dm), dtype_code(z.dtype), ptr(dz), dm.numel(), stream_ptr()),
+              "qpam_cmagnitude_bwd")
+        return dz
+
+
+def complex_magnitude(z: torch.Tensor) -> torch.Tensor:
+    """sqrt(re^2 + im^2 + 1e-8) over the last axis of [..., 2] (the `_magnitude` of v11/complex_ops.py)."""
+    _require_cuda(z)
+    if z.shape[-1] != 2 or (z.numel() // 2) % 4 or z.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"complex_magnitude: expected a float32/bfloat16 [..., 2] tensor with a multiple of 4 values, got "
+                             f"{tuple(z.shape)} {z.dtype}")
+    return _MagnitudeFn.apply(z)

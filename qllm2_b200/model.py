@@ -367,22 +367,29 @@ class V11PAMLayer(nn.Module):
             gamma, omp = self._gates(x)
             return gamma, omp, self._coef(x)
         B, T = x.shape[0], x.shape[1]
-        H, K = self.num_heads, self.n_states
-        flat = _concat_planes(x)
+        H, K, D = self.num_heads, self.n_states, self.dim
+        x = x.contiguous()
+        flat = x.view(B, T, 2 * D)                        # interleaved (re, im) columns: no copy
+
+        def planar(lin):      # a Linear over [x_re | x_im] applied to the interleaved columns (weight columns permuted)
+            w = lin.weight
+            return F.linear(flat, w.view(w.shape[0], 2, D).transpose(1, 2).reshape(w.shape[0], 2 * D), lin.bias)
+
+        fused_mag = x.dtype in (torch.float32, torch.bfloat16) and (x.numel() // 2) % 4 == 0
         mag = None
-        dt = self.dt_proj(flat)
+        dt = planar(self.dt_proj)
         pg = phase = score = None
         if self.use_gsp:
             if not self.gate_content_aware:
-                mag = _magnitude(x)
-            pg = self.protect_gate(flat if self.gate_content_aware else mag)
+                mag = FE.complex_magnitude(x) if fused_mag else _magnitude(x)
+            pg = planar(self.protect_gate) if self.gate_content_aware else self.protect_gate(mag)
         if K > 1:
             if not self.routing_content_aware and mag is None:
-                mag = _magnitude(x)
-            r = flat if self.routing_content_aware else mag
-            phase = self.phase_proj(r).view(B, T, H, K)
+                mag = FE.complex_magnitude(x) if fused_mag else _magnitude(x)
+            proj = planar if self.routing_content_aware else (lambda lin: lin(mag))
+            phase = proj(self.phase_proj).view(B, T, H, K)
             if self.state_compete:
-                score = self.score_proj(r).view(B, T, H, K)
+                score = proj(self.score_proj).view(B, T, H, K)
         self._route_aux = None
         return FE.pam_gates(dt, pg, phase, score, self.dt_bias, self.state_dt_offset if K > 1 else None,
                             float(self.gamma_floor or 0.0), K)
@@ -459,11 +466,12 @@ class V11PAMLayer(nn.Module):
         H, d, K = self.num_heads, self.head_dim, self.n_states
         q, k, vprime, gamma, coef = self.project_gated(x, step_offset)
         if state is None and T > 1:
-            y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, head_dim=d, chunk=self.chunk_size)
+            y, s = ops.pam_scan(q, k, vprime, gamma, coef=coef, head_dim=d, chunk=self.chunk_size, token_major=True)
             new_state = (s[0] if K == 1 else s).to(x.dtype)
         else:
             y, new_state = self._recurrent(q, k, vprime, gamma, coef, state)
-        out = self.o_proj(y.transpose(1, 2).contiguous().view(B, T, self.inner_dim, 2))
+            y = y.transpose(1, 2).contiguous().view(B, T, self.inner_dim, 2)
+        out = self.o_proj(y)
         if self.training and self.dropout.p > 0:
             out = out * _dropout_mask(self.dropout, out)
         return out, new_state

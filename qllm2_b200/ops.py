@@ -94,8 +94,9 @@ class _PamScanFn(torch.autograd.Function):
 
 
 def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: Optional[int] = None,
-             eps: float = GAMMA_EPS, chunk: int = 64, save_states: bool = True):
-    """Chunked dual-form PAM scan on the GPU.
+             eps: float = GAMMA_EPS, chunk: int = 64, save_states: bool = True, token_major: bool = False):
+    """Chunked dual-form PAM scan on the GPU.  (token_major=True returns y as [B, T, H*d, 2], the head merge
+    of v11/model.py:835-836, straight from the last kernel where that kernel can write it.)
 
     q, k, v  [B,H,T,d,2] (float32 or bfloat16; q unscaled -- it is multiplied by head_dim**-0.5
              inside, as V11PAMLayer._forward_chunked_head does, v11/model.py:381-382)
@@ -156,9 +157,17 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
                 y = y + yk
         else:
             from .fused_elementwise import state_combine
-            y = state_combine(coef, ys)
-        return y, torch.cat(finals, dim=0)
-    return _PamScanFn.apply(q, k, v, gamma, coef, s0, cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
+            return state_combine(coef, ys, token_major=token_major), torch.cat(finals, dim=0)
+        return (_merge_heads(y) if token_major else y), torch.cat(finals, dim=0)
+    if token_major and not needs_grad:
+        return pam_scan_tokens(q, k, v, gamma, coef=coef, s0=s0, cu_seqlens=cu_seqlens, head_dim=head_dim, eps=eps, chunk=chunk)
+    y, s = _PamScanFn.apply(q, k, v, gamma, coef, s0, cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
+    return (_merge_heads(y) if token_major else y), s
+
+
+def _merge_heads(y):
+    B, H, T, d = y.shape[:4]
+    return y.transpose(1, 2).reshape(B, T, H * d, 2)
 
 
 @torch.no_grad()

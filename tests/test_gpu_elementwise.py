@@ -327,3 +327,34 @@ def test_pam_gates_match_torch_arithmetic(K, use_pg, use_score, floor):
     gb = torch.autograd.grad(sum((o * u).sum() for o, u in zip(refs, ups)), wrt)
     for a, b in zip(ga, gb):
         assert a.shape == b.shape and rel(a, b) < 1e-4
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 1e-2)])
+def test_complex_magnitude_matches_torch(dtype, tol):
+    g = torch.Generator().manual_seed(31)
+    z32 = torch.randn(3, 17, 24, 2, generator=g).to(DEV)
+    z32[0, 0, :4] = 0                                     # the 1e-8 guard keeps the gradient finite at zero
+    dm = torch.randn(3, 17, 24, generator=g).to(DEV)
+    z = z32.to(dtype).requires_grad_(True)
+    m = FE.complex_magnitude(z)
+    (gz,) = torch.autograd.grad((m.float() * dm).sum(), [z])
+    zr = z.detach().float().requires_grad_(True)
+    mr = torch.sqrt(zr[..., 0] ** 2 + zr[..., 1] ** 2 + 1e-8)
+    (gr,) = torch.autograd.grad((mr * dm).sum(), [zr])
+    assert m.dtype == dtype and m.shape == (3, 17, 24)
+    assert rel(m, mr) < tol and rel(gz, gr) < tol and torch.isfinite(gz.float()).all()
+
+
+def test_state_combine_token_major_with_gradients():
+    g = torch.Generator().manual_seed(41)
+    B, H, T, d, K = 2, 3, 21, 64, 3
+    yks = [torch.randn(B, H, T, d, 2, generator=g).to(DEV).requires_grad_(True) for _ in range(K)]
+    coef = torch.randn(K, B, H, T, 2, generator=g).to(DEV).requires_grad_(True)
+    dy = torch.randn(B, T, H * d, 2, generator=g).to(DEV)
+    y_tm = FE.state_combine(coef, yks, token_major=True)
+    y = FE.state_combine(coef, yks)
+    assert y_tm.shape == (B, T, H * d, 2) and torch.equal(y_tm, y.transpose(1, 2).reshape(B, T, H * d, 2))
+    ga = torch.autograd.grad((y_tm * dy).sum(), [coef] + yks)
+    gb = torch.autograd.grad((y.transpose(1, 2).reshape(B, T, H * d, 2) * dy).sum(), [coef] + yks)
+    for a, b in zip(ga, gb):
+        assert torch.allclose(a, b, rtol=1e-5, atol=1e-5)
