@@ -29,6 +29,7 @@ int cuda_fail(cudaError_t e, const char* what) {
 // ------------------------------------------------------------------ launch accounting
 static std::atomic<long long> g_launches{0};
 static std::atomic<bool> g_profiling{false};
+bool profiling_active() { return g_profiling.load(std::memory_order_relaxed); }
 static std::mutex g_prof_mu;
 struct ProfRec {
   const char* name;

@@ -29,6 +29,8 @@ int cuda_fail(cudaError_t e, const char* what);
 
 // Counts the launch and, while profiling is on, records an event behind it on `stream_`.
 void note_launch(const char* name, cudaStream_t stream_);
+// True while qpam_profile_begin .. qpam_profile_end is recording (entry points then keep to one stream).
+bool profiling_active();
 
 #define QPAM_LAUNCH_CHECK_ON(name, stream_)                              \
   do {                                                                   \

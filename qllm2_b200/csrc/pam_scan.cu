@@ -16,7 +16,7 @@ struct ScanLayout {
   int32_t ch;           // tokens per chunk of this layout
   int32_t nc_uniform;
   int32_t grid_chunks;  // upper bound on the number of chunks (grid.x of the chunk kernels)
-  size_t off_prefix, off_states, off_decay, off_dstates, off_anchors, total_fwd, total_bwd;
+  size_t off_prefix, off_states, off_decay, off_dstates, off_anchors, off_dak, total_fwd, total_bwd;
 };
 
 // Tensor-core kernels take bf16 token tensors with head dim 64 and a single state; their chunk is
@@ -60,6 +60,8 @@ static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   off += align256(sizeof(float2) * (size_t)a->K * a->H * L.nslots * dd);
   L.off_anchors = off;
   off += align256(sizeof(float) * (size_t)a->K * a->H * L.nslots);
+  L.off_dak = off;
+  off += align256(sizeof(float) * (size_t)a->B * a->H * a->T);
   L.total_bwd = off;
   return L;
 }
@@ -218,6 +220,34 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
   return QPAM_OK;
 }
 
+// Side streams of the tensor-core backward (one set per device, created on first use; never destroyed).
+struct SideStreams {
+  cudaStream_t s[3];
+  cudaEvent_t fork, join[3];
+  std::mutex mu;          // one enqueue at a time reuses the events
+};
+static SideStreams* side_streams() {
+  static std::mutex mu;
+  static SideStreams* per_dev[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (per_dev[dev] == nullptr) {
+    SideStreams* ss = new SideStreams();
+    bool ok = cudaEventCreateWithFlags(&ss->fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 3 && ok; ++i)
+      ok = cudaStreamCreateWithFlags(&ss->s[i], cudaStreamNonBlocking) == cudaSuccess &&
+           cudaEventCreateWithFlags(&ss->join[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+      cudaGetLastError();
+      delete ss;
+      return nullptr;     // the caller stays on its own stream
+    }
+    per_dev[dev] = ss;
+  }
+  return per_dev[dev];
+}
+
 static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk, void* dv,
                        float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st) {
   ScanParams p = make_params(a, L);
@@ -243,12 +273,32 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
   QPAM_LAUNCH_CHECK("k_state_scan<rev>");
   if (L.grid_chunks > 0) {
-    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", st))) return rc;
-    if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
-    if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk<dk>", st))) return rc;
+    p.dA_k = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_dak);
     float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
-    tcs::k_tc_state_anchors<<<dim3((unsigned)L.nslots, a->H), 256, 0, st>>>(p, anchors);
-    QPAM_LAUNCH_CHECK("k_tc_state_anchors");
+    // dv, dq, dk and the anchors depend only on what precedes them: on side streams they overlap, so the
+    // partly filled last wave of one kernel is topped up by the next (768 CTAs over 296 slots = 2.6 waves
+    // each).  While the per-kernel profiler records on one stream everything stays on it.
+    SideStreams* ss = profiling_active() ? nullptr : side_streams();
+    cudaStream_t s_dv = st, s_dk = st, s_an = st;
+    std::unique_lock<std::mutex> lk;
+    if (ss != nullptr) {
+      lk = std::unique_lock<std::mutex>(ss->mu);
+      QPAM_CUDA(cudaEventRecord(ss->fork, st));
+      for (int i = 0; i < 3; ++i) QPAM_CUDA(cudaStreamWaitEvent(ss->s[i], ss->fork, 0));
+      s_dv = ss->s[0]; s_dk = ss->s[1]; s_an = ss->s[2];
+    }
+    if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
+    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", s_dv))) return rc;
+    if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk<dk>", s_dk))) return rc;
+    tcs::k_tc_state_anchors<<<dim3((unsigned)L.nslots, a->H), 256, 0, s_an>>>(p, anchors);
+    QPAM_LAUNCH_CHECK_ON("k_tc_state_anchors", s_an);
+    if (ss != nullptr) {
+      for (int i = 0; i < 3; ++i) {
+        QPAM_CUDA(cudaEventRecord(ss->join[i], ss->s[i]));
+        QPAM_CUDA(cudaStreamWaitEvent(st, ss->join[i], 0));
+      }
+      lk.unlock();
+    }
     tcs::k_tc_dgamma_finalize<<<dim3(L.grid_chunks, a->H), 128, 0, st>>>(p, anchors);
     QPAM_LAUNCH_CHECK("k_tc_dgamma_finalize");
   }

@@ -95,6 +95,7 @@ struct ScanParams {
   const float* coef;    // [K,B,H,T,2] or null
   void *y, *dq, *dk, *dv;
   float* dgamma;        // [K,B,H,T] (raw dA first, finalised in place)
+  float* dA_k;          // tensor-core backward: Re<k_t, dk_t> per token [B,H,T] (the dq and dk kernels may overlap)
   float* dcoef;         // [K,B,H,T,2] or null
   float2* states;       // [K,H,nslots,D,D]
   float2* dstates;      // [K,H,nslots,D,D]

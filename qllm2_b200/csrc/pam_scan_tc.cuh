@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(128) k_tc_dgamma_finalize(ScanParams p, const 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int len = L.len;
   const int j = TC - 1 - tid;                         // thread tid sums the tokens j .. len-1 of the chunk
-  float v = (j < len) ? p.dgamma[base + j] : 0.f;
+  float v = (j < len) ? p.dgamma[base + j] - p.dA_k[base + j] : 0.f;   // dA_t = Re<q,dq> - Re<k,dk>
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const float n = __shfl_up_sync(0xffffffffu, v, o);

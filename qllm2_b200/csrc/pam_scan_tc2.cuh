@@ -332,8 +332,8 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk2(const __grid_constant__ Ch
       __syncthreads();
       if (tid < L.len && ok) {
         const float d2 = dots[tid] + dots[TC + tid];
-        float* g = p.dgamma + gamma_base(p, 0, L.b, h, L.t0 + tid);
-        if (MODE == M_DQ) *g = d2; else *g -= d2;
+        const size_t gi = gamma_base(p, 0, L.b, h, L.t0 + tid);
+        if (MODE == M_DQ) p.dgamma[gi] = d2; else p.dA_k[gi] = d2;   // combined by k_tc_dgamma_finalize
       }
     }
   }
