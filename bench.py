@@ -668,6 +668,7 @@ def continuous_decode(dev, peaks, n_seq=512, n_slots=256, new_tokens=32, max_pro
         eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, **kw)
         for p_ in prompts:
             eng.submit(p_.tolist(), new_tokens)
+        eng.warmup()                                     # graph capture of the decode step, outside the timed run
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         res = eng.run()

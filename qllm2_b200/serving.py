@@ -254,6 +254,22 @@ class ContinuousBatcher:
         return m.greedy_next(lm[0])
 
     @torch.no_grad()
+    def warmup(self):
+        """Capture the decode step now (cuda_graph=True) instead of at the first decode step: a warm-up run on
+        idle rows only (slot id -1, no state changes), then the capture, which records and does not execute."""
+        if not self.cuda_graph or self._graph is not None:
+            return
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._decode_tensors(self._g_ids, self._g_pos, torch.full_like(self._g_slots, -1))
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._g_out = self._decode_tensors(self._g_ids, self._g_pos, self._g_slots)
+        self._graph = graph
+
+    @torch.no_grad()
     def _decode(self, live: List[Request]):
         n = len(live)
         self._ensure_rope(max(r.position for r in live) + 1)
@@ -267,16 +283,7 @@ class ContinuousBatcher:
             self._g_ids[:n, 0] = ids.to(self.device)
             self._g_pos[:n, 0] = positions.to(self.device)
             self._g_slots[:n] = slots.to(self.device)
-            if self._graph is None:
-                side = torch.cuda.Stream()
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side):   # warm-up outside the capture, on idle rows only (no slot changes)
-                    self._decode_tensors(self._g_ids, self._g_pos, torch.full_like(self._g_slots, -1))
-                torch.cuda.current_stream().wait_stream(side)
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self._g_out = self._decode_tensors(self._g_ids, self._g_pos, self._g_slots)
-                self._graph = graph
+            self.warmup()
             self._graph.replay()
             nxt = self._g_out[:n]
         else:
