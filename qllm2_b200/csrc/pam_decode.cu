@@ -141,10 +141,6 @@ __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uin
                : "l"(reinterpret_cast<uint64_t>(gdst)), "r"(umma::smem_u32(smem_src)), "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ void bulk_commit_and_wait_read() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
 
 constexpr int DEC_BULK_STATE_BYTES = 64 * 64 * 2 * 2;  // one bf16 state
 
@@ -153,7 +149,7 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
   constexpr int D = 64, NC = 4, LPR = D / NC, RPP = 256 / LPR, PASSES = D / RPP;
   extern __shared__ __align__(128) unsigned char dec_smem[];
   __shared__ float2 sq[D], sk[D], sv[D];
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar[QPAM_MAX_STATES];   // one per state: work on state k starts when it has landed
   const int tid = threadIdx.x;
   const int seq = blockIdx.x / p.H, h = blockIdx.x - seq * p.H;
   const int slot = p.slot_ids[seq];
@@ -162,12 +158,13 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
   const size_t state_elems = (size_t)D * D * 2;
   const size_t base = (((size_t)slot * p.L + p.layer) * p.K) * p.H + h;  // + k * H per state
   if (tid == 0) {
-    umma::mbar_init(&bar, 1);
+    for (int k = 0; k < p.K; ++k) umma::mbar_init(&bar[k], 1);
     umma::fence_barrier_init();
-    umma::mbar_arrive_expect_tx(&bar, (uint32_t)(p.K * DEC_BULK_STATE_BYTES));
-    for (int k = 0; k < p.K; ++k)
+    for (int k = 0; k < p.K; ++k) {
+      umma::mbar_arrive_expect_tx(&bar[k], (uint32_t)DEC_BULK_STATE_BYTES);
       bulk_load(dec_smem + (size_t)k * DEC_BULK_STATE_BYTES, pool + (base + (size_t)k * p.H) * state_elems,
-                DEC_BULK_STATE_BYTES, &bar);
+                DEC_BULK_STATE_BYTES, &bar[k]);
+    }
   }
   const size_t vb = ((size_t)seq * p.H + h) * D * 2;
   if (tid < D) {
@@ -175,8 +172,8 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
     sk[tid] = IO<T>::ld2(reinterpret_cast<const T*>(p.k) + vb + 2 * tid);
     sv[tid] = IO<T>::ld2(reinterpret_cast<const T*>(p.v) + vb + 2 * tid);
   }
-  __syncthreads();  // also publishes the barrier's initialisation to the waiters
-  const bool arrived = umma::mbar_wait(&bar, 0, 31);
+  __syncthreads();  // also publishes the barriers' initialisation to the waiters
+  bool arrived = true;
   const int row0 = tid / LPR, j0 = (tid % LPR) * NC;
   float2 kq[NC], qq[NC], yacc[PASSES];
 #pragma unroll
@@ -186,8 +183,10 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
   }
 #pragma unroll
   for (int r = 0; r < PASSES; ++r) yacc[r] = make_float2(0.f, 0.f);
-  if (arrived) {
+  {
     for (int k = 0; k < p.K; ++k) {
+      // on a give-up the error word is set and the arithmetic below is skipped; the barriers are not
+      arrived = umma::mbar_wait(&bar[k], 0, 31) && arrived;
       __nv_bfloat16* S = reinterpret_cast<__nv_bfloat16*>(dec_smem + (size_t)k * DEC_BULK_STATE_BYTES);
       const size_t gi = ((size_t)k * p.n + seq) * p.H + h;
       const float g = p.gamma[gi];
@@ -195,6 +194,7 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
       if (p.coef != nullptr) cf = *reinterpret_cast<const float2*>(p.coef + gi * 2);
 #pragma unroll
       for (int r = 0; r < PASSES; ++r) {
+        if (!arrived) break;
         const int row = row0 + r * RPP;
         uint4* cell = reinterpret_cast<uint4*>(S + ((size_t)row * D + j0) * 2);
         uint4 raw = *cell;
@@ -215,16 +215,16 @@ __global__ void __launch_bounds__(256) k_decode_step_bulk(DecodeParams p) {
         yacc[r].x += m.x;
         yacc[r].y += m.y;
       }
+      umma::fence_proxy_async();  // the bulk store below reads what the generic proxy just wrote
+      __syncthreads();
+      if (tid == 0 && arrived) {    // state k goes back while state k+1 is being updated
+        bulk_store(pool + (base + (size_t)k * p.H) * state_elems, dec_smem + (size_t)k * DEC_BULK_STATE_BYTES,
+                   DEC_BULK_STATE_BYTES);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
     }
   }
-  umma::fence_proxy_async();  // the bulk stores below read what the generic proxy just wrote
-  __syncthreads();
-  if (tid == 0 && arrived) {
-    for (int k = 0; k < p.K; ++k)
-      bulk_store(pool + (base + (size_t)k * p.H) * state_elems, dec_smem + (size_t)k * DEC_BULK_STATE_BYTES,
-                 DEC_BULK_STATE_BYTES);
-    bulk_commit_and_wait_read();  // shared memory must outlive the copies that read it
-  }
+  if (tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory must outlive the copies
 #pragma unroll
   for (int r = 0; r < PASSES; ++r) {
     float2 a = yacc[r];
