@@ -65,3 +65,28 @@ def test_out_of_range_slot_is_skipped():
     ops.pam_decode_step(pool, torch.tensor([-1, 1], dtype=torch.int32, device=DEV), x, x, x,
                         torch.ones(1, 2, 1, device=DEV))
     assert float(pool[0].abs().max()) == 0.0 and float(pool[1].abs().max()) > 0.0
+
+
+@pytest.mark.parametrize("state_dtype,tol", [(torch.float32, 2e-2), (torch.bfloat16, 3e-2)])
+def test_full_size_decode_steps_equal_the_scan(state_dtype, tol):
+    """Config-5 size (256 slots, 12 layers, H=12, d=64, K=3, bf16 tokens): a run of decode steps from empty slots
+    equals the chunked scan over the same tokens -- last output and final state -- in one layer of the pool,
+    and leaves every other layer untouched.  (The recurrent step takes gamma as is, the scan gamma + 1e-6.)"""
+    n, L, K, H, d, steps, layer = 256, 12, 3, 12, 64, 6, 7
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q, k, v = (torch.randn(n, H, steps, d, 2, device=DEV, generator=g).mul_(0.125).bfloat16() for _ in range(3))
+    gamma = torch.sigmoid(torch.randn(K, n, H, steps, device=DEV, generator=g) + 2.0)
+    coef = torch.randn(K, n, H, steps, 2, device=DEV, generator=g)
+    pool = torch.zeros(n, L, K, H, d, d, 2, dtype=state_dtype, device=DEV)
+    slots = torch.randperm(n, device=DEV, generator=g).int()           # sequence i lives in slot slots[i]
+    for t in range(steps):
+        y = ops.pam_decode_step(pool, slots, (q[:, :, t].float() * d ** -0.5).bfloat16().contiguous(), k[:, :, t].contiguous(),
+                                v[:, :, t].contiguous(), gamma[..., t].contiguous(), coef[:, :, :, t].contiguous(), layer=layer)
+    with torch.no_grad():
+        y_ref, s_ref = ops.pam_scan(q, k, v, gamma, coef=coef, eps=0.0)
+    ref = y_ref[:, :, -1].float()
+    assert float((y.float() - ref).norm() / ref.norm()) < tol
+    got = pool[slots.long(), layer].float().permute(1, 0, 2, 3, 4, 5)    # [K,n,H,d,d,2]
+    assert float((got - s_ref).norm() / s_ref.norm()) < tol
+    others = [i for i in range(L) if i != layer]
+    assert float(pool[:, others].float().abs().max()) == 0.0

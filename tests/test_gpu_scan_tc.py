@@ -187,3 +187,55 @@ def test_fused_k_state_forward_packed_and_launch_count():
     y_ref, s_ref = po.scan_varlen(qc, kc, vc, gamma.double().numpy(), p.cu_seqlens.numpy(), coef=po.to_complex(coef.numpy()))
     assert_close(y[0].float().cpu().numpy(), po.to_split(y_ref), TOL, "Y packed")
     assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S packed")
+
+
+def test_full_size_adjoint_identity_headline_shape():
+    """Headline shape (B=8, H=6, T=2048, d=64, bf16), tensor-core forward and backward: Y is linear in V, so
+    <dY, Y(V)> = <dV(dY), V>; and with Y = Y(Q) linear in Q, <dY, Y> = <dQ, Q>.  (Size-independent checks of
+    the gradients at the size the benchmark runs; bf16 bar 2e-2.)"""
+    inp = synthetic.scan_inputs(8, 6, 2048, 64, seed=51, dtype=torch.bfloat16)
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+    gam = inp.gamma.to(DEV).requires_grad_(True)
+    dy = inp.dy.to(DEV)
+    y, _ = ops.pam_scan(q, k, v, gam)
+    dq, dk, dv, dg = torch.autograd.grad(y, [q, k, v, gam], dy)
+    assert _lib.device_status() == 0
+    lhs = float((dy.double() * y.detach().double()).sum())
+    for name, g, x in (("V", dv, v), ("Q", dq, q)):
+        rhs = float((g.double() * x.detach().double()).sum())
+        assert abs(lhs - rhs) <= 2e-2 * abs(lhs), (name, lhs, rhs)
+    # conj-linearity in K gives the same pairing for dK
+    rhs = float((dk.double() * k.detach().double()).sum())
+    assert abs(lhs - rhs) <= 2e-2 * abs(lhs), ("K", lhs, rhs)
+    assert torch.isfinite(dg).all()
+
+
+def test_full_size_packed_prefill_properties():
+    """Config-4 size (32 packed sequences of 512..16384 tokens, H=16, d=64, bf16): a sequence scanned inside the
+    packed batch equals the same sequence scanned alone (chunks never straddle a boundary: bit for bit), and a
+    sequence split at a chunk boundary and chained through its state equals the unsplit scan."""
+    gen = torch.Generator().manual_seed(0)
+    lens = torch.randint(512, 16385, (32,), generator=gen)
+    cu = torch.zeros(33, dtype=torch.int32)
+    cu[1:] = lens.cumsum(0).int()
+    total, H = int(cu[-1]), 16
+    g2 = torch.Generator(device=DEV).manual_seed(1)
+    q, k, v = (torch.randn(1, H, total, 64, 2, device=DEV, generator=g2).mul_(128 ** -0.5).bfloat16() for _ in range(3))
+    gamma = torch.sigmoid(torch.randn(1, H, total, device=DEV, generator=g2) + 3.0)
+    with torch.no_grad():
+        y, s = ops.pam_scan(q, k, v, gamma, cu_seqlens=cu)
+        assert _lib.device_status() == 0
+        for i in (0, 13, 31):
+            a, b = int(cu[i]), int(cu[i + 1])
+            yi, si = ops.pam_scan(q[:, :, a:b].contiguous(), k[:, :, a:b].contiguous(), v[:, :, a:b].contiguous(),
+                                  gamma[:, :, a:b].contiguous())
+            assert torch.equal(yi, y[:, :, a:b]) and torch.equal(si[:, 0], s[:, i])
+        a, b = int(cu[5]), int(cu[6])
+        m = a + 128 * ((b - a) // 256)                      # a chunk boundary inside sequence 5
+        _, s_head = ops.pam_scan(q[:, :, a:m].contiguous(), k[:, :, a:m].contiguous(), v[:, :, a:m].contiguous(),
+                                 gamma[:, :, a:m].contiguous())
+        y_tail, s_tail = ops.pam_scan(q[:, :, m:b].contiguous(), k[:, :, m:b].contiguous(), v[:, :, m:b].contiguous(),
+                                      gamma[:, :, m:b].contiguous(), s0=s_head)
+    ref = y[:, :, m:b].float()
+    assert float((y_tail.float() - ref).norm() / ref.norm()) < 2e-3
+    assert float((s_tail[:, 0] - s[:, 5]).norm() / s[:, 5].norm()) < 1e-4
