@@ -151,7 +151,12 @@ static int scan_fwd_t(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t
 
 // chunk-local state sums on tensor cores, then the carry over the chunk axis
 static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
-  if (L.grid_chunks > 0) {
+  if (L.grid_chunks > 0 && a->K > 1) {      // all states from one load of the key / value tiles
+    int rc = set_smem(tcs::k_tc_chunk_outerK, tcs::OUTERK_SMEM);
+    if (rc) return rc;
+    tcs::k_tc_chunk_outerK<<<dim3(L.grid_chunks, a->H), 256, tcs::OUTERK_SMEM, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_outerK");
+  } else if (L.grid_chunks > 0) {
     int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);
     if (rc) return rc;
     tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H, a->K), 256, tcs::OUTER_SMEM, st>>>(p);

@@ -162,6 +162,132 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// State sums of K states from ONE load of the key / value tiles (forward only, 2 <= K <= 4).  The decay
+// weights of a state scale the rows, so they are moved to the value operand: A (the unweighted key rows
+// cj(k_s), (ki, kr)) is built once, and for every state B_k = w^k_s (Re v_s, Im v_s) is rewritten from the
+// registers that hold the value tile, followed by its MMA chain into that state's 64 TMEM columns.
+// grid = (chunks, H); 256 threads; same shared memory as k_tc_chunk_outer, 256 TMEM columns.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t OUTERK_SMEM = 1024 + 65536 + 32768 + 4096;
+
+__global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(ScanParams p) {
+  using namespace umma;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;            // [2 blocks][256 rows][128 B]
+  unsigned char* sB = smem + 65536;    // [256 rows][128 B]
+  float* Acum = reinterpret_cast<float*>(smem + 65536 + 32768);  // [KMAX][128]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + KMAX * TC);  // one per state
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + KMAX);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
+  if (!L.valid) return;
+  const int h = blockIdx.y;
+  const int K = p.K;
+  const size_t tb = token_base(p, L.b, h, L.t0, TD);
+  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + tb);
+  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.v) + tb);
+  uint4 kxa[8], vxa[8];
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = tid + 256 * it;
+    kxa[it] = make_uint4(0, 0, 0, 0);
+    vxa[it] = make_uint4(0, 0, 0, 0);
+    if ((idx >> 4) < L.len) {
+      kxa[it] = __ldg(kg + idx);
+      vxa[it] = __ldg(vg + idx);
+    }
+  }
+  if (tid == 0) {
+    for (int k = 0; k < K; ++k) mbar_init(&bar[k], 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  if (warp >= 1 && warp <= K)
+    warp_cumsum128(Acum + (warp - 1) * TC, p.gamma + gamma_base(p, warp - 1, L.b, h, L.t0), L.len, p.eps, lane);
+  // the key operand, unweighted, once
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = tid + 256 * it;
+    const int row = idx >> 4, c16 = idx & 15;
+    const uint4 kx = kxa[it];
+    const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w};
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 kk = unpack_bf162(kw[e]);
+      lo[e] = pack_bf162(kk.x, -kk.y);
+      hi[e] = pack_bf162(kk.y, kk.x);
+    }
+    unsigned char* ablk = sA + (c16 >> 3) * 32768;
+    *reinterpret_cast<uint4*>(ablk + sw128(row, c16 & 7)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4*>(ablk + sw128(128 + row, c16 & 7)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = true;
+  for (int k = 0; k < K; ++k) {
+    if (k > 0) {                       // the previous state's MMAs must have read the value operand
+      ok = mbar_wait(&bar[k - 1], 0, 205) && ok;
+      tc_fence_after();
+    }
+    const float a_last = Acum[k * TC + TC - 1];
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int idx = tid + 256 * it;
+      const int row = idx >> 4, c16 = idx & 15;
+      const uint4 vx = vxa[it];
+      const float w = __expf(fminf(0.f, a_last - Acum[k * TC + row]));
+      const uint32_t vw[4] = {vx.x, vx.y, vx.z, vx.w};
+      float vr[4], vi[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 vv = unpack_bf162(vw[e]);
+        vr[e] = w * vv.x;
+        vi[e] = w * vv.y;
+      }
+      const uint32_t boff = (c16 & 1) * 8;
+      *reinterpret_cast<uint2*>(sB + sw128(row, c16 >> 1) + boff) = make_uint2(pack_bf162(vr[0], vr[1]), pack_bf162(vr[2], vr[3]));
+      *reinterpret_cast<uint2*>(sB + sw128(128 + row, c16 >> 1) + boff) = make_uint2(pack_bf162(vi[0], vi[1]), pack_bf162(vi[2], vi[3]));
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (warp == 0 && elect_one()) {
+      tc_fence_after();
+      constexpr uint32_t idesc = idesc_bf16(128, 64, true, true);
+      const uint32_t a0 = smem_u32(sA), b0 = smem_u32(sB);
+#pragma unroll
+      for (int kk = 0; kk < 16; ++kk)
+        mma_bf16(tmem + k * 64, smem_desc_sw128(a0 + kk * 2048, 32768, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
+      mma_commit(&bar[k]);
+    }
+    __syncwarp();
+  }
+  ok = mbar_wait(&bar[K - 1], 0, 206) && ok;
+  tc_fence_after();
+  if (ok) {
+    const int q4 = warp & 3, cc = warp >> 2;   // TMEM lane quarter, column half
+    for (int k = 0; k < K; ++k) {
+      float2* slot = p.states + state_base(p, k, h, L.slot0 + L.c + 1, TD);
+      float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
+      float v[32];
+      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + k * 64 + cc * 32, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
+      if (tid == 0) p.chunk_decay[((size_t)k * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(Acum[k * TC + TC - 1]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc<256>(tmem);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Decay gradient on the tensor-core path.  The chunk kernels leave the raw per-token values
 // dA_t = Re<q_t,dq_t> - Re<k_t,dk_t>; da_u = sum_{t>=u} dA_t would accumulate their bf16-level errors
 // as a random walk over the whole sequence.  Instead the suffix sum is anchored at every chunk
