@@ -213,8 +213,9 @@ class ContinuousBatcher:
         state its predecessor left in the slot; a request emits its first token when its last piece is done."""
         lens = [take for _, _, take in items]
         self._ensure_rope(max(st + take for _, st, take in items))
+        # token ids and positions are assembled on the host and copied once each
         ids = torch.cat([torch.as_tensor(r.prompt[st:st + take], dtype=torch.long) for r, st, take in items]).to(self.device)[None]
-        positions = torch.cat([torch.arange(st, st + take, device=self.device) for _, st, take in items])[None]
+        positions = torch.cat([torch.arange(st, st + take) for _, st, take in items]).to(self.device)[None]
         cu = torch.zeros(len(items) + 1, dtype=torch.int32)
         cu[1:] = torch.tensor(lens).cumsum(0).int()
         cu = cu.to(self.device)
