@@ -5,7 +5,9 @@
 //
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      TMEM allocation + MMA issue (one elected lane)
-//   warps 2..5  epilogue; warp w owns TMEM lanes 32*(w%4) .. +31 (= tile rows)
+//   warps 2..9  epilogue; warp w owns TMEM lanes 32*(w%4) .. +31 (= tile rows); warps 2..5 take the lower
+//               half of a tile's columns, warps 6..9 the upper half, so every scheduler holds two epilogue
+//               warps and one covers the other's tcgen05.ld latency
 //
 // A CTA owns one 128-row tile and walks the N tiles [n_begin, n_end) over the K blocks
 // [kb_begin, kb_end).  Operands may be K-major (rows of 64 K elements) or MN-major (rows of 64
@@ -18,7 +20,8 @@ namespace qpam {
 namespace tc {
 
 constexpr int BM = 128, BK = 64;
-constexpr int NTHREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 
 enum Epi { EPI_STATS = 0, EPI_PROBS = 1, EPI_STORE = 2 };
 
@@ -91,7 +94,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 4);  // one arrival per epilogue warp
+      mbar_init(&tempty[b], EPI_WARPS);  // one arrival per epilogue warp
     }
     fence_barrier_init();
   }
@@ -166,8 +169,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         }
       }
     } else {
-      // ------------------------------------------------------------- epilogue (4 warps)
+      // ------------------------------------------------------------- epilogue (8 warps)
       const int quarter = warp & 3;
+      const int half = (warp - 2) >> 2;                        // which half of the tile's columns
+      constexpr int CC_HALF = BN / 64;                         // 32-column groups per half
       const int r_tile = quarter * 32 + lane;                  // row within the tile == TMEM lane
       const int64_t row = (int64_t)m_tile * BM + r_tile;       // row of D
       const bool row_ok = row < p.M;
@@ -198,7 +203,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         tc_fence_after();
         const int64_t col0 = (int64_t)n * BN;
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 32; ++cc) {
+        for (int cc = half * CC_HALF; cc < (half + 1) * CC_HALF; ++cc) {
           float v[32];
           tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
           const int64_t cbase = col0 + cc * 32;
@@ -263,7 +268,25 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         __syncwarp();
         if (lane == 0) mbar_arrive(&tempty[buf]);
       }
-      if (EPI == EPI_STATS && ok && row_ok) {
+      if (EPI == EPI_STATS) {
+        // The two warps of a row fold their running statistics through shared memory.  The ring's first
+        // stage is free by now: a warp that saw the last accumulator complete has seen every load consumed.
+        float* mg = reinterpret_cast<float*>(smem) + r_tile * 5;
+        if (half == 1 && ok) {
+          mg[0] = m_run; mg[1] = s_run; mg[2] = tz; mg[3] = best; mg[4] = __int_as_float(bidx);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
+        if (half == 0 && ok) {
+          const float m1 = mg[0], s1 = mg[1], b1 = mg[3];
+          const int i1 = __float_as_int(mg[4]);
+          const float m_new = fmaxf(m_run, m1);
+          if (m_new > -INFINITY) s_run = s_run * __expf(m_run - m_new) + s1 * __expf(m1 - m_new);
+          m_run = m_new;
+          tz += mg[2];
+          if (b1 > best || (b1 == best && i1 < bidx)) { best = b1; bidx = i1; }
+        }
+      }
+      if (EPI == EPI_STATS && ok && row_ok && half == 0) {
         const size_t o = (size_t)blockIdx.x * p.stats_ld + p.row_base + row;
         p.pm[o] = m_run;
         p.ps[o] = s_run;

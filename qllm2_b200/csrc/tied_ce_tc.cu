@@ -38,13 +38,31 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   if (rows < tc::BM) rows = tc::BM;
   pl.chunk_rows = rows;
   const int64_t f_tiles = (a->F + 255) / 256;
-  int64_t ks = (296 + f_tiles * (rows / tc::BM) - 1) / (f_tiles * (rows / tc::BM));
+  // split-K of dH: one CTA per SM, so the cost is (waves of 148 CTAs) x (K blocks per split)
   const int64_t kb_total = (a->V + tc::BK - 1) / tc::BK;
-  if (ks > 8) ks = 8;
-  if (ks > kb_total) ks = kb_total;
-  if (ks < 1) ks = 1;
+  int64_t ks = 1, ks_cost = -1;
+  for (int64_t s = 1; s <= 8 && s <= kb_total; ++s) {
+    const int64_t ctas = f_tiles * (rows / tc::BM) * s;
+    const int64_t cost = ((ctas + 147) / 148) * ((kb_total + s - 1) / s + 8);   // + 8: prologue and epilogue of a CTA
+    if (ks_cost < 0 || cost < ks_cost) { ks_cost = cost; ks = s; }
+  }
   pl.ksplit = (int32_t)ks;
   return pl;
+}
+
+// Vocabulary tiles one CTA of the probability pass walks for its row tile: more tiles hide the epilogue of one
+// tile behind the MMAs of the next (two accumulator buffers), fewer fill the last wave better.
+static int probs_tiles_per_cta(int64_t row_tiles, int n_tiles) {
+  int best = 1;
+  double best_eff = -1.0;
+  for (int t = 1; t <= 32 && t <= n_tiles; ++t) {
+    const int groups = (n_tiles + t - 1) / t;
+    const double ctas = (double)row_tiles * groups;
+    const double waves = (double)(int64_t)((ctas + 147) / 148);
+    const double eff = (ctas / (waves * 148)) * ((double)n_tiles / ((double)t * groups)) * (t / (t + 1.2));
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = t; }
+  }
+  return best;
 }
 
 // ------------------------------------------------------------------ forward statistics
@@ -118,9 +136,10 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     if ((rc = make_map(&tmHmn, hchunk, F, rows, F, 64, 64))) return rc;              // MN-major B of dW ([K=rows][N=F])
     if ((rc = make_map(&tmPk, b.pbuf, V, rows, b.ldp, tc::BK, tc::BM))) return rc;   // K-major A of dH ([M=rows][K=V])
     if ((rc = make_map(&tmPmn, b.pbuf, V, rows, b.ldp, 64, 64))) return rc;          // MN-major A of dW ([K=rows][M=V])
-    // 1) P = (softmax - onehot) * scale, bf16, one 128 x 256 tile per CTA
+    // 1) P = (softmax - onehot) * scale, bf16, 128 x 256 tiles; a CTA walks a few vocabulary tiles of its rows
     tc::GemmParams p{};
-    p.n_tiles = pl.n_tiles; p.tiles_per_cta = 1;
+    p.n_tiles = pl.n_tiles; p.tiles_per_cta = probs_tiles_per_cta(row_tiles, pl.n_tiles);
+    const unsigned n_groups = (unsigned)((pl.n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta);
     p.kb_total = (F + tc::BK - 1) / tc::BK; p.kb_per_split = p.kb_total;
     p.M = rows; p.N = V;
     p.targets = a->targets; p.v_offset = a->v_offset; p.ignore_index = a->ignore_index;
@@ -128,7 +147,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
     p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
     p.swap_xy = 1;   // consecutive CTAs take the row tiles of one vocabulary tile: W is read from DRAM once
-    k_probs<<<dim3(row_tiles, pl.n_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
+    k_probs<<<dim3(row_tiles, n_groups, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
     QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
     // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
     tc::GemmParams g{};
