@@ -60,7 +60,9 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int EPI_STAGE_BYTES = 4096;               // per epilogue warp: 32 rows x 64 bf16, swizzled
+  static constexpr size_t SMEM_BYTES =
+      (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
 };
 
 template <int BN, int EPI, bool A_MN, bool B_MN>
@@ -202,65 +204,89 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (!mbar_wait(&tfull[buf], bphase, 104)) { ok = false; break; }
         tc_fence_after();
         const int64_t col0 = (int64_t)n * BN;
+        if constexpr (EPI == EPI_PROBS) {
+          // Probability tiles leave through a per-warp staging block so that global stores are whole 128-byte
+          // rows: a lane owns a tile row in TMEM, but 8 lanes share a row when storing.  16-byte pieces are
+          // placed at (piece ^ (row & 7)) within their 128-byte row: both phases are free of bank conflicts.
+          unsigned char* stg = smem + (size_t)C::STAGES * C::STAGE_BYTES + 256 + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
+          const int64_t row0 = (int64_t)m_tile * BM + quarter * 32;
 #pragma unroll 1
-        for (int cc = half * CC_HALF; cc < (half + 1) * CC_HALF; ++cc) {
-          float v[32];
-          tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
-          const int64_t cbase = col0 + cc * 32;
-          if (EPI == EPI_STATS) {
-            if (cbase >= p.N) continue;
-            const int nvalid = (int)min((int64_t)32, p.N - cbase);
-            float cmax = -INFINITY;
-            int ci = 0;
+          for (int g = half * (BN / 128); g < (half + 1) * (BN / 128); ++g) {   // groups of 64 columns
+            const int64_t cb = col0 + g * 64;
+            if (cb >= p.ldp) break;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid && v[j] > cmax) { cmax = v[j]; ci = j; }
-            if (cmax > best) { best = cmax; bidx = (int)cbase + ci; }
-            const float m_new = fmaxf(m_run, cmax);
-            float se = 0.f;
+            for (int hh = 0; hh < 2; ++hh) {
+              float v[32];
+              tmem_ld32(tmem_base + lane_addr + buf * BN + g * 64 + hh * 32, v);
+              const int64_t dt = tcol - (cb + hh * 32);
+              const int tj = (dt >= 0 && dt < 32) ? (int)dt : -1;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) se += __expf(v[j] - m_new);
-            s_run = s_run * __expf(m_run - m_new) + se;
-            m_run = m_new;
-            if (tcol >= cbase && tcol < cbase + 32) {
-              const int tj = (int)(tcol - cbase);
+              for (int g8 = 0; g8 < 4; ++g8) {
+                uint4 pk;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const int j0 = g8 * 8 + 2 * j;
+                  float a = __expf(v[j0] - lse_r);
+                  float b = __expf(v[j0 + 1] - lse_r);
+                  if (j0 == tj) a -= 1.f;
+                  if (j0 + 1 == tj) b -= 1.f;
+                  h2[j] = __floats2bfloat162_rn(a * sc_r, b * sc_r);
+                }
+                *reinterpret_cast<uint4*>(stg + lane * 128 + (((hh * 4 + g8) ^ (lane & 7)) << 4)) = pk;
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int r = 4 * i + (lane >> 3), c = lane & 7;
+              const uint4 pk = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+              if (row0 + r < p.M && cb + c * 8 + 8 <= p.ldp)
+                *reinterpret_cast<uint4*>(p.pbuf + (row0 + r) * p.ldp + cb + c * 8) = pk;
+            }
+            __syncwarp();
+          }
+        } else {
+#pragma unroll 1
+          for (int cc = half * CC_HALF; cc < (half + 1) * CC_HALF; ++cc) {
+            float v[32];
+            tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
+            const int64_t cbase = col0 + cc * 32;
+            if (EPI == EPI_STATS) {
+              if (cbase >= p.N) continue;
+              const int nvalid = (int)min((int64_t)32, p.N - cbase);
+              float cmax = -INFINITY;
+              int ci = 0;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (j == tj) tz = v[j];
-            }
-          } else if (EPI == EPI_PROBS) {
-            if (!row_ok || cbase >= p.ldp) continue;
-            __nv_bfloat16* dst = p.pbuf + row * p.ldp + cbase;
-            const int tj = (tcol >= cbase && tcol < cbase + 32) ? (int)(tcol - cbase) : -1;
+                if (j < nvalid && v[j] > cmax) { cmax = v[j]; ci = j; }
+              if (cmax > best) { best = cmax; bidx = (int)cbase + ci; }
+              const float m_new = fmaxf(m_run, cmax);
+              float se = 0.f;
 #pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              if (cbase + g8 * 8 + 8 > p.ldp) break;
-              uint4 pk;
-              __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+              for (int j = 0; j < 32; ++j)
+                if (j < nvalid) se += __expf(v[j] - m_new);
+              s_run = s_run * __expf(m_run - m_new) + se;
+              m_run = m_new;
+              if (tcol >= cbase && tcol < cbase + 32) {
+                const int tj = (int)(tcol - cbase);
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int j0 = g8 * 8 + 2 * j;
-                float a = __expf(v[j0] - lse_r);
-                float b = __expf(v[j0 + 1] - lse_r);
-                if (j0 == tj) a -= 1.f;
-                if (j0 + 1 == tj) b -= 1.f;
-                h2[j] = __floats2bfloat162_rn(a * sc_r, b * sc_r);
+                for (int j = 0; j < 32; ++j)
+                  if (j == tj) tz = v[j];
               }
-              *reinterpret_cast<uint4*>(dst + g8 * 8) = pk;
-            }
-          } else {  // EPI_STORE
-            if (!row_ok || cbase >= p.N) continue;
-            float* dst = p.c + ((size_t)blockIdx.z * p.M + row) * p.ldc + cbase;
+            } else {  // EPI_STORE
+              if (!row_ok || cbase >= p.N) continue;
+              float* dst = p.c + ((size_t)blockIdx.z * p.M + row) * p.ldc + cbase;
 #pragma unroll
-            for (int g4 = 0; g4 < 8; ++g4) {
-              if (cbase + g4 * 4 + 4 > p.N) break;
-              float4 o = make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
-              if (p.beta) {
-                const float4 c0 = *reinterpret_cast<const float4*>(dst + g4 * 4);
-                o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+              for (int g4 = 0; g4 < 8; ++g4) {
+                if (cbase + g4 * 4 + 4 > p.N) break;
+                float4 o = make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+                if (p.beta) {
+                  const float4 c0 = *reinterpret_cast<const float4*>(dst + g4 * 4);
+                  o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+                }
+                *reinterpret_cast<float4*>(dst + g4 * 4) = o;
               }
-              *reinterpret_cast<float4*>(dst + g4 * 4) = o;
             }
           }
         }
