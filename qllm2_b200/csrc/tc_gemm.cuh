@@ -61,8 +61,9 @@ struct Cfg {
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers
   static constexpr int EPI_STAGE_BYTES = 4096;               // per epilogue warp: 32 rows x 64 bf16, swizzled
-  static constexpr size_t SMEM_BYTES =
-      (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // EPI_PROBS and EPI_STORE launches add the staging blocks (EPI_STATS keeps the bytes for L1)
+  static constexpr size_t SMEM_BYTES_STAGED = SMEM_BYTES + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
 };
 
 template <int BN, int EPI, bool A_MN, bool B_MN>
@@ -274,19 +275,30 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 for (int j = 0; j < 32; ++j)
                   if (j == tj) tz = v[j];
               }
-            } else {  // EPI_STORE
-              if (!row_ok || cbase >= p.N) continue;
-              float* dst = p.c + ((size_t)blockIdx.z * p.M + row) * p.ldc + cbase;
+            } else {  // EPI_STORE: through the staging block, whole 128-byte rows per 8 lanes
+              if (cbase >= p.N) continue;
+              unsigned char* stg =
+                  smem + (size_t)C::STAGES * C::STAGE_BYTES + 256 + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
+              const int64_t row0 = (int64_t)m_tile * BM + quarter * 32;
 #pragma unroll
-              for (int g4 = 0; g4 < 8; ++g4) {
-                if (cbase + g4 * 4 + 4 > p.N) break;
-                float4 o = make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
-                if (p.beta) {
-                  const float4 c0 = *reinterpret_cast<const float4*>(dst + g4 * 4);
-                  o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+              for (int g4 = 0; g4 < 8; ++g4)
+                *reinterpret_cast<float4*>(stg + lane * 128 + ((g4 ^ (lane & 7)) << 4)) =
+                    make_float4(v[g4 * 4], v[g4 * 4 + 1], v[g4 * 4 + 2], v[g4 * 4 + 3]);
+              __syncwarp();
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int r = 4 * i + (lane >> 3), c = lane & 7;
+                float4 o = *reinterpret_cast<const float4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
+                if (row0 + r < p.M && cbase + c * 4 + 4 <= p.N) {
+                  float* dst = p.c + ((size_t)blockIdx.z * p.M + row0 + r) * p.ldc + cbase + c * 4;
+                  if (p.beta) {
+                    const float4 c0 = *reinterpret_cast<const float4*>(dst);
+                    o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+                  }
+                  *reinterpret_cast<float4*>(dst) = o;
                 }
-                *reinterpret_cast<float4*>(dst + g4 * 4) = o;
               }
+              __syncwarp();
             }
           }
         }

@@ -114,11 +114,11 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
   auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false>;
   auto k_dh = tc::k_tc_gemm<256, tc::EPI_STORE, false, true>;
   auto k_dw = tc::k_tc_gemm<256, tc::EPI_STORE, true, true>;
-  int rc = opt_in_smem(k_probs, tc::Cfg<256>::SMEM_BYTES);
+  int rc = opt_in_smem(k_probs, tc::Cfg<256>::SMEM_BYTES_STAGED);
   if (rc) return rc;
-  rc = opt_in_smem(k_dh, tc::Cfg<256>::SMEM_BYTES);
+  rc = opt_in_smem(k_dh, tc::Cfg<256>::SMEM_BYTES_STAGED);
   if (rc) return rc;
-  rc = opt_in_smem(k_dw, tc::Cfg<256>::SMEM_BYTES);
+  rc = opt_in_smem(k_dw, tc::Cfg<256>::SMEM_BYTES_STAGED);
   if (rc) return rc;
   CUtensorMap tmWk, tmWmn;
   rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 256);   // K-major B of the logits GEMM
@@ -147,7 +147,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
     p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
     p.swap_xy = 1;   // consecutive CTAs take the row tiles of one vocabulary tile: W is read from DRAM once
-    k_probs<<<dim3(row_tiles, n_groups, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmHk, tmWk, p);
+    k_probs<<<dim3(row_tiles, n_groups, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED, st>>>(tmHk, tmWk, p);
     QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
     // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
     tc::GemmParams g{};
@@ -157,7 +157,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     const int ks = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
     g.M = rows; g.N = F;
     g.c = b.dh_part; g.ldc = F; g.beta = 0;
-    k_dh<<<dim3(f_tiles, row_tiles, ks), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmPk, tmWmn, g);
+    k_dh<<<dim3(f_tiles, row_tiles, ks), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED, st>>>(tmPk, tmWmn, g);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dH>");
     k_reduce_splits_bf16<<<592, 256, 0, st>>>(b.dh_part, reinterpret_cast<__nv_bfloat16*>(dh) + r0 * F, rows * F, ks,
                                              rows * F);
@@ -168,7 +168,8 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     w.kb_total = (int32_t)((rows + tc::BK - 1) / tc::BK); w.kb_per_split = w.kb_total;
     w.M = V; w.N = F;
     w.c = b.dwacc; w.ldc = F; w.beta = first ? 0 : 1;
-    k_dw<<<dim3(f_tiles, (unsigned)((V + tc::BM - 1) / tc::BM), 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(
+    k_dw<<<dim3(f_tiles, (unsigned)((V + tc::BM - 1) / tc::BM), 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED,
+           st>>>(
         tmPmn, tmHmn, w);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dW>");
     first = 0;
