@@ -49,7 +49,7 @@ static CELayout ce_layout(const qpam_ce_args* a) {
   if (L.tc.enabled && (size_t)L.tc.chunk_rows * row_bytes > pbuf_bytes) pbuf_bytes = (size_t)L.tc.chunk_rows * row_bytes;
   L.off_pbuf = off; off += ce_align(pbuf_bytes);
   L.off_dwacc = off;
-  if (a->io_dtype != QPAM_F32) off += ce_align((size_t)a->V * a->F * 4);
+  if (a->io_dtype != QPAM_F32) off += ce_align((size_t)(L.tc.enabled ? L.tc.dw_bufs : 1) * a->V * a->F * 4);
   L.off_dhpart = off;
   if (L.tc.enabled) off += ce_align((size_t)L.tc.ksplit * L.tc.chunk_rows * a->F * 4);
   L.total_bwd = off;

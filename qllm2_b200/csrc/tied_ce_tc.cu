@@ -34,7 +34,7 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   pl.nsplit = best;
   pl.tiles_per_split = (pl.n_tiles + best - 1) / best;
   int64_t rows = ((a->N + tc::BM - 1) / tc::BM) * tc::BM;
-  if (rows > 4096) rows = 4096;
+  if (rows > 8192) rows = 8192;
   if (rows < tc::BM) rows = tc::BM;
   pl.chunk_rows = rows;
   const int64_t f_tiles = (a->F + 255) / 256;
@@ -47,6 +47,10 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
     if (ks_cost < 0 || cost < ks_cost) { ks_cost = cost; ks = s; }
   }
   pl.ksplit = (int32_t)ks;
+  // every row chunk (up to 4) sums its dW into a buffer of its own: adding into one buffer made the epilogue
+  // of the later chunks read what it writes (+50 % on that launch); the final bf16 pass adds the buffers
+  const int64_t n_chunks = (a->N + rows - 1) / rows;
+  pl.dw_bufs = (int32_t)(n_chunks < 1 ? 1 : (n_chunks > 4 ? 4 : n_chunks));
   return pl;
 }
 
@@ -126,7 +130,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
   rc = make_map(&tmWmn, a->w, F, V, F, 64, 64);        // MN-major B of dH = P W   ([K=V][N=F])
   if (rc) return rc;
   const int f_tiles = (F + 255) / 256;
-  int first = 1;
+  int chunk_idx = 0;
   for (int64_t r0 = 0; r0 < a->N; r0 += pl.chunk_rows) {
     const int64_t rows = (a->N - r0 < pl.chunk_rows) ? a->N - r0 : pl.chunk_rows;
     const unsigned row_tiles = (unsigned)((rows + tc::BM - 1) / tc::BM);
@@ -167,14 +171,15 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     w.n_tiles = f_tiles; w.tiles_per_cta = 1;
     w.kb_total = (int32_t)((rows + tc::BK - 1) / tc::BK); w.kb_per_split = w.kb_total;
     w.M = V; w.N = F;
-    w.c = b.dwacc; w.ldc = F; w.beta = first ? 0 : 1;
+    w.c = b.dwacc + (size_t)(chunk_idx % pl.dw_bufs) * V * F; w.ldc = F; w.beta = chunk_idx >= pl.dw_bufs ? 1 : 0;
     k_dw<<<dim3(f_tiles, (unsigned)((V + tc::BM - 1) / tc::BM), 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED,
            st>>>(
         tmPmn, tmHmn, w);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dW>");
-    first = 0;
+    ++chunk_idx;
   }
-  k_reduce_splits_bf16<<<1184, 256, 0, st>>>(b.dwacc, reinterpret_cast<__nv_bfloat16*>(dw), V * (int64_t)F, 1, 0);
+  k_reduce_splits_bf16<<<1184, 256, 0, st>>>(b.dwacc, reinterpret_cast<__nv_bfloat16*>(dw), V * (int64_t)F,
+                                            chunk_idx < pl.dw_bufs ? (chunk_idx > 0 ? chunk_idx : 1) : pl.dw_bufs, V * (int64_t)F);
   QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
   return QPAM_OK;
 }

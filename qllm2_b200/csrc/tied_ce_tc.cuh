@@ -11,6 +11,7 @@ struct CETcPlan {
   int32_t tiles_per_split;
   int64_t chunk_rows;    // rows per backward chunk (multiple of 128)
   int32_t ksplit;        // split-K factor of the dH GEMM
+  int32_t dw_bufs;       // fp32 [V][F] accumulation buffers of dW (one per row chunk, at most 4)
 };
 
 CETcPlan ce_tc_plan(const qpam_ce_args* a);
@@ -21,7 +22,7 @@ struct CETcBuffers {
   void* pbuf;       // bf16 [chunk_rows][ldp]
   int64_t ldp;
   float* dh_part;   // [ksplit][chunk_rows][F]
-  float* dwacc;     // [V][F]
+  float* dwacc;     // [dw_bufs][V][F]
 };
 
 // per-row partial statistics [nsplit][N] via the tensor-core logits GEMM

@@ -51,3 +51,24 @@ def test_masked_and_scaled():
     assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
     assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("N", [8192 + 300, 4 * 8192 + 200])
+def test_many_row_chunks(N):
+    """Backward over several row chunks: two chunks sum dW in buffers of their own, a fifth chunk adds into the
+    first buffer again.  Checked against fp64 arithmetic on the same bf16 values (numpy, vectorised)."""
+    D, V = 32, 520
+    c = synthetic.ce_inputs(N, D, V, seed=11, dtype=torch.bfloat16)
+    w_host = (c.w.float() * 20).bfloat16()
+    t_host = c.targets.clone()
+    t_host[::7] = -100
+    h = c.h.to(DEV).requires_grad_(True)
+    w = w_host.to(DEV).requires_grad_(True)
+    loss = fused_ce.fused_linear_cross_entropy(h, w, t_host.to(DEV))
+    loss.backward()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    r = ce_oracle.linear_ce(c.h.float().numpy(), w_host.float().numpy(), t_host.numpy())
+    assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"])
+    assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
+    assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
