@@ -176,12 +176,12 @@ class _CguGateFn(torch.autograd.Function):
         gate, N, C, ldg = _rows(gate)
         up, _, _, ldu = _rows(up)
         dout = dout.to(gate.dtype).contiguous()
-        # one buffer [..., 2C, 2]: when gate and up are the two halves of one projection output, autograd
-        # can hand the buffer on without re-assembling it
-        both = torch.empty(*gate.shape[:-2], 2 * C, 2, dtype=gate.dtype, device=gate.device)
-        dgate, dup = both[..., :C, :], both[..., C:, :]
+        # two dense tensors: the consumers (the activation's backward, the projections' GEMMs) take them as they
+        # are; halves of one buffer would be copied by the first consumer that needs dense rows
+        dgate = torch.empty(*gate.shape[:-2], C, 2, dtype=gate.dtype, device=gate.device)
+        dup = torch.empty_like(dgate)
         check(_lib.lib().qpam_cgu_gate_bwd(ptr(gate), ldg, ptr(up), ldu, ptr(dout), dtype_code(gate.dtype),
-                                           ptr(dgate), 4 * C, dup.data_ptr(), 4 * C, N, C, stream_ptr()),
+                                           ptr(dgate), 2 * C, ptr(dup), 2 * C, N, C, stream_ptr()),
               "qpam_cgu_gate_bwd")
         return dgate, dup
 
