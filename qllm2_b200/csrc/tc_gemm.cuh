@@ -86,11 +86,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const int n_end = min(p.n_tiles, n_begin + p.tiles_per_cta);
   const int kb_begin = blockIdx.z * p.kb_per_split;
   const int kb_end = min(p.kb_total, kb_begin + p.kb_per_split);
-  // after a failed handshake anywhere on the device, later CTAs do not start new work
-  const bool has_work = (n_begin < n_end) && (kb_begin < kb_end) &&
-                        (*reinterpret_cast<volatile int*>(&g_device_error) == 0);
+  uint32_t* err_slot = tmem_slot + 1;
 
   if (threadIdx.x == 0) {
+    // one read of the device error word for the whole CTA: every warp must take the same side of has_work
+    // (the epilogue warps meet at a named barrier), whatever another CTA writes meanwhile
+    *err_slot = (uint32_t) * reinterpret_cast<volatile int*>(&g_device_error);
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -106,6 +107,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // after a failed handshake anywhere on the device, later CTAs do not start new work
+  const bool has_work = (n_begin < n_end) && (kb_begin < kb_end) && (*err_slot == 0);
 
   if (has_work) {
     if (warp == 0) {
