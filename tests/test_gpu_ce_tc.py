@@ -72,3 +72,26 @@ def test_many_row_chunks(N):
     assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"])
     assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
     assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
+
+
+@pytest.mark.parametrize("N,D,V", [(8191, 32, 1000), (257, 4, 9), (640, 100, 4099), (5, 32, 100000), (127, 36, 255)])
+def test_odd_shapes_masked_scaled(N, D, V):
+    """Rows one short of a chunk, fewer columns than one tile, a vocabulary of one row tile of logits per
+    hundred thousand columns, widths that are not a power of two; mask, ignored rows and an upstream factor."""
+    c = synthetic.ce_inputs(N, D, V, seed=N + 3 * V, dtype=torch.bfloat16)
+    w_host = (c.w.float() * 20).bfloat16()
+    t_host = c.targets.clone()
+    t_host[::9] = -100
+    gen = torch.Generator().manual_seed(N)
+    mask = (torch.rand(N, generator=gen) > 0.2).float()
+    h = c.h.to(DEV).requires_grad_(True)
+    w = w_host.to(DEV).requires_grad_(True)
+    loss = fused_ce.fused_linear_cross_entropy(h, w, t_host.to(DEV), mask=mask.to(DEV))
+    (1.7 * loss).backward()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    r = ce_oracle.linear_ce(c.h.float().numpy(), w_host.float().numpy(), t_host.numpy(), mask=mask.numpy(),
+                            grad_output=1.7)
+    assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"])
+    assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
+    assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
