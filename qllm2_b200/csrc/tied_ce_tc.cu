@@ -21,14 +21,16 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   // vocabulary splits: fill the 148 SMs in whole waves (one CTA per SM: the ring takes ~193 KB)
   int best = 1;
   double best_eff = -1.0;
-  const int max_split = pl.n_tiles < 64 ? pl.n_tiles : 64;
+  const int max_split = pl.n_tiles < 128 ? pl.n_tiles : 128;
   for (int s = 1; s <= max_split; ++s) {
     const int tps = (pl.n_tiles + s - 1) / s;
     const int real = (pl.n_tiles + tps - 1) / tps;
     if (real != s) continue;
     const double ctas = (double)row_tiles * s;
     const double waves = (ctas + 147) / 148;
-    const double eff = ctas / ((double)(int64_t)waves * 148) * ((double)pl.n_tiles / ((double)tps * s));
+    // last factor: a CTA pays its prologue and one epilogue that no MMA overlaps (~0.7 of a tile's time)
+    const double eff = ctas / ((double)(int64_t)waves * 148) * ((double)pl.n_tiles / ((double)tps * s)) *
+                       (tps / (tps + 0.7));
     if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
   }
   pl.nsplit = best;
