@@ -228,7 +228,7 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
 // Side streams of the tensor-core backward (one set per device, created on first use; never destroyed).
 struct SideStreams {
   cudaStream_t s[3];
-  cudaEvent_t fork, join[3];
+  cudaEvent_t fork, fork2, join[3];
   std::mutex mu;          // one enqueue at a time reuses the events
 };
 static SideStreams* side_streams() {
@@ -239,9 +239,14 @@ static SideStreams* side_streams() {
   std::lock_guard<std::mutex> lk(mu);
   if (per_dev[dev] == nullptr) {
     SideStreams* ss = new SideStreams();
-    bool ok = cudaEventCreateWithFlags(&ss->fork, cudaEventDisableTiming) == cudaSuccess;
+    // the side streams carry the critical chain of the backward at the highest priority the device offers: a
+    // caller's stream has the default (lowest) one, so what stays on it only fills the slots they leave
+    int prio_least = 0, prio_greatest = 0;
+    bool ok = cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ss->fork, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&ss->fork2, cudaEventDisableTiming) == cudaSuccess;
     for (int i = 0; i < 3 && ok; ++i)
-      ok = cudaStreamCreateWithFlags(&ss->s[i], cudaStreamNonBlocking) == cudaSuccess &&
+      ok = cudaStreamCreateWithPriority(&ss->s[i], cudaStreamNonBlocking, prio_greatest) == cudaSuccess &&
            cudaEventCreateWithFlags(&ss->join[i], cudaEventDisableTiming) == cudaSuccess;
     if (!ok) {
       cudaGetLastError();
@@ -269,31 +274,39 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     rc = tc_states(pf, L, a, st);
     if (rc) return rc;
   }
+  float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
+  p.dA_k = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_dak);
+  // Order of the backward: gradient state sums -> reverse carry -> dv, dk (and the anchors) is the critical
+  // chain; dq needs only the forward states.  The chain runs on high-priority side streams and dq on the
+  // caller's stream from the start: its CTAs take the slots the chain leaves free (the partly filled last
+  // wave of each 768-CTA kernel over 296 resident slots, and the SMs idle under the small carry kernel).
+  // While the per-kernel profiler records on one stream everything stays on it, in dependency order.
+  SideStreams* ss = (L.grid_chunks > 0 && !profiling_active()) ? side_streams() : nullptr;
+  std::unique_lock<std::mutex> lk;
+  cudaStream_t sc = st;                  // stream of the critical chain
+  if (ss != nullptr) {
+    lk = std::unique_lock<std::mutex>(ss->mu);
+    QPAM_CUDA(cudaEventRecord(ss->fork, st));
+    QPAM_CUDA(cudaStreamWaitEvent(ss->s[0], ss->fork, 0));
+    sc = ss->s[0];
+  }
   if (L.grid_chunks > 0) {
     rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
-    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<dstate>");
+    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, sc>>>(p);
+    QPAM_LAUNCH_CHECK_ON("k_tc_chunk_outer<dstate>", sc);
   }
-  k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
-  QPAM_LAUNCH_CHECK("k_state_scan<rev>");
+  k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, sc>>>(p, 64);
+  QPAM_LAUNCH_CHECK_ON("k_state_scan<rev>", sc);
   if (L.grid_chunks > 0) {
-    p.dA_k = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_dak);
-    float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
-    // dv, dq, dk and the anchors depend only on what precedes them: on side streams they overlap, so the
-    // partly filled last wave of one kernel is topped up by the next (768 CTAs over 296 slots = 2.6 waves
-    // each).  While the per-kernel profiler records on one stream everything stays on it.
-    SideStreams* ss = profiling_active() ? nullptr : side_streams();
-    cudaStream_t s_dv = st, s_dk = st, s_an = st;
-    std::unique_lock<std::mutex> lk;
-    if (ss != nullptr) {
-      lk = std::unique_lock<std::mutex>(ss->mu);
-      QPAM_CUDA(cudaEventRecord(ss->fork, st));
-      for (int i = 0; i < 3; ++i) QPAM_CUDA(cudaStreamWaitEvent(ss->s[i], ss->fork, 0));
-      s_dv = ss->s[0]; s_dk = ss->s[1]; s_an = ss->s[2];
-    }
     if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
-    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", s_dv))) return rc;
+    cudaStream_t s_dk = st, s_an = st;
+    if (ss != nullptr) {
+      QPAM_CUDA(cudaEventRecord(ss->fork2, sc));
+      for (int i = 1; i < 3; ++i) QPAM_CUDA(cudaStreamWaitEvent(ss->s[i], ss->fork2, 0));
+      s_dk = ss->s[1]; s_an = ss->s[2];
+    }
+    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", sc))) return rc;
     if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk<dk>", s_dk))) return rc;
     tcs::k_tc_state_anchors<<<dim3((unsigned)L.nslots, a->H), 256, 0, s_an>>>(p, anchors);
     QPAM_LAUNCH_CHECK_ON("k_tc_state_anchors", s_an);
