@@ -346,12 +346,9 @@ def main():
         "k_tc_chunk<fwd>": (4 * TT + ST, f_fwd - 8 * d * d * th),          # q,k,v,S -> y
         "k_tc_chunk_outer<state>": (2 * TT + ST, 8 * d * d * th),          # k,v -> U
         "k_tc_chunk_outer<dstate>": (2 * TT + ST, 8 * d * d * th),         # dy,q -> G
-        "k_tc_chunk<dv>": (4 * TT + ST, bwd_each),                         # k,q,dy,dS -> dv
-        "k_tc_chunk<dq>": (5 * TT + ST, bwd_each),                         # dy,v,k,S,q -> dq
-        "k_tc_chunk<dk>": (5 * TT + ST, bwd_each),                         # v,dy,q,dS,k -> dk
+        "k_tc_chunk<dq,dv,dk>": (7 * TT + 2 * ST, 3 * bwd_each),           # q,k,v,dy,S,dS -> dq,dk,dv (one launch)
         "k_state_scan<fwd>": (2 * ST, 0.0),
-        "k_state_scan<rev>": (2 * ST, 0.0),
-        "k_tc_state_anchors": (2 * ST, 0.0),
+        "k_tc_state_scan_rev": (3 * ST, 0.0),                              # G,S in; dS out (+ decay-gradient anchors)
     }
     roof_all = {}
     for n, kinfo in kernels.items():

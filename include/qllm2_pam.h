@@ -58,7 +58,8 @@ extern "C" {
  * channel, v11/model.py:939-947) or NULL.
  * d in {16,32,64}; 1 <= K <= QPAM_MAX_STATES.  `chunk` is accepted for interface
  * compatibility only: the result of the scan does not depend on the chunk length and the
- * kernels use their own tile of 64 tokens.
+ * kernels use their own tile (64 tokens in the fp32-math kernels, 128 in the tensor-core ones).
+ * cu_seqlens is checked on the device: see qpam_device_status, code 301.
  * ------------------------------------------------------------------------------------------ */
 typedef struct {
   const void* q;
@@ -348,10 +349,19 @@ long long qpam_launch_count(void);
 int qpam_profile_begin(void* stream);
 int qpam_profile_end(char* buf, size_t buf_bytes);
 
-/* Status word written by the tensor-core kernels: 0 = ok; a non-zero value means that a bounded
- * on-device wait (mbarrier) gave up and the affected outputs are invalid.  Synchronises the
- * device.  clear != 0 resets the word.  (No counterpart in the reference.) */
+/* Status word written by the kernels: 0 = ok.  Non-zero values:
+ *   2xx  a bounded on-device wait (mbarrier) gave up: the outputs of that launch are invalid, and every
+ *        tensor-core scan launch that starts while the word is set returns without touching its outputs;
+ *   301  a packed-mode scan was given a cu_seqlens descriptor that does not start at 0, decreases, or ends
+ *        beyond T: no kernel of that call read or wrote through it, its outputs are untouched.
+ * Synchronises the device.  clear != 0 resets the word.  Callers should read it at a point where they
+ * synchronise anyway (once per optimizer step, once per decode step).  (No counterpart in the reference.) */
 int qpam_device_status(int32_t* status, int32_t clear);
+
+/* Diagnostic: launches one thread that waits on an mbarrier nobody arrives at and gives up after limit_ns
+ * (0 < limit_ns <= 1e8), leaving 299 in the status word -- the give-up path of every bounded wait in this
+ * library, exercised without hanging or faulting anything.  (No counterpart in the reference.) */
+int qpam_selftest_wait_expiry(int64_t limit_ns, void* stream);
 
 const char* qpam_last_error(void);
 /* "qllm2_pam_b200 <version> sm_100a" */

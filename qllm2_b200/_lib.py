@@ -107,6 +107,7 @@ SIGNATURES = {
     "qpam_profile_begin": (c_int32, [c_void_p]),
     "qpam_profile_end": (c_int32, [C.c_char_p, c_size_t]),
     "qpam_device_status": (c_int32, [C.POINTER(c_int32), c_int32]),
+    "qpam_selftest_wait_expiry": (c_int32, [c_int64, c_void_p]),
     "qpam_last_error": (C.c_char_p, []),
     "qpam_version": (C.c_char_p, []),
 }
@@ -179,7 +180,18 @@ def profile_end() -> dict:
 
 
 def device_status(clear: bool = True) -> int:
-    """0 when every tensor-core kernel so far completed its on-device handshakes."""
+    """0 when every kernel so far completed its on-device handshakes and accepted its descriptors
+    (2xx: a bounded wait gave up; 301: bad cu_seqlens).  Synchronises the device."""
     v = c_int32(0)
     check(lib().qpam_device_status(C.byref(v), 1 if clear else 0), "qpam_device_status")
     return int(v.value)
+
+
+def raise_on_device_error(where: str = "") -> None:
+    """Read (and clear) the device status word; raise QPamError when a kernel reported a failure.  Meant for
+    points where the caller synchronises anyway: after an optimizer step, after a decode step's host read."""
+    code = device_status(clear=True)
+    if code != 0:
+        what = "a packed scan was given an invalid cu_seqlens descriptor" if code == 301 else \
+            "a bounded on-device wait gave up: the results of that launch are invalid"
+        raise QPamError(f"device status {code}{' in ' + where if where else ''}: {what}")

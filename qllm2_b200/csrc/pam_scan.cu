@@ -11,6 +11,29 @@ namespace qpam {
 
 static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
+// Chunks-before-sequence prefix of the packed layout, with the descriptor checked on the way: cu_seqlens must
+// start at 0, never decrease and end at or before T.  A descriptor that fails leaves an all-zero prefix (no
+// kernel of the call then finds a chunk to work on, so nothing is read or written through it) and records
+// QPAM_DEV_BAD_CU_SEQLENS in the device status word.
+constexpr int QPAM_DEV_BAD_CU_SEQLENS = 301;
+constexpr int QPAM_DEV_WAIT_SELFTEST = 299;
+__global__ void k_chunk_prefix_checked(const int32_t* __restrict__ cu, int32_t* __restrict__ prefix, int S, int ch, int T) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  bool good = cu[0] == 0;
+  int acc = 0;
+  prefix[0] = 0;
+  for (int s = 0; s < S; ++s) {
+    const int a = cu[s], e = cu[s + 1];
+    good = good && e >= a && e <= T;
+    acc += (max(0, e - a) + ch - 1) / ch;
+    prefix[s + 1] = acc;
+  }
+  if (!good) {
+    for (int s = 0; s <= S; ++s) prefix[s] = 0;
+    umma::record_device_error(QPAM_DEV_BAD_CU_SEQLENS);
+  }
+}
+
 struct ScanLayout {
   int64_t nslots;
   int32_t ch;           // tokens per chunk of this layout
@@ -58,9 +81,9 @@ static ScanLayout scan_layout(const qpam_scan_args* a, int ch) {
   L.total_fwd = off;
   L.off_dstates = off;
   off += align256(sizeof(float2) * (size_t)a->K * a->H * L.nslots * dd);
-  L.off_anchors = off;
-  off += align256(sizeof(float) * (size_t)a->K * a->H * L.nslots);
-  L.off_dak = off;
+  L.off_anchors = off;   // partial sums of the decay-gradient anchors (tensor-core backward)
+  off += align256(sizeof(float) * (size_t)a->K * a->H * L.nslots * tcs::ANCHOR_PARTS);
+  L.off_dak = off;       // Re<k_t, dk_t> per token (tensor-core backward)
   off += align256(sizeof(float) * (size_t)a->B * a->H * a->T);
   L.total_bwd = off;
   return L;
@@ -118,7 +141,7 @@ template <int D, typename T>
 static int launch_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
   // chunk-local state sums, then the carry over the chunk axis
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   if (L.grid_chunks > 0) {
@@ -167,37 +190,26 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   return QPAM_OK;
 }
 
-// one chunk kernel for the forward output and the three gradients (output rows follow A1)
-template <int MODE>
-static int tc_chunk2_launch(const qpam_scan_args* a, const ScanLayout& L, const ScanParams& p, const void* a1,
-                            const void* b1, const void* x2, const char* name, cudaStream_t st) {
-  tcs::ChunkMaps maps;
-  const int64_t rows = (int64_t)a->B * a->H * a->T;
-  int rc;
-  if ((rc = make_map(&maps.a1, a1, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = make_map(&maps.b1, b1, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = make_map(&maps.x2, x2, 128, rows, 128, 64, 128))) return rc;
-  if ((rc = set_smem(tcs::k_tc_chunk2<MODE>, tcs::CHUNK2_SMEM))) return rc;
-  tcs::k_tc_chunk2<MODE><<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e, name);
-  note_launch(name, st);
-  return QPAM_OK;
-}
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
 static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st, bool token_major = false) {
   ScanParams p = make_params(a, L);
   p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   int rc;
   rc = tc_states(p, L, a, st);
   if (rc) return rc;
   if (L.grid_chunks > 0 && a->y != nullptr) {
-    rc = tc_chunk2_launch<tcs::M_FWD>(a, L, p, a->q, a->k, a->v, "k_tc_chunk<fwd>", st);
-    if (rc) return rc;
+    tcs::ChunkMaps maps;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = set_smem(tcs::k_tc_chunk_fwd, tcs::CHUNK2_SMEM))) return rc;
+    tcs::k_tc_chunk_fwd<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk<fwd>");
   }
   return QPAM_OK;
 }
@@ -207,7 +219,7 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
   ScanParams p = make_params(a, L);
   p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   int rc = tc_states(p, L, a, st);
@@ -225,39 +237,8 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
   return QPAM_OK;
 }
 
-// Side streams of the tensor-core backward (one set per device, created on first use; never destroyed).
-struct SideStreams {
-  cudaStream_t s[3];
-  cudaEvent_t fork, fork2, join[3];
-  std::mutex mu;          // one enqueue at a time reuses the events
-};
-static SideStreams* side_streams() {
-  static std::mutex mu;
-  static SideStreams* per_dev[64] = {nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  std::lock_guard<std::mutex> lk(mu);
-  if (per_dev[dev] == nullptr) {
-    SideStreams* ss = new SideStreams();
-    // the side streams carry the critical chain of the backward at the highest priority the device offers: a
-    // caller's stream has the default (lowest) one, so what stays on it only fills the slots they leave
-    int prio_least = 0, prio_greatest = 0;
-    bool ok = cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) == cudaSuccess &&
-              cudaEventCreateWithFlags(&ss->fork, cudaEventDisableTiming) == cudaSuccess &&
-              cudaEventCreateWithFlags(&ss->fork2, cudaEventDisableTiming) == cudaSuccess;
-    for (int i = 0; i < 3 && ok; ++i)
-      ok = cudaStreamCreateWithPriority(&ss->s[i], cudaStreamNonBlocking, prio_greatest) == cudaSuccess &&
-           cudaEventCreateWithFlags(&ss->join[i], cudaEventDisableTiming) == cudaSuccess;
-    if (!ok) {
-      cudaGetLastError();
-      delete ss;
-      return nullptr;     // the caller stays on its own stream
-    }
-    per_dev[dev] = ss;
-  }
-  return per_dev[dev];
-}
-
+// bf16 / d = 64 / one state, backward: gradient state sums -> reverse carry (with the anchors of the decay
+// gradient) -> ONE launch for the dq, dv, dk jobs of every chunk -> dgamma.  Everything stays on the caller's stream.
 static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk, void* dv,
                        float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st) {
   ScanParams p = make_params(a, L);
@@ -268,7 +249,7 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     ScanParams pf = p;
     pf.s_final = nullptr;
     if (a->cu_seqlens != nullptr) {
-      k_chunk_prefix<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch);
+      k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
       QPAM_LAUNCH_CHECK("k_chunk_prefix");
     }
     rc = tc_states(pf, L, a, st);
@@ -276,47 +257,24 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   }
   float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
   p.dA_k = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_dak);
-  // Order of the backward: gradient state sums -> reverse carry -> dv, dk (and the anchors) is the critical
-  // chain; dq needs only the forward states.  The chain runs on high-priority side streams and dq on the
-  // caller's stream from the start: its CTAs take the slots the chain leaves free (the partly filled last
-  // wave of each 768-CTA kernel over 296 resident slots, and the SMs idle under the small carry kernel).
-  // While the per-kernel profiler records on one stream everything stays on it, in dependency order.
-  SideStreams* ss = (L.grid_chunks > 0 && !profiling_active()) ? side_streams() : nullptr;
-  std::unique_lock<std::mutex> lk;
-  cudaStream_t sc = st;                  // stream of the critical chain
-  if (ss != nullptr) {
-    lk = std::unique_lock<std::mutex>(ss->mu);
-    QPAM_CUDA(cudaEventRecord(ss->fork, st));
-    QPAM_CUDA(cudaStreamWaitEvent(ss->s[0], ss->fork, 0));
-    sc = ss->s[0];
-  }
   if (L.grid_chunks > 0) {
     rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, sc>>>(p);
-    QPAM_LAUNCH_CHECK_ON("k_tc_chunk_outer<dstate>", sc);
+    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk_outer<dstate>");
   }
-  k_state_scan<true><<<dim3(a->S, a->H, (64 * 64 / 2 + 255) / 256), 256, 0, sc>>>(p, 64);
-  QPAM_LAUNCH_CHECK_ON("k_state_scan<rev>", sc);
+  tcs::k_tc_state_scan_rev<<<dim3(a->S, a->H, 64 * 64 / 2 / 256), 256, 0, st>>>(p, anchors);
+  QPAM_LAUNCH_CHECK("k_tc_state_scan_rev");
   if (L.grid_chunks > 0) {
-    if ((rc = tc_chunk2_launch<tcs::M_DQ>(a, L, p, dy, a->v, a->k, "k_tc_chunk<dq>", st))) return rc;
-    cudaStream_t s_dk = st, s_an = st;
-    if (ss != nullptr) {
-      QPAM_CUDA(cudaEventRecord(ss->fork2, sc));
-      for (int i = 1; i < 3; ++i) QPAM_CUDA(cudaStreamWaitEvent(ss->s[i], ss->fork2, 0));
-      s_dk = ss->s[1]; s_an = ss->s[2];
-    }
-    if ((rc = tc_chunk2_launch<tcs::M_DV>(a, L, p, a->k, a->q, dy, "k_tc_chunk<dv>", sc))) return rc;
-    if ((rc = tc_chunk2_launch<tcs::M_DK>(a, L, p, a->v, dy, a->q, "k_tc_chunk<dk>", s_dk))) return rc;
-    tcs::k_tc_state_anchors<<<dim3((unsigned)L.nslots, a->H), 256, 0, s_an>>>(p, anchors);
-    QPAM_LAUNCH_CHECK_ON("k_tc_state_anchors", s_an);
-    if (ss != nullptr) {
-      for (int i = 0; i < 3; ++i) {
-        QPAM_CUDA(cudaEventRecord(ss->join[i], ss->s[i]));
-        QPAM_CUDA(cudaStreamWaitEvent(st, ss->join[i], 0));
-      }
-      lk.unlock();
-    }
+    tcs::BwdMaps maps;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&maps.q, a->q, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.k, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.v, a->v, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.dy, dy, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = set_smem(tcs::k_tc_chunk_bwd, tcs::CHUNK2_SMEM))) return rc;
+    tcs::k_tc_chunk_bwd<<<dim3(3 * L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+    QPAM_LAUNCH_CHECK("k_tc_chunk<dq,dv,dk>");
     tcs::k_tc_dgamma_finalize<<<dim3(L.grid_chunks, a->H), 128, 0, st>>>(p, anchors);
     QPAM_LAUNCH_CHECK("k_tc_dgamma_finalize");
   }
@@ -362,6 +320,16 @@ static int scan_bwd_t(const qpam_scan_args* a, const ScanLayout& L, const void* 
 }  // namespace qpam
 
 namespace qpam {
+// one thread waits on an mbarrier nobody arrives at, with a short limit: exercises the give-up path of every
+// bounded wait (status word, return) without hanging anything
+__global__ void k_wait_selftest(unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    umma::mbar_init(&bar, 1);
+    umma::fence_barrier_init();
+    umma::mbar_wait(&bar, 0, QPAM_DEV_WAIT_SELFTEST, limit_ns);
+  }
+}
 int scan_tc_device_status(int* value, bool clear) {
   QPAM_CUDA(umma::read_device_error(value, clear));
   return QPAM_OK;
@@ -369,6 +337,14 @@ int scan_tc_device_status(int* value, bool clear) {
 }  // namespace qpam
 
 using namespace qpam;
+
+extern "C" int qpam_selftest_wait_expiry(int64_t limit_ns, void* stream) {
+  QPAM_REQUIRE(limit_ns > 0 && limit_ns <= 100000000, "wait self-test: limit_ns=%lld outside (0, 1e8]", (long long)limit_ns);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  k_wait_selftest<<<1, 32, 0, st>>>((unsigned long long)limit_ns);
+  QPAM_LAUNCH_CHECK("k_wait_selftest");
+  return QPAM_OK;
+}
 
 extern "C" size_t qpam_scan_workspace_bytes(const qpam_scan_args* a, int32_t with_backward) {
   if (a == nullptr || a->d <= 0 || a->K <= 0 || a->H <= 0 || a->S <= 0 || a->T < 0) return 0;

@@ -258,17 +258,4 @@ __global__ void __launch_bounds__(256) k_state_scan(ScanParams p, int D) {
   }
 }
 
-// chunks-before-sequence prefix for the packed layout (S is small; one thread suffices)
-__global__ void k_chunk_prefix(const int32_t* __restrict__ cu, int32_t* __restrict__ prefix, int S, int ch) {
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    int acc = 0;
-    prefix[0] = 0;
-    for (int s = 0; s < S; ++s) {
-      const int len = max(0, cu[s + 1] - cu[s]);
-      acc += (len + ch - 1) / ch;
-      prefix[s + 1] = acc;
-    }
-  }
-}
-
 }  // namespace qpam

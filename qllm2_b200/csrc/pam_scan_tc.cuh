@@ -1,7 +1,7 @@
 // Tensor-core (tcgen05 / TMEM / TMA) kernels of the chunked PAM scan for bf16 token tensors,
 // head dim 64, one state.  Chunks are 128 tokens, so every MMA is M = 128.
 //
-// This file: the chunk-local state sums (k_tc_chunk_outer) and the anchored decay gradient.  The
+// This file: the chunk-local state sums (k_tc_chunk_outer).  The
 // state sums run as real bf16 MMAs on the INTERLEAVED (re, im) rows as they sit in memory: a token
 // row of 64 complex numbers is a 128-element real vector x = (r0, i0, r1, i1, ...); with
 // cj(x) = (r0, -i0, ...) the real and imaginary parts of v (x) conj(k) come from the operand rows
@@ -284,70 +284,6 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(ScanParams p) {
   if (warp == 0) {
     tc_fence_after();
     tmem_dealloc<256>(tmem);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Decay gradient on the tensor-core path.  The chunk kernels leave the raw per-token values
-// dA_t = Re<q_t,dq_t> - Re<k_t,dk_t>; da_u = sum_{t>=u} dA_t would accumulate their bf16-level errors
-// as a random walk over the whole sequence.  Instead the suffix sum is anchored at every chunk
-// boundary, where it is known from fp32 quantities:  da at the first token of chunk c equals
-// Re<dS_c, S_c> (S_c: state entering the chunk, dS_c: gradient reaching it -- scaling S_c by e^x
-// changes the loss by x Re<dS_c, S_c>).  Inside a chunk the raw values are summed from the next
-// anchor and the small mismatch at the chunk's first token is spread linearly over its tokens.
-// ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) k_tc_state_anchors(ScanParams p, float* __restrict__ anchors) {
-  // grid = (nslots, H): anchors[h][slot] = Re<dstates[slot], states[slot]>
-  __shared__ double red[8];
-  const int64_t slot = blockIdx.x;
-  const int h = blockIdx.y;
-  const float4* a = reinterpret_cast<const float4*>(p.states + state_base(p, 0, h, slot, TD));
-  const float4* b = reinterpret_cast<const float4*>(p.dstates + state_base(p, 0, h, slot, TD));
-  double acc = 0.0;
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const float4 x = __ldg(a + threadIdx.x + 256 * it), y = __ldg(b + threadIdx.x + 256 * it);
-    acc += (double)(x.x * y.x + x.y * y.y) + (double)(x.z * y.z + x.w * y.w);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    double t = 0.0;
-    for (int w8 = 0; w8 < 8; ++w8) t += red[w8];
-    anchors[(size_t)h * p.nslots + slot] = (float)t;
-  }
-}
-
-__global__ void __launch_bounds__(128) k_tc_dgamma_finalize(ScanParams p, const float* __restrict__ anchors) {
-  // grid = (chunks, H); one thread per token; chunks are independent once anchored
-  __shared__ float wsum[4];
-  const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
-  if (!L.valid) return;
-  const int h = blockIdx.y;
-  const size_t base = gamma_base(p, 0, L.b, h, L.t0);
-  const float* anc = anchors + (size_t)h * p.nslots + L.slot0 + L.c;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int len = L.len;
-  const int j = TC - 1 - tid;                         // thread tid sums the tokens j .. len-1 of the chunk
-  float v = (j < len) ? p.dgamma[base + j] - p.dA_k[base + j] : 0.f;   // dA_t = Re<q,dq> - Re<k,dk>
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const float n = __shfl_up_sync(0xffffffffu, v, o);
-    if (lane >= o) v += n;
-  }
-  if (lane == 31) wsum[warp] = v;
-  __syncthreads();
-  float off = 0.f;
-  for (int w4 = 0; w4 < warp; ++w4) off += wsum[w4];
-  const float suffix = v + off;                        // sum of raw values over tokens j .. len-1
-  const float total = wsum[0] + wsum[1] + wsum[2] + wsum[3];
-  const float hi = anc[1], lo = anc[0];                // da just after the chunk / at its first token
-  const float mismatch = total - (lo - hi);
-  if (j < len) {
-    const float da = hi + suffix - mismatch * (float)(len - j) / (float)len;
-    p.dgamma[base + j] = da / (p.gamma[base + j] + p.eps);
   }
 }
 

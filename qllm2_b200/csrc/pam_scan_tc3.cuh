@@ -6,7 +6,8 @@
 // The score product Q conj(K)^T and the product with V do not depend on the state (the fused form of the
 // reference, v11/model.py:657-781): only the weight applied to the scores does,
 //   G[t][s] = sum_k rho_k[t] cf_k[s],   rho_k[t] = c_{k,t} scale e^{A^k_t - A^k_m} (complex),  cf_k[s] = e^{A^k_m - A^k_s},
-// with the decay of every state factored around its own mid-chunk reference A^k_m.  So stage 1, the TMEM
+// with the decay of every state factored around its own mid-chunk reference A^k_m (a state whose chunk decays
+// by more than e^-80 is taken unfactored: per-score exp(A^k_t - A^k_s), see pam_scan_tc2.cuh).  So stage 1, the TMEM
 // rewrite of the weighted scores and stage 2 run once, as in the single-state kernel (pam_scan_tc2.cuh).
 // The carried-state terms use the same tensor-core path as "extra score columns": for state k the rows
 // T'_k[t][j] = rho_k[t] q_t[j] are written to TMEM (into the columns the scores no longer need) and multiplied
@@ -38,9 +39,11 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
   float2* rho = reinterpret_cast<float2*>(cfac + KMAX * TC); // [KMAX][128]  c_k scale e^{A_t - A_m}
   uint64_t* bars = reinterpret_cast<uint64_t*>(rho + KMAX * TC);  // [0] tma [1] stage 1 [2] stage 2 [3],[4] state passes
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+  int* failed = reinterpret_cast<int*>(tmem_slot + 1);      // error word as found at the start of this CTA
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
+  if (tid == 160) *failed = device_error_now();
   const int h = blockIdx.y;
   const int K = p.K;
   const bool has_state = (L.c > 0) || (p.s0 != nullptr);
@@ -65,14 +68,26 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  auto cexp = [](float x) { return __expf(fminf(80.f, fmaxf(-80.f, x))); };
+  if (*failed != 0) {       // an earlier launch gave up on a wait: outputs stay untouched (see pam_scan_tc2.cuh)
+    mbar_wait(&bars[0], 0, 239);
+    __syncthreads();
+    if (warp == 0) tmem_dealloc<256>(tmem);
+    return;
+  }
+  // a state whose chunk decays by more than e^-80 leaves the factored form (its exponents would overflow): its
+  // scores get exp(A_t - A_s) one by one and its carried-state rows their own e^{A_t}
+  uint32_t strong_mask = 0;
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k)
+    if (k < K && Acum[k * TC + TC - 1] < STRONG_DECAY) strong_mask |= 1u << k;
   for (int e = tid; e < K * TC; e += 256) {
     const int k = e / TC, t = e - k * TC;
+    const bool strong = (strong_mask >> k) & 1u;
     const float a = Acum[e], a_mid = Acum[k * TC + TC / 2 - 1];
-    cfac[e] = cexp(a_mid - a);
+    cfac[e] = strong ? 1.f : __expf(a_mid - a);
     float2 c = make_float2(1.f, 0.f);
     if (p.coef != nullptr && t < L.len) c = *reinterpret_cast<const float2*>(p.coef + gamma_base(p, k, L.b, h, L.t0 + t) * 2);
-    const float rf = p.q_scale * cexp(a - a_mid);
+    const float rf = p.q_scale * (strong ? 1.f : __expf(a - a_mid));
     rho[e] = make_float2(c.x * rf, c.y * rf);
   }
   bool ok = mbar_wait(&bars[0], 0, 231);
@@ -121,7 +136,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
 
   // carried-state planes of state k (times its chunk constant e^{A^k_m}) into slot s of the K-plane region
   auto stage_state = [&](int k, int s) {
-    const float cst = cexp(Acum[k * TC + TC / 2 - 1]);
+    const float cst = ((strong_mask >> k) & 1u) ? 1.f : __expf(Acum[k * TC + TC / 2 - 1]);
     const float4* sg = reinterpret_cast<const float4*>(p.states + state_base(p, k, h, L.slot0 + L.c, TD));
     unsigned char* dstp = RB + s * 16384;
 #pragma unroll
@@ -159,7 +174,8 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
 #pragma unroll
             for (int k = 0; k < KMAX; ++k)
               if (k < K) {
-                const float cf = cfac[k * TC + c];
+                const float cf = ((strong_mask >> k) & 1u) ? __expf(fminf(0.f, Acum[k * TC + r] - Acum[k * TC + c]))
+                                                           : cfac[k * TC + c];
                 gr = fmaf(rk[k].x, cf, gr);
                 gi = fmaf(rk[k].y, cf, gi);
               }
@@ -230,6 +246,11 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
 #pragma unroll
         for (int k = 1; k < KMAX; ++k)
           if (k_mine == k) rr = rk[k];
+        if ((strong_mask >> k_mine) & 1u) {          // unfactored state: the row's own decay goes here
+          const float ea = __expf(Acum[k_mine * TC + r]);
+          rr.x *= ea;
+          rr.y *= ea;
+        }
         uint32_t wr[32], wi[32];
 #pragma unroll
         for (int c = 0; c < 8; ++c) {

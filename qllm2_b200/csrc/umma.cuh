@@ -66,7 +66,7 @@ __device__ __forceinline__ uint64_t global_ns() {
 // Bounded wait: gives up after WAIT_NS of wall time (or WAIT_LIMIT polls), records `code` in the
 // device error word and returns false.  A healthy wait on this path lasts microseconds.
 constexpr uint64_t WAIT_NS = 2000000000ull;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code, uint64_t limit_ns = WAIT_NS) {
   const uint32_t addr = smem_u32(bar);
   uint64_t t0 = 0;
   for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
@@ -81,16 +81,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if ((it & 1023) == 1023) {
+    if ((it & 63) == 63) {
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > WAIT_NS) break;
+      else if (now - t0 > limit_ns) break;
       if (*reinterpret_cast<volatile int*>(&g_device_error) != 0) break;  // another waiter already gave up
     }
   }
   atomicCAS(&g_device_error, 0, code);
   return false;
 }
+
+// Kernels read the error word once at their start (one thread, into shared memory) and return without touching
+// their outputs when an earlier launch has recorded a failure: results stay as the caller left them until the
+// host has read and cleared the word (qpam_device_status).
+__device__ __forceinline__ int device_error_now() { return *reinterpret_cast<volatile int*>(&g_device_error); }
+__device__ __forceinline__ void record_device_error(int code) { atomicCAS(&g_device_error, 0, code); }
 
 // ------------------------------------------------------------------ TMA (no multicast anywhere)
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t c0,
@@ -181,6 +187,45 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+// two loads of 16 columns each in flight together, one wait
+__device__ __forceinline__ void tmem_ld16x2(uint32_t ta, float (&a)[16], uint32_t tb, float (&b)[16]) {
+  uint32_t r[16], s[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(ta));
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(s[0]), "=r"(s[1]), "=r"(s[2]), "=r"(s[3]), "=r"(s[4]), "=r"(s[5]), "=r"(s[6]), "=r"(s[7]), "=r"(s[8]),
+        "=r"(s[9]), "=r"(s[10]), "=r"(s[11]), "=r"(s[12]), "=r"(s[13]), "=r"(s[14]), "=r"(s[15])
+      : "r"(tb));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    a[i] = __uint_as_float(r[i]);
+    b[i] = __uint_as_float(s[i]);
+  }
+}
+// four loads of 16 columns each in flight together, one wait
+#define QPAM_TMEM_LD16(arr, addr)                                                                                  \
+  asm volatile(                                                                                                    \
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                                    \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                            \
+      : "=r"(arr[0]), "=r"(arr[1]), "=r"(arr[2]), "=r"(arr[3]), "=r"(arr[4]), "=r"(arr[5]), "=r"(arr[6]),          \
+        "=r"(arr[7]), "=r"(arr[8]), "=r"(arr[9]), "=r"(arr[10]), "=r"(arr[11]), "=r"(arr[12]), "=r"(arr[13]),      \
+        "=r"(arr[14]), "=r"(arr[15])                                                                               \
+      : "r"(addr))
+__device__ __forceinline__ void tmem_ld16x4(uint32_t ta, uint32_t (&a)[16], uint32_t tb, uint32_t (&b)[16], uint32_t tc,
+                                            uint32_t (&c)[16], uint32_t td, uint32_t (&d)[16]) {
+  QPAM_TMEM_LD16(a, ta);
+  QPAM_TMEM_LD16(b, tb);
+  QPAM_TMEM_LD16(c, tc);
+  QPAM_TMEM_LD16(d, td);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 // store 16 consecutive 32-bit columns of this thread's lane (issue only; see tmem_st_wait)
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {

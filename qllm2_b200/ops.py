@@ -137,6 +137,12 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
     d = q.shape[3]
     head_dim = d if head_dim is None else head_dim
     if cu_seqlens is not None:
+        if not cu_seqlens.is_cuda:
+            # a host descriptor is checked here (the kernels check a device descriptor themselves and report
+            # through the status word, see _lib.device_status)
+            c = cu_seqlens.to(torch.int64)
+            if c.numel() < 2 or int(c[0]) != 0 or bool((c[1:] < c[:-1]).any()) or int(c[-1]) > T_:
+                raise _lib.QPamError(f"cu_seqlens must start at 0, never decrease and end at or before T={T_}; got {c.tolist()[:8]}...")
         cu_seqlens = cu_seqlens.to(device=q.device, dtype=torch.int32).contiguous()
     K = gamma.shape[0]
     needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, gamma, coef, s0))

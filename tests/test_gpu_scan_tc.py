@@ -87,6 +87,68 @@ def test_backward_shapes(B, H, T):
     _grads_vs_oracle(synthetic.scan_inputs(B, H, T, 64, seed=80 + T, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("lo,hi", [(0.05, 0.3), (0.02, 0.999), (0.45, 0.6)])
+def test_strong_decay_is_exact(lo, hi):
+    """gamma far below the usual sigmoid(N(3,1)) range: a 128-token chunk then decays by more than e^-80 and the
+    factored decay of the fast path would overflow; the kernels must switch to the per-score form.  Forward,
+    final state and every gradient against the oracle, with an initial state and a gradient into the final one."""
+    B, H, T = 1, 2, 300
+    inp = synthetic.scan_inputs(B, H, T, 64, seed=123, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(11)
+    gamma = lo + (hi - lo) * torch.rand(B, H, T, generator=gen)
+    inp.g = torch.log(gamma / (1 - gamma))
+    s0 = torch.randn(1, B, H, 64, 64, 2, generator=gen) * 0.05
+    dsf = torch.randn(1, B, H, 64, 64, 2, generator=gen) * 0.05
+    _grads_vs_oracle(inp, s0=s0, ds_final=dsf)
+    with torch.no_grad():
+        y, s = ops.pam_scan(inp.q.to(DEV), inp.k.to(DEV), inp.v.to(DEV), inp.gamma.to(DEV), s0=s0.to(DEV))
+    q, k, v = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v))
+    y_ref, s_ref = po.scan_recurrence(q, k, v, inp.gamma.double().numpy(), s0=po.to_complex(s0.numpy()))
+    assert_close(y.float().cpu().numpy(), po.to_split(y_ref), TOL, "Y")
+    assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S")
+
+
+def test_strong_decay_k_states_forward():
+    """The fused K-state output kernel under strong decay in one of its states."""
+    K, B, H, T = 3, 1, 2, 300
+    inp, gamma, coef = _k_state_inputs(B, H, T, K, seed=170)
+    gen = torch.Generator().manual_seed(12)
+    gamma[1] = 0.05 + 0.3 * torch.rand(B, H, T, generator=gen)
+    s0 = torch.randn(K, B, H, 64, 64, 2, generator=gen) * 0.05
+    with torch.no_grad():
+        y, s = ops.pam_scan(inp.q.to(DEV), inp.k.to(DEV), inp.v.to(DEV), gamma.to(DEV), coef=coef.to(DEV), s0=s0.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    qc, kc, vc = (po.to_complex(t.float().numpy()) for t in (inp.q, inp.k, inp.v))
+    y_ref, s_ref = po.scan_recurrence(qc, kc, vc, gamma.double().numpy(), coef=po.to_complex(coef.numpy()),
+                                      s0=po.to_complex(s0.numpy()))
+    assert_close(y.float().cpu().numpy(), po.to_split(y_ref), TOL, "Y")
+    assert_close(s.cpu().numpy(), po.to_split(s_ref), TOL, "S")
+
+
+def test_packed_backward_matches_oracle():
+    """Gradients through the packed (cu_seqlens) layout: ragged sequences, one of them shorter than a chunk."""
+    p = synthetic.packed_inputs(4, 40, 500, 2, 64, seed=29, dtype=torch.bfloat16)
+    total = p.q.shape[1]
+    gen = torch.Generator().manual_seed(7)
+    dy = (torch.randn(2, total, 64, 2, generator=gen) / 2 ** 0.5).bfloat16()
+    q, k, v = (t.unsqueeze(0).to(DEV).requires_grad_(True) for t in (p.q, p.k, p.v))
+    gam = p.gamma.unsqueeze(0).to(DEV).requires_grad_(True)
+    y, _ = ops.pam_scan(q, k, v, gam, cu_seqlens=p.cu_seqlens)
+    dq, dk, dv, dgam = torch.autograd.grad(y, [q, k, v, gam], dy.unsqueeze(0).to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    cu = p.cu_seqlens.numpy()
+    for i in range(4):
+        a, b = int(cu[i]), int(cu[i + 1])
+        qc, kc, vc, dyc = (po.to_complex(t[:, a:b].float().numpy())[None] for t in (p.q, p.k, p.v, dy))
+        ref = po.scan_backward(qc, kc, vc, p.gamma[:, a:b].double().numpy()[None], dyc)
+        assert_close(dq[0, :, a:b].float().cpu().numpy(), po.to_split(ref["dq"])[0], TOL, f"dq seq {i}")
+        assert_close(dk[0, :, a:b].float().cpu().numpy(), po.to_split(ref["dk"])[0], TOL, f"dk seq {i}")
+        assert_close(dv[0, :, a:b].float().cpu().numpy(), po.to_split(ref["dv"])[0], TOL, f"dv seq {i}")
+        assert_close(dgam[0, :, a:b].cpu().numpy(), ref["dgamma"][0][0], TOL, f"dgamma seq {i}")
+
+
 def test_backward_with_state_gradients():
     gen = torch.Generator().manual_seed(6)
     s0 = torch.randn(1, 1, 2, 64, 64, 2, generator=gen) * 0.05
@@ -210,6 +272,51 @@ def test_full_size_adjoint_identity_headline_shape():
     assert torch.isfinite(dg).all()
 
 
+def test_headline_shape_against_oracle():
+    """Headline shape (B=8, H=6, T=2048, d=64, bf16), forward and backward through the tensor-core kernels:
+    two of the 48 (batch, head) pairs compared with the oracle's exact recurrence and its adjoint."""
+    inp = synthetic.scan_inputs(8, 6, 2048, 64, seed=0, dtype=torch.bfloat16)
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+    g = inp.g.to(DEV).requires_grad_(True)
+    y, s = ops.pam_scan(q, k, v, torch.sigmoid(g))
+    dq, dk, dv, dg = torch.autograd.grad(y, [q, k, v, g], inp.dy.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    for b, h in ((0, 0), (5, 3)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        qc, kc, vc, dyc = (po.to_complex(t[sl].float().numpy()) for t in (inp.q, inp.k, inp.v, inp.dy))
+        gam = torch.sigmoid(inp.g[sl].double()).numpy()
+        y_ref, s_ref = po.scan_recurrence(qc, kc, vc, gam)
+        ref = po.scan_backward(qc, kc, vc, gam, dyc)
+        assert_close(y[sl].detach().float().cpu().numpy(), po.to_split(y_ref), TOL, f"Y {b},{h}")
+        assert_close(s.detach()[0][sl].cpu().numpy(), po.to_split(s_ref)[0], TOL, f"S {b},{h}")
+        assert_close(dq[sl].float().cpu().numpy(), po.to_split(ref["dq"]), TOL, f"dq {b},{h}")
+        assert_close(dk[sl].float().cpu().numpy(), po.to_split(ref["dk"]), TOL, f"dk {b},{h}")
+        assert_close(dv[sl].float().cpu().numpy(), po.to_split(ref["dv"]), TOL, f"dv {b},{h}")
+        assert_close(dg[sl].cpu().numpy(), ref["dgamma"][0] * gam * (1 - gam), TOL, f"dg {b},{h}")
+
+
+def test_config4_sequences_against_oracle():
+    """The packed ragged prefill at its configured size (32 sequences of 512..16384 tokens, H=16, d=64, bf16,
+    seed 0): the shortest, the median and the longest sequence, outputs and final states of four heads,
+    against the oracle."""
+    p = synthetic.config4()
+    q, k, v = (t.unsqueeze(0).to(DEV) for t in (p.q, p.k, p.v))
+    with torch.no_grad():
+        y, s = ops.pam_scan(q, k, v, p.gamma.unsqueeze(0).to(DEV), cu_seqlens=p.cu_seqlens, chunk=128)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    order = torch.argsort(p.lengths)
+    cu = p.cu_seqlens.numpy()
+    heads = [0, 5, 10, 15]
+    for i in (int(order[0]), int(order[16]), int(order[31])):
+        a, b = int(cu[i]), int(cu[i + 1])
+        qc, kc, vc = (po.to_complex(t[heads, a:b].float().numpy())[None] for t in (p.q, p.k, p.v))
+        y_ref, s_ref = po.scan_recurrence(qc, kc, vc, p.gamma[heads, a:b].double().numpy()[None])
+        assert_close(y[0, heads, a:b].float().cpu().numpy(), po.to_split(y_ref)[0], TOL, f"Y seq {i} ({b - a} tokens)")
+        assert_close(s[0, i][heads].cpu().numpy(), po.to_split(s_ref)[0, 0], TOL, f"S seq {i}")
+
+
 def test_full_size_packed_prefill_properties():
     """Config-4 size (32 packed sequences of 512..16384 tokens, H=16, d=64, bf16): a sequence scanned inside the
     packed batch equals the same sequence scanned alone (chunks never straddle a boundary: bit for bit), and a
@@ -239,3 +346,65 @@ def test_full_size_packed_prefill_properties():
     ref = y[:, :, m:b].float()
     assert float((y_tail.float() - ref).norm() / ref.norm()) < 2e-3
     assert float((s_tail[:, 0] - s[:, 5]).norm() / s[:, 5].norm()) < 1e-4
+
+
+def _direct_forward(q, k, v, gamma, cu, y, s_final):
+    """qpam_scan_fwd through the C ABI with caller-made output buffers (so that they can be poisoned first)."""
+    import ctypes as C
+    L = _lib.lib()
+    H, T = q.shape[1], q.shape[2]
+    a = _lib.ScanArgs()
+    a.q, a.k, a.v, a.gamma = q.data_ptr(), k.data_ptr(), v.data_ptr(), gamma.data_ptr()
+    a.cu_seqlens = cu.data_ptr() if cu is not None else None
+    a.y, a.s_final = y.data_ptr(), s_final.data_ptr()
+    a.B, a.H, a.T, a.d, a.K = q.shape[0], H, T, 64, 1
+    a.S = cu.numel() - 1 if cu is not None else q.shape[0]
+    a.chunk, a.io_dtype, a.q_scale, a.gamma_eps = 128, _lib.QPAM_BF16, 64 ** -0.5, 1e-6
+    ws = torch.empty(L.qpam_scan_workspace_bytes(C.byref(a), 0), dtype=torch.uint8, device=DEV)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    rc = L.qpam_scan_fwd(C.byref(a), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return rc
+
+
+@pytest.mark.parametrize("bad", [[0, 100, 90, 300], [5, 100, 200, 300], [0, 100, 200, 400], [0, -3, 200, 300]])
+def test_bad_cu_seqlens_is_reported_not_followed(bad):
+    """A device-side cu_seqlens that decreases, does not start at 0 or runs past T: the call touches nothing
+    through it (outputs keep their poison) and the status word says 301; the next good call works."""
+    assert _lib.device_status() == 0
+    p = synthetic.packed_inputs(3, 100, 100, 2, 64, seed=3, dtype=torch.bfloat16)     # T = 300
+    q, k, v = (t.unsqueeze(0).to(DEV) for t in (p.q, p.k, p.v))
+    gamma = p.gamma.unsqueeze(0).unsqueeze(0).to(DEV).contiguous()
+    y = torch.full_like(q, float("nan"))
+    cu = torch.tensor(bad, dtype=torch.int32, device=DEV)
+    s_final = torch.full((1, 3, 2, 64, 64, 2), float("nan"), device=DEV)
+    assert _direct_forward(q, k, v, gamma, cu, y, s_final) == 0
+    assert _lib.device_status(clear=False) == 301
+    assert torch.isnan(y).all()
+    assert _lib.device_status(clear=True) == 301 and _lib.device_status() == 0
+    good = torch.tensor([0, 100, 200, 300], dtype=torch.int32, device=DEV)
+    assert _direct_forward(q, k, v, gamma, good, y, s_final) == 0
+    assert _lib.device_status() == 0 and torch.isfinite(y.float()).all()
+    with pytest.raises(_lib.QPamError):                   # the same descriptor on the host is refused before any launch
+        ops.pam_scan(q, k, v, gamma[0], cu_seqlens=torch.tensor(bad, dtype=torch.int32))
+
+
+def test_expired_wait_sets_status_and_later_launches_skip():
+    """A bounded wait that runs out (a barrier nobody arrives at, 2 ms limit): the status word is set, a scan
+    launched while it is set leaves its outputs untouched, clearing the word restores normal service."""
+    assert _lib.device_status() == 0
+    assert _lib.lib().qpam_selftest_wait_expiry(2_000_000, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert _lib.device_status(clear=False) == 299
+    inp = synthetic.scan_inputs(1, 2, 300, 64, seed=5, dtype=torch.bfloat16)
+    q, k, v = (t.to(DEV) for t in (inp.q, inp.k, inp.v))
+    gamma = inp.gamma.unsqueeze(0).to(DEV).contiguous()
+    y = torch.full_like(q, float("nan"))
+    s_final = torch.zeros(1, 1, 2, 64, 64, 2, device=DEV)
+    assert _direct_forward(q, k, v, gamma, None, y, s_final) == 0
+    assert torch.isnan(y).all()                          # skipped
+    with pytest.raises(_lib.QPamError):
+        _lib.raise_on_device_error("test")
+    assert _lib.device_status() == 0
+    assert _direct_forward(q, k, v, gamma, None, y, s_final) == 0
+    assert _lib.device_status() == 0 and torch.isfinite(y.float()).all()
