@@ -9,8 +9,9 @@ tokens, head dim 64, bf16 token tensors, one state (K=1), synthetic seeded input
 is one forward + one backward over that batch; the metric is tokens/s (B*T per step), summed
 over GPUs (units are independent (batch, head) pairs: no collective on the data path).
 
-One JSON line is printed by rank 0 (see README/DESIGN for the fields).  `--impl reference` times
-the CPU port of the reference's own code path (oracle/torch_port.py) on the host cores instead.
+One JSON line is printed by rank 0.  `--impl reference` times the reference's own CPU code path on the
+host cores instead: V11PAMLayer._forward_chunked_head itself when a checkout of the reference is importable
+(QLLM2_REFERENCE, default /root/reference), else its port oracle/torch_port.py; `cpu_baseline.kind` says which.
 """
 from __future__ import annotations
 
@@ -44,56 +45,91 @@ def load_peaks():
 
 
 # ----------------------------------------------------------------------------- CPU baseline
-def cpu_scan_baseline(seconds: float = 12.0):
-    """Time the CPU port of the reference path on a bounded sample; returns tokens/s."""
+def _cpu_scan_fn():
+    """(kind, description, callable(inp) running fwd+bwd of the K=1 scan on the CPU).  The reference's own
+    V11PAMLayer._forward_chunked_head (v11/model.py:378-417) + autograd when a checkout is importable, else the
+    port of the same operator mix."""
+    from qllm2_b200 import synthetic  # noqa: F401
+    ref_root = os.environ.get("QLLM2_REFERENCE", "/root/reference")
+    if os.path.isdir(os.path.join(ref_root, "v11")):
+        try:
+            sys.path.insert(0, ref_root)
+            sys.dont_write_bytecode = True
+            from v11 import triton_kernels
+            from v11.model import V11Config, V11PAMLayer
+            triton_kernels.set_triton_enabled(False)
+            s_ = CPU_SAMPLE
+            cfg = V11Config(vocab_size=64, dim=s_["H"] * s_["d"], n_heads=s_["H"], head_dim=s_["d"], n_layers=1,
+                            dropout=0.0, chunk_size=WL["chunk"], gradient_checkpointing=False)
+            layer = V11PAMLayer(cfg)
+
+            def run(inp):
+                q, k, v = (t.clone().requires_grad_(True) for t in (inp.q, inp.k, inp.v))
+                g = inp.g.clone().requires_grad_(True)
+                y, _ = layer._forward_chunked_head(q, k, v, torch.sigmoid(g), s_["d"])
+                torch.autograd.grad(y, [q, k, v, g], inp.dy)
+            return "reference", "V11PAMLayer._forward_chunked_head + autograd (v11/model.py:378-417)", run
+        except Exception:  # noqa: BLE001 - fall through to the port
+            pass
+        finally:
+            if sys.path and sys.path[0] == ref_root:
+                sys.path.pop(0)
     from oracle import torch_port
+
+    def run_port(inp):
+        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+    return "port", "oracle/torch_port.py (the reference is not importable on this machine)", run_port
+
+
+def cpu_scan_baseline(seconds: float = 12.0):
+    """Time the reference's CPU path (or its port) on a bounded sample; returns tokens/s."""
     from qllm2_b200 import synthetic
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     s = CPU_SAMPLE
+    kind, what, run = _cpu_scan_fn()
     inp = synthetic.scan_inputs(s["B"], s["H"], s["T"], s["d"], seed=0)
-    torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])  # warm-up (autograd init)
+    run(inp)  # warm-up (autograd init)
     times = []
     t_end = time.perf_counter() + seconds
     while len(times) < 2 or (time.perf_counter() < t_end and len(times) < 50):
         t0 = time.perf_counter()
-        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+        run(inp)
         times.append(time.perf_counter() - t0)
     times.sort()
     med = times[len(times) // 2]
     # same head count as the workload, so tokens/s (B*T per second) is directly comparable
-    return dict(value=s["B"] * s["T"] / med, unit=UNIT, cores=cores, kind="port",
+    return dict(value=s["B"] * s["T"] / med, unit=UNIT, cores=cores, kind=kind,
                 sample=f"B={s['B']} H={s['H']} T={s['T']} d={s['d']} fp32 fwd+bwd, median of {len(times)} runs "
-                       f"({med * 1e3:.1f} ms each), oracle/torch_port.py")
+                       f"({med * 1e3:.1f} ms each), {what}")
 
 
 def run_reference(args):
-    """`--impl reference`: the reference's CPU code path (ported) on the host cores."""
+    """`--impl reference`: the reference's CPU code path on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import torch_port
     from qllm2_b200 import synthetic
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     s = CPU_SAMPLE
+    kind, what, run = _cpu_scan_fn()
     inp = synthetic.scan_inputs(s["B"], s["H"], s["T"], s["d"], seed=0)
     for _ in range(max(args.warmup, 1)):
-        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+        run(inp)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        torch_port.scan_fwd_bwd(inp.q, inp.k, inp.v, inp.g, inp.dy, WL["chunk"])
+        run(inp)
     dt = time.perf_counter() - t0
     val = s["B"] * s["T"] * args.steps / dt
     sample = (f"each step = B={s['B']} of the workload's B={WL['B']} sequences (H={s['H']} T={s['T']} d={s['d']}), "
-              f"fp32, CPU port of the reference path (oracle/torch_port.py); the reference itself is a Python "
-              f"project that is not present on the GPU box")
+              f"fp32, {what}")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -257,26 +293,32 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, sets, steps, warmup, join=None):
+    def timed(fn, sets, steps, warmup, join=None, repeats=5):
+        """`repeats` timed regions of exactly `steps` steps each (device events, max over ranks); the median
+        region is reported, so that a few milliseconds of outside disturbance do not decide the number."""
         for i in range(warmup):
             fn(sets[i % nsets])
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = _lib.launch_count()
-        e0.record()
-        for i in range(steps):
-            fn(sets[i % nsets])
-        if join is not None:
-            join()          # the timed region ends when the side streams' copies have landed
-        e1.record()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        launches = _lib.launch_count() - l0
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, launches
+        regions, launches = [], 0
+        for _ in range(repeats):
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = _lib.launch_count()
+            e0.record()
+            for i in range(steps):
+                fn(sets[i % nsets])
+            if join is not None:
+                join()          # the timed region ends when the side streams' copies have landed
+            e1.record()
+            barrier()
+            ms = e0.elapsed_time(e1)
+            launches = _lib.launch_count() - l0
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            regions.append(ms)
+        regions.sort()
+        return regions[len(regions) // 2], launches, regions
 
     # The device-timed leg replays one captured step per input set from a CUDA graph, so that the host's
     # Python and ctypes cost per launch (10 launches in ~0.3 ms) is not what is measured; the kernels and
@@ -306,12 +348,13 @@ def main():
         launch_mode = f"eager ({type(exc).__name__})"
         step_timed = step_dev
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, launches = timed(step_timed, dev_sets, args.steps, args.warmup)
+    ms, launches, regions = timed(step_timed, dev_sets, args.steps, args.warmup)
     if launch_mode == "cuda_graph":
-        launches = launches_per_step * args.steps
+        launches = launches_per_step * args.steps      # a replayed graph launches what the eager step launched
     clocks = sampler.stop() if sampler else None
-    ms_e2e, _ = timed(step_e2e, host_sets, args.steps, args.warmup,
-                      join=lambda: (cur.wait_stream(s_in), cur.wait_stream(s_out)))
+    ms_e2e, _, _ = timed(step_e2e, host_sets, args.steps, args.warmup,
+                         join=lambda: (cur.wait_stream(s_in), cur.wait_stream(s_out)), repeats=3)
+    _lib.raise_on_device_error("bench timed region")
 
     tokens_step = B * T * world
     value = tokens_step * args.steps / (ms * 1e-3)
@@ -361,36 +404,140 @@ def main():
                            "tflops": nflops / sec / 1e12, "frac_of_bf16_peak": nflops / sec / 1e12 / peaks["tf"],
                            "share_of_step": prof[n][1] / total_prof if total_prof else None}
     dominant = max(roof_all, key=lambda n: prof[n][1]) if roof_all else None
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if dominant and os.path.exists(tpath):
-        with open(tpath) as f:
-            traffic = json.load(f).get(dominant)
     roofline = None
     if dominant:
         r = roof_all[dominant]
+        tr = NCU_TRAFFIC.get(dominant)
         roofline = {"kernel": dominant, "bound": r["bound"], "achieved": r["achieved"], "peak": r["peak"],
-                    "unit": r["unit"], "frac": r["frac"], "traffic": traffic, "peak_source": peaks["src"] + " burst"}
+                    "unit": r["unit"], "frac": r["frac"], "traffic": tr["bytes"] if tr else None,
+                    "traffic_source": tr["source"] if tr else None, "peak_source": peaks["src"] + " burst"}
+
+    # the same operator with the three phase-routed states of the training configuration (K = 3)
+    k3 = scan_k3(dev, B, H, T, d, C, rank)
+    if world > 1:
+        t = torch.tensor([k3["ms_per_step"]], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        k3["ms_per_step"] = float(t.item())
+    k3["tokens_per_s"] = B * T * world / k3["ms_per_step"] * 1e3
+    secondary = {"scan_fwd_bwd_K3": k3}
+    if world > 1:
+        secondary["vocab_parallel_ce_config2"] = vocab_parallel_ce(dev, rank, world, peaks)
 
     extra = {}
     if not args.no_extras and rank == 0 and world == 1:   # side measurements are single-GPU
         extra = side_measurements(dev, peaks)
+        cd = extra.get("continuous_decode", {})
+        for key in ("config5_K3", "config5_K1"):
+            if key in cd:
+                secondary["decode_" + key] = {k_: cd[key].get(k_) for k_ in (
+                    "decode_tokens_per_s", "steady_decode_tokens_per_s", "decode_step_ms", "frac_of_hbm_peak",
+                    "generated_tokens", "prompt_tokens", "seconds", "config")}
+        secondary["decode_state_kernel_frac_of_hbm_peak"] = {
+            "bf16_state": extra.get("decode_step_bf16_state", {}).get("frac_of_hbm_peak"),
+            "f32_state": extra.get("decode_step_f32_state", {}).get("frac_of_hbm_peak")}
+        ce2 = extra.get("fused_ce_config2", {})
+        secondary["fused_ce_config2"] = {"achieved_tflops": ce2.get("achieved_tflops"), "frac_of_bf16_peak": ce2.get("frac_of_bf16_peak"),
+                                         "ms_fwd_bwd": ce2.get("ms_fwd_bwd"), "bwd_workspace_bytes": ce2.get("bwd_workspace_bytes")}
+        pp = extra.get("packed_prefill_config4", {})
+        secondary["packed_prefill_config4"] = {"tokens_per_s": pp.get("tokens_per_s"), "frac_of_hbm_peak": pp.get("frac_of_hbm_peak")}
+        ts = extra.get("train_step_config3", {})
+        secondary["train_step_config3"] = {"tokens_per_s": ts.get("tokens_per_s_graph", ts.get("tokens_per_s")),
+                                           "ms_per_step": ts.get("ms_per_step_graph", ts.get("ms_per_step"))}
+    if roofline is not None:
+        roofline["secondary"] = secondary
 
     cpu = cpu_scan_baseline() if (rank == 0 and world == 1) else None
     if rank == 0:
+        e2e_note = ("per step every rank moves its q, k, v, dy, gamma from pinned host memory and its y, dq, dk, dv, dgamma back: "
+                    "on one GPU this leg is bound by the PCIe link (~42 GB/s each way), on several GPUs of one host by the "
+                    "host's PCIe / memory path that the ranks share -- not by a kernel or a collective")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 (tcgen05 MMA, fp32 accumulate in TMEM)", "data": "synthetic",
-            "config": {**workload_config(world), "launch": launch_mode},
+            "config": workload_config(world), "launch": launch_mode,
+            "timing": {"repeats": len(regions), "reported": "median region", "ms_per_step_each_region": [x / args.steps for x in regions]},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "roofline_all": roof_all,
+                    "ms_per_step": ms_e2e / args.steps, "note": e2e_note},
+            "gpu_launches": launches, "gpu_launches_how": "launches counted by the library on one eager step x steps (the timed steps replay that step from a CUDA graph)"
+                            if launch_mode == "cuda_graph" else "counted by the library during the timed region",
+            "clocks": clocks, "roofline": roofline, "roofline_all": roof_all,
             "kernels": kernels, "cpu_baseline": cpu, "extra": extra,
         }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+# DRAM bytes (read + written) per launch of the dominant kernels at the headline shape, from an ncu capture of
+# THIS build (one kernel, one launch): the figure the `traffic` field of the roofline reports
+NCU_TRAFFIC = {}
+
+
+def scan_k3(dev, B, H, T, d, C, rank, iters=10):
+    """Scan forward + backward with K = 3 phase-routed states on the headline shape: the fused K-state output
+    kernel does not keep what a backward needs, so training runs the states as single-state scans combined by
+    the read-out weights (ops.pam_scan)."""
+    from qllm2_b200 import ops, synthetic
+    K = 3
+    inp = synthetic.scan_inputs(B, H, T, d, seed=700 + rank, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(701 + rank)
+    gamma = torch.sigmoid(torch.randn(K, B, H, T, generator=gen) + torch.tensor([1.0, 3.0, 5.0]).view(K, 1, 1, 1)).to(dev)
+    coef = torch.randn(K, B, H, T, 2, generator=gen).to(dev)
+    q, k, v, dy = (t.to(dev) for t in (inp.q, inp.k, inp.v, inp.dy))
+
+    def step():
+        qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+        gg, cc = gamma.detach().requires_grad_(True), coef.detach().requires_grad_(True)
+        y, _ = ops.pam_scan(qq, kk, vv, gg, coef=cc, chunk=C)
+        return torch.autograd.grad(y, [qq, kk, vv, gg, cc], dy)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return {"ms_per_step": e0.elapsed_time(e1) / iters,
+            "config": f"B={B} H={H} T={T} d={d} K=3 bf16, read-out weights and all five gradients, eager launches"}
+
+
+def vocab_parallel_ce(dev, rank, world, peaks, iters=5):
+    """Config 2 with the tied matrix sharded by vocabulary rows over the ranks (hidden rows replicated): forward +
+    backward of the fused CE; one all-gather of the row statistics, dH all-reduced under the dW products."""
+    import torch.distributed as dist
+    from qllm2_b200 import fused_ce, synthetic
+    c2 = synthetic.config2()
+    V = c2.w.shape[0]
+    lo, hi = rank * V // world, (rank + 1) * V // world
+    h = c2.h.to(dev).requires_grad_(True)
+    w = c2.w[lo:hi].contiguous().to(dev).requires_grad_(True)
+    t = c2.targets.to(dev)
+
+    def step():
+        loss = fused_ce.fused_linear_cross_entropy(h, w, t, group=dist.group.WORLD, vocab_start=lo)
+        torch.autograd.grad(loss, [h, w])
+        return loss
+    for _ in range(2):
+        loss = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    tms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    fl = 6 * 8192 * V * 768
+    return {"ms_fwd_bwd": ms, "tokens_per_s": 8192 / ms * 1e3, "achieved_tflops_total": fl / ms / 1e9,
+            "achieved_tflops_per_gpu": fl / ms / 1e9 / world, "frac_of_bf16_peak_per_gpu": fl / ms / 1e9 / world / peaks["tf"],
+            "loss": float(loss.detach()),
+            "config": f"N=8192 rows, F=768, vocabulary 50261 in {world} row shards, bf16; device events, max over ranks"}
 
 
 def side_measurements(dev, peaks):
@@ -441,8 +588,12 @@ def side_measurements(dev, peaks):
         torch.autograd.grad(loss, [h, w])
     ms = time_ms(ce, 3, warm=1)
     fl = 6 * 8192 * 50261 * 768
+    import ctypes as C_
+    from qllm2_b200 import _lib as L_
+    a_ = ops._ce_args(h.detach(), w.detach(), t, None, -100)
     out["fused_ce_config2"] = {"ms_fwd_bwd": ms, "tokens_per_s": 8192 / ms * 1e3, "achieved_tflops": fl / ms / 1e9,
-                               "frac_of_bf16_peak": fl / ms / 1e9 / peaks["tf"]}
+                               "frac_of_bf16_peak": fl / ms / 1e9 / peaks["tf"],
+                               "bwd_workspace_bytes": int(L_.lib().qpam_ce_workspace_bytes(C_.byref(a_), 1))}
     del h, w, t
     torch.cuda.empty_cache()
     out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
@@ -640,29 +791,57 @@ def inference_small(dev, n_seq=48, n_slots=48, new_tokens=3, max_prompt=1024):
             "generated_tokens": sum(len(v_) for v_ in res.values()), "engine_steps": eng.steps}
 
 
-def continuous_decode(dev, peaks, n_seq=512, n_slots=256, new_tokens=32, max_prompt=1024):
-    """Continuous-batching greedy decode through the 12-block model of config 5: 256 state slots, a bounded
-    sample of the 2048-prompt job (512 prompts of 32..1024 tokens, 32 new tokens each).  Three engines:
-    packed weights + fused block kernels replayed from one CUDA graph (the product path), the same without
-    the graph, and the module path (`V11Block` operators).  `steady_decode_tokens_per_s` is the decode step
-    alone with every slot busy; its roofline counts the state pool read+written once per layer and every
-    weight read once per step."""
-    from qllm2_b200 import model as M, synthetic
-    from qllm2_b200.serving import ContinuousBatcher
+def _config5_model(dev, n_states):
+    from qllm2_b200 import model as M
     torch.manual_seed(0)
-    cfg = M.V11Config(vocab_size=50261, dim=768, n_heads=12, head_dim=64, n_layers=12, n_states=3,
+    cfg = M.V11Config(vocab_size=50261, dim=768, n_heads=12, head_dim=64, n_layers=12, n_states=n_states,
                       gate_content_aware=True, dropout=0.0, gradient_checkpointing=False, max_seq_len=8192)
-    net = M.V11LM(cfg).to(dev).bfloat16().eval()
-    prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
+    return M.V11LM(cfg).to(dev).bfloat16().eval(), cfg
+
+
+def _steady_decode_step(eng, n_slots, dev, peaks):
+    """The captured decode step alone, every slot busy: state pool read + written once per layer, every packed
+    weight read once per step."""
+    eng._g_slots.copy_(torch.arange(n_slots, dtype=torch.int32, device=dev))
+    for _ in range(3):
+        eng._graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(20):
+        eng._graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 20
+    state_bytes = 2 * eng.pool.numel() * eng.pool.element_size()
+    weight_bytes = sum(t.numel() * t.element_size() for L_ in eng.ff.layers
+                       for t in (L_.w_gu, L_.w_down, L_.w_front, L_.w_o)) + eng.ff.w_vocab.numel() * 2
+    return {"decode_step_ms": ms, "steady_decode_tokens_per_s": n_slots / ms * 1e3,
+            "state_bytes_per_step": state_bytes, "weight_bytes_per_step": weight_bytes,
+            "achieved_gbs": (state_bytes + weight_bytes) / ms / 1e6,
+            "frac_of_hbm_peak": (state_bytes + weight_bytes) / ms / 1e6 / peaks["hbm"]}
+
+
+def continuous_decode(dev, peaks, n_seq=2048, n_slots=256, new_tokens=256, max_prompt=4096):
+    """Continuous-batching greedy decode through the 12-block model of config 5 at its stated size: 2048 prompts
+    of 32..4096 uniformly random ids, 256 state slots, 256 new tokens per sequence, a new sequence joining whenever
+    one finishes; K = 3 states and K = 1.  The engine is the product path (packed weights, fused block kernels,
+    the decode step replayed from one CUDA graph, packed ragged prefill of joining prompts between steps).
+    `decode_tokens_per_s` = generated tokens / wall time of the whole job (prefill of all prompts included);
+    `steady_decode_tokens_per_s` is the decode step alone with every slot busy.  A reduced sample (512 prompts
+    <= 1024, 32 new tokens) then compares that engine with the same forward without the graph and with the module
+    path."""
+    from qllm2_b200 import _lib, synthetic
+    from qllm2_b200.serving import ContinuousBatcher
     out = {}
-    warm = ContinuousBatcher(net, n_slots=8, max_prefill_tokens=1 << 16)     # first use of every kernel, untimed
-    for p_ in prompts[:8]:
-        warm.submit(p_.tolist(), 2)
-    warm.run()
-    del warm
-    for mode, kw in (("fused_graph", dict(cuda_graph=True, fused=True)), ("fused", dict(cuda_graph=False, fused=True)),
-                     ("modules", dict(cuda_graph=False, fused=False))):
-        eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, **kw)
+    for n_states in (3, 1):
+        net, cfg = _config5_model(dev, n_states)
+        prompts = synthetic.decode_prompts(n_seq, 32, max_prompt, cfg.vocab_size, seed=0)
+        warm = ContinuousBatcher(net, n_slots=8, max_prefill_tokens=1 << 16)     # first use of every kernel, untimed
+        for p_ in prompts[:8]:
+            warm.submit(p_[:256].tolist(), 2)
+        warm.run()
+        del warm
+        eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, cuda_graph=True, fused=True)
         for p_ in prompts:
             eng.submit(p_.tolist(), new_tokens)
         eng.warmup()                                     # graph capture of the decode step, outside the timed run
@@ -672,32 +851,33 @@ def continuous_decode(dev, peaks, n_seq=512, n_slots=256, new_tokens=32, max_pro
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         gen_tokens = sum(len(v_) for v_ in res.values())
-        out[mode] = {"generated_tokens": gen_tokens, "seconds": dt, "tokens_per_s_incl_prefill": gen_tokens / dt,
-                     "engine_steps": eng.steps}
-        if eng._graph is not None:
-            # the decode step alone, every slot busy: replay the captured step with all rows pointed at slots
-            eng._g_slots.copy_(torch.arange(n_slots, dtype=torch.int32, device=dev))
-            for _ in range(3):
-                eng._graph.replay()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(20):
-                eng._graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            ms = e0.elapsed_time(e1) / 20
-            state_bytes = 2 * eng.pool.numel() * eng.pool.element_size()
-            weight_bytes = sum(t.numel() * t.element_size() for L_ in eng.ff.layers
-                               for t in (L_.w_gu, L_.w_down, L_.w_front, L_.w_o)) + eng.ff.w_vocab.numel() * 2
-            out[mode].update({"decode_step_ms": ms, "steady_decode_tokens_per_s": n_slots / ms * 1e3,
-                              "state_bytes_per_step": state_bytes, "weight_bytes_per_step": weight_bytes,
-                              "achieved_gbs": (state_bytes + weight_bytes) / ms / 1e6,
-                              "frac_of_hbm_peak": (state_bytes + weight_bytes) / ms / 1e6 / peaks["hbm"]})
+        r = {"generated_tokens": gen_tokens, "prompt_tokens": int(sum(len(p_) for p_ in prompts)), "seconds": dt,
+             "decode_tokens_per_s": gen_tokens / dt, "engine_steps": eng.steps, "sequences": len(res),
+             "config": f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
+                       f"12 blocks dim 768 H12 d64 K{n_states} vocab 50261 bf16 random init (seed 0)"}
+        r.update(_steady_decode_step(eng, n_slots, dev, peaks))
+        out[f"config5_K{n_states}"] = r
+        _lib.raise_on_device_error("continuous decode")
         del eng
+        if n_states == 3:
+            small = prompts[:512]
+            for mode, kw in (("fused", dict(cuda_graph=False, fused=True)), ("modules", dict(cuda_graph=False, fused=False)),
+                             ("fused_graph", dict(cuda_graph=True, fused=True))):
+                e2 = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, **kw)
+                for p_ in small:
+                    e2.submit(p_[:1024].tolist(), 32)
+                e2.warmup()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                res = e2.run()
+                torch.cuda.synchronize()
+                dt = time.perf_counter() - t0
+                gen = sum(len(v_) for v_ in res.values())
+                out["engines_small_sample_" + mode] = {"generated_tokens": gen, "seconds": dt, "tokens_per_s_incl_prefill": gen / dt,
+                                                       "engine_steps": e2.steps}
+                del e2
+        del net
         torch.cuda.empty_cache()
-    out["prompt_tokens"] = int(sum(len(p_) for p_ in prompts))
-    out["config"] = (f"{n_seq} sequences, prompts U[32,{max_prompt}], {new_tokens} new tokens each, {n_slots} state slots, "
-                     f"12 blocks dim 768 H12 d64 K3 vocab 50261 bf16 random init")
     return out
 
 

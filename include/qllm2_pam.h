@@ -190,6 +190,13 @@ int qpam_ce_finalize(const qpam_ce_args* args, const float* row_max, const float
 int qpam_ce_bwd(const qpam_ce_args* args, const float* lse, const float* grad_scale,
                 const float* denom, void* dh, void* dw, void* stream);
 
+/* Same as qpam_ce_bwd; in addition `dh_ready_stream` (a CUDA stream of the caller, may be NULL) is made to wait
+ * until dh is complete, while the products for dw are still running on `stream`.  The vocabulary-parallel
+ * form enqueues its all-reduce of dh (v11/fused_ce.py:80 computes the same grad_H on one device) on that
+ * stream, so the exchange over NVLink overlaps the dw GEMM.  The caller joins the two streams afterwards. */
+int qpam_ce_bwd_overlap(const qpam_ce_args* args, const float* lse, const float* grad_scale,
+                        const float* denom, void* dh, void* dw, void* stream, void* dh_ready_stream);
+
 /* Decode head: argmax_v (h @ w^T)[n, v] -> ids[N] (int64) and the winning logit (fp32). */
 int qpam_head_argmax(const qpam_ce_args* args, int64_t* ids, float* best, void* stream);
 

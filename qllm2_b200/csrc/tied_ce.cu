@@ -203,6 +203,11 @@ extern "C" int qpam_ce_finalize(const qpam_ce_args* a, const float* row_max, con
 
 extern "C" int qpam_ce_bwd(const qpam_ce_args* a, const float* lse, const float* grad_scale, const float* denom,
                            void* dh, void* dw, void* stream) {
+  return qpam_ce_bwd_overlap(a, lse, grad_scale, denom, dh, dw, stream, nullptr);
+}
+
+extern "C" int qpam_ce_bwd_overlap(const qpam_ce_args* a, const float* lse, const float* grad_scale, const float* denom,
+                                   void* dh, void* dw, void* stream, void* dh_ready_stream) {
   int rc = check_ce_args(a, true);
   if (rc) return rc;
   QPAM_REQUIRE(lse && grad_scale && denom && dh && dw, "ce bwd: NULL pointer argument");
@@ -212,10 +217,13 @@ extern "C" int qpam_ce_bwd(const qpam_ce_args* a, const float* lse, const float*
     return QPAM_EWORKSPACE;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaStream_t side = reinterpret_cast<cudaStream_t>(dh_ready_stream);
   if (a->N > 0 && tc_usable(a, L) && ((uintptr_t)dh & 15) == 0 && ((uintptr_t)dw & 15) == 0)
-    return ce_tc_backward(a, L.tc, tc_buffers(a, L), lse, grad_scale, denom, dh, dw, st);
-  return a->io_dtype == QPAM_BF16 ? ce_bwd_t<__nv_bfloat16>(a, L, lse, grad_scale, denom, dh, dw, st)
-                                  : ce_bwd_t<float>(a, L, lse, grad_scale, denom, dh, dw, st);
+    return ce_tc_backward(a, L.tc, tc_buffers(a, L), lse, grad_scale, denom, dh, dw, st, side);
+  rc = a->io_dtype == QPAM_BF16 ? ce_bwd_t<__nv_bfloat16>(a, L, lse, grad_scale, denom, dh, dw, st)
+                                : ce_bwd_t<float>(a, L, lse, grad_scale, denom, dh, dw, st);
+  if (rc == QPAM_OK && side != nullptr) rc = signal_stream(st, side);    // these kernels finish dh and dw together
+  return rc;
 }
 
 extern "C" int qpam_head_argmax(const qpam_ce_args* a, int64_t* ids, float* best, void* stream) {

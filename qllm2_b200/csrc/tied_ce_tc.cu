@@ -113,8 +113,20 @@ __global__ void k_reduce_splits_bf16(const float* __restrict__ part, __nv_bfloat
   }
 }
 
+// make `waiter` wait for everything enqueued on `st` so far
+int signal_stream(cudaStream_t st, cudaStream_t waiter) {
+  cudaEvent_t ev;
+  QPAM_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  cudaError_t e = cudaEventRecord(ev, st);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(waiter, ev, 0);
+  cudaEventDestroy(ev);      // released once the record has completed
+  if (e != cudaSuccess) return cuda_fail(e, "signal_stream");
+  return QPAM_OK;
+}
+
 int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& b, const float* lse,
-                   const float* grad_scale, const float* denom, void* dh, void* dw, cudaStream_t st) {
+                   const float* grad_scale, const float* denom, void* dh, void* dw, cudaStream_t st,
+                   cudaStream_t dh_ready_stream) {
   const int F = a->F;
   const int64_t V = a->V;
   auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false>;
@@ -168,6 +180,12 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     k_reduce_splits_bf16<<<592, 256, 0, st>>>(b.dh_part, reinterpret_cast<__nv_bfloat16*>(dh) + r0 * F, rows * F, ks,
                                              rows * F);
     QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
+    if (dh_ready_stream != nullptr && r0 + rows >= a->N) {
+      // dH is complete: a caller's side stream (the all-reduce of the vocabulary-parallel form) may start on it
+      // while the dW products below still run
+      int rc2 = signal_stream(st, dh_ready_stream);
+      if (rc2) return rc2;
+    }
     // 3) dW (+)= P^T H[r0:r0+rows]
     tc::GemmParams w{};
     w.n_tiles = f_tiles; w.tiles_per_cta = 1;

@@ -28,8 +28,12 @@ struct CETcBuffers {
 // per-row partial statistics [nsplit][N] via the tensor-core logits GEMM
 int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& plan, const CETcBuffers& b, cudaStream_t st);
 // dH, dW via recomputed probabilities (bf16 tiles) and two tensor-core GEMMs per row chunk
+// dh_ready_stream (may be NULL): a stream of the caller that is made to wait until dh is complete, while the
+// dw products continue on `st`
 int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& plan, const CETcBuffers& b, const float* lse,
-                   const float* grad_scale, const float* denom, void* dh, void* dw, cudaStream_t st);
+                   const float* grad_scale, const float* denom, void* dh, void* dw, cudaStream_t st,
+                   cudaStream_t dh_ready_stream);
+int signal_stream(cudaStream_t st, cudaStream_t waiter);
 
 // device error word of the tensor-core kernels (0 = ok; 101..104 = a bounded wait gave up)
 int ce_tc_device_status(int* value, bool clear);

@@ -7,8 +7,9 @@ accepted and ignored: the kernels tile the vocabulary themselves and never hold 
 
 An optional ``group`` (a torch.distributed process group) turns on the vocabulary-parallel form:
 every rank passes its own row-shard ``weight_matrix`` [V/world, F] with ``vocab_start``; the
-per-row (max, sum-exp, target-logit) statistics are all-reduced (NCCL over NVLink), ``grad_H``
-is all-reduced and ``grad_W`` stays local to the shard.
+per-row (max, sum-exp, target-logit, arg-max) statistics cross the group in ONE all-gather (NCCL over
+NVLink), ``grad_H`` is all-reduced on a side stream under the ``grad_W`` products, and ``grad_W`` stays
+local to the shard.
 """
 from __future__ import annotations
 
@@ -20,17 +21,33 @@ from . import ops
 
 
 def _combine_stats(stats, group):
-    """All-reduce shard statistics into global ones: max, rescaled sum-exp, summed target logit."""
+    """Shard statistics -> global ones with ONE exchange: every rank contributes [4, N] floats (max, sum-exp,
+    target logit, arg-max column) to an all-gather, and each rank folds the world's rows itself:
+    M = max_r m_r,  S = sum_r s_r e^{m_r - M},  target logit = sum_r (only the owner's is non-zero),
+    arg-max = lowest column among the ranks that attain M.  (Columns are carried as fp32: exact below 2^24.)"""
     import torch.distributed as dist
     row_max, row_sum, row_tgt, row_arg = stats
-    gmax = row_max.clone()
-    dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
-    packed = torch.stack([row_sum * torch.exp(row_max - gmax), row_tgt])
-    dist.all_reduce(packed, op=dist.ReduceOp.SUM, group=group)
-    # arg-max: the rank holding the global max wins; ties go to the lowest column index
-    cand = torch.where(row_max == gmax, row_arg, torch.full_like(row_arg, torch.iinfo(torch.int64).max))
-    dist.all_reduce(cand, op=dist.ReduceOp.MIN, group=group)
-    return gmax, packed[0].contiguous(), packed[1].contiguous(), cand
+    world = dist.get_world_size(group)
+    mine = torch.stack([row_max, row_sum, row_tgt, row_arg.to(row_max.dtype)])        # [4, N]
+    everyone = torch.empty((world,) + tuple(mine.shape), dtype=mine.dtype, device=mine.device)
+    dist.all_gather(list(everyone.unbind(0)), mine, group=group)       # one collective (NCCL and gloo alike)
+    m, s_, t, a = everyone[:, 0], everyone[:, 1], everyone[:, 2], everyone[:, 3]
+    gmax = m.max(dim=0).values
+    gsum = (s_ * torch.exp(m - gmax)).sum(dim=0)
+    gtgt = t.sum(dim=0)
+    cand = torch.where(m == gmax, a, torch.full_like(a, float(1 << 24)))
+    return gmax, gsum, gtgt, cand.min(dim=0).values.to(torch.int64)
+
+
+_COMM_STREAMS = {}
+
+
+def _comm_stream(device):
+    """One side stream per device for the gradient all-reduce of the vocabulary-parallel form."""
+    key = (device.type, device.index)
+    if key not in _COMM_STREAMS:
+        _COMM_STREAMS[key] = torch.cuda.Stream(device=device)
+    return _COMM_STREAMS[key]
 
 
 class _FusedLinearCE(torch.autograd.Function):
@@ -65,11 +82,19 @@ class _FusedLinearCE(torch.autograd.Function):
         h, w, targets, maskf, lse, denom = ctx.saved_tensors
         ignore_index, group, vocab_start, h_dtype, w_dtype = ctx.cfg
         gs = grad_output.detach().float().reshape(1).contiguous()
-        dh, dw = ops.ce_backward(h, w, targets, maskf, lse, gs, denom, ignore_index=ignore_index,
-                                 v_offset=vocab_start)
-        if group is not None:
+        if group is None:
+            dh, dw = ops.ce_backward(h, w, targets, maskf, lse, gs, denom, ignore_index=ignore_index, v_offset=vocab_start)
+        else:
+            # dH of the shards is summed over the group on a side stream that the library releases as soon as dH
+            # is complete: the exchange runs under the dW products, which stay local to the shard
             import torch.distributed as dist
-            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=group)
+            cur, comm = torch.cuda.current_stream(h.device), _comm_stream(h.device)
+            dh, dw = ops.ce_backward(h, w, targets, maskf, lse, gs, denom, ignore_index=ignore_index, v_offset=vocab_start,
+                                     dh_ready_stream=comm)
+            with torch.cuda.stream(comm):
+                dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=group)
+            dh.record_stream(comm)
+            cur.wait_stream(comm)
         return dh.to(h_dtype), dw.to(w_dtype), None, None, None, None, None
 
 

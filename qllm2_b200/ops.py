@@ -351,15 +351,17 @@ def ce_finalize(h, w, targets, mask, stats, *, ignore_index=-100):
     return out
 
 
-def ce_backward(h, w, targets, mask, lse, grad_scale, denom, *, ignore_index=-100, v_offset=0):
-    """dH [N,F], dW [V,F] (dtype of h / w) for  grad_scale * loss_sum / denom."""
+def ce_backward(h, w, targets, mask, lse, grad_scale, denom, *, ignore_index=-100, v_offset=0, dh_ready_stream=None):
+    """dH [N,F], dW [V,F] (dtype of h / w) for  grad_scale * loss_sum / denom.  `dh_ready_stream` (a
+    torch.cuda.Stream) is made to wait until dH is complete while dW is still being formed on the current stream."""
     L = _lib.lib()
     dh = torch.empty_like(h)
     dw = torch.empty_like(w)
     a = _ce_args(h, w, targets, mask, ignore_index, v_offset)
     ws = _workspace(L.qpam_ce_workspace_bytes(C.byref(a), 1), h.device)
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-    check(L.qpam_ce_bwd(C.byref(a), ptr(lse), ptr(grad_scale), ptr(denom), ptr(dh), ptr(dw), stream_ptr()),
+    side = None if dh_ready_stream is None else dh_ready_stream.cuda_stream
+    check(L.qpam_ce_bwd_overlap(C.byref(a), ptr(lse), ptr(grad_scale), ptr(denom), ptr(dh), ptr(dw), stream_ptr(), side),
           "qpam_ce_bwd")
     return dh, dw
 

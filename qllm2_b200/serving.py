@@ -17,7 +17,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 
 import torch
 
-from . import ops
+from . import _lib, ops
 from .fused_forward import FusedForward
 from .model import V11LM
 
@@ -327,11 +327,16 @@ class ContinuousBatcher:
             self._decode(live_before)
         self.sched.retire_finished()
         self.steps += 1
+        if self.steps % 64 == 0:
+            # the host has just read this step's tokens, so the device is idle: a cheap point to learn of a kernel that
+            # gave up on a wait (its outputs, and every token since, would be invalid)
+            _lib.raise_on_device_error("ContinuousBatcher.step")
         return len(live_before) + len(batch)
 
     def run(self) -> Dict[int, List[int]]:
         while not self.sched.idle:
             self.step()
+        _lib.raise_on_device_error("ContinuousBatcher.run")
         return {r.rid: r.generated for r in self.sched.finished}
 
 
