@@ -1,7 +1,7 @@
 """Multi-threaded CPU port of the reference's chunked PAM scan and row-chunked linear+CE.
 
-TEST / BASELINE INFRASTRUCTURE ONLY.  The reference (a Python/PyTorch project) cannot travel to
-the GPU box, so this file restates its CPU code path with the same operator mix -- batched
+TEST / BASELINE INFRASTRUCTURE ONLY.  Where no checkout of the reference (a Python/PyTorch project) is
+importable, this file restates its CPU code path with the same operator mix -- batched
 matmuls per chunk inside a Python chunk loop, autograd for the backward -- so that timing it on
 the host cores is a fair stand-in for timing the reference itself
 (v11/model.py:354-417 ``_dual_form_block`` + ``_forward_chunked_head``;

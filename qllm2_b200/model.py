@@ -25,6 +25,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from . import _lib
 from . import fused_elementwise as FE
 from . import ops
 from .fused_ce import fused_linear_cross_entropy
@@ -147,12 +148,7 @@ class ComplexNorm(nn.Module):
         self.eps = eps
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        if z.is_cuda:
-            return FE.fused_complex_norm(z, self.scale, self.eps)
-        mag = _magnitude(z)
-        rms = torch.sqrt((mag ** 2).mean(dim=-1, keepdim=True) + self.eps)
-        unit = z / (mag.unsqueeze(-1) + 1e-8)
-        return unit * ((mag / rms) * self.scale).unsqueeze(-1)
+        return FE.fused_complex_norm(z, self.scale, self.eps)      # CUDA only: the kernel wrapper refuses CPU tensors
 
 
 class ModSwish(nn.Module):
@@ -162,11 +158,7 @@ class ModSwish(nn.Module):
         self.beta = nn.Parameter(torch.ones(dim))
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        if z.is_cuda:
-            return FE.fused_mod_swish(z, self.bias, self.beta)
-        mag = _magnitude(z)
-        act = mag * torch.sigmoid(self.beta * mag + self.bias)
-        return z / (mag.unsqueeze(-1) + 1e-8) * act.unsqueeze(-1)
+        return FE.fused_mod_swish(z, self.bias, self.beta)
 
 
 class ModReLU(nn.Module):
@@ -175,10 +167,7 @@ class ModReLU(nn.Module):
         self.bias = nn.Parameter(torch.full((dim,), -0.1))
 
     def forward(self, z: torch.Tensor) -> torch.Tensor:
-        if z.is_cuda:
-            return FE.fused_mod_relu(z, self.bias)
-        mag = _magnitude(z)
-        return z / (mag.unsqueeze(-1) + 1e-8) * F.relu(mag + self.bias).unsqueeze(-1)
+        return FE.fused_mod_relu(z, self.bias)
 
 
 class ComplexGatedUnit(nn.Module):
@@ -198,12 +187,7 @@ class ComplexGatedUnit(nn.Module):
     def forward(self, z: torch.Tensor) -> torch.Tensor:
         gate = self.gate_proj(z)
         up = self.act(self.up_proj(z))
-        if z.is_cuda:
-            return self.down_proj(FE.fused_cgu_gate(gate, up))
-        gmag = _magnitude(gate)
-        phase = gate / (gmag.unsqueeze(-1) + 1e-8)
-        gated = _complex_mul(phase, up) * torch.sigmoid(gmag).unsqueeze(-1)
-        return self.down_proj(gated)
+        return self.down_proj(FE.fused_cgu_gate(gate, up))
 
 
 class ComplexEmbed(nn.Module):
@@ -523,10 +507,11 @@ class V11Block(nn.Module):
 
     @staticmethod
     def _residual(x, delta, scale):
-        if x.is_cuda and x.numel() % 4 == 0 and x.dtype in (torch.float32, torch.bfloat16) \
-                and delta.dtype in (torch.float32, torch.bfloat16):
+        if not x.is_cuda:
+            raise _lib.QPamError("V11Block runs on CUDA tensors only (there is no CPU path in this package)")
+        if x.numel() % 4 == 0 and x.dtype in (torch.float32, torch.bfloat16) and delta.dtype in (torch.float32, torch.bfloat16):
             return FE.scaled_residual(x, delta, scale)
-        return x + delta * scale
+        return x + delta * scale        # other dtypes (fp16, fp64): the residual add stays a torch operator
 
 
 class ComplexPosEmbed(nn.Module):

@@ -1,6 +1,6 @@
 """Generate golden fixtures by RUNNING THE REFERENCE ITSELF on seeded inputs.
 
-Usage (only where the reference checkout is importable; it is not on the GPU box):
+Usage (only where a checkout of the reference is importable):
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/qllm2
 

@@ -1,5 +1,5 @@
 """Model-level golden fixtures: run the REFERENCE V11LM (tiny random-init configurations) and store
-its parameters, inputs and outputs, so the drop-in modules can be checked on the GPU box where the
+its parameters, inputs and outputs, so the drop-in modules can be checked on machines where the
 reference is absent.
 
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden_model.py /path/to/qllm2
