@@ -200,6 +200,29 @@ int qpam_ce_bwd_overlap(const qpam_ce_args* args, const float* lse, const float*
 /* Decode head: argmax_v (h @ w^T)[n, v] -> ids[N] (int64) and the winning logit (fp32). */
 int qpam_head_argmax(const qpam_ce_args* args, int64_t* ids, float* best, void* stream);
 
+/* Token sampling on the device, one row of logits per sequence: the sampling block of V11LM.generate
+ * (v11/model.py:1221-1244) -- logits / temperature, repetition penalty over the tokens already in the sequence
+ * (x > 0 ? x / penalty : x * penalty), top-k (values below the k-th largest dropped, ties kept), top-p (in
+ * descending order a token is dropped when the probability mass before it is >= top_p; tokens that tie with the
+ * threshold are all kept), then one draw from the softmax of what is left -- as ONE kernel, without a sort and
+ * without a host round trip.  The draw is the inverse CDF in vocabulary order of uniforms[row] in [0,1), which
+ * the caller supplies (the reference draws with torch.multinomial: same distribution, different stream of random
+ * numbers).  top_k == 0 and top_p == 0 (or >= 1) switch the filters off, repetition_penalty == 1 the penalty.
+ *   logits      [n, V] (row stride ld_logits), fp32 or bf16
+ *   history     optional int64 [n_hist_rows, ld_hist]: token ids of every sequence so far; row r of the logits
+ *               uses history row slot_ids[r] (or r when slot_ids is NULL; a slot outside [0, n_hist_rows) marks a
+ *               padded row, which draws nothing and returns id 0); hist_len optional int32 [n_hist_rows]
+ *               (NULL: all hist_cols entries count); append != 0 stores the drawn id at history[row][hist_len]
+ *               and increments hist_len
+ *   next_ids    int64 [n];  stats optional float [n,4] = (max, kept mass, kept count, mass after top-k)
+ *   workspace   qpam_sample_workspace_bytes(n, V) bytes (0 while a row fits in shared memory, V <= ~56k) */
+size_t qpam_sample_workspace_bytes(int32_t n, int32_t V);
+int qpam_sample_logits(const void* logits, int32_t io_dtype, int32_t n, int32_t V, int64_t ld_logits,
+                       float temperature, int32_t top_k, float top_p, float repetition_penalty,
+                       const int32_t* slot_ids, int64_t* history, int32_t n_hist_rows, int32_t hist_cols,
+                       int64_t ld_hist, int32_t* hist_len, int32_t append, const float* uniforms,
+                       int64_t* next_ids, float* stats, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * Fused element-wise complex operators of a V11 block (interleaved [..., C, 2] rows, N rows).
  * They replace the reference's fused operators and their autograd functions:

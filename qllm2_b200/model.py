@@ -636,27 +636,20 @@ class V11LM(nn.Module):
     def generate(self, input_ids, max_new_tokens=100, temperature=1.0, top_k=50, top_p=0.0,
                  repetition_penalty=1.0, eos_token_id=None, fused: bool = True):
         """Prefill once (parallel scan), then one O(1) recurrent step per token.  temperature <= 0
-        selects greedy decoding (arg-max of the logits).  On CUDA the loop runs on the packed forward with
-        the decode step replayed from a CUDA graph (`fused=False` keeps the module-by-module loop)."""
+        selects greedy decoding (arg-max of the logits); otherwise the reference's sampling block
+        (v11/model.py:1221-1244) runs as one kernel per token (`ops.sample_logits`).  The loop runs on the packed
+        forward with the decode step replayed from a CUDA graph (`fused=False` keeps the module-by-module loop)."""
         self.eval()
         greedy = temperature is None or temperature <= 0
 
         def sample(nl, out):
+            """nl: logits [B, V] of the last position; out: token ids so far [B, T] (for the repetition penalty)."""
             if greedy:
                 return nl.argmax(dim=-1, keepdim=True)
-            nl = nl / temperature
-            if repetition_penalty != 1.0:
-                sc = torch.gather(nl, 1, out)
-                nl.scatter_(1, out, torch.where(sc > 0, sc / repetition_penalty, sc * repetition_penalty))
-            if top_k > 0:
-                kth = nl.topk(min(top_k, nl.size(-1))).values[:, -1:]
-                nl[nl < kth] = float("-inf")
-            if top_p > 0:
-                sl, si = nl.sort(descending=True)
-                pr = sl.softmax(dim=-1)
-                sl[(pr.cumsum(dim=-1) - pr) >= top_p] = float("-inf")
-                nl = sl.scatter(1, si, sl)
-            return torch.multinomial(nl.softmax(dim=-1), 1)
+            # temperature, penalty, top-k, top-p and the draw in one kernel (random numbers from torch's generator)
+            return ops.sample_logits(nl, temperature=temperature, top_k=top_k, top_p=top_p,
+                                     repetition_penalty=repetition_penalty,
+                                     history=out.contiguous() if repetition_penalty != 1.0 else None)[:, None]
 
         if fused and input_ids.is_cuda and max_new_tokens > 0:
             from .fused_forward import FusedForward

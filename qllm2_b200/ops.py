@@ -370,3 +370,48 @@ def head_argmax(h, w):
     """Greedy decode head: (ids int64 [N], best logit float32 [N]) of argmax_v (h @ w^T)."""
     row_max, _, _, row_arg = ce_row_stats(h, w, None)
     return row_arg, row_max
+
+
+def sample_logits(logits, uniforms=None, *, temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0,
+                  repetition_penalty: float = 1.0, history=None, hist_len=None, slot_ids=None, append: bool = False,
+                  return_stats: bool = False):
+    """Draw one token per row of `logits` [n, V] on the device (one kernel; v11/model.py:1221-1244): temperature,
+    repetition penalty over `history` (int64 [rows, cols] token ids; `hist_len` int32 [rows] valid entries per
+    row, `slot_ids` int32 [n] maps logits rows to history rows), top-k, top-p, then the inverse-CDF draw of
+    `uniforms` [n] (default: torch.rand on the logits' device, i.e. torch's generator).  `append=True` also writes
+    the drawn id behind the row's history and advances `hist_len`.  Returns ids int64 [n] (and, with
+    `return_stats`, float32 [n,4] = (max, kept mass, kept count, mass after top-k))."""
+    L = _lib.lib()
+    _require_cuda(logits)
+    if logits.dim() != 2 or logits.dtype not in (torch.float32, torch.bfloat16):
+        raise _lib.QPamError(f"sample_logits: logits must be [n, V] float32 or bfloat16, got {tuple(logits.shape)} {logits.dtype}")
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    n, V = logits.shape
+    dev = logits.device
+    if uniforms is None:
+        uniforms = torch.rand(n, device=dev, dtype=torch.float32)
+    if uniforms.dtype != torch.float32 or uniforms.numel() != n or not uniforms.is_cuda:
+        raise _lib.QPamError("sample_logits: uniforms must be a float32 CUDA tensor with one entry per row")
+    rows = cols = ld = 0
+    if history is not None:
+        if history.dim() != 2 or history.dtype != torch.int64 or not history.is_cuda or history.stride(1) != 1:
+            raise _lib.QPamError("sample_logits: history must be a 2-D int64 CUDA tensor with unit column stride")
+        rows, cols, ld = history.shape[0], history.shape[1], history.stride(0)
+        if slot_ids is None and rows < n:
+            raise _lib.QPamError(f"sample_logits: history has {rows} rows for {n} rows of logits")
+    if hist_len is not None and (history is None or hist_len.dtype != torch.int32 or hist_len.numel() != rows or not hist_len.is_cuda):
+        raise _lib.QPamError("sample_logits: hist_len must be int32 [history rows] on the device")
+    if slot_ids is not None and (slot_ids.dtype != torch.int32 or slot_ids.numel() != n or not slot_ids.is_cuda):
+        raise _lib.QPamError("sample_logits: slot_ids must be int32 [n] on the device")
+    if append and (history is None or hist_len is None):
+        raise _lib.QPamError("sample_logits: append needs history and hist_len")
+    ids = torch.empty(n, dtype=torch.int64, device=dev)
+    stats = torch.empty(n, 4, dtype=torch.float32, device=dev) if return_stats else None
+    need = L.qpam_sample_workspace_bytes(n, V)
+    ws = _workspace(need, dev) if need else None
+    check(L.qpam_sample_logits(logits.data_ptr(), dtype_code(logits.dtype), n, V, logits.stride(0), float(temperature), int(top_k),
+                               float(top_p), float(repetition_penalty), ptr(slot_ids), ptr(history), rows, cols, ld,
+                               ptr(hist_len), int(bool(append)), uniforms.data_ptr(), ids.data_ptr(), ptr(stats),
+                               ptr(ws), need, stream_ptr()), "qpam_sample_logits")
+    return (ids, stats) if return_stats else ids

@@ -1,4 +1,4 @@
-"""Continuous-batching greedy decode on a pool of per-sequence PAM state slots.
+"""Continuous-batching decode (greedy or sampled) on a pool of per-sequence PAM state slots.
 
 The reference decodes one batch with a single `step_offset` for all rows (v11/model.py:785,
 1206-1245), so sequences of different lengths cannot share a step.  Here every live sequence owns
@@ -160,14 +160,18 @@ class ContinuousBatcher:
 
     def __init__(self, model: V11LM, n_slots: int, state_dtype: Optional[torch.dtype] = None,
                  max_prefill_tokens: int = 1 << 17, cuda_graph: bool = False, max_position: int = 8192,
-                 fused: bool = True, chunked_prefill: bool = False):
+                 fused: bool = True, chunked_prefill: bool = False, sampling: Optional[dict] = None):
         """cuda_graph=True captures the decode step once for a full batch of n_slots rows (idle rows carry
         slot id -1, which the step kernel skips) and replays it every step: the per-token cost is then the
         kernels', not the launches' of the Python layer loop.  fused=True runs the blocks through
         `FusedForward` (packed weights, ~10 launches per layer) when the configuration allows it;
         fused=False keeps the module path (`V11Block` operators).  chunked_prefill=True absorbs prompts in
         pieces of at most max_prefill_tokens per step, each piece scanned from the state its predecessor left in
-        the slot (the streaming use of the reference's stateful forward, v11/duplex/infer_stream.py:101-102)."""
+        the slot (the streaming use of the reference's stateful forward, v11/duplex/infer_stream.py:101-102).
+        sampling=dict(temperature=, top_k=, top_p=, repetition_penalty=) draws every token with the reference's
+        sampling block (v11/model.py:1221-1244) as one kernel inside the step -- the token history of every slot
+        lives on the device and the kernel appends to it, so a captured step needs no host data; None (or a
+        temperature <= 0) decodes greedily."""
         self.model = model.eval()
         cfg = model.config
         p = next(model.parameters())
@@ -184,6 +188,13 @@ class ContinuousBatcher:
         self.max_position = max_position
         self.ff = FusedForward(model, max_position) if fused and FusedForward.unsupported_reason(model) is None else None
         self._ensure_rope(max_position)    # tables must not grow while a captured graph reads them
+        self.sampling = None
+        if sampling is not None and float(sampling.get("temperature", 1.0)) > 0:
+            self.sampling = dict(temperature=float(sampling.get("temperature", 1.0)), top_k=int(sampling.get("top_k", 0)),
+                                 top_p=float(sampling.get("top_p", 0.0)),
+                                 repetition_penalty=float(sampling.get("repetition_penalty", 1.0)))
+            self._hist = torch.zeros(n_slots, max_position + 1, dtype=torch.long, device=self.device)
+            self._hist_len = torch.zeros(n_slots, dtype=torch.int32, device=self.device)
         if cuda_graph:
             self._g_ids = torch.zeros(n_slots, 1, dtype=torch.long, device=self.device)
             self._g_pos = torch.zeros(n_slots, 1, dtype=torch.long, device=self.device)
@@ -207,6 +218,19 @@ class ContinuousBatcher:
                 blk.pam.register_buffer("rope_cache", build_rope_cache(max(need, 2 * blk.pam.rope_cache.shape[0]), blk.pam.head_dim).to(self.device),
                                         persistent=False)
 
+    def _pick(self, lm_rows, slots):
+        """Next token of every row from its head hidden state lm_rows [n, D, 2]: arg-max of the tied head, or one
+        draw of the sampling kernel (which also appends the token to the slot's history)."""
+        if self.sampling is None:
+            return self.ff.greedy_next(lm_rows) if self.ff is not None else self.model.greedy_next(lm_rows)
+        if self.ff is not None:
+            logits = self.ff.logits(lm_rows)
+        else:
+            Hm, W = self.model.tied_head_matrices(lm_rows.unsqueeze(1))
+            logits = (Hm @ W.to(Hm.dtype).T).float()
+        return ops.sample_logits(logits, history=self._hist, hist_len=self._hist_len, slot_ids=slots, append=True,
+                                 **self.sampling)
+
     @torch.no_grad()
     def _prefill(self, items):
         """items: (request, first prompt token, token count).  A piece that starts mid-prompt is scanned from the
@@ -227,17 +251,26 @@ class ContinuousBatcher:
             def s0_of(layer):      # [K,S,H,d,d,2] float32; fresh sequences start from zero whatever the slot held
                 s = self.pool[slots.long(), layer].float() * resumed[:, None, None, None, None, None]
                 return s.permute(1, 0, 2, 3, 4, 5).contiguous()
+        if self.sampling is not None:      # the penalty looks at the whole prompt: load the slots' histories
+            for r, st, take in items:
+                self._hist[r.slot, st:st + take] = torch.as_tensor(r.prompt[st:st + take], dtype=torch.long).to(self.device)
+            self._hist_len[slots.long()] = torch.tensor([st + take for _, st, take in items], dtype=torch.int32, device=self.device)
+            # a piece that ends mid-prompt draws nothing: its row is padded out (slot -1)
+            pick_slots = torch.tensor([r.slot if st + take == len(r.prompt) else -1 for r, st, take in items],
+                                      dtype=torch.int32, device=self.device)
+        else:
+            pick_slots = slots
         if self.ff is not None:
             xn = self.ff.hidden(ids, _PrefillMix(self, cu, slots, s0_of), positions=positions)
-            nxt = self.ff.greedy_next(self.ff.head_hidden(xn[(cu[1:] - 1).long()]))
+            nxt = self._pick(self.ff.head_hidden(xn[(cu[1:] - 1).long()]), pick_slots)
         else:
-            nxt = self._prefill_modules(ids, positions, cu, slots, s0_of)
+            nxt = self._prefill_modules(ids, positions, cu, slots, s0_of, pick_slots)
         for (r, st, take), t in zip(items, nxt.tolist()):
             r.prefilled = st + take
             if not r.prefilling:
                 r.generated.append(int(t))
 
-    def _prefill_modules(self, ids, positions, cu, slots, s0_of=None):
+    def _prefill_modules(self, ids, positions, cu, slots, s0_of=None, pick_slots=None):
         m = self.model
         z = m.embed_norm(m.embed(ids))
         for li, blk in enumerate(m.blocks):
@@ -252,7 +285,7 @@ class ContinuousBatcher:
             z = z + out * blk.pam_scale
         last = (cu[1:] - 1).long()
         lm = m._head_hidden(z[:, last])                                     # [1, n, D, 2]
-        return m.greedy_next(lm[0])
+        return self._pick(lm[0], slots if pick_slots is None else pick_slots)
 
     @torch.no_grad()
     def warmup(self):
@@ -299,7 +332,7 @@ class ContinuousBatcher:
         """One decode step for rows (ids [n,1], positions [n,1], slots [n]); returns next ids [n]."""
         if self.ff is not None:
             xn = self.ff.hidden(ids, _DecodeMix(self, slots), positions=positions)
-            return self.ff.greedy_next(self.ff.head_hidden(xn))
+            return self._pick(self.ff.head_hidden(xn), slots)
         m = self.model
         n = ids.shape[0]
         z = m.embed_norm(m.embed(ids))                                      # [n,1,D,2]
@@ -314,7 +347,47 @@ class ContinuousBatcher:
                                     layer=li)
             out = pam.o_proj(y.reshape(n, 1, pam.inner_dim, 2))
             z = z + out * blk.pam_scale
-        return m.greedy_next(m._head_hidden(z)[:, 0])
+        return self._pick(m._head_hidden(z)[:, 0], slots)
+
+    # ---------------------------------------------------------------- live sessions
+    def export_session(self, rid: int, remove: bool = True) -> dict:
+        """Everything needed to continue request `rid` later or elsewhere: its prompt and generated tokens, its
+        budget and its recurrent state, the slot's [L, K, H, d, d, 2] block of the pool, as host tensors (the
+        state is what the reference carries between `forward(..., states=)` calls, v11/model.py:785-841).  Only
+        a sequence that has finished its prefill and is not done can be exported; `remove=True` frees the slot."""
+        req = next((r for r in self.sched.live.values() if r.rid == rid), None)
+        if req is None or req.prefilling or req.done:
+            raise KeyError(f"request {rid} is not a live, prefilled, unfinished sequence")
+        torch.cuda.current_stream().synchronize()
+        blob = {"prompt": list(req.prompt), "generated": list(req.generated), "max_new_tokens": req.max_new_tokens,
+                "state": self.pool[req.slot].cpu(), "state_dtype": str(self.state_dtype).replace("torch.", ""),
+                "shape": tuple(self.pool.shape[1:])}
+        if remove:
+            del self.sched.live[req.slot]
+            self.sched.free.append(req.slot)
+        return blob
+
+    def import_session(self, blob: dict, max_new_tokens: Optional[int] = None) -> int:
+        """Continue an exported sequence in a free slot of this engine (same model shape); returns its new request
+        id.  The state is copied into the pool (converted to the pool's dtype), the token history into the
+        sampler's, and the sequence joins the next decode step."""
+        if tuple(blob["shape"]) != tuple(self.pool.shape[1:]):
+            raise ValueError(f"session state {tuple(blob['shape'])} does not fit this pool {tuple(self.pool.shape[1:])}")
+        if not self.sched.free:
+            raise RuntimeError("no free slot for the imported session")
+        slot = self.sched.free.popleft()
+        rid = self.sched._next_id
+        self.sched._next_id += 1
+        req = Request(rid, list(blob["prompt"]), int(max_new_tokens or blob["max_new_tokens"]), list(blob["generated"]), slot,
+                      len(blob["prompt"]))
+        self._ensure_rope(req.position + 1)
+        self.pool[slot].copy_(blob["state"].to(self.device, self.pool.dtype))
+        if self.sampling is not None:
+            toks = torch.as_tensor(req.prompt + req.generated, dtype=torch.long)
+            self._hist[slot, :toks.numel()] = toks.to(self.device)
+            self._hist_len[slot] = toks.numel()
+        self.sched.live[slot] = req
+        return rid
 
     def step(self) -> int:
         """Admit + prefill waiting sequences, then advance every live sequence by one token."""

@@ -48,3 +48,73 @@ def test_batcher_equals_sequential_generate(golden_dir, graph):
         alone = net.generate(p[None].to(DEV), max_new_tokens=6, temperature=0.0)[0, len(p):].tolist()
         mism += int(alone != out[rid])
     assert mism == 0
+
+
+@pytest.mark.parametrize("graph,fused", [(False, True), (True, True), (False, False)])
+def test_sampling_engine_with_top_k_one_equals_greedy(golden_dir, graph, fused):
+    """The sampling kernel inside the step (history on the device, appended by the kernel): with top_k = 1 only the
+    arg-max survives the filter, so the sampled tokens must equal greedy decoding whatever the random numbers."""
+    g, net = _load(golden_dir, "k3")
+    V = net.config.vocab_size
+    gen = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, V, (int(n),), generator=gen).tolist() for n in (9, 30, 4, 55, 18)]
+    greedy = ContinuousBatcher(net, n_slots=3, fused=fused)
+    want = [greedy.submit(p, 7) for p in prompts]
+    want_out = greedy.run()
+    eng = ContinuousBatcher(net, n_slots=3, cuda_graph=graph, fused=fused,
+                            sampling=dict(temperature=0.7, top_k=1, top_p=0.9, repetition_penalty=1.0))
+    rids = [eng.submit(p, 7) for p in prompts]
+    out = eng.run()
+    assert [out[r] for r in rids] == [want_out[r] for r in want]
+    # the histories on the device hold prompt + generated tokens of the sequences that used each slot last
+    lens = eng._hist_len.cpu().tolist()
+    assert all(0 < n <= 55 + 7 for n in lens)
+
+
+def test_sampling_engine_is_reproducible(golden_dir):
+    g, net = _load(golden_dir, "k3")
+    V = net.config.vocab_size
+    prompts = [[5, 6, 7, 8] * 6, list(range(10, 40))]
+
+    def run(seed):
+        torch.manual_seed(seed)
+        eng = ContinuousBatcher(net, n_slots=2, sampling=dict(temperature=1.0, top_k=0, top_p=0.95, repetition_penalty=1.3))
+        rids = [eng.submit(p, 24) for p in prompts]
+        out = eng.run()
+        hist, lens = eng._hist.cpu(), eng._hist_len.cpu().tolist()
+        for slot, n_ in enumerate(lens):          # each slot's device history = prompt + generated of its sequence
+            assert any(hist[slot, :n_].tolist() == p + out[r] for p, r in zip(prompts, rids))
+        return [out[r] for r in rids]
+
+    a, b, c = run(1), run(1), run(2)
+    assert a == b and a != c
+    assert all(0 <= t < V for seq in a for t in seq)
+
+
+def test_session_export_import_continues_exactly(golden_dir):
+    """A live sequence taken out of one engine (state block of its slot + tokens) and put into another continues
+    with the tokens it would have produced where it was."""
+    g, net = _load(golden_dir, "k3")
+    V = net.config.vocab_size
+    gen = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, V, (int(n),), generator=gen).tolist() for n in (21, 8, 40)]
+    ref_eng = ContinuousBatcher(net, n_slots=3)
+    ref_ids = [ref_eng.submit(p, 12) for p in prompts]
+    ref = ref_eng.run()
+    a = ContinuousBatcher(net, n_slots=3)
+    rids = [a.submit(p, 12) for p in prompts]
+    for _ in range(5):
+        a.step()
+    blob = a.export_session(rids[1])
+    assert blob["state"].device.type == "cpu" and len(blob["generated"]) == 5
+    assert len(a.sched.free) == 1
+    with pytest.raises(KeyError):
+        a.export_session(rids[1])
+    b = ContinuousBatcher(net, n_slots=2, cuda_graph=True)
+    other = b.submit(prompts[2], 3)
+    new_rid = b.import_session(blob)
+    out_b = b.run()
+    out_a = a.run()
+    assert out_b[new_rid] == ref[ref_ids[1]]
+    assert out_b[other] == ref[ref_ids[2]][:3]
+    assert out_a[rids[0]] == ref[ref_ids[0]] and out_a[rids[2]] == ref[ref_ids[2]] and rids[1] not in out_a
