@@ -432,6 +432,8 @@ def main():
                 secondary["decode_" + key] = {k_: cd[key].get(k_) for k_ in (
                     "decode_tokens_per_s", "steady_decode_tokens_per_s", "decode_step_ms", "frac_of_hbm_peak",
                     "generated_tokens", "prompt_tokens", "seconds", "config")}
+        if "sampled_decode" in cd:
+            secondary["sampled_decode_config5_K3"] = cd["sampled_decode"]
         secondary["decode_state_kernel_frac_of_hbm_peak"] = {
             "bf16_state": extra.get("decode_step_bf16_state", {}).get("frac_of_hbm_peak"),
             "f32_state": extra.get("decode_step_f32_state", {}).get("frac_of_hbm_peak")}
@@ -824,6 +826,55 @@ def _steady_decode_step(eng, n_slots, dev, peaks):
             "frac_of_hbm_peak": (state_bytes + weight_bytes) / ms / 1e6 / peaks["hbm"]}
 
 
+def sampled_decode(dev, peaks, net, cfg, prompts, n_slots):
+    """Decode with the sampling kernel inside the captured step (temperature 0.8, top-k 50, top-p 0.9, repetition
+    penalty 1.1 over the whole sequence): the step with every slot busy, and the kernel alone on [256, 50261]
+    float32 logits beside the same filter written with torch operators (sort, cumsum, multinomial), which is what
+    the reference's generate runs per token (v11/model.py:1221-1244)."""
+    from qllm2_b200 import ops
+    from qllm2_b200.serving import ContinuousBatcher
+    samp = dict(temperature=0.8, top_k=50, top_p=0.9, repetition_penalty=1.1)
+    eng = ContinuousBatcher(net, n_slots=n_slots, max_prefill_tokens=1 << 16, cuda_graph=True, fused=True, sampling=samp)
+    for p_ in prompts[:n_slots]:
+        eng.submit(p_[:256].tolist(), 16)
+    eng.warmup()
+    for _ in range(4):
+        eng.step()
+    r = _steady_decode_step(eng, n_slots, dev, peaks)
+    out = {"sampling": samp, "decode_step_ms": r["decode_step_ms"], "steady_decode_tokens_per_s": r["steady_decode_tokens_per_s"]}
+    del eng
+    V, n = cfg.vocab_size, n_slots
+    logits = torch.randn(n, V, device=dev) * 3
+    hist = torch.randint(0, V, (n, 1024), device=dev)
+
+    def kernel():
+        return ops.sample_logits(logits, history=hist, **samp)
+
+    def torch_block():
+        nl = logits / samp["temperature"]
+        sc = torch.gather(nl, 1, hist)
+        nl.scatter_(1, hist, torch.where(sc > 0, sc / samp["repetition_penalty"], sc * samp["repetition_penalty"]))
+        kth = nl.topk(samp["top_k"]).values[:, -1:]
+        nl[nl < kth] = float("-inf")
+        sl, si = nl.sort(descending=True)
+        pr = sl.softmax(dim=-1)
+        sl[(pr.cumsum(dim=-1) - pr) >= samp["top_p"]] = float("-inf")
+        return torch.multinomial(sl.scatter(1, si, sl).softmax(dim=-1), 1)
+
+    for name, fn in (("kernel_ms", kernel), ("torch_operators_ms", torch_block)):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        out[name] = e0.elapsed_time(e1) / 10
+    out["kernel_config"] = f"{n} rows x {V} float32 logits, 1024-token histories; includes torch.rand for the uniforms"
+    return out
+
+
 def continuous_decode(dev, peaks, n_seq=2048, n_slots=256, new_tokens=256, max_prompt=4096):
     """Continuous-batching greedy decode through the 12-block model of config 5 at its stated size: 2048 prompts
     of 32..4096 uniformly random ids, 256 state slots, 256 new tokens per sequence, a new sequence joining whenever
@@ -863,6 +914,7 @@ def continuous_decode(dev, peaks, n_seq=2048, n_slots=256, new_tokens=256, max_p
         _lib.raise_on_device_error("continuous decode")
         del eng
         if n_states == 3:
+            out["sampled_decode"] = sampled_decode(dev, peaks, net, cfg, prompts, n_slots)
             small = prompts[:512]
             for mode, kw in (("fused", dict(cuda_graph=False, fused=True)), ("modules", dict(cuda_graph=False, fused=False)),
                              ("fused_graph", dict(cuda_graph=True, fused=True))):

@@ -7,9 +7,11 @@
 //   top-p : in descending order, drop a token when the probability mass BEFORE it is >= top_p
 //   draw from softmax of what is left
 // The row lives in shared memory (V <= ~56k floats) or in a caller workspace; the k-th largest value and the
-// nucleus threshold are found by radix selection over order-preserving integer keys (4 passes of 8 bits, counts
-// for top-k, probability mass for top-p); the draw is the inverse CDF in vocabulary order of a uniform number the
-// caller supplies.  Tokens that tie with the nucleus threshold are all kept (a sort would keep an arbitrary
+// nucleus threshold are found without sorting: the k-th largest value by radix selection over order-preserving
+// integer keys (4 passes of 8 bits over count histograms), the nucleus threshold by a 4-way search over the bit
+// patterns of the unnormalised probabilities (each probe a deterministic block reduction); the draw is the inverse
+// CDF in vocabulary order of a uniform number the caller supplies.  Nothing depends on the order of atomics, so the
+// same inputs give the same token on every run.  Tokens that tie with the nucleus threshold are all kept (a sort would keep an arbitrary
 // subset of them).
 #include "common.cuh"
 
@@ -17,7 +19,8 @@ namespace qpam {
 namespace {
 
 constexpr int SAMPLE_THREADS = 1024;
-constexpr int SAMPLE_SMEM_EXTRA = 4096;  // histograms, scan scratch, scalars
+constexpr int SAMPLE_SMEM_EXTRA = 12288;  // histograms, scan scratch, scalars, compact list of the top-k survivors
+constexpr int SAMPLE_COMPACT = 1024;       // survivors of top-k that the later stages handle one per thread
 
 struct SampleParams {
   const void* logits;
@@ -39,27 +42,12 @@ __device__ __forceinline__ uint32_t order_key(float x) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-// Histogram updates of a whole warp (every lane calls; bin < 0 = this lane adds nothing).  Lanes that hit the same
+// Histogram update of a whole warp (every lane calls; bin < 0 = this lane adds nothing).  Lanes that hit the same
 // bin are combined before the shared-memory atomic, so a row whose keys share their leading bits (the usual case
 // at the first radix level) does not serialise 32 ways on one address.
 __device__ __forceinline__ void warp_hist_count(uint32_t* hist, int bin) {
   const unsigned peers = __match_any_sync(0xffffffffu, bin);
   if (bin >= 0 && (threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist[bin], (uint32_t)__popc(peers));
-}
-__device__ __forceinline__ void warp_hist_mass(float* hist, int bin, float val) {
-  const unsigned peers = __match_any_sync(0xffffffffu, bin);
-  const int lane = threadIdx.x & 31;
-  const bool big = bin >= 0 && __popc(peers) >= 8;
-  unsigned leaders = __ballot_sync(0xffffffffu, big && lane == __ffs(peers) - 1);   // at most four groups of >= 8
-  while (leaders) {
-    const int ld = __ffs(leaders) - 1;
-    leaders &= leaders - 1;
-    const int b = __shfl_sync(0xffffffffu, bin, ld);
-    float s = (bin == b) ? val : 0.f;
-    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == ld) atomicAdd(&hist[b], s);
-  }
-  if (bin >= 0 && !big) atomicAdd(&hist[bin], val);
 }
 
 struct Scratch {
@@ -69,7 +57,6 @@ struct Scratch {
   float bcast_f[4];
   uint32_t prefix;
   uint32_t remaining;
-  float mass_above;
   int chosen;
   int last_kept;
 };
@@ -165,7 +152,11 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample_rows(SampleParams p) 
       for (int base = 0; base < V; base += SAMPLE_THREADS) {
         const int i = base + tid;
         const uint32_t key = i < V ? order_key(w[i]) : 0u;
-        warp_hist_count(sc->count, (i < V && (key & himask) == prefix) ? (int)((key >> shift) & 255u) : -1);
+        const bool in = i < V && (key & himask) == prefix;
+        if (__ballot_sync(0xffffffffu, in) == 0u) continue;     // below the first level few warps hold a candidate
+        // first level: few distinct leading bytes, lanes are combined; deeper levels spread over the bins
+        if (shift == 24) warp_hist_count(sc->count, in ? (int)((key >> shift) & 255u) : -1);
+        else if (in) atomicAdd(&sc->count[(key >> shift) & 255u], 1u);
       }
       __syncthreads();
       if (tid < 32) {  // warp 0: lane l owns bins 255-8l .. 248-8l (descending order of keys)
@@ -198,85 +189,107 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample_rows(SampleParams p) 
     key_k = sc->prefix;
   }
 
-  // ---- softmax statistics of what top-k left
+  // ---- what top-k left, as unnormalised probabilities e = exp(x - max) in place of the logits (0 = dropped).
+  // e is monotone in x, and for non-negative floats the bit pattern orders like the value.
   float mx = -INFINITY;
   for (int i = tid; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, w[i]);
   mx = block_max(mx, sc);
   float z = 0.f;
   for (int i = tid; i < V; i += SAMPLE_THREADS) {
     const float x = w[i];
-    if (order_key(x) >= key_k) z += __expf(x - mx);
+    const float e = order_key(x) >= key_k ? __expf(x - mx) : 0.f;
+    w[i] = e;
+    z += e;
   }
   z = block_sum(z, sc);
 
-  // ---- top-p: the key at which the descending cumulative mass first reaches top_p * z
-  uint32_t key_p = 0;
-  if (p.top_p > 0.f && p.top_p < 1.f) {
-    const float target = p.top_p * z;
-    __syncthreads();
-    if (tid == 0) { sc->prefix = 0; sc->mass_above = 0.f; }
-    for (int shift = 24; shift >= 0; shift -= 8) {
-      if (tid < 256) sc->mass[tid] = 0.f;
-      __syncthreads();
-      const uint32_t prefix = sc->prefix;
-      const uint32_t himask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-      for (int base = 0; base < V; base += SAMPLE_THREADS) {
-        const int i = base + tid;
-        const float x = i < V ? w[i] : 0.f;
-        const uint32_t key = order_key(x);
-        const bool in = i < V && key >= key_k && (key & himask) == prefix;
-        warp_hist_mass(sc->mass, in ? (int)((key >> shift) & 255u) : -1, __expf(x - mx));
-      }
-      __syncthreads();
-      if (tid < 32) {  // warp 0: lane l owns bins 255-8l .. 248-8l
-        const int top = 255 - 8 * tid;
-        float mine = 0.f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) mine += sc->mass[top - j];
-        float inc = mine;
-        for (int o = 1; o < 32; o <<= 1) {
-          const float t = __shfl_up_sync(0xffffffffu, inc, o);
-          if (tid >= o) inc += t;
-        }
-        const float before = sc->mass_above + (inc - mine);
-        const unsigned hit = __ballot_sync(0xffffffffu, mine > 0.f && before + mine >= target);
-        const unsigned occupied = __ballot_sync(0xffffffffu, mine > 0.f);
-        // rounding can leave the whole sum just below the target: the lowest occupied bin closes the nucleus then
-        const int owner = hit ? __ffs(hit) - 1 : (occupied ? 31 - __clz(occupied) : 31);
-        if (tid == owner) {
-          float cum = before;
-          int b = top, found = -1, lowest = top - 7;
-          for (; b > top - 8; --b) {
-            const float m = sc->mass[b];
-            if (m > 0.f) {
-              lowest = b;
-              if (cum + m >= target) { found = b; break; }
-              cum += m;
-            }
-          }
-          if (found < 0) {
-            found = lowest;
-            cum -= sc->mass[found];
-          }
-          sc->mass_above = cum;
-          sc->prefix = prefix | ((uint32_t)found << shift);
+  // ---- a short list of survivors (top-k with a small k): the nucleus search and the draw then touch one element
+  // per thread instead of the whole row.  The list keeps vocabulary order.
+  float* cval = reinterpret_cast<float*>(smem_raw + sizeof(Scratch));
+  int* cidx = reinterpret_cast<int*>(cval + SAMPLE_COMPACT);
+  const float* ev = w;
+  int n_el = V;
+  if (p.top_k > 0 && p.top_k <= SAMPLE_COMPACT / 2 && p.top_k < V) {
+    const int per_v = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int a0 = min(V, tid * per_v), a1 = min(V, a0 + per_v);
+    int c = 0;
+    for (int i = a0; i < a1; ++i) c += w[i] > 0.f ? 1 : 0;
+    float tot;
+    const int at = (int)block_exclusive_scan((float)c, sc, &tot);      // counts <= V: exact in float
+    if ((int)tot <= SAMPLE_COMPACT) {                                    // block-uniform
+      int o = at;
+      for (int i = a0; i < a1; ++i) {
+        const float e = w[i];
+        if (e > 0.f) {
+          cval[o] = e;
+          cidx[o] = i;
+          ++o;
         }
       }
+      ev = cval;
+      n_el = (int)tot;
       __syncthreads();
     }
-    key_p = sc->prefix;
   }
-  const uint32_t key_min = key_k > key_p ? key_k : key_p;
+  const bool compact = ev != w;
+
+  // ---- top-p: the largest threshold t (as a bit pattern) with mass{e >= t} >= top_p * z, i.e. the value at which
+  // the descending cumulative mass first reaches the target; found by a 4-way search over the bit patterns of
+  // (0, 1].  Every probe is one pass with a fixed reduction tree: no atomics, the same result on every run.
+  uint32_t bits_min = 1u;                       // keeps every e > 0
+  if (p.top_p > 0.f && p.top_p < 1.f) {
+    const float target = p.top_p * z;
+    uint32_t lo = 1u, hi = 0x3f800001u;         // mass{>= lo} >= target > mass{>= hi}
+    while (hi - lo > 1u) {
+      const uint32_t step = (hi - lo) >> 2;
+      const uint32_t m2 = lo + ((hi - lo) >> 1);
+      const uint32_t m1 = step ? lo + step : m2, m3 = step ? m2 + step : m2;
+      float f1 = 0.f, f2 = 0.f, f3 = 0.f;
+      for (int i = tid; i < n_el; i += SAMPLE_THREADS) {
+        const float e = ev[i];
+        const uint32_t eb = __float_as_uint(e);
+        f1 += eb >= m1 ? e : 0.f;
+        f2 += eb >= m2 ? e : 0.f;
+        f3 += eb >= m3 ? e : 0.f;
+      }
+      // one reduction for the three sums
+      for (int o = 16; o; o >>= 1) {
+        f1 += __shfl_xor_sync(0xffffffffu, f1, o);
+        f2 += __shfl_xor_sync(0xffffffffu, f2, o);
+        f3 += __shfl_xor_sync(0xffffffffu, f3, o);
+      }
+      __syncthreads();
+      if ((tid & 31) == 0) {
+        sc->mass[tid >> 5] = f1;
+        sc->mass[32 + (tid >> 5)] = f2;
+        sc->mass[64 + (tid >> 5)] = f3;
+      }
+      __syncthreads();
+      f1 = sc->mass[tid & 31];
+      f2 = sc->mass[32 + (tid & 31)];
+      f3 = sc->mass[64 + (tid & 31)];
+      for (int o = 16; o; o >>= 1) {
+        f1 += __shfl_xor_sync(0xffffffffu, f1, o);
+        f2 += __shfl_xor_sync(0xffffffffu, f2, o);
+        f3 += __shfl_xor_sync(0xffffffffu, f3, o);
+      }
+      if (f3 >= target && m3 > m2) lo = m3;
+      else if (f2 >= target) { lo = m2; if (m3 > m2) hi = m3; }
+      else if (f1 >= target && m1 < m2) { lo = m1; hi = m2; }
+      else hi = (m1 < m2) ? m1 : m2;
+    }
+    bits_min = lo;
+  }
 
   // ---- the draw: inverse CDF in vocabulary order over the kept tokens
-  const int per = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-  const int i0 = min(V, tid * per), i1 = min(V, i0 + per);
+  const int per = (n_el + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+  const int i0 = min(n_el, tid * per), i1 = min(n_el, i0 + per);
   float mine = 0.f;
   int last = -1, cnt = 0;
   for (int i = i0; i < i1; ++i) {
-    const float x = w[i];
-    if (order_key(x) >= key_min) {
-      mine += __expf(x - mx);
+    const float e = ev[i];
+    if (__float_as_uint(e) >= bits_min) {
+      mine += e;
       last = i;
       ++cnt;
     }
@@ -291,9 +304,9 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample_rows(SampleParams p) 
     float cum = before;
     int pick = last;
     for (int i = i0; i < i1; ++i) {
-      const float x = w[i];
-      if (order_key(x) >= key_min) {
-        cum += __expf(x - mx);
+      const float e = ev[i];
+      if (__float_as_uint(e) >= bits_min) {
+        cum += e;
         if (cum > target) { pick = i; break; }
       }
     }
@@ -301,7 +314,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample_rows(SampleParams p) 
   }
   __syncthreads();
   if (tid == 0) {
-    const int pick = sc->chosen >= 0 ? sc->chosen : sc->last_kept;
+    int pick = sc->chosen >= 0 ? sc->chosen : sc->last_kept;
+    if (compact) pick = cidx[pick];
     p.next_ids[row] = pick;
     if (p.stats) {
       float* s = p.stats + 4 * (size_t)row;
@@ -360,7 +374,7 @@ extern "C" int qpam_sample_logits(const void* logits, int32_t io_dtype, int32_t 
     QPAM_REQUIRE(workspace && workspace_bytes >= need, "sample: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     p.work = reinterpret_cast<float*>(workspace);
   }
-  static_assert(sizeof(Scratch) <= SAMPLE_SMEM_EXTRA, "scratch does not fit");
+  static_assert(sizeof(Scratch) + SAMPLE_COMPACT * 8 <= SAMPLE_SMEM_EXTRA, "scratch does not fit");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (io_dtype == QPAM_F32) {
     QPAM_CUDA(cudaFuncSetAttribute(k_sample_rows<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
