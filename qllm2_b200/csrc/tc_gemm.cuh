@@ -53,24 +53,30 @@ struct GemmParams {
   int32_t beta;             // 1: accumulate into c
 };
 
-template <int BN>
+// MT = row tiles of one CTA.  MT == 1: one 128 x BN tile at a time, two accumulator buffers, so the epilogue of a
+// tile overlaps the MMAs of the next (short-K products with heavy epilogues).  MT == 2: two 128-row tiles share
+// every B block (a 256 x BN tile per CTA: a third less operand traffic from L2 per MAC, half the barrier
+// hand-offs), both accumulators live at once and the epilogue runs at the end (long-K products).
+template <int BN, int MT = 1>
 struct Cfg {
-  static constexpr int A_BYTES = BM * BK * 2;                // 16 KB
+  static constexpr int A_BYTES = MT * BM * BK * 2;           // 16 KB per row tile
   static constexpr int B_BYTES = BN * BK * 2;                // 16 / 32 KB
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers
+  static constexpr int STAGES = (MT == 2) ? 3 : (BN == 256) ? 4 : 6;
+  static constexpr int NBUF = (MT == 2) ? 1 : 2;             // accumulator sets in flight
+  static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers, or two row tiles
   static constexpr int EPI_STAGE_BYTES = 4096;               // per epilogue warp: 32 rows x 64 bf16, swizzled
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   // EPI_PROBS and EPI_STORE launches add the staging blocks (EPI_STATS keeps the bytes for L1)
   static constexpr size_t SMEM_BYTES_STAGED = SMEM_BYTES + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
 };
 
-template <int BN, int EPI, bool A_MN, bool B_MN>
+template <int BN, int EPI, bool A_MN, bool B_MN, int MT = 1>
 __global__ void __launch_bounds__(NTHREADS, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using namespace umma;
-  using C = Cfg<BN>;
+  using C = Cfg<BN, MT>;
+  static_assert(MT == 1 || EPI == EPI_STORE, "two row tiles per CTA: plain stores only");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
@@ -125,12 +131,17 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             unsigned char* sa = smem + (size_t)stage * C::STAGE_BYTES;
             unsigned char* sb = sa + C::A_BYTES;
             mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
-            if (!A_MN) {
-              tma_load_2d(sa, &tmA, &full[stage], kb * BK, m_tile * BM);
-            } else {
 #pragma unroll
-              for (int j = 0; j < BM / 64; ++j)
-                tma_load_2d(sa + j * 8192, &tmA, &full[stage], m_tile * BM + j * 64, kb * BK);
+            for (int mt = 0; mt < MT; ++mt) {
+              unsigned char* sam = sa + mt * (BM * BK * 2);
+              const int m0 = (m_tile * MT + mt) * BM;       // rows past M arrive as zeros
+              if (!A_MN) {
+                tma_load_2d(sam, &tmA, &full[stage], kb * BK, m0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BM / 64; ++j)
+                  tma_load_2d(sam + j * 8192, &tmA, &full[stage], m0 + j * 64, kb * BK);
+              }
             }
             if (!B_MN) {
               tma_load_2d(sb, &tmB, &full[stage], kb * BK, n * BN);
@@ -152,8 +163,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         bool ok = true;
         int it = 0;
         for (int n = n_begin; n < n_end && ok; ++n, ++it) {
-          const int buf = it & 1;
-          const uint32_t bphase = (it >> 1) & 1;
+          const int buf = it % C::NBUF;
+          const uint32_t bphase = (it / C::NBUF) & 1;
           if (!mbar_wait(&tempty[buf], bphase ^ 1, 102)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
@@ -164,9 +175,13 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             const uint32_t sb = sa + C::A_BYTES;
 #pragma unroll
             for (int kk = 0; kk < BK / 16; ++kk) {
-              const uint64_t ad = A_MN ? smem_desc_sw128(sa + kk * 2048, 8192, 1024) : smem_desc_sw128(sa + kk * 32, 16, 1024);
               const uint64_t bd = B_MN ? smem_desc_sw128(sb + kk * 2048, 8192, 1024) : smem_desc_sw128(sb + kk * 32, 16, 1024);
-              mma_bf16(d_tmem, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
+#pragma unroll
+              for (int mt = 0; mt < MT; ++mt) {
+                const uint32_t sam = sa + mt * (BM * BK * 2);
+                const uint64_t ad = A_MN ? smem_desc_sw128(sam + kk * 2048, 8192, 1024) : smem_desc_sw128(sam + kk * 32, 16, 1024);
+                mma_bf16(d_tmem + mt * BN, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
+              }
             }
             mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
             if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -203,8 +218,8 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
       bool ok = true;
       int it = 0;
       for (int n = n_begin; n < n_end && ok; ++n, ++it) {
-        const int buf = it & 1;
-        const uint32_t bphase = (it >> 1) & 1;
+        const int buf = it % C::NBUF;
+        const uint32_t bphase = (it / C::NBUF) & 1;
         if (!mbar_wait(&tfull[buf], bphase, 104)) { ok = false; break; }
         tc_fence_after();
         const int64_t col0 = (int64_t)n * BN;
@@ -252,9 +267,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           }
         } else {
 #pragma unroll 1
-          for (int cc = half * CC_HALF; cc < (half + 1) * CC_HALF; ++cc) {
+          for (int ccm = half * CC_HALF; ccm < half * CC_HALF + MT * CC_HALF; ++ccm) {
+            const int mt = (ccm - half * CC_HALF) / CC_HALF;          // row tile of this CTA (EPI_STORE only)
+            const int cc = ccm - mt * CC_HALF;
             float v[32];
-            tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
+            tmem_ld32(tmem_base + lane_addr + buf * BN + mt * BN + cc * 32, v);
             const int64_t cbase = col0 + cc * 32;
             if (EPI == EPI_STATS) {
               if (cbase >= p.N) continue;
@@ -282,7 +299,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               if (cbase >= p.N) continue;
               unsigned char* stg =
                   smem + (size_t)C::STAGES * C::STAGE_BYTES + 256 + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
-              const int64_t row0 = (int64_t)m_tile * BM + quarter * 32;
+              const int64_t row0 = ((int64_t)m_tile * MT + mt) * BM + quarter * 32;
 #pragma unroll
               for (int g4 = 0; g4 < 8; ++g4)
                 *reinterpret_cast<float4*>(stg + lane * 128 + ((g4 ^ (lane & 7)) << 4)) =

@@ -44,7 +44,7 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   const int64_t kb_total = (a->V + tc::BK - 1) / tc::BK;
   int64_t ks = 1, ks_cost = -1;
   for (int64_t s = 1; s <= 8 && s <= kb_total; ++s) {
-    const int64_t ctas = f_tiles * (rows / tc::BM) * s;
+    const int64_t ctas = f_tiles * ((rows + 2 * tc::BM - 1) / (2 * tc::BM)) * s;     // CTAs of two row tiles
     const int64_t cost = ((ctas + 147) / 148) * ((kb_total + s - 1) / s + 8);   // + 8: prologue and epilogue of a CTA
     if (ks_cost < 0 || cost < ks_cost) { ks_cost = cost; ks = s; }
   }
@@ -130,13 +130,15 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
   const int F = a->F;
   const int64_t V = a->V;
   auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false>;
-  auto k_dh = tc::k_tc_gemm<256, tc::EPI_STORE, false, true>;
-  auto k_dw = tc::k_tc_gemm<256, tc::EPI_STORE, true, true>;
+  // dH and dW run long K loops into few output tiles: two row tiles per CTA share every B block
+  constexpr int MT = 2;
+  auto k_dh = tc::k_tc_gemm<256, tc::EPI_STORE, false, true, MT>;
+  auto k_dw = tc::k_tc_gemm<256, tc::EPI_STORE, true, true, MT>;
   int rc = opt_in_smem(k_probs, tc::Cfg<256>::SMEM_BYTES_STAGED);
   if (rc) return rc;
-  rc = opt_in_smem(k_dh, tc::Cfg<256>::SMEM_BYTES_STAGED);
+  rc = opt_in_smem(k_dh, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
   if (rc) return rc;
-  rc = opt_in_smem(k_dw, tc::Cfg<256>::SMEM_BYTES_STAGED);
+  rc = opt_in_smem(k_dw, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
   if (rc) return rc;
   CUtensorMap tmWk, tmWmn;
   rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 256);   // K-major B of the logits GEMM
@@ -175,7 +177,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     const int ks = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
     g.M = rows; g.N = F;
     g.c = b.dh_part; g.ldc = F; g.beta = 0;
-    k_dh<<<dim3(f_tiles, row_tiles, ks), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED, st>>>(tmPk, tmWmn, g);
+    k_dh<<<dim3(f_tiles, (row_tiles + MT - 1) / MT, ks), tc::NTHREADS, tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPk, tmWmn, g);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dH>");
     k_reduce_splits_bf16<<<592, 256, 0, st>>>(b.dh_part, reinterpret_cast<__nv_bfloat16*>(dh) + r0 * F, rows * F, ks,
                                              rows * F);
@@ -192,9 +194,8 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     w.kb_total = (int32_t)((rows + tc::BK - 1) / tc::BK); w.kb_per_split = w.kb_total;
     w.M = V; w.N = F;
     w.c = b.dwacc + (size_t)(chunk_idx % pl.dw_bufs) * V * F; w.ldc = F; w.beta = chunk_idx >= pl.dw_bufs ? 1 : 0;
-    k_dw<<<dim3(f_tiles, (unsigned)((V + tc::BM - 1) / tc::BM), 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED,
-           st>>>(
-        tmPmn, tmHmn, w);
+    k_dw<<<dim3(f_tiles, (unsigned)((V + MT * tc::BM - 1) / (MT * tc::BM)), 1), tc::NTHREADS,
+           tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPmn, tmHmn, w);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dW>");
     ++chunk_idx;
   }
