@@ -25,6 +25,13 @@ constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 
 enum Epi { EPI_STATS = 0, EPI_PROBS = 1, EPI_STORE = 2 };
 
+constexpr float LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct GemmParams {
   // tile walk
   int32_t n_tiles;          // N tiles in total
@@ -57,12 +64,15 @@ struct GemmParams {
 // tile overlaps the MMAs of the next (short-K products with heavy epilogues).  MT == 2: two 128-row tiles share
 // every B block (a 256 x BN tile per CTA: a third less operand traffic from L2 per MAC, half the barrier
 // hand-offs), both accumulators live at once and the epilogue runs at the end (long-K products).
-template <int BN, int MT = 1>
+// PAIR: two CTAs of a cluster (neighbouring SMs) work on one 256-row tile with cta_group::2 MMAs: each CTA loads
+// its own 128 rows of A and only HALF of the B tile, so the operand traffic per MAC drops by a third while both
+// accumulator buffers stay (short-K products with heavy epilogues).
+template <int BN, int MT = 1, bool PAIR = false>
 struct Cfg {
   static constexpr int A_BYTES = MT * BM * BK * 2;           // 16 KB per row tile
-  static constexpr int B_BYTES = BN * BK * 2;                // 16 / 32 KB
+  static constexpr int B_BYTES = (PAIR ? BN / 2 : BN) * BK * 2;   // this CTA's share of the B tile
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (MT == 2) ? 3 : (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = PAIR ? 6 : (MT == 2) ? 3 : (BN == 256) ? 4 : 6;
   static constexpr int NBUF = (MT == 2) ? 1 : 2;             // accumulator sets in flight
   static constexpr int TMEM_COLS = 2 * BN;                   // two accumulator buffers, or two row tiles
   static constexpr int EPI_STAGE_BYTES = 4096;               // per epilogue warp: 32 rows x 64 bf16, swizzled
@@ -71,12 +81,16 @@ struct Cfg {
   static constexpr size_t SMEM_BYTES_STAGED = SMEM_BYTES + (size_t)EPI_WARPS * EPI_STAGE_BYTES;
 };
 
-template <int BN, int EPI, bool A_MN, bool B_MN, int MT = 1>
+template <int BN, int EPI, bool A_MN, bool B_MN, int MT = 1, bool PAIR = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
 k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
   using namespace umma;
-  using C = Cfg<BN, MT>;
+  using C = Cfg<BN, MT, PAIR>;
   static_assert(MT == 1 || EPI == EPI_STORE, "two row tiles per CTA: plain stores only");
+  static_assert(!PAIR || (MT == 1 && !A_MN && !B_MN), "CTA pairs: K-major operands, one row tile per CTA");
+  // PAIR: launched as clusters of two CTAs along the row-tile axis; tmB's box holds BN / 2 rows
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0u;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
@@ -104,13 +118,17 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], EPI_WARPS);  // one arrival per epilogue warp
+      mbar_init(&tempty[b], (PAIR ? 2 : 1) * EPI_WARPS);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     fence_barrier_init();
   }
-  if (warp == 1) tmem_alloc<C::TMEM_COLS>(tmem_slot);
+  if (warp == 1) {
+    if (PAIR) tmem_alloc_pair<C::TMEM_COLS>(tmem_slot);
+    else tmem_alloc<C::TMEM_COLS>(tmem_slot);
+  }
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // after a failed handshake anywhere on the device, later CTAs do not start new work
@@ -130,6 +148,15 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             if (!mbar_wait(&empty[stage], phase ^ 1, 101)) { ok = false; break; }
             unsigned char* sa = smem + (size_t)stage * C::STAGE_BYTES;
             unsigned char* sb = sa + C::A_BYTES;
+            if constexpr (PAIR) {
+              // the leader's barrier counts the bytes of both CTAs; each CTA loads its rows of A and its half of B
+              if (leader) mbar_arrive_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
+              const uint32_t fb = cluster_map(&full[stage], 0);
+              tma_load_2d_pair(sa, &tmA, fb, kb * BK, m_tile * BM);
+              tma_load_2d_pair(sb, &tmB, fb, kb * BK, n * BN + (int)crank * (BN / 2));
+              if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+              continue;
+            }
             mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
@@ -155,9 +182,9 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         }
       }
     } else if (warp == 1) {
-      // ------------------------------------------------------------- MMA issuer
-      if (elect_one()) {
-        constexpr uint32_t idesc = idesc_bf16(BM, BN, A_MN, B_MN);
+      // ------------------------------------------------------------- MMA issuer (PAIR: the leader's, for both CTAs)
+      if (leader && elect_one()) {
+        constexpr uint32_t idesc = idesc_bf16(PAIR ? 2 * BM : BM, BN, A_MN, B_MN);
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -180,13 +207,19 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               for (int mt = 0; mt < MT; ++mt) {
                 const uint32_t sam = sa + mt * (BM * BK * 2);
                 const uint64_t ad = A_MN ? smem_desc_sw128(sam + kk * 2048, 8192, 1024) : smem_desc_sw128(sam + kk * 32, 16, 1024);
-                mma_bf16(d_tmem + mt * BN, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
+                if (PAIR) mma_bf16_pair(d_tmem + mt * BN, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
+                else mma_bf16(d_tmem + mt * BN, ad, bd, idesc, (kb > kb_begin) || (kk > 0));
               }
             }
-            mma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if (PAIR) mma_commit_pair(&empty[stage]);
+            else mma_commit(&empty[stage]);
             if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
           }
-          if (ok) mma_commit(&tfull[buf]);
+          if (ok) {
+            if (PAIR) mma_commit_pair(&tfull[buf]);
+            else mma_commit(&tfull[buf]);
+          }
         }
       }
     } else {
@@ -215,6 +248,11 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         lse_r = p.lse[grow];
         sc_r = valid ? (p.grad_scale[0] / p.denom[0]) * (p.mask ? p.mask[grow] : 1.f) : 0.f;
       }
+      // exp(v - lse) * sc = 2^(v log2e - off) with off = lse log2e - log2(sc): two instructions per element.
+      // Rows whose scale is not positive (ignored rows, a negative upstream gradient) multiply instead.
+      const bool sc_pos = sc_r > 0.f;
+      const float off_r = sc_pos ? fmaf(lse_r, LOG2E, -__log2f(sc_r)) : lse_r * LOG2E;
+      const float mul_r = sc_pos ? 1.f : sc_r;
       bool ok = true;
       int it = 0;
       for (int n = n_begin; n < n_end && ok; ++n, ++it) {
@@ -238,21 +276,26 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               float v[32];
               tmem_ld32(tmem_base + lane_addr + buf * BN + g * 64 + hh * 32, v);
               const int64_t dt = tcol - (cb + hh * 32);
-              const int tj = (dt >= 0 && dt < 32) ? (int)dt : -1;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = ex2_fast(fmaf(v[j], LOG2E, -off_r));
+              if (!sc_pos) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] *= mul_r;
+              }
 #pragma unroll
               for (int g8 = 0; g8 < 4; ++g8) {
                 uint4 pk;
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const int j0 = g8 * 8 + 2 * j;
-                  float a = __expf(v[j0] - lse_r);
-                  float b = __expf(v[j0 + 1] - lse_r);
-                  if (j0 == tj) a -= 1.f;
-                  if (j0 + 1 == tj) b -= 1.f;
-                  h2[j] = __floats2bfloat162_rn(a * sc_r, b * sc_r);
-                }
+                for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[g8 * 8 + 2 * j], v[g8 * 8 + 2 * j + 1]);
                 *reinterpret_cast<uint4*>(stg + lane * 128 + (((hh * 4 + g8) ^ (lane & 7)) << 4)) = pk;
+              }
+              if (dt >= 0 && dt < 32) {
+                // the target column lies in this group: (p - 1) * scale there.  The thread patches the one value it
+                // has just staged (its own row), which keeps the 32 values above in registers.
+                __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(
+                    stg + lane * 128 + (((hh * 4 + ((int)dt >> 3)) ^ (lane & 7)) << 4)) + ((int)dt & 7);
+                *e = __float2bfloat16_rn(__bfloat162float(*e) - sc_r);
               }
             }
             __syncwarp();
@@ -276,18 +319,28 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             if (EPI == EPI_STATS) {
               if (cbase >= p.N) continue;
               const int nvalid = (int)min((int64_t)32, p.N - cbase);
-              float cmax = -INFINITY;
-              int ci = 0;
+              if (nvalid < 32) {             // the ragged last group: columns past N can neither win nor add
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nvalid && v[j] > cmax) { cmax = v[j]; ci = j; }
-              if (cmax > best) { best = cmax; bidx = (int)cbase + ci; }
+                for (int j = 0; j < 32; ++j)
+                  if (j >= nvalid) v[j] = -INFINITY;
+              }
+              float cmax = v[0];
+#pragma unroll
+              for (int j = 1; j < 32; ++j) cmax = fmaxf(cmax, v[j]);
+              if (cmax > best) {             // rarer and rarer as the walk goes on: only then is the column looked up
+                best = cmax;
+                int ci = 31;
+#pragma unroll
+                for (int j = 30; j >= 0; --j)
+                  if (v[j] == cmax) ci = j;  // lowest column among equals
+                bidx = (int)cbase + ci;
+              }
               const float m_new = fmaxf(m_run, cmax);
+              const float ml2 = m_new * LOG2E;
               float se = 0.f;
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < nvalid) se += __expf(v[j] - m_new);
-              s_run = s_run * __expf(m_run - m_new) + se;
+              for (int j = 0; j < 32; ++j) se += ex2_fast(fmaf(v[j], LOG2E, -ml2));
+              s_run = s_run * ex2_fast((m_run - m_new) * LOG2E) + se;
               m_run = m_new;
               if (tcol >= cbase && tcol < cbase + 32) {
                 const int tj = (int)(tcol - cbase);
@@ -324,7 +377,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
+        if (lane == 0) {
+          if (PAIR && !leader) mbar_arrive_cluster(cluster_map(&tempty[buf], 0));   // the leader issues the MMAs
+          else mbar_arrive(&tempty[buf]);
+        }
       }
       if (EPI == EPI_STATS) {
         // The two warps of a row fold their running statistics through shared memory.  The ring's first
@@ -345,7 +401,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         }
       }
       if (EPI == EPI_STATS && ok && row_ok && half == 0) {
-        const size_t o = (size_t)blockIdx.x * p.stats_ld + p.row_base + row;
+        const size_t o = (size_t)(p.swap_xy ? blockIdx.y : blockIdx.x) * p.stats_ld + p.row_base + row;   // [split][row]
         p.pm[o] = m_run;
         p.ps[o] = s_run;
         p.pt[o] = tz;
@@ -356,10 +412,12 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   }
   // ------------------------------------------------------------- teardown
   tc_fence_before();
-  __syncthreads();
+  if (PAIR) cluster_sync_all();   // no signal of the peer is still on its way to this CTA's barriers
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<C::TMEM_COLS>(tmem_base);
+    if (PAIR) tmem_dealloc_pair<C::TMEM_COLS>(tmem_base);
+    else tmem_dealloc<C::TMEM_COLS>(tmem_base);
   }
 }
 

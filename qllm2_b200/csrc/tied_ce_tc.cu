@@ -12,6 +12,24 @@ static int opt_in_smem(K kern, size_t bytes) {
   return QPAM_OK;
 }
 
+// Launch a kernel of CTA pairs: clusters of two CTAs along x (pair_axis 0) or y (pair_axis 1).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_pairs(void (*kern)(KArgs...), dim3 grid, int pair_axis, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(tc::NTHREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = pair_axis == 0 ? 2 : 1;
+  at[0].val.clusterDim.y = pair_axis == 1 ? 2 : 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 // ------------------------------------------------------------------ plan
 CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   CETcPlan pl{};
@@ -76,7 +94,7 @@ int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& 
   CUtensorMap tmH, tmW;
   int rc = make_map(&tmH, a->h, a->F, a->N, a->F, tc::BK, tc::BM);
   if (rc) return rc;
-  rc = make_map(&tmW, a->w, a->F, a->V, a->F, tc::BK, 256);
+  rc = make_map(&tmW, a->w, a->F, a->V, a->F, tc::BK, 128);     // a CTA of a pair loads half of a 256-row B tile
   if (rc) return rc;
   tc::GemmParams p{};
   p.n_tiles = pl.n_tiles;
@@ -87,11 +105,14 @@ int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& 
   p.targets = a->targets; p.v_offset = a->v_offset; p.ignore_index = a->ignore_index;
   p.pm = b.pm; p.ps = b.ps; p.pt = b.pt; p.pbest = b.pbest; p.pidx = b.pidx;
   p.stats_ld = a->N; p.row_base = 0;
-  auto kern = tc::k_tc_gemm<256, tc::EPI_STATS, false, false>;
-  rc = opt_in_smem(kern, tc::Cfg<256>::SMEM_BYTES);
+  // CTA pairs (cta_group::2): two row tiles share one 256-column B tile, each CTA loading half of it
+  auto kern = tc::k_tc_gemm<256, tc::EPI_STATS, false, false, 1, true>;
+  using CfgP = tc::Cfg<256, 1, true>;
+  rc = opt_in_smem(kern, CfgP::SMEM_BYTES);
   if (rc) return rc;
   const unsigned row_tiles = (unsigned)((a->N + tc::BM - 1) / tc::BM);
-  kern<<<dim3(pl.nsplit, row_tiles, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES, st>>>(tmH, tmW, p);
+  p.swap_xy = 1;      // blockIdx.x walks the row tiles: the two CTAs of a pair are neighbours in x
+  QPAM_CUDA(launch_pairs(kern, dim3((row_tiles + 1) & ~1u, pl.nsplit, 1), 0, CfgP::SMEM_BYTES, st, tmH, tmW, p));
   QPAM_LAUNCH_CHECK("k_tc_gemm<stats>");
   return QPAM_OK;
 }
@@ -129,19 +150,20 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
                    cudaStream_t dh_ready_stream) {
   const int F = a->F;
   const int64_t V = a->V;
-  auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false>;
+  auto k_probs = tc::k_tc_gemm<256, tc::EPI_PROBS, false, false, 1, true>;      // CTA pairs, as the forward pass
+  using CfgP = tc::Cfg<256, 1, true>;
   // dH and dW run long K loops into few output tiles: two row tiles per CTA share every B block
   constexpr int MT = 2;
   auto k_dh = tc::k_tc_gemm<256, tc::EPI_STORE, false, true, MT>;
   auto k_dw = tc::k_tc_gemm<256, tc::EPI_STORE, true, true, MT>;
-  int rc = opt_in_smem(k_probs, tc::Cfg<256>::SMEM_BYTES_STAGED);
+  int rc = opt_in_smem(k_probs, CfgP::SMEM_BYTES_STAGED);
   if (rc) return rc;
   rc = opt_in_smem(k_dh, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
   if (rc) return rc;
   rc = opt_in_smem(k_dw, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
   if (rc) return rc;
   CUtensorMap tmWk, tmWmn;
-  rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 256);   // K-major B of the logits GEMM
+  rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 128);   // K-major B of the logits GEMM: half a tile per CTA of a pair
   if (rc) return rc;
   rc = make_map(&tmWmn, a->w, F, V, F, 64, 64);        // MN-major B of dH = P W   ([K=V][N=F])
   if (rc) return rc;
@@ -167,7 +189,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
     p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
     p.swap_xy = 1;   // consecutive CTAs take the row tiles of one vocabulary tile: W is read from DRAM once
-    k_probs<<<dim3(row_tiles, n_groups, 1), tc::NTHREADS, tc::Cfg<256>::SMEM_BYTES_STAGED, st>>>(tmHk, tmWk, p);
+    QPAM_CUDA(launch_pairs(k_probs, dim3((row_tiles + 1) & ~1u, n_groups, 1), 0, CfgP::SMEM_BYTES_STAGED, st, tmHk, tmWk, p));
     QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
     // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
     tc::GemmParams g{};
