@@ -342,7 +342,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               for (int j = 0; j < 32; ++j) se += ex2_fast(fmaf(v[j], LOG2E, -ml2));
               s_run = s_run * ex2_fast((m_run - m_new) * LOG2E) + se;
               m_run = m_new;
-              if (tcol >= cbase && tcol < cbase + 32) {
+              if (tcol >= cbase && tcol < cbase + nvalid) {   // a target past N belongs to another vocabulary shard
                 const int tj = (int)(tcol - cbase);
 #pragma unroll
                 for (int j = 0; j < 32; ++j)

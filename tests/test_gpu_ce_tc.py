@@ -95,3 +95,29 @@ def test_odd_shapes_masked_scaled(N, D, V):
     assert abs(float(loss.detach()) - r["loss"]) <= 1e-5 * abs(r["loss"])
     assert_close(h.grad.float().cpu().numpy(), r["dH"], 2e-2, "dH")
     assert_close(w.grad.float().cpu().numpy(), r["dW"], 2e-2, "dW")
+
+
+def test_vocabulary_shard_statistics_with_ragged_last_group():
+    """Row statistics of a vocabulary shard whose width is not a multiple of 32, with targets that live in the
+    OTHER shard just past its last column: max, sum-exp and arg-max match the shard's logits, the target logit is
+    the logit for rows whose target is inside the shard and exactly 0 otherwise (never a padding value)."""
+    N, F, V = 300, 64, 1003
+    g = torch.Generator().manual_seed(31)
+    h = (torch.randn(N, F, generator=g) * 0.5).bfloat16().to("cuda")
+    w = (torch.randn(V, F, generator=g) * 0.5).bfloat16().to("cuda")
+    split = 501                                                        # 501 = 15 * 32 + 21
+    t = torch.randint(0, V, (N,), generator=g)
+    t[:40] = torch.arange(split, split + 40) % V                        # targets in the first columns of shard 1
+    t = t.to("cuda")
+    for a, b in ((0, split), (split, V)):
+        ws = w[a:b].contiguous()
+        m, s, tz, arg = ops.ce_row_stats(h, ws, t, v_offset=a)
+        lg = h.float() @ ws.float().T
+        mr = lg.max(1).values
+        assert torch.isfinite(tz).all() and torch.isfinite(s).all()
+        assert float((m - mr).abs().max()) < 1e-4
+        assert float(((s - torch.exp(lg - mr[:, None]).sum(1)) / s).abs().max()) < 1e-4
+        assert torch.equal(arg, lg.argmax(1) + a)
+        inside = (t >= a) & (t < b)
+        want = torch.where(inside, lg.gather(1, (t - a).clamp(0, b - a - 1)[:, None])[:, 0], torch.zeros_like(mr))
+        assert float((tz - want).abs().max()) < 1e-4
