@@ -23,7 +23,7 @@ constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 8;
 constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 
-enum Epi { EPI_STATS = 0, EPI_PROBS = 1, EPI_STORE = 2 };
+enum Epi { EPI_STATS = 0, EPI_PROBS = 1, EPI_STORE = 2, EPI_STORE_BF16 = 3 };   // 3: D as bf16 through tmC (boxes of 64 x 32)
 
 constexpr float LOG2E = 1.4426950408889634f;
 __device__ __forceinline__ float ex2_fast(float x) {
@@ -83,17 +83,20 @@ struct Cfg {
 
 template <int BN, int EPI, bool A_MN, bool B_MN, int MT = 1, bool PAIR = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
-k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+          const __grid_constant__ CUtensorMap tmC, const GemmParams p) {   // tmC: EPI_PROBS output, boxes of 64 x 32
   using namespace umma;
   using C = Cfg<BN, MT, PAIR>;
-  static_assert(MT == 1 || EPI == EPI_STORE, "two row tiles per CTA: plain stores only");
+  static_assert(MT == 1 || EPI == EPI_STORE || EPI == EPI_STORE_BF16, "two row tiles per CTA: plain stores only");
   static_assert(!PAIR || (MT == 1 && !A_MN && !B_MN), "CTA pairs: K-major operands, one row tile per CTA");
   // PAIR: launched as clusters of two CTAs along the row-tile axis; tmB's box holds BN / 2 rows
   const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = crank == 0u;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)C::STAGES * C::STAGE_BYTES);
+  // [operand ring][staging blocks of the epilogue warps (1024-byte aligned: TMA stores read them)][barriers]
+  unsigned char* stg_base = smem + (size_t)C::STAGES * C::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stg_base + (EPI == EPI_STATS ? 0 : (size_t)EPI_WARPS * C::EPI_STAGE_BYTES));
   uint64_t* full = bars;                      // [STAGES]
   uint64_t* empty = bars + C::STAGES;         // [STAGES]
   uint64_t* tfull = bars + 2 * C::STAGES;     // [2]
@@ -261,26 +264,33 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (!mbar_wait(&tfull[buf], bphase, 104)) { ok = false; break; }
         tc_fence_after();
         const int64_t col0 = (int64_t)n * BN;
-        if constexpr (EPI == EPI_PROBS) {
+        if constexpr (EPI == EPI_PROBS || EPI == EPI_STORE_BF16) {
           // Probability tiles leave through a per-warp staging block so that global stores are whole 128-byte
           // rows: a lane owns a tile row in TMEM, but 8 lanes share a row when storing.  16-byte pieces are
           // placed at (piece ^ (row & 7)) within their 128-byte row: both phases are free of bank conflicts.
-          unsigned char* stg = smem + (size_t)C::STAGES * C::STAGE_BYTES + 256 + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
-          const int64_t row0 = (int64_t)m_tile * BM + quarter * 32;
+          unsigned char* stg = stg_base + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
+          constexpr int G_HALF = BN / 128;                                   // groups of 64 columns per half tile
 #pragma unroll 1
-          for (int g = half * (BN / 128); g < (half + 1) * (BN / 128); ++g) {   // groups of 64 columns
+          for (int gm = 0; gm < MT * G_HALF; ++gm) {
+            const int mt = gm / G_HALF, g = half * G_HALF + gm % G_HALF;
+            const int64_t row0 = ((int64_t)m_tile * MT + mt) * BM + quarter * 32;
             const int64_t cb = col0 + g * 64;
-            if (cb >= p.ldp) break;
+            if (cb >= p.N) continue;
+            // the block may still be read by the store of the previous group
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
               float v[32];
-              tmem_ld32(tmem_base + lane_addr + buf * BN + g * 64 + hh * 32, v);
-              const int64_t dt = tcol - (cb + hh * 32);
+              tmem_ld32(tmem_base + lane_addr + buf * BN + mt * BN + g * 64 + hh * 32, v);
+              const int64_t dt = EPI == EPI_PROBS ? tcol - (cb + hh * 32) : -1;
+              if constexpr (EPI == EPI_PROBS) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = ex2_fast(fmaf(v[j], LOG2E, -off_r));
-              if (!sc_pos) {
+                for (int j = 0; j < 32; ++j) v[j] = ex2_fast(fmaf(v[j], LOG2E, -off_r));
+                if (!sc_pos) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] *= mul_r;
+                  for (int j = 0; j < 32; ++j) v[j] *= mul_r;
+                }
               }
 #pragma unroll
               for (int g8 = 0; g8 < 4; ++g8) {
@@ -298,15 +308,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 *e = __float2bfloat16_rn(__bfloat162float(*e) - sc_r);
               }
             }
+            // one TMA store per 32 x 64 block: rows past M and columns past N are clipped by the tensor map
+            fence_proxy_async();
             __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int r = 4 * i + (lane >> 3), c = lane & 7;
-              const uint4 pk = *reinterpret_cast<const uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4));
-              if (row0 + r < p.M && cb + c * 8 + 8 <= p.ldp)
-                *reinterpret_cast<uint4*>(p.pbuf + (row0 + r) * p.ldp + cb + c * 8) = pk;
-            }
-            __syncwarp();
+            if (lane == 0 && row0 < p.M) tma_store_2d(&tmC, stg, (int32_t)cb, (int32_t)row0);
           }
         } else {
 #pragma unroll 1
@@ -350,8 +355,7 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               }
             } else {  // EPI_STORE: through the staging block, whole 128-byte rows per 8 lanes
               if (cbase >= p.N) continue;
-              unsigned char* stg =
-                  smem + (size_t)C::STAGES * C::STAGE_BYTES + 256 + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
+              unsigned char* stg = stg_base + (size_t)(warp - 2) * C::EPI_STAGE_BYTES;
               const int64_t row0 = ((int64_t)m_tile * MT + mt) * BM + quarter * 32;
 #pragma unroll
               for (int g4 = 0; g4 < 8; ++g4)
@@ -381,6 +385,10 @@ k_tc_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           if (PAIR && !leader) mbar_arrive_cluster(cluster_map(&tempty[buf], 0));   // the leader issues the MMAs
           else mbar_arrive(&tempty[buf]);
         }
+      }
+      if (EPI == EPI_PROBS || EPI == EPI_STORE_BF16) {
+        if (lane == 0) tma_store_wait_all();     // the staging block and the stores outlive no one
+        __syncwarp();
       }
       if (EPI == EPI_STATS) {
         // The two warps of a row fold their running statistics through shared memory.  The ring's first

@@ -70,7 +70,8 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   // every row chunk (up to 4) sums its dW into a buffer of its own: adding into one buffer made the epilogue
   // of the later chunks read what it writes (+50 % on that launch); the final bf16 pass adds the buffers
   const int64_t n_chunks = (a->N + rows - 1) / rows;
-  pl.dw_bufs = (int32_t)(n_chunks < 1 ? 1 : (n_chunks > 4 ? 4 : n_chunks));
+  // (one row chunk needs none: its dW leaves the accumulators as bf16)
+  pl.dw_bufs = (int32_t)(n_chunks <= 1 ? 0 : (n_chunks > 4 ? 4 : n_chunks));
   return pl;
 }
 
@@ -112,7 +113,7 @@ int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& 
   if (rc) return rc;
   const unsigned row_tiles = (unsigned)((a->N + tc::BM - 1) / tc::BM);
   p.swap_xy = 1;      // blockIdx.x walks the row tiles: the two CTAs of a pair are neighbours in x
-  QPAM_CUDA(launch_pairs(kern, dim3((row_tiles + 1) & ~1u, pl.nsplit, 1), 0, CfgP::SMEM_BYTES, st, tmH, tmW, p));
+  QPAM_CUDA(launch_pairs(kern, dim3((row_tiles + 1) & ~1u, pl.nsplit, 1), 0, CfgP::SMEM_BYTES, st, tmH, tmW, tmW, p));
   QPAM_LAUNCH_CHECK("k_tc_gemm<stats>");
   return QPAM_OK;
 }
@@ -162,6 +163,11 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
   if (rc) return rc;
   rc = opt_in_smem(k_dw, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
   if (rc) return rc;
+  // one row chunk: dW is complete after one product and leaves as bf16 straight from the accumulators
+  auto k_dw16 = tc::k_tc_gemm<256, tc::EPI_STORE_BF16, true, true, MT>;
+  const bool dw_direct = a->N <= pl.chunk_rows;
+  rc = opt_in_smem(k_dw16, tc::Cfg<256, MT>::SMEM_BYTES_STAGED);
+  if (rc) return rc;
   CUtensorMap tmWk, tmWmn;
   rc = make_map(&tmWk, a->w, F, V, F, tc::BK, 128);   // K-major B of the logits GEMM: half a tile per CTA of a pair
   if (rc) return rc;
@@ -189,7 +195,9 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     p.pbuf = reinterpret_cast<__nv_bfloat16*>(b.pbuf); p.ldp = b.ldp;
     p.lse = lse; p.mask = a->mask; p.grad_scale = grad_scale; p.denom = denom;
     p.swap_xy = 1;   // consecutive CTAs take the row tiles of one vocabulary tile: W is read from DRAM once
-    QPAM_CUDA(launch_pairs(k_probs, dim3((row_tiles + 1) & ~1u, n_groups, 1), 0, CfgP::SMEM_BYTES_STAGED, st, tmHk, tmWk, p));
+    CUtensorMap tmPst;                                                                 // P as the output of TMA stores
+    if ((rc = make_map(&tmPst, b.pbuf, V, rows, b.ldp, 64, 32))) return rc;
+    QPAM_CUDA(launch_pairs(k_probs, dim3((row_tiles + 1) & ~1u, n_groups, 1), 0, CfgP::SMEM_BYTES_STAGED, st, tmHk, tmWk, tmPst, p));
     QPAM_LAUNCH_CHECK("k_tc_gemm<probs>");
     // 2) dH[r0:r0+rows] = P W, split over the vocabulary (K) axis, fp32 partials then bf16
     tc::GemmParams g{};
@@ -199,7 +207,7 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     const int ks = (g.kb_total + g.kb_per_split - 1) / g.kb_per_split;
     g.M = rows; g.N = F;
     g.c = b.dh_part; g.ldc = F; g.beta = 0;
-    k_dh<<<dim3(f_tiles, (row_tiles + MT - 1) / MT, ks), tc::NTHREADS, tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPk, tmWmn, g);
+    k_dh<<<dim3(f_tiles, (row_tiles + MT - 1) / MT, ks), tc::NTHREADS, tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPk, tmWmn, tmWmn, g);
     QPAM_LAUNCH_CHECK("k_tc_gemm<dH>");
     k_reduce_splits_bf16<<<592, 256, 0, st>>>(b.dh_part, reinterpret_cast<__nv_bfloat16*>(dh) + r0 * F, rows * F, ks,
                                              rows * F);
@@ -215,15 +223,25 @@ int ce_tc_backward(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers&
     w.n_tiles = f_tiles; w.tiles_per_cta = 1;
     w.kb_total = (int32_t)((rows + tc::BK - 1) / tc::BK); w.kb_per_split = w.kb_total;
     w.M = V; w.N = F;
-    w.c = b.dwacc + (size_t)(chunk_idx % pl.dw_bufs) * V * F; w.ldc = F; w.beta = chunk_idx >= pl.dw_bufs ? 1 : 0;
-    k_dw<<<dim3(f_tiles, (unsigned)((V + MT * tc::BM - 1) / (MT * tc::BM)), 1), tc::NTHREADS,
-           tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPmn, tmHmn, w);
+    if (!dw_direct) { w.c = b.dwacc + (size_t)(chunk_idx % pl.dw_bufs) * V * F; w.beta = chunk_idx >= pl.dw_bufs ? 1 : 0; }
+    w.ldc = F;
+    if (dw_direct) {
+      CUtensorMap tmDw;
+      if ((rc = make_map(&tmDw, dw, F, V, F, 64, 32))) return rc;
+      k_dw16<<<dim3(f_tiles, (unsigned)((V + MT * tc::BM - 1) / (MT * tc::BM)), 1), tc::NTHREADS,
+               tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPmn, tmHmn, tmDw, w);
+    } else {
+      k_dw<<<dim3(f_tiles, (unsigned)((V + MT * tc::BM - 1) / (MT * tc::BM)), 1), tc::NTHREADS,
+             tc::Cfg<256, MT>::SMEM_BYTES_STAGED, st>>>(tmPmn, tmHmn, tmHmn, w);
+    }
     QPAM_LAUNCH_CHECK("k_tc_gemm<dW>");
     ++chunk_idx;
   }
-  k_reduce_splits_bf16<<<1184, 256, 0, st>>>(b.dwacc, reinterpret_cast<__nv_bfloat16*>(dw), V * (int64_t)F,
-                                            chunk_idx < pl.dw_bufs ? (chunk_idx > 0 ? chunk_idx : 1) : pl.dw_bufs, V * (int64_t)F);
-  QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
+  if (!dw_direct) {
+    k_reduce_splits_bf16<<<1184, 256, 0, st>>>(b.dwacc, reinterpret_cast<__nv_bfloat16*>(dw), V * (int64_t)F,
+                                              chunk_idx < pl.dw_bufs ? (chunk_idx > 0 ? chunk_idx : 1) : pl.dw_bufs, V * (int64_t)F);
+    QPAM_LAUNCH_CHECK("k_reduce_splits_bf16");
+  }
   return QPAM_OK;
 }
 

@@ -11,7 +11,7 @@ struct CETcPlan {
   int32_t tiles_per_split;
   int64_t chunk_rows;    // rows per backward chunk (multiple of 128)
   int32_t ksplit;        // split-K factor of the dH GEMM
-  int32_t dw_bufs;       // fp32 [V][F] accumulation buffers of dW (one per row chunk, at most 4)
+  int32_t dw_bufs;       // fp32 [V][F] accumulation buffers of dW (one per row chunk, at most 4; 0 for a single chunk)
 };
 
 CETcPlan ce_tc_plan(const qpam_ce_args* a);
