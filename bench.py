@@ -208,6 +208,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the decode / CE side measurements")
     ap.add_argument("--only-inference", action="store_true",
                     help="run only a small packed prefill + decode of the config-5 model (a profiling target)")
+    ap.add_argument("--only-ce", action="store_true",
+                    help="run only the fused cross-entropy of config 2 (forward, forward + backward, per-kernel times)")
     ap.add_argument("--only-elementwise", action="store_true",
                     help="run only the element-wise block kernels at the config-3 layer shape and print their line")
     args = ap.parse_args()
@@ -215,6 +217,10 @@ def main():
     if args.only_inference:
         torch.cuda.set_device(0)
         print(json.dumps({"inference_small": inference_small(torch.device("cuda:0"))}))
+        return
+    if args.only_ce:
+        torch.cuda.set_device(0)
+        print(json.dumps({"fused_ce_config2": fused_ce_config2(torch.device("cuda:0"), load_peaks())}))
         return
     if args.only_elementwise:
         torch.cuda.set_device(0)
@@ -438,8 +444,9 @@ def main():
             "bf16_state": extra.get("decode_step_bf16_state", {}).get("frac_of_hbm_peak"),
             "f32_state": extra.get("decode_step_f32_state", {}).get("frac_of_hbm_peak")}
         ce2 = extra.get("fused_ce_config2", {})
-        secondary["fused_ce_config2"] = {"achieved_tflops": ce2.get("achieved_tflops"), "frac_of_bf16_peak": ce2.get("frac_of_bf16_peak"),
-                                         "ms_fwd_bwd": ce2.get("ms_fwd_bwd"), "bwd_workspace_bytes": ce2.get("bwd_workspace_bytes")}
+        secondary["fused_ce_config2"] = {k_: ce2.get(k_) for k_ in (
+            "achieved_tflops", "frac_of_bf16_peak", "ms_fwd_bwd", "ms_fwd", "achieved_tflops_fwd", "frac_of_bf16_peak_fwd",
+            "bwd_workspace_bytes")}
         pp = extra.get("packed_prefill_config4", {})
         secondary["packed_prefill_config4"] = {"tokens_per_s": pp.get("tokens_per_s"), "frac_of_hbm_peak": pp.get("frac_of_hbm_peak")}
         ts = extra.get("train_step_config3", {})
@@ -545,6 +552,56 @@ def vocab_parallel_ce(dev, rank, world, peaks, iters=5):
             "config": f"N=8192 rows, F=768, vocabulary 50261 in {world} row shards, bf16; device events, max over ranks"}
 
 
+def fused_ce_config2(dev, peaks):
+    """Fused tied-head cross-entropy at config 2 (N = 8192 rows, F = 768, V = 50261, bf16): forward alone and forward
+    + backward, device events over 10 calls each; per-kernel times of one forward + backward from the library's
+    event recorder.  Algorithmic work: 2 N V F flops forward, 6 N V F forward + backward (the backward's second
+    logits product is a recompute and is not counted)."""
+    import ctypes as C_
+
+    from qllm2_b200 import _lib as L_
+    from qllm2_b200 import fused_ce, ops, synthetic
+    c2 = synthetic.config2()
+    h = c2.h.to(dev).requires_grad_(True)
+    w = c2.w.to(dev).requires_grad_(True)
+    t = c2.targets.to(dev)
+
+    def both():
+        loss = fused_ce.fused_linear_cross_entropy(h, w, t)
+        torch.autograd.grad(loss, [h, w])
+        return loss
+
+    def fwd():
+        with torch.no_grad():
+            return fused_ce.fused_linear_cross_entropy(h, w, t)
+
+    def time_ms(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    loss = float(both().detach())
+    ms, ms_f = time_ms(both), time_ms(fwd)
+    L_.profile_begin()
+    both()
+    torch.cuda.synchronize()
+    kern = {k_: {"launches": v_[0], "ms": v_[1]} for k_, v_ in L_.profile_end().items()}
+    fl = 2 * 8192 * 50261 * 768
+    a_ = ops._ce_args(h.detach(), w.detach(), t, None, -100)
+    return {"ms_fwd_bwd": ms, "ms_fwd": ms_f, "tokens_per_s": 8192 / ms * 1e3, "loss": loss,
+            "achieved_tflops": 3 * fl / ms / 1e9, "frac_of_bf16_peak": 3 * fl / ms / 1e9 / peaks["tf"],
+            "achieved_tflops_fwd": fl / ms_f / 1e9, "frac_of_bf16_peak_fwd": fl / ms_f / 1e9 / peaks["tf"],
+            "kernels_one_fwd_bwd": kern,
+            "bwd_workspace_bytes": int(L_.lib().qpam_ce_workspace_bytes(C_.byref(a_), 1))}
+
+
 def side_measurements(dev, peaks):
     """Decode step (HBM-bound) and fused CE (config 2) timed on their own; reported under `extra`."""
     from qllm2_b200 import fused_ce, ops, synthetic
@@ -582,24 +639,7 @@ def side_measurements(dev, peaks):
             "frac_of_hbm_peak": by / ms / 1e6 / peaks["hbm"],
             "config": f"n={n} H={H} d={d} K={K}, pool {pool.numel() * pool.element_size() / 1e9:.2f} GB rotating over {L} layers"}
         del pool
-    # fused tied-head CE, config 2
-    c2 = synthetic.config2()
-    h = c2.h.to(dev).requires_grad_(True)
-    w = c2.w.to(dev).requires_grad_(True)
-    t = c2.targets.to(dev)
-
-    def ce():
-        loss = fused_ce.fused_linear_cross_entropy(h, w, t)
-        torch.autograd.grad(loss, [h, w])
-    ms = time_ms(ce, 3, warm=1)
-    fl = 6 * 8192 * 50261 * 768
-    import ctypes as C_
-    from qllm2_b200 import _lib as L_
-    a_ = ops._ce_args(h.detach(), w.detach(), t, None, -100)
-    out["fused_ce_config2"] = {"ms_fwd_bwd": ms, "tokens_per_s": 8192 / ms * 1e3, "achieved_tflops": fl / ms / 1e9,
-                               "frac_of_bf16_peak": fl / ms / 1e9 / peaks["tf"],
-                               "bwd_workspace_bytes": int(L_.lib().qpam_ce_workspace_bytes(C_.byref(a_), 1))}
-    del h, w, t
+    out["fused_ce_config2"] = fused_ce_config2(dev, peaks)
     torch.cuda.empty_cache()
     out["packed_prefill_config4"] = packed_prefill(dev, peaks, time_ms)
     out["elementwise_kernels"] = elementwise_kernels(dev, peaks)
