@@ -325,7 +325,7 @@ extern "C" int qpam_act_gate_packed_fwd(const void* gate_up, int64_t ld, int32_t
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int groups = C / 4, threads = pick_threads(groups), xb = (groups + threads - 1) / threads;
-  dim3 grid(xb, (unsigned)std::min<int64_t>((N + 1) / 2, std::max(1, (148 * 2048) / (xb * threads))));
+  dim3 grid(xb, (unsigned)std::min<int64_t>((N + 1) / 2, std::max(1, (sm_count() * 2048) / (xb * threads))));
 #define QPAM_AG(T)                                                                                                  \
   if (beta) k_act_gate_packed<T, true><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C); \
   else k_act_gate_packed<T, false><<<grid, threads, 0, st>>>((const T*)gate_up, ld, bias, beta, (T*)out, N, C);
@@ -344,7 +344,7 @@ extern "C" int qpam_residual_cnorm_fwd(void* z, const void* delta, const float* 
   QPAM_REQUIRE(is_dtype(dtype) && N >= 0 && D > 0 && D % 4 == 0, "residual_cnorm: D must be a multiple of 4 (got %d)", D);
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (N <= 148 * 8 && D <= 4096) {  // few rows: a CTA per row keeps every SM busy
+  if (N <= sm_count() * 8 && D <= 4096) {  // few rows: a CTA per row keeps every SM busy
     const int threads = (D / 4 + 31) / 32 * 32;
     if (dtype == QPAM_F32)
       k_residual_cnorm_row<float><<<(unsigned)N, threads, 0, st>>>((float*)z, (const float*)delta, res_scale, norm_scale, (float*)xn, (float*)mag, D, eps);
@@ -354,7 +354,7 @@ extern "C" int qpam_residual_cnorm_fwd(void* z, const void* delta, const float* 
     QPAM_LAUNCH_CHECK("k_residual_cnorm_row");
     return QPAM_OK;
   }
-  const int blocks = (int)std::min<int64_t>((N + 3) / 4, 148 * 8);
+  const int blocks = (int)std::min<int64_t>((N + 3) / 4, sm_count() * 8);
   if (dtype == QPAM_F32)
     k_residual_cnorm<float><<<blocks, 128, 0, st>>>((float*)z, (const float*)delta, res_scale, norm_scale, (float*)xn, (float*)mag, N, D, eps);
   else
@@ -382,7 +382,7 @@ extern "C" int qpam_pam_front_fwd(const qpam_front_args* a, void* stream) {
   const int main_threads = std::min(pick_threads(per_tok), 384);
   const int gate_threads = std::min((FRONT_U * a->H * a->K + 31) / 32 * 32, 128);
   const int threads = main_threads + gate_threads;
-  const int grid = (int)std::min<int64_t>(((int64_t)a->B * a->T + FRONT_U - 1) / FRONT_U, (148 * 2048) / threads);
+  const int grid = (int)std::min<int64_t>(((int64_t)a->B * a->T + FRONT_U - 1) / FRONT_U, (sm_count() * 2048) / threads);
   if (a->io_dtype == QPAM_F32) k_pam_front<float><<<grid, threads, 0, st>>>(fp, main_threads);
   else k_pam_front<__nv_bfloat16><<<grid, threads, 0, st>>>(fp, main_threads);
   QPAM_LAUNCH_CHECK("k_pam_front");

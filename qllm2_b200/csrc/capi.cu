@@ -26,6 +26,19 @@ int cuda_fail(cudaError_t e, const char* what) {
   return QPAM_ECUDA;
 }
 
+// SMs of the current device (grids and split heuristics are sized from it); 148 if the query fails.
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 // ------------------------------------------------------------------ launch accounting
 static std::atomic<long long> g_launches{0};
 static std::atomic<bool> g_profiling{false};

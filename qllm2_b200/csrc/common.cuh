@@ -12,6 +12,7 @@ namespace qpam {
 // ------------------------------------------------------------------ error reporting
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+int sm_count();   // multiprocessors of the current device
 
 #define QPAM_REQUIRE(cond, ...)            \
   do {                                     \

@@ -498,7 +498,7 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
 }
 
 inline int act_grid_y(int64_t N, int xblocks, int threads) {  // enough rows in flight to fill every SM's thread slots
-  const int64_t y = std::max<int64_t>(1, (148 * 2048) / ((int64_t)xblocks * threads));
+  const int64_t y = std::max<int64_t>(1, (sm_count() * 2048) / ((int64_t)xblocks * threads));
   return (int)std::min<int64_t>(std::min<int64_t>(y, N), 65535);
 }
 
@@ -515,7 +515,7 @@ extern "C" int qpam_cnorm_fwd(const void* z, int32_t z_dtype, const float* scale
   QPAM_REQUIRE(N >= 0 && D > 0 && D % 4 == 0 && D <= 3072, "cnorm_fwd: D must be a multiple of 4 and <= 3072 (got %d)", D);
   if (N == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int P = (int)std::min<int64_t>(N, 148 * 32);
+  const int P = (int)std::min<int64_t>(N, sm_count() * 32);
   if (z_dtype == QPAM_F32 && out_dtype == QPAM_F32) return cnorm_launch<float, float>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
   if (z_dtype == QPAM_F32) return cnorm_launch<float, __nv_bfloat16>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
   return cnorm_launch<__nv_bfloat16, __nv_bfloat16>(false, z, scale, out, nullptr, nullptr, P, N, D, eps, st);
@@ -624,7 +624,7 @@ static int pam_prep(bool bwd, const void* qkv, int32_t dtype, const float* rope,
   PrepParams p{qkv, rope, positions, omp, q, k, v, dqkv, (bwd && omp) ? domp : nullptr, offset, rope_len, B, T, H, d};
   const int per_tok = H * (d / 4);
   const int threads = pick_threads(per_tok);
-  const int grid = (int)std::min<int64_t>(((int64_t)B * T + PREP_U - 1) / PREP_U, (148 * 2048) / threads);
+  const int grid = (int)std::min<int64_t>(((int64_t)B * T + PREP_U - 1) / PREP_U, (sm_count() * 2048) / threads);
   if (dtype == QPAM_F32) {
     if (bwd) k_pam_prep<float, true><<<grid, threads, 0, st>>>(p);
     else k_pam_prep<float, false><<<grid, threads, 0, st>>>(p);
@@ -872,7 +872,7 @@ static int state_combine(bool bwd, const void* const* yk, void* const* dyk, cons
   p.coef = coef; p.y = y; p.dcoef = dcoef; p.R = R; p.d = d; p.K = K; p.H = H; p.T = T;
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = R * (d / 4);
-  const int grid = (int)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  const int grid = (int)std::min<int64_t>((total + 255) / 256, sm_count() * 16);
   if (dtype == QPAM_F32) {
     if (bwd) k_state_combine<float, true><<<grid, 256, 0, st>>>(p);
     else k_state_combine<float, false><<<grid, 256, 0, st>>>(p);
@@ -898,7 +898,7 @@ template <typename TX, typename TD>
 static int scaled_residual(bool bwd, const void* x_or_dout, const void* delta, const float* s, void* out_or_ddelta,
                            float* ds_part, int32_t P, int64_t n, cudaStream_t st) {
   if (!bwd) {
-    const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256 + 1, 148 * 8);
+    const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256 + 1, sm_count() * 8);
     k_scaled_residual_fwd<TX, TD><<<grid, 256, 0, st>>>((const TX*)x_or_dout, (const TD*)delta, s, (TX*)out_or_ddelta, n);
     QPAM_LAUNCH_CHECK("k_scaled_residual_fwd");
   } else {
@@ -941,7 +941,7 @@ extern "C" int qpam_block_weight_fwd(const void* wr, const void* wi, int32_t w_d
   QPAM_REQUIRE(wr && wi && w, "block_weight_fwd: NULL pointer argument");
   QPAM_REQUIRE(is_dtype(w_dtype) && is_dtype(out_dtype) && out_dim > 0 && in_dim > 0, "block_weight_fwd: bad dtype or shape");
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, 148 * 8);
+  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, sm_count() * 8);
 #define QPAM_BW(TW, TO) k_block_weight_fwd<TW, TO><<<grid, 256, 0, st>>>((const TW*)wr, (const TW*)wi, (TO*)w, out_dim, in_dim)
   if (w_dtype == QPAM_F32 && out_dtype == QPAM_F32) QPAM_BW(float, float);
   else if (w_dtype == QPAM_F32) QPAM_BW(float, __nv_bfloat16);
@@ -957,7 +957,7 @@ extern "C" int qpam_block_weight_bwd(const void* dw, int32_t out_dtype, void* dw
   QPAM_REQUIRE(dw && dwr && dwi, "block_weight_bwd: NULL pointer argument");
   QPAM_REQUIRE(is_dtype(w_dtype) && is_dtype(out_dtype) && out_dim > 0 && in_dim > 0, "block_weight_bwd: bad dtype or shape");
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, 148 * 8);
+  const int grid = (int)std::min<int64_t>(((int64_t)out_dim * in_dim + 255) / 256, sm_count() * 8);
 #define QPAM_BW(TW, TO) k_block_weight_bwd<TW, TO><<<grid, 256, 0, st>>>((const TO*)dw, (TW*)dwr, (TW*)dwi, out_dim, in_dim)
   if (w_dtype == QPAM_F32 && out_dtype == QPAM_F32) QPAM_BW(float, float);
   else if (w_dtype == QPAM_F32) QPAM_BW(float, __nv_bfloat16);
@@ -982,12 +982,12 @@ static int pam_gates(bool bwd, GateParams& p, int32_t P, void* stream) {
   const int64_t n = (int64_t)p.B * p.T * p.H;
   if (!bwd) {
     QPAM_REQUIRE(p.gamma && (!p.pg || p.omp), "pam_gates_fwd: NULL output");
-    const int grid = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, sm_count() * 8);
     k_pam_gates<false><<<grid, 256, 0, st>>>(p);
     QPAM_LAUNCH_CHECK("k_pam_gates_fwd");
   } else {
     QPAM_REQUIRE(p.dgamma && p.ddt && p.dx_part && (!p.pg || p.dpg), "pam_gates_bwd: NULL pointer argument");
-    QPAM_REQUIRE(P > 0 && P <= 148 * 8, "pam_gates_bwd: partial rows must be in [1, %d]", 148 * 8);
+    QPAM_REQUIRE(P > 0 && P <= 65535, "pam_gates_bwd: partial rows must be in [1, 65535]");   // one CTA per partial row
     k_pam_gates<true><<<P, 256, sizeof(float) * p.H * p.K, st>>>(p);
     QPAM_LAUNCH_CHECK("k_pam_gates_bwd");
   }
@@ -1020,7 +1020,7 @@ extern "C" int qpam_cmagnitude_fwd(const void* z, int32_t dtype, void* mag, int6
   QPAM_REQUIRE(z && mag && is_dtype(dtype) && n >= 0 && n % 4 == 0, "cmagnitude_fwd: NULL pointer, bad dtype or n not a multiple of 4");
   if (n == 0) return QPAM_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 8);
+  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, sm_count() * 8);
   if (dtype == QPAM_F32) k_cmagnitude<float, false><<<grid, 256, 0, st>>>((const float*)z, nullptr, (float*)mag, n);
   else k_cmagnitude<__nv_bfloat16, false><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, nullptr, (__nv_bfloat16*)mag, n);
   QPAM_LAUNCH_CHECK("k_cmagnitude_fwd");
@@ -1030,7 +1030,7 @@ extern "C" int qpam_cmagnitude_fwd(const void* z, int32_t dtype, void* mag, int6
 extern "C" int qpam_cmagnitude_bwd(const void* z, const void* dmag, int32_t dtype, void* dz, int64_t n, void* stream) {
   QPAM_REQUIRE(z && dmag && dz && is_dtype(dtype) && n > 0 && n % 4 == 0, "cmagnitude_bwd: NULL pointer, bad dtype or n not a multiple of 4");
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 8);
+  const int grid = (int)std::min<int64_t>((n / 4 + 255) / 256, sm_count() * 8);
   if (dtype == QPAM_F32) k_cmagnitude<float, true><<<grid, 256, 0, st>>>((const float*)z, (const float*)dmag, (float*)dz, n);
   else k_cmagnitude<__nv_bfloat16, true><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, (const __nv_bfloat16*)dmag, (__nv_bfloat16*)dz, n);
   QPAM_LAUNCH_CHECK("k_cmagnitude_bwd");

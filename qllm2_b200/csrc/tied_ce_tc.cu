@@ -36,7 +36,8 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   pl.enabled = a->io_dtype == QPAM_BF16 && (a->F % 8) == 0 && a->N > 0;
   pl.n_tiles = (int32_t)((a->V + 255) / 256);
   const int64_t row_tiles = (a->N + tc::BM - 1) / tc::BM;
-  // vocabulary splits: fill the 148 SMs in whole waves (one CTA per SM: the ring takes ~193 KB)
+  // vocabulary splits: fill the SMs in whole waves (one CTA per SM: the ring takes ~193 KB)
+  const int sms = sm_count();
   int best = 1;
   double best_eff = -1.0;
   const int max_split = pl.n_tiles < 128 ? pl.n_tiles : 128;
@@ -45,9 +46,9 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
     const int real = (pl.n_tiles + tps - 1) / tps;
     if (real != s) continue;
     const double ctas = (double)row_tiles * s;
-    const double waves = (ctas + 147) / 148;
+    const double waves = (ctas + sms - 1) / sms;
     // last factor: a CTA pays its prologue and one epilogue that no MMA overlaps (~0.7 of a tile's time)
-    const double eff = ctas / ((double)(int64_t)waves * 148) * ((double)pl.n_tiles / ((double)tps * s)) *
+    const double eff = ctas / ((double)(int64_t)waves * sms) * ((double)pl.n_tiles / ((double)tps * s)) *
                        (tps / (tps + 0.7));
     if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
   }
@@ -58,12 +59,12 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
   if (rows < tc::BM) rows = tc::BM;
   pl.chunk_rows = rows;
   const int64_t f_tiles = (a->F + 255) / 256;
-  // split-K of dH: one CTA per SM, so the cost is (waves of 148 CTAs) x (K blocks per split)
+  // split-K of dH: one CTA per SM, so the cost is (waves of CTAs) x (K blocks per split)
   const int64_t kb_total = (a->V + tc::BK - 1) / tc::BK;
   int64_t ks = 1, ks_cost = -1;
   for (int64_t s = 1; s <= 8 && s <= kb_total; ++s) {
     const int64_t ctas = f_tiles * ((rows + 2 * tc::BM - 1) / (2 * tc::BM)) * s;     // CTAs of two row tiles
-    const int64_t cost = ((ctas + 147) / 148) * ((kb_total + s - 1) / s + 8);   // + 8: prologue and epilogue of a CTA
+    const int64_t cost = ((ctas + sms - 1) / sms) * ((kb_total + s - 1) / s + 8);   // + 8: prologue and epilogue of a CTA
     if (ks_cost < 0 || cost < ks_cost) { ks_cost = cost; ks = s; }
   }
   pl.ksplit = (int32_t)ks;
@@ -78,13 +79,14 @@ CETcPlan ce_tc_plan(const qpam_ce_args* a) {
 // Vocabulary tiles one CTA of the probability pass walks for its row tile: more tiles hide the epilogue of one
 // tile behind the MMAs of the next (two accumulator buffers), fewer fill the last wave better.
 static int probs_tiles_per_cta(int64_t row_tiles, int n_tiles) {
+  const int sms = sm_count();
   int best = 1;
   double best_eff = -1.0;
   for (int t = 1; t <= 32 && t <= n_tiles; ++t) {
     const int groups = (n_tiles + t - 1) / t;
     const double ctas = (double)row_tiles * groups;
-    const double waves = (double)(int64_t)((ctas + 147) / 148);
-    const double eff = (ctas / (waves * 148)) * ((double)n_tiles / ((double)t * groups)) * (t / (t + 1.2));
+    const double waves = (double)(int64_t)((ctas + sms - 1) / sms);
+    const double eff = (ctas / (waves * sms)) * ((double)n_tiles / ((double)t * groups)) * (t / (t + 1.2));
     if (eff > best_eff + 1e-9) { best_eff = eff; best = t; }
   }
   return best;
