@@ -336,7 +336,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   bool ok = mbar_wait(&bars[0], 0, 221);
   {
     // de-interleave the three tiles in place (read all, barrier, write all)
-    const int row = tid >> 1, hb = tid & 1;
+    const int row = tid & 127, hb = tid >> 7;      // a quarter-warp reads eight rows of one block: no bank conflict
     uint4 ra[8], rb[8], rc[8];
     deint_read(RA, row, hb, ra);
     deint_read(RB, row, hb, rb);

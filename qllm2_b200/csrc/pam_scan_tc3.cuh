@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
   }
   bool ok = mbar_wait(&bars[0], 0, 231);
   {
-    const int row = tid >> 1, hb = tid & 1;
+    const int row = tid & 127, hb = tid >> 7;      // a quarter-warp reads eight rows of one block: no bank conflict
     uint4 ra[8], rb[8], rc[8];
     deint_read(RA, row, hb, ra);
     deint_read(RB, row, hb, rb);
