@@ -207,6 +207,8 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
     if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
+    if (token_major) maps.out = maps.a1;     // not used: the token-major layout is stored per lane
+    else if ((rc = make_map(&maps.out, a->y, 128, rows, 128, 64, 32))) return rc;
     if ((rc = set_smem(tcs::k_tc_chunk_fwd, tcs::CHUNK2_SMEM))) return rc;
     tcs::k_tc_chunk_fwd<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk<fwd>");
@@ -230,6 +232,7 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
     if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
+    maps.out = maps.a1;      // not used by this kernel
     if ((rc = set_smem(tcs::k_tc_chunk_fwdK, tcs::CHUNKK_SMEM))) return rc;
     tcs::k_tc_chunk_fwdK<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNKK_SMEM, st>>>(maps, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_fwdK");
@@ -272,6 +275,9 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     if ((rc = make_map(&maps.k, a->k, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.v, a->v, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.dy, dy, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&maps.dq, dq, 128, rows, 128, 64, 32))) return rc;
+    if ((rc = make_map(&maps.dk, dk, 128, rows, 128, 64, 32))) return rc;
+    if ((rc = make_map(&maps.dv, dv, 128, rows, 128, 64, 32))) return rc;
     if ((rc = set_smem(tcs::k_tc_chunk_bwd, tcs::CHUNK2_SMEM))) return rc;
     tcs::k_tc_chunk_bwd<<<dim3(3 * L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk<dq,dv,dk>");

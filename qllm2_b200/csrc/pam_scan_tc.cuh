@@ -291,6 +291,7 @@ enum ChunkMode { M_FWD = 0, M_DQ = 1, M_DV = 2, M_DK = 3 };
 
 struct ChunkMaps {
   CUtensorMap a1, b1, x2;  // [B*H*T rows][128 bf16], boxes of 64 x 128, 128-byte swizzle
+  CUtensorMap out;         // the output tensor, same shape, boxes of 64 x 32 (one per epilogue warp)
 };
 
 }  // namespace tcs

@@ -42,6 +42,7 @@ constexpr int ANCHOR_PARTS = 64;           // partial sums per decay-gradient an
 
 struct BwdMaps {
   CUtensorMap q, k, v, dy;   // [B*H*T rows][128 bf16], boxes of 64 x 128, 128-byte swizzle
+  CUtensorMap dq, dk, dv;    // outputs, same shape, boxes of 64 x 32 (one per epilogue warp)
 };
 
 // De-interleave one [2 blocks][128 rows][128 B] tile in place: thread (row, hb) owns block hb of its
@@ -198,9 +199,11 @@ __device__ __forceinline__ void bw_epi_scores(uint32_t tlane_slot, int q4, int c
 
 // ---- epilogue 2: out[r][16 cb .. 16 cb + 16) = rf * acc -> global; optional part of Re<x_r, out_r>, x_r given as the
 // four 16-byte pieces of the interleaved bf16 row that cover these channels ------------------------------------
+// `stage` != nullptr: the 16-byte pieces go to this row of a 128-byte-swizzled staging block (piece index
+// 4 * (cb & 1) + g, row & 7 = `sw`) instead of global memory; a TMA store moves the block afterwards.
 template <bool DOT>
 __device__ __forceinline__ float bw_epi_out(uint32_t tlane_slot, int cb, float rf, __nv_bfloat16* __restrict__ orow,
-                                            const uint4 (&xg)[4], bool valid) {
+                                            const uint4 (&xg)[4], bool valid, unsigned char* stage = nullptr, int sw = 0) {
   using namespace umma;
   float vr[16], vi[16];
   tmem_ld16x2(tlane_slot + 128 + 16 * cb, vr, tlane_slot + 192 + 16 * cb, vi);
@@ -213,9 +216,10 @@ __device__ __forceinline__ float bw_epi_out(uint32_t tlane_slot, int cb, float r
   if (valid) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {   // 4 complex channels -> one 16-byte store
-      *reinterpret_cast<uint4*>(orow + g * 8) =
-          make_uint4(pack_bf162(vr[4 * g], vi[4 * g]), pack_bf162(vr[4 * g + 1], vi[4 * g + 1]),
-                     pack_bf162(vr[4 * g + 2], vi[4 * g + 2]), pack_bf162(vr[4 * g + 3], vi[4 * g + 3]));
+      const uint4 pk = make_uint4(pack_bf162(vr[4 * g], vi[4 * g]), pack_bf162(vr[4 * g + 1], vi[4 * g + 1]),
+                                  pack_bf162(vr[4 * g + 2], vi[4 * g + 2]), pack_bf162(vr[4 * g + 3], vi[4 * g + 3]));
+      if (stage != nullptr) *reinterpret_cast<uint4*>(stage + (((4 * (cb & 1) + g) ^ sw) << 4)) = pk;
+      else *reinterpret_cast<uint4*>(orow + g * 8) = pk;
       if (DOT) {
         const uint32_t xw[4] = {xg[g].x, xg[g].y, xg[g].z, xg[g].w};
 #pragma unroll
@@ -253,8 +257,8 @@ __device__ __forceinline__ void rescale_acc_half(uint32_t tlane_slot, int hf, fl
 // ---------------------------------------------------------------------------------------------
 template <int MODE>
 __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, const CUtensorMap* __restrict__ mb1,
-                                          const CUtensorMap* __restrict__ mx2, const ScanParams& p, int chunk_x, int h,
-                                          unsigned char* smem) {
+                                          const CUtensorMap* __restrict__ mx2, const CUtensorMap* __restrict__ mout,
+                                          const ScanParams& p, int chunk_x, int h, unsigned char* smem) {
   using namespace umma;
   constexpr bool LOWER = (MODE == M_FWD || MODE == M_DQ);       // mask col <= row
   constexpr bool OP_H = (MODE == M_DQ || MODE == M_DK);         // carried operand conj-transposed
@@ -417,10 +421,21 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     ok = mbar_wait(&bars[2], 0, 223) && ok;
     tc_fence_after();
     const float rf = strong ? 1.f : rfac[r];
+    // A full chunk leaves through the A1 region, which every MMA has finished reading: each warp stages its 32 rows
+    // x 128 bytes there and one TMA store moves the block (whole 128-byte lines instead of 16 bytes per lane and
+    // row).  A ragged chunk (its rows past `len` belong to someone else) and the token-major layout store per lane.
+    const bool bulk = ok && L.len == TC && !(MODE == M_FWD && p.y_token_major);      // CTA-uniform
+    unsigned char* wbox = RA + hf * 16384 + q4 * 4096;                               // this warp's 32 x 128 B block
     float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc)
-      dot += bw_epi_out<(MODE == M_DQ || MODE == M_DK)>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok);
+      dot += bw_epi_out<(MODE == M_DQ || MODE == M_DK)>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok,
+                                                      bulk ? wbox + lane * 128 : nullptr, lane & 7);
+    if (bulk) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) tma_store_2d_keep(mout, wbox, hf * 64, row0 + q4 * 32);
+    }
     if (MODE == M_DQ || MODE == M_DK) {
       dots[hf * TC + r] = dot;
       __syncthreads();
@@ -431,6 +446,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
       }
     }
   }
+  if (lane == 0) tma_store_wait_read();      // the staging block is read before this CTA's shared memory goes away
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
@@ -443,7 +459,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
 __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwd(const __grid_constant__ ChunkMaps maps, ScanParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  chunk_job<M_FWD>(&maps.a1, &maps.b1, &maps.x2, p, blockIdx.x, blockIdx.y, smem);
+  chunk_job<M_FWD>(&maps.a1, &maps.b1, &maps.x2, &maps.out, p, blockIdx.x, blockIdx.y, smem);
 }
 
 // the three gradients: grid = (3 * chunks, H); CTA x works on chunk x / 3, job x % 3 (dq, dv, dk), so the CTAs that
@@ -452,9 +468,9 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_bwd(const __grid_constant__
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int chunk_x = blockIdx.x / 3, job = blockIdx.x - 3 * chunk_x;
-  if (job == 0) chunk_job<M_DQ>(&maps.dy, &maps.v, &maps.k, p, chunk_x, blockIdx.y, smem);
-  else if (job == 1) chunk_job<M_DV>(&maps.k, &maps.q, &maps.dy, p, chunk_x, blockIdx.y, smem);
-  else chunk_job<M_DK>(&maps.v, &maps.dy, &maps.q, p, chunk_x, blockIdx.y, smem);
+  if (job == 0) chunk_job<M_DQ>(&maps.dy, &maps.v, &maps.k, &maps.dq, p, chunk_x, blockIdx.y, smem);
+  else if (job == 1) chunk_job<M_DV>(&maps.k, &maps.q, &maps.dy, &maps.dv, p, chunk_x, blockIdx.y, smem);
+  else chunk_job<M_DK>(&maps.v, &maps.dy, &maps.q, &maps.dk, p, chunk_x, blockIdx.y, smem);
 }
 
 // ---------------------------------------------------------------------------------------------
