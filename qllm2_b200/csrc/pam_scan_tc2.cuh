@@ -258,10 +258,12 @@ __device__ __forceinline__ void rescale_acc_half(uint32_t tlane_slot, int hf, fl
 template <int MODE>
 __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, const CUtensorMap* __restrict__ mb1,
                                           const CUtensorMap* __restrict__ mx2, const CUtensorMap* __restrict__ mout,
-                                          const ScanParams& p, int chunk_x, int h, unsigned char* smem) {
+                                          const CUtensorMap* __restrict__ mdot, const ScanParams& p, int chunk_x, int h,
+                                          unsigned char* smem) {
   using namespace umma;
   constexpr bool LOWER = (MODE == M_FWD || MODE == M_DQ);       // mask col <= row
   constexpr bool OP_H = (MODE == M_DQ || MODE == M_DK);         // carried operand conj-transposed
+  constexpr bool DOT = (MODE == M_DQ || MODE == M_DK);          // also leaves Re<x_row, out_row>, x = q (dq) or k (dk): mdot
   unsigned char* RA = smem;                  // A1: real plane, imaginary plane  (2 x [128 rows][128 B])
   unsigned char* RB = RA + 32768;            // B1 planes; after stage 1: carried state planes (2 x [64 rows][128 B])
   unsigned char* RC = RB + 32768;            // X2 planes
@@ -400,9 +402,24 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   }
   if (warp == 0 && elect_one()) {
     tc_fence_after();
-    bw_issue_out(tmem, x_r, two_step);
-    if (has_state && !strong) bw_issue_state<OP_H>(tmem, a_r, b_r, true);
+    const bool state_now = has_state && !strong;
+    if (state_now) {        // the carried-state product first: it is the last reader of the A1 planes
+      bw_issue_state<OP_H>(tmem, a_r, b_r, false);
+      if (DOT) mma_commit(&bars[3]);
+    }
+    bw_issue_out(tmem, x_r, two_step || state_now);
     mma_commit(&bars[2]);
+    if (DOT) {
+      // The rows of q (k) for the decay dots arrive by TMA in the A1 region as soon as no MMA reads it any more (a
+      // per-lane global read of one's own row costs 32 cache lines per instruction).
+      bool free_now = true;
+      if (state_now) free_now = mbar_wait(&bars[3], 0, 227);
+      if (free_now) {
+        mbar_arrive_expect_tx(&bars[0], 2 * 16384);
+        tma_load_2d(RA, mdot, &bars[0], 0, row0);
+        tma_load_2d(RA + 16384, mdot, &bars[0], 64, row0);
+      }
+    }
   }
   __syncwarp();
   {
@@ -411,32 +428,32 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     const size_t obase = (MODE == M_FWD && p.y_token_major)
                              ? (((size_t)L.b * p.T + L.t0 + r) * p.H + h) * (size_t)(TD * 2) + hf * 64 : rbase;
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(outp) + obase;
-    const __nv_bfloat16* drow = reinterpret_cast<const __nv_bfloat16*>(MODE == M_DQ ? p.q : p.k) + rbase;
     const bool valid = r < L.len;
     uint4 dpre[2][4];
-    if ((MODE == M_DQ || MODE == M_DK) && valid) {
-#pragma unroll
-      for (int g = 0; g < 8; ++g) dpre[g >> 2][g & 3] = __ldg(reinterpret_cast<const uint4*>(drow) + g);
-    }
     ok = mbar_wait(&bars[2], 0, 223) && ok;
     tc_fence_after();
+    if (DOT) {
+      ok = mbar_wait(&bars[0], 1, 228) && ok;      // second use of the tile barrier: the rows for the dots
+#pragma unroll
+      for (int g = 0; g < 8; ++g) dpre[g >> 2][g & 3] = *reinterpret_cast<const uint4*>(RA + hf * 16384 + sw128(r, g));
+    }
     const float rf = strong ? 1.f : rfac[r];
-    // A full chunk leaves through the A1 region, which every MMA has finished reading: each warp stages its 32 rows
+    // A full chunk leaves through the X2 region, which every MMA has finished reading: each warp stages its 32 rows
     // x 128 bytes there and one TMA store moves the block (whole 128-byte lines instead of 16 bytes per lane and
     // row).  A ragged chunk (its rows past `len` belong to someone else) and the token-major layout store per lane.
     const bool bulk = ok && L.len == TC && !(MODE == M_FWD && p.y_token_major);      // CTA-uniform
-    unsigned char* wbox = RA + hf * 16384 + q4 * 4096;                               // this warp's 32 x 128 B block
+    unsigned char* wbox = RC + hf * 16384 + q4 * 4096;                               // this warp's 32 x 128 B block
     float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc)
-      dot += bw_epi_out<(MODE == M_DQ || MODE == M_DK)>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok,
+      dot += bw_epi_out<DOT>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok,
                                                       bulk ? wbox + lane * 128 : nullptr, lane & 7);
     if (bulk) {
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) tma_store_2d_keep(mout, wbox, hf * 64, row0 + q4 * 32);
     }
-    if (MODE == M_DQ || MODE == M_DK) {
+    if (DOT) {
       dots[hf * TC + r] = dot;
       __syncthreads();
       if (tid < L.len && ok) {
@@ -459,7 +476,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
 __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwd(const __grid_constant__ ChunkMaps maps, ScanParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  chunk_job<M_FWD>(&maps.a1, &maps.b1, &maps.x2, &maps.out, p, blockIdx.x, blockIdx.y, smem);
+  chunk_job<M_FWD>(&maps.a1, &maps.b1, &maps.x2, &maps.out, &maps.a1, p, blockIdx.x, blockIdx.y, smem);
 }
 
 // the three gradients: grid = (3 * chunks, H); CTA x works on chunk x / 3, job x % 3 (dq, dv, dk), so the CTAs that
@@ -468,9 +485,9 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_bwd(const __grid_constant__
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int chunk_x = blockIdx.x / 3, job = blockIdx.x - 3 * chunk_x;
-  if (job == 0) chunk_job<M_DQ>(&maps.dy, &maps.v, &maps.k, &maps.dq, p, chunk_x, blockIdx.y, smem);
-  else if (job == 1) chunk_job<M_DV>(&maps.k, &maps.q, &maps.dy, &maps.dv, p, chunk_x, blockIdx.y, smem);
-  else chunk_job<M_DK>(&maps.v, &maps.dy, &maps.q, &maps.dk, p, chunk_x, blockIdx.y, smem);
+  if (job == 0) chunk_job<M_DQ>(&maps.dy, &maps.v, &maps.k, &maps.dq, &maps.q, p, chunk_x, blockIdx.y, smem);
+  else if (job == 1) chunk_job<M_DV>(&maps.k, &maps.q, &maps.dy, &maps.dv, &maps.k, p, chunk_x, blockIdx.y, smem);
+  else chunk_job<M_DK>(&maps.v, &maps.dy, &maps.q, &maps.dk, &maps.k, p, chunk_x, blockIdx.y, smem);
 }
 
 // ---------------------------------------------------------------------------------------------
