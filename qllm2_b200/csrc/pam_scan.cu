@@ -190,6 +190,13 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   return QPAM_OK;
 }
 
+// Output tensor as the target of the chunk kernels' TMA stores (boxes of 64 elements x 32 rows): [B*H*T rows][128], or
+// for the token-major layout [B*T rows][H*128].
+static int make_out_map(CUtensorMap* m, const qpam_scan_args* a, bool token_major) {
+  if (token_major) return make_map(m, a->y, (int64_t)a->H * 128, (int64_t)a->B * a->T, (int64_t)a->H * 128, 64, 32);
+  return make_map(m, a->y, 128, (int64_t)a->B * a->H * a->T, 128, 64, 32);
+}
+
 // bf16 / d = 64 / one state: tensor-core kernels on 128-token chunks
 static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t st, bool token_major = false) {
   ScanParams p = make_params(a, L);
@@ -207,8 +214,7 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
     if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
-    if (token_major) maps.out = maps.a1;     // not used: the token-major layout is stored per lane
-    else if ((rc = make_map(&maps.out, a->y, 128, rows, 128, 64, 32))) return rc;
+    if ((rc = make_out_map(&maps.out, a, token_major))) return rc;
     if ((rc = set_smem(tcs::k_tc_chunk_fwd, tcs::CHUNK2_SMEM))) return rc;
     tcs::k_tc_chunk_fwd<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk<fwd>");
@@ -232,7 +238,7 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
     if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
     if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
-    maps.out = maps.a1;      // not used by this kernel
+    if ((rc = make_out_map(&maps.out, a, token_major))) return rc;
     if ((rc = set_smem(tcs::k_tc_chunk_fwdK, tcs::CHUNKK_SMEM))) return rc;
     tcs::k_tc_chunk_fwdK<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNKK_SMEM, st>>>(maps, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_fwdK");

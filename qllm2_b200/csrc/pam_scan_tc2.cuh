@@ -440,8 +440,9 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     const float rf = strong ? 1.f : rfac[r];
     // A full chunk leaves through the X2 region, which every MMA has finished reading: each warp stages its 32 rows
     // x 128 bytes there and one TMA store moves the block (whole 128-byte lines instead of 16 bytes per lane and
-    // row).  A ragged chunk (its rows past `len` belong to someone else) and the token-major layout store per lane.
-    const bool bulk = ok && L.len == TC && !(MODE == M_FWD && p.y_token_major);      // CTA-uniform
+    // row).  A ragged chunk (its rows past `len` belong to someone else) stores per lane.
+    const bool bulk = ok && L.len == TC;                                             // CTA-uniform
+    const bool tok = MODE == M_FWD && p.y_token_major;     // [B, T, H, d, 2]: the map's rows are tokens, a row holds all heads
     unsigned char* wbox = RC + hf * 16384 + q4 * 4096;                               // this warp's 32 x 128 B block
     float dot = 0.f;
 #pragma unroll
@@ -451,7 +452,8 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     if (bulk) {
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) tma_store_2d_keep(mout, wbox, hf * 64, row0 + q4 * 32);
+      if (lane == 0)
+        tma_store_2d_keep(mout, wbox, tok ? h * 128 + hf * 64 : hf * 64, (tok ? L.b * p.T + L.t0 : row0) + q4 * 32);
     }
     if (DOT) {
       dots[hf * TC + r] = dot;

@@ -304,6 +304,10 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
     const size_t rbase = (p.y_token_major ? (((size_t)L.b * p.T + L.t0 + r) * p.H + h) * (size_t)(TD * 2)
                                           : token_base(p, L.b, h, L.t0 + r, TD)) + hf * 64;   // channels [32 hf, 32 hf + 32)
     __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.y) + rbase;
+    // a full chunk leaves through the X2 region (no MMA reads it any more): 32 rows x 128 bytes per warp, one TMA
+    // store each; a ragged chunk stores per lane
+    const bool bulk = ok && L.len == TC;                                             // CTA-uniform
+    unsigned char* wrow = RC + hf * 16384 + (warp & 3) * 4096 + lane * 128;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc) {
       float vr[16], vi[16];
@@ -311,11 +315,21 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
       tmem_ld16(tlane + 192 + hf * 32 + cc * 16, vi);
       if (ok && r < L.len) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) =
-              make_uint4(pack_bf162(vr[4 * g], vi[4 * g]), pack_bf162(vr[4 * g + 1], vi[4 * g + 1]),
-                         pack_bf162(vr[4 * g + 2], vi[4 * g + 2]), pack_bf162(vr[4 * g + 3], vi[4 * g + 3]));
+        for (int g = 0; g < 4; ++g) {
+          const uint4 pk = make_uint4(pack_bf162(vr[4 * g], vi[4 * g]), pack_bf162(vr[4 * g + 1], vi[4 * g + 1]),
+                                      pack_bf162(vr[4 * g + 2], vi[4 * g + 2]), pack_bf162(vr[4 * g + 3], vi[4 * g + 3]));
+          if (bulk) *reinterpret_cast<uint4*>(wrow + (((4 * cc + g) ^ (lane & 7)) << 4)) = pk;
+          else *reinterpret_cast<uint4*>(orow + cc * 32 + g * 8) = pk;
+        }
       }
+    }
+    if (bulk) {
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0)
+        tma_store_2d_keep(&maps.out, RC + hf * 16384 + (warp & 3) * 4096, p.y_token_major ? h * 128 + hf * 64 : hf * 64,
+                          (p.y_token_major ? L.b * p.T + L.t0 : (L.b * p.H + h) * p.T + L.t0) + (warp & 3) * 32);
+      if (lane == 0) tma_store_wait_read();
     }
   }
   tc_fence_before();
