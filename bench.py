@@ -503,17 +503,36 @@ def scan_k3(dev, B, H, T, d, C, rank, iters=10):
         gg, cc = gamma.detach().requires_grad_(True), coef.detach().requires_grad_(True)
         y, _ = ops.pam_scan(qq, kk, vv, gg, coef=cc, chunk=C)
         return torch.autograd.grad(y, [qq, kk, vv, gg, cc], dy)
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    return {"ms_per_step": e0.elapsed_time(e1) / iters,
-            "config": f"B={B} H={H} T={T} d={d} K=3 bf16, read-out weights and all five gradients, eager launches"}
+    def time_ms(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    eager = time_ms(step)
+    out = {"ms_per_step": eager, "ms_per_step_eager": eager,
+           "config": f"B={B} H={H} T={T} d={d} K=3 bf16, read-out weights and all five gradients"}
+    try:      # the same step replayed from a CUDA graph, as the headline is
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        g_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_):
+            keep = step()
+        out["ms_per_step"] = time_ms(g_.replay)
+        out["launch"] = "cuda_graph"
+        del keep
+    except Exception as exc:  # noqa: BLE001
+        out["launch"] = f"eager ({type(exc).__name__})"
+    return out
 
 
 def vocab_parallel_ce(dev, rank, world, peaks, iters=5):

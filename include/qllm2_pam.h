@@ -118,6 +118,14 @@ int qpam_scan_bwd(const qpam_scan_args* args, const void* dy, void* dq, void* dk
                   float* dgamma, float* dcoef, const float* ds_final, float* ds0,
                   int32_t states_valid, void* stream);
 
+/* qpam_scan_bwd for one state with dq, dk, dv ADDED to the values the buffers already hold (dgamma, ds0 are
+ * written as usual).  The K phase-routed states of a layer (v11/model.py:657-781) are K scans over the same
+ * q, k, v whose gradients sum (autograd does that sum in the reference): the first state's backward writes, the
+ * others accumulate, with the additions done by the copy engine (TMA reduce).  Offered where the tensor-core
+ * kernels run (bf16, d = 64, K = 1 per call, no coef); QPAM_EUNSUPPORTED otherwise. */
+int qpam_scan_bwd_accumulate(const qpam_scan_args* args, const void* dy, void* dq, void* dk, void* dv,
+                             float* dgamma, const float* ds_final, float* ds0, int32_t states_valid, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * O(1) recurrent decode step over a pool of per-sequence state slots.
  *

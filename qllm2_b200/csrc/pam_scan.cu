@@ -249,7 +249,8 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
 // bf16 / d = 64 / one state, backward: gradient state sums -> reverse carry (with the anchors of the decay
 // gradient) -> ONE launch for the dq, dv, dk jobs of every chunk -> dgamma.  Everything stays on the caller's stream.
 static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk, void* dv,
-                       float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st) {
+                       float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st,
+                       bool accumulate = false) {
   ScanParams p = make_params(a, L);
   p.dy = dy; p.dq = dq; p.dk = dk; p.dv = dv;
   p.dgamma = dgamma; p.dcoef = nullptr; p.ds_final = ds_final; p.ds0 = ds0;
@@ -284,8 +285,13 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     if ((rc = make_map(&maps.dq, dq, 128, rows, 128, 64, 32))) return rc;
     if ((rc = make_map(&maps.dk, dk, 128, rows, 128, 64, 32))) return rc;
     if ((rc = make_map(&maps.dv, dv, 128, rows, 128, 64, 32))) return rc;
-    if ((rc = set_smem(tcs::k_tc_chunk_bwd, tcs::CHUNK2_SMEM))) return rc;
-    tcs::k_tc_chunk_bwd<<<dim3(3 * L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+    if (accumulate) {
+      if ((rc = set_smem(tcs::k_tc_chunk_bwd<true>, tcs::CHUNK2_SMEM))) return rc;
+      tcs::k_tc_chunk_bwd<true><<<dim3(3 * L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+    } else {
+      if ((rc = set_smem(tcs::k_tc_chunk_bwd<false>, tcs::CHUNK2_SMEM))) return rc;
+      tcs::k_tc_chunk_bwd<false><<<dim3(3 * L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, p);
+    }
     QPAM_LAUNCH_CHECK("k_tc_chunk<dq,dv,dk>");
     tcs::k_tc_dgamma_finalize<<<dim3(L.grid_chunks, a->H), 128, 0, st>>>(p, anchors);
     QPAM_LAUNCH_CHECK("k_tc_dgamma_finalize");
@@ -414,6 +420,29 @@ extern "C" int qpam_scan_bwd(const qpam_scan_args* a, const void* dy, void* dq, 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (tc_bwd) return scan_bwd_tc(a, L, dy, dq, dk, dv, dgamma, ds_final, ds0, states_valid, st);
   QPAM_DISPATCH_SCAN(scan_bwd_t, a, L, dy, dq, dk, dv, dgamma, dcoef, ds_final, ds0, states_valid, st);
+}
+
+// The same backward with dq, dk, dv ADDED to what the buffers hold: the K phase-routed states of a layer are K
+// scans over the same q, k, v, and their gradients sum.  Tensor-core path only (one state per call).
+extern "C" int qpam_scan_bwd_accumulate(const qpam_scan_args* a, const void* dy, void* dq, void* dk, void* dv,
+                                        float* dgamma, const float* ds_final, float* ds0, int32_t states_valid,
+                                        void* stream) {
+  int rc = check_scan_args(a);
+  if (rc) return rc;
+  QPAM_REQUIRE(dy && dq && dk && dv && dgamma, "scan bwd: dy/dq/dk/dv/dgamma must not be NULL");
+  const bool tc_bwd = tc_fwd_eligible(a) && a->T > 0 &&
+                      (((uintptr_t)dy | (uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv) & 15) == 0;
+  if (!tc_bwd) {
+    set_error("scan bwd (accumulate): offered on the tensor-core path only (bf16, d = 64, one state, 16-byte aligned tensors)");
+    return QPAM_EUNSUPPORTED;
+  }
+  const ScanLayout L = scan_layout(a, tcs::TC);
+  if (fwd_chunk_len(a) != L.ch) states_valid = 0;
+  if (a->workspace_bytes < L.total_bwd) {
+    set_error("scan bwd: workspace %zu bytes < required %zu", a->workspace_bytes, L.total_bwd);
+    return QPAM_EWORKSPACE;
+  }
+  return scan_bwd_tc(a, L, dy, dq, dk, dv, dgamma, ds_final, ds0, states_valid, reinterpret_cast<cudaStream_t>(stream), true);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -201,7 +201,7 @@ __device__ __forceinline__ void bw_epi_scores(uint32_t tlane_slot, int q4, int c
 // four 16-byte pieces of the interleaved bf16 row that cover these channels ------------------------------------
 // `stage` != nullptr: the 16-byte pieces go to this row of a 128-byte-swizzled staging block (piece index
 // 4 * (cb & 1) + g, row & 7 = `sw`) instead of global memory; a TMA store moves the block afterwards.
-template <bool DOT>
+template <bool DOT, bool ADD = false>
 __device__ __forceinline__ float bw_epi_out(uint32_t tlane_slot, int cb, float rf, __nv_bfloat16* __restrict__ orow,
                                             const uint4 (&xg)[4], bool valid, unsigned char* stage = nullptr, int sw = 0) {
   using namespace umma;
@@ -218,8 +218,21 @@ __device__ __forceinline__ float bw_epi_out(uint32_t tlane_slot, int cb, float r
     for (int g = 0; g < 4; ++g) {   // 4 complex channels -> one 16-byte store
       const uint4 pk = make_uint4(pack_bf162(vr[4 * g], vi[4 * g]), pack_bf162(vr[4 * g + 1], vi[4 * g + 1]),
                                   pack_bf162(vr[4 * g + 2], vi[4 * g + 2]), pack_bf162(vr[4 * g + 3], vi[4 * g + 3]));
-      if (stage != nullptr) *reinterpret_cast<uint4*>(stage + (((4 * (cb & 1) + g) ^ sw) << 4)) = pk;
-      else *reinterpret_cast<uint4*>(orow + g * 8) = pk;
+      if (stage != nullptr) {
+        *reinterpret_cast<uint4*>(stage + (((4 * (cb & 1) + g) ^ sw) << 4)) = pk;
+      } else if (ADD) {          // ragged chunk of an accumulating call: read, add, write (this lane's own row)
+        const uint4 o = *reinterpret_cast<const uint4*>(orow + g * 8);
+        const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+        uint32_t nw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x2 = unpack_bf162(ow[e]);
+          nw[e] = pack_bf162(x2.x + vr[4 * g + e], x2.y + vi[4 * g + e]);
+        }
+        *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(nw[0], nw[1], nw[2], nw[3]);
+      } else {
+        *reinterpret_cast<uint4*>(orow + g * 8) = pk;
+      }
       if (DOT) {
         const uint32_t xw[4] = {xg[g].x, xg[g].y, xg[g].z, xg[g].w};
 #pragma unroll
@@ -255,7 +268,7 @@ __device__ __forceinline__ void rescale_acc_half(uint32_t tlane_slot, int hf, fl
 // ---------------------------------------------------------------------------------------------
 // One job of one chunk (256 threads; the caller's CTA holds nothing else).
 // ---------------------------------------------------------------------------------------------
-template <int MODE>
+template <int MODE, bool ACC = false>      // ACC: the output is added to what the buffer holds (gradients only)
 __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, const CUtensorMap* __restrict__ mb1,
                                           const CUtensorMap* __restrict__ mx2, const CUtensorMap* __restrict__ mout,
                                           const CUtensorMap* __restrict__ mdot, const ScanParams& p, int chunk_x, int h,
@@ -443,17 +456,21 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     // row).  A ragged chunk (its rows past `len` belong to someone else) stores per lane.
     const bool bulk = ok && L.len == TC;                                             // CTA-uniform
     const bool tok = MODE == M_FWD && p.y_token_major;     // [B, T, H, d, 2]: the map's rows are tokens, a row holds all heads
+    constexpr bool accum = ACC && MODE != M_FWD;             // gradients of several scans over the same q, k, v add up
     unsigned char* wbox = RC + hf * 16384 + q4 * 4096;                               // this warp's 32 x 128 B block
     float dot = 0.f;
 #pragma unroll
     for (int cc = 0; cc < 2; ++cc)
-      dot += bw_epi_out<DOT>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok,
-                                                      bulk ? wbox + lane * 128 : nullptr, lane & 7);
+      dot += bw_epi_out<DOT, accum>(tl, 2 * hf + cc, rf, orow + cc * 32, dpre[cc], valid && ok,
+                                    bulk ? wbox + lane * 128 : nullptr, lane & 7);
     if (bulk) {
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0)
-        tma_store_2d_keep(mout, wbox, tok ? h * 128 + hf * 64 : hf * 64, (tok ? L.b * p.T + L.t0 : row0) + q4 * 32);
+      if (lane == 0) {
+        const int ox = tok ? h * 128 + hf * 64 : hf * 64, oy = (tok ? L.b * p.T + L.t0 : row0) + q4 * 32;
+        if (accum) tma_reduce_add_2d(mout, wbox, ox, oy);      // global += tile, done by the copy engine
+        else tma_store_2d_keep(mout, wbox, ox, oy);
+      }
     }
     if (DOT) {
       dots[hf * TC + r] = dot;
@@ -483,13 +500,15 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwd(const __grid_constant__
 
 // the three gradients: grid = (3 * chunks, H); CTA x works on chunk x / 3, job x % 3 (dq, dv, dk), so the CTAs that
 // read the same q, k, v, dy tiles are scheduled together
+// ACC: dq, dk, dv are added to what the buffers hold (the K states of a layer share q, k, v)
+template <bool ACC>
 __global__ void __launch_bounds__(256, 2) k_tc_chunk_bwd(const __grid_constant__ BwdMaps maps, ScanParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int chunk_x = blockIdx.x / 3, job = blockIdx.x - 3 * chunk_x;
-  if (job == 0) chunk_job<M_DQ>(&maps.dy, &maps.v, &maps.k, &maps.dq, &maps.q, p, chunk_x, blockIdx.y, smem);
-  else if (job == 1) chunk_job<M_DV>(&maps.k, &maps.q, &maps.dy, &maps.dv, &maps.k, p, chunk_x, blockIdx.y, smem);
-  else chunk_job<M_DK>(&maps.v, &maps.dy, &maps.q, &maps.dk, &maps.k, p, chunk_x, blockIdx.y, smem);
+  if (job == 0) chunk_job<M_DQ, ACC>(&maps.dy, &maps.v, &maps.k, &maps.dq, &maps.q, p, chunk_x, blockIdx.y, smem);
+  else if (job == 1) chunk_job<M_DV, ACC>(&maps.k, &maps.q, &maps.dy, &maps.dv, &maps.k, p, chunk_x, blockIdx.y, smem);
+  else chunk_job<M_DK, ACC>(&maps.v, &maps.dy, &maps.q, &maps.dk, &maps.k, p, chunk_x, blockIdx.y, smem);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -336,6 +336,69 @@ class _StateCombineFn(torch.autograd.Function):
         return (dcoef.to(coef_dtype), None, *dyks)
 
 
+class _StateCombineStackedFn(torch.autograd.Function):
+    """`_StateCombineFn` for state outputs held in ONE tensor [K, ..., d, 2]: the gradient comes back as one tensor of
+    the same shape, so a producer that made all K outputs at once gets it without a stacking copy."""
+
+    @staticmethod
+    def forward(ctx, coef, token_major, ys):
+        ys = ys.contiguous()
+        K = ys.shape[0]
+        d = ys.shape[-2]
+        R = ys[0].numel() // (2 * d)
+        cf = coef.detach().float().contiguous()
+        arr = (_lib.c_void_p * K)(*[ys[k_].data_ptr() for k_ in range(K)])
+        if token_major:
+            B, H, T = ys.shape[1:4]
+            y = torch.empty(B, T, H * d, 2, dtype=ys.dtype, device=ys.device)
+            check(_lib.lib().qpam_state_combine_tokens_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, B, H, T, d,
+                                                           stream_ptr()), "qpam_state_combine_tokens_fwd")
+        else:
+            y = torch.empty_like(ys[0])
+            check(_lib.lib().qpam_state_combine_fwd(arr, ptr(cf), ptr(y), dtype_code(y.dtype), K, R, d, stream_ptr()),
+                  "qpam_state_combine_fwd")
+        ctx.save_for_backward(cf, ys)
+        ctx.meta = (coef.dtype, token_major)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cf, ys = ctx.saved_tensors
+        coef_dtype, token_major = ctx.meta
+        K = ys.shape[0]
+        d = ys.shape[-2]
+        R = ys[0].numel() // (2 * d)
+        dy = dy.to(ys.dtype).contiguous()
+        dys = torch.empty_like(ys)
+        dcoef = torch.empty_like(cf)
+        arr = (_lib.c_void_p * K)(*[ys[k_].data_ptr() for k_ in range(K)])
+        darr = (_lib.c_void_p * K)(*[dys[k_].data_ptr() for k_ in range(K)])
+        if token_major:
+            B, H, T = ys.shape[1:4]
+            check(_lib.lib().qpam_state_combine_tokens_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K,
+                                                           B, H, T, d, stream_ptr()), "qpam_state_combine_tokens_bwd")
+        else:
+            check(_lib.lib().qpam_state_combine_bwd(arr, ptr(cf), ptr(dy), darr, ptr(dcoef), dtype_code(dy.dtype), K, R, d,
+                                                    stream_ptr()), "qpam_state_combine_bwd")
+        return dcoef.to(coef_dtype), None, dys
+
+
+def state_combine_stacked(coef: torch.Tensor, ys: torch.Tensor, token_major: bool = False) -> torch.Tensor:
+    """`state_combine` for the K state outputs as one tensor ys [K, ..., d, 2] (same checks, same kernels)."""
+    _require_cuda(coef, ys)
+    K, shape, dt = ys.shape[0], ys.shape[1:], ys.dtype
+    d = shape[-2]
+    if not 1 <= K <= 4 or shape[-1] != 2:
+        raise _lib.QPamError(f"state_combine: 1..4 states of shape [..., d, 2]; got {tuple(ys.shape)}")
+    if dt not in (torch.float32, torch.bfloat16) or d < 4 or d > 128 or d & (d - 1):
+        raise _lib.QPamError(f"state_combine: bf16/f32 and d a power of two in [4,128]; got {dt}, d={d}")
+    if tuple(coef.shape) != (K, *shape[:-2], 2):
+        raise _lib.QPamError(f"state_combine: coef must be {(K, *shape[:-2], 2)}, got {tuple(coef.shape)}")
+    if token_major and len(shape) != 5:
+        raise _lib.QPamError("state_combine: token_major needs [B,H,T,d,2] state outputs")
+    return _StateCombineStackedFn.apply(coef, token_major, ys)
+
+
 @torch.no_grad()
 def state_combine_tokens(coef: torch.Tensor, yks) -> torch.Tensor:
     """Inference form of `state_combine` for yks[k] [B, H, T, d, 2]: the result is written token-major,

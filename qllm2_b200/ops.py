@@ -93,6 +93,68 @@ class _PamScanFn(torch.autograd.Function):
         return dq, dk, dv, dgamma, dcoef, ds0, None, None, None, None, None
 
 
+class _PamScanStatesFn(torch.autograd.Function):
+    """K single-state scans over the same q, k, v (bf16, d = 64: the tensor-core kernels), one per decay row of
+    `gamma` [K,B,H,T]: returns the per-state outputs ys [K,B,H,T,d,2] and final states [K,S,H,d,d,2].  The
+    backward runs the K backward scans into ONE set of dq, dk, dv buffers: the first writes, the others add
+    (qpam_scan_bwd_accumulate), so the sum over the states costs no extra pass."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, gamma, s0, cu_seqlens, q_scale, eps, chunk):
+        L = _lib.lib()
+        _require_cuda(q, k, v, gamma)
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        gamma = gamma.float().contiguous()
+        s0 = None if s0 is None else s0.float().contiguous()
+        B, H, T, d = q.shape[:4]
+        K = gamma.shape[0]
+        S = B if cu_seqlens is None else cu_seqlens.numel() - 1
+        ys = torch.empty((K,) + tuple(q.shape), dtype=q.dtype, device=q.device)
+        s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=q.device)
+        need_bwd = any(t is not None and t.requires_grad for t in (q, k, v, gamma, s0))
+        wss = []
+        for kk in range(K):
+            a = _scan_args(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1], cu_seqlens, ys[kk],
+                           s_final[kk:kk + 1], q_scale, eps, chunk)
+            ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 1 if need_bwd else 0), q.device)
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            check(L.qpam_scan_fwd(C.byref(a), stream_ptr()), "qpam_scan_fwd")
+            wss.append(ws if need_bwd else None)
+        ctx.save_for_backward(q, k, v, gamma, s0, cu_seqlens, *[w_ for w_ in wss if w_ is not None])
+        ctx.cfg = (q_scale, eps, chunk, need_bwd)
+        ctx.set_materialize_grads(False)
+        return ys, s_final
+
+    @staticmethod
+    def backward(ctx, dys, ds_final):
+        L = _lib.lib()
+        q, k, v, gamma, s0, cu_seqlens, *wss = ctx.saved_tensors
+        q_scale, eps, chunk, _ = ctx.cfg
+        K = gamma.shape[0]
+        dys = torch.zeros((K,) + tuple(q.shape), dtype=q.dtype, device=q.device) if dys is None else dys.contiguous().to(q.dtype)
+        if dys.shape != (K,) + tuple(q.shape):
+            raise _lib.QPamError(f"dys shape {tuple(dys.shape)} != ys shape {(K,) + tuple(q.shape)}")
+        if ds_final is not None:
+            ds_final = ds_final.float().contiguous()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dgamma = torch.empty_like(gamma)
+        ds0 = torch.empty_like(s0) if (s0 is not None and ctx.needs_input_grad[4]) else None
+        for kk in range(K):
+            a = _scan_args(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1], cu_seqlens, None, None,
+                           q_scale, eps, chunk)
+            ws = wss[kk]
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            dsf = None if ds_final is None else ds_final[kk:kk + 1]
+            d0 = None if ds0 is None else ds0[kk:kk + 1]
+            if kk == 0:
+                check(L.qpam_scan_bwd(C.byref(a), ptr(dys[kk]), ptr(dq), ptr(dk), ptr(dv), ptr(dgamma[kk:kk + 1]), None,
+                                      ptr(dsf), ptr(d0), 1, stream_ptr()), "qpam_scan_bwd")
+            else:
+                check(L.qpam_scan_bwd_accumulate(C.byref(a), ptr(dys[kk]), ptr(dq), ptr(dk), ptr(dv), ptr(dgamma[kk:kk + 1]),
+                                                 ptr(dsf), ptr(d0), 1, stream_ptr()), "qpam_scan_bwd_accumulate")
+        return dq, dk, dv, dgamma, ds0, None, None, None, None
+
+
 def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: Optional[int] = None,
              eps: float = GAMMA_EPS, chunk: int = 64, save_states: bool = True, token_major: bool = False):
     """Chunked dual-form PAM scan on the GPU.  (token_major=True returns y as [B, T, H*d, 2], the head merge
@@ -150,9 +212,18 @@ def pam_scan(q, k, v, gamma, *, coef=None, s0=None, cu_seqlens=None, head_dim: O
         # Phase-routed K-state scan on the tensor-core kernels: y = sum_k c_k y^(k), where y^(k) is the
         # single-state scan with decay gamma^(k) on the same q, k, v (the fused K-state form of the
         # reference, v11/model.py:657-781, is algebraically this sum).  autograd composes the backward:
-        # K single-state backward scans with upstream conj(c_k) dy, and dc_k = <dy, y^(k)>.
+        # K single-state backward scans with upstream conj(c_k) dy, and dc_k = <dy, y^(k)>.  With the chunk states kept
+        # for the backward (save_states) the K scans share one autograd node whose backward accumulates dq, dk, dv in
+        # place (qpam_scan_bwd_accumulate) instead of leaving K partial gradients for autograd to add.
+        if save_states:
+            ys_all, finals = _PamScanStatesFn.apply(q, k, v, gamma, s0, cu_seqlens, head_dim ** -0.5, eps, chunk)
+            if coef is not None:
+                from .fused_elementwise import state_combine_stacked
+                return state_combine_stacked(coef, ys_all, token_major=token_major), finals
+            y = ys_all.sum(dim=0)
+            return (_merge_heads(y) if token_major else y), finals
         ys, finals = [], []
-        for kk in range(K):
+        for kk in range(K):        # states recomputed in the backward: one scan per state, autograd sums the gradients
             yk, sk = _PamScanFn.apply(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1],
                                       cu_seqlens, head_dim ** -0.5, eps, chunk, save_states)
             ys.append(yk)
