@@ -11,7 +11,7 @@ over GPUs (units are independent (batch, head) pairs: no collective on the data 
 
 One JSON line is printed by rank 0.  `--impl reference` times the reference's own CPU code path on the
 host cores instead: V11PAMLayer._forward_chunked_head itself when a checkout of the reference is importable
-(QLLM2_REFERENCE, default /root/reference), else its port oracle/torch_port.py; `cpu_baseline.kind` says which.
+(its path in the environment variable QLLM2_REFERENCE), else its port oracle/torch_port.py; `cpu_baseline.kind` says which.
 """
 from __future__ import annotations
 
@@ -50,8 +50,8 @@ def _cpu_scan_fn():
     V11PAMLayer._forward_chunked_head (v11/model.py:378-417) + autograd when a checkout is importable, else the
     port of the same operator mix."""
     from qllm2_b200 import synthetic  # noqa: F401
-    ref_root = os.environ.get("QLLM2_REFERENCE", "/root/reference")
-    if os.path.isdir(os.path.join(ref_root, "v11")):
+    ref_root = os.environ.get("QLLM2_REFERENCE", "")
+    if ref_root and os.path.isdir(os.path.join(ref_root, "v11")):
         try:
             sys.path.insert(0, ref_root)
             sys.dont_write_bytecode = True
