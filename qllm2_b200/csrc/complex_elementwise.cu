@@ -446,7 +446,9 @@ struct CombineParams {
   int H, T;       // > 0: y (forward) and dy (backward) are token-major, [b, t, h, :] for row r = (b, h, t)
 };
 
-template <typename T, bool BWD>
+// KK: the number of states as a compile-time constant, so that the K loads of a group are all in flight before the
+// first one is used
+template <typename T, bool BWD, int KK>
 __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
   const int gpr = p.d >> 2;  // vector groups per row
   const int64_t total = p.R * gpr;
@@ -464,10 +466,20 @@ __global__ void __launch_bounds__(256) k_state_combine(CombineParams p) {
       yo = (((b * p.T + t) * p.H + h) * p.d + g * 4) * 2;
     }
     if (BWD && on) V4<T>::ld(reinterpret_cast<const T*>(p.y) + yo, ar, ai);
-    for (int k = 0; k < p.K; ++k) {
-      const float2 c = on ? *reinterpret_cast<const float2*>(p.coef + ((int64_t)k * p.R + r) * 2) : make_float2(0.f, 0.f);
-      float yr[4] = {0.f, 0.f, 0.f, 0.f}, yi[4] = {0.f, 0.f, 0.f, 0.f};
-      if (on) V4<T>::ld(reinterpret_cast<const T*>(p.yk[k]) + off, yr, yi);
+    float2 cs[KK];
+    float yrs[KK][4], yis[KK][4];
+#pragma unroll
+    for (int k = 0; k < KK; ++k) {
+      cs[k] = on ? *reinterpret_cast<const float2*>(p.coef + ((int64_t)k * p.R + r) * 2) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) yrs[k][j] = yis[k][j] = 0.f;
+      if (on) V4<T>::ld(reinterpret_cast<const T*>(p.yk[k]) + off, yrs[k], yis[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < KK; ++k) {
+      const float2 c = cs[k];
+      const float (&yr)[4] = yrs[k];
+      const float (&yi)[4] = yis[k];
       if (!BWD) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -873,13 +885,17 @@ static int state_combine(bool bwd, const void* const* yk, void* const* dyk, cons
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t total = R * (d / 4);
   const int grid = (int)std::min<int64_t>((total + 255) / 256, sm_count() * 16);
-  if (dtype == QPAM_F32) {
-    if (bwd) k_state_combine<float, true><<<grid, 256, 0, st>>>(p);
-    else k_state_combine<float, false><<<grid, 256, 0, st>>>(p);
-  } else {
-    if (bwd) k_state_combine<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
-    else k_state_combine<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+#define QPAM_COMBINE(TT, KK_)                                                   \
+  if (K == KK_) {                                                              \
+    if (bwd) k_state_combine<TT, true, KK_><<<grid, 256, 0, st>>>(p);          \
+    else k_state_combine<TT, false, KK_><<<grid, 256, 0, st>>>(p);             \
   }
+  if (dtype == QPAM_F32) {
+    QPAM_COMBINE(float, 1) QPAM_COMBINE(float, 2) QPAM_COMBINE(float, 3) QPAM_COMBINE(float, 4)
+  } else {
+    QPAM_COMBINE(__nv_bfloat16, 1) QPAM_COMBINE(__nv_bfloat16, 2) QPAM_COMBINE(__nv_bfloat16, 3) QPAM_COMBINE(__nv_bfloat16, 4)
+  }
+#undef QPAM_COMBINE
   if (bwd) { QPAM_LAUNCH_CHECK("k_state_combine_bwd"); } else { QPAM_LAUNCH_CHECK("k_state_combine_fwd"); }
   return QPAM_OK;
 }
