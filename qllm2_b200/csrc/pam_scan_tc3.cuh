@@ -164,27 +164,53 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
         float xr[16], xi[16];
         tmem_ld16(tlane + c0, xr);
         tmem_ld16(tlane + 128 + c0, xi);
+        // (the two loops differ only in how a state's column factor is formed: the common case -- no state of this
+        // chunk decays strongly, CTA-uniform -- keeps the exponentials out of the per-score code)
+        if (strong_mask == 0u) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          float wr[2], wi[2];
+          for (int j = 0; j < 16; j += 2) {
+            float wr[2], wi[2];
 #pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int c = c0 + j + e;
-            float gr = 0.f, gi = 0.f;
+            for (int e = 0; e < 2; ++e) {
+              const int c = c0 + j + e;
+              float gr = 0.f, gi = 0.f;
 #pragma unroll
-            for (int k = 0; k < KMAX; ++k)
-              if (k < K) {
-                const float cf = ((strong_mask >> k) & 1u) ? __expf(fminf(0.f, Acum[k * TC + r] - Acum[k * TC + c]))
-                                                           : cfac[k * TC + c];
-                gr = fmaf(rk[k].x, cf, gr);
-                gi = fmaf(rk[k].y, cf, gi);
-              }
-            if (c > r) gr = gi = 0.f;
-            wr[e] = xr[j + e] * gr - xi[j + e] * gi;
-            wi[e] = xr[j + e] * gi + xi[j + e] * gr;
+              for (int k = 0; k < KMAX; ++k)
+                if (k < K) {
+                  const float cf = cfac[k * TC + c];
+                  gr = fmaf(rk[k].x, cf, gr);
+                  gi = fmaf(rk[k].y, cf, gi);
+                }
+              if (c > r) gr = gi = 0.f;
+              wr[e] = xr[j + e] * gr - xi[j + e] * gi;
+              wi[e] = xr[j + e] * gi + xi[j + e] * gr;
+            }
+            tr[cc * 8 + (j >> 1)] = pack_bf162(wr[0], wr[1]);
+            ti[cc * 8 + (j >> 1)] = pack_bf162(wi[0], wi[1]);
           }
-          tr[cc * 8 + (j >> 1)] = pack_bf162(wr[0], wr[1]);
-          ti[cc * 8 + (j >> 1)] = pack_bf162(wi[0], wi[1]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            float wr[2], wi[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int c = c0 + j + e;
+              float gr = 0.f, gi = 0.f;
+#pragma unroll
+              for (int k = 0; k < KMAX; ++k)
+                if (k < K) {
+                  const float cf = ((strong_mask >> k) & 1u) ? __expf(fminf(0.f, Acum[k * TC + r] - Acum[k * TC + c]))
+                                                             : cfac[k * TC + c];
+                  gr = fmaf(rk[k].x, cf, gr);
+                  gi = fmaf(rk[k].y, cf, gi);
+                }
+              if (c > r) gr = gi = 0.f;
+              wr[e] = xr[j + e] * gr - xi[j + e] * gi;
+              wi[e] = xr[j + e] * gi + xi[j + e] * gr;
+            }
+            tr[cc * 8 + (j >> 1)] = pack_bf162(wr[0], wr[1]);
+            ti[cc * 8 + (j >> 1)] = pack_bf162(wi[0], wi[1]);
+          }
         }
       }
     }
