@@ -17,20 +17,43 @@ static inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 // QPAM_DEV_BAD_CU_SEQLENS in the device status word.
 constexpr int QPAM_DEV_BAD_CU_SEQLENS = 301;
 constexpr int QPAM_DEV_WAIT_SELFTEST = 299;
-__global__ void k_chunk_prefix_checked(const int32_t* __restrict__ cu, int32_t* __restrict__ prefix, int S, int ch, int T) {
-  if (blockIdx.x != 0 || threadIdx.x != 0) return;
-  bool good = cu[0] == 0;
-  int acc = 0;
-  prefix[0] = 0;
-  for (int s = 0; s < S; ++s) {
-    const int a = cu[s], e = cu[s + 1];
-    good = good && e >= a && e <= T;
-    acc += (max(0, e - a) + ch - 1) / ch;
-    prefix[s + 1] = acc;
+__global__ void __launch_bounds__(256) k_chunk_prefix_checked(const int32_t* __restrict__ cu, int32_t* __restrict__ prefix,
+                                                               int S, int ch, int T) {
+  // one CTA: sequences in tiles of 256, each tile an inclusive scan of the chunk counts (warp shuffles + one
+  // exchange through shared memory) on top of the running total; the descriptor is checked on the way
+  __shared__ int wsum[8];
+  __shared__ int carry_s, bad_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) { carry_s = 0; bad_s = (cu[0] != 0) ? 1 : 0; prefix[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < S; base += 256) {
+    const int s_ = base + tid;
+    int n = 0;
+    bool bad = false;
+    if (s_ < S) {
+      const int a = cu[s_], e = cu[s_ + 1];
+      bad = !(e >= a && e <= T);
+      n = (max(0, e - a) + ch - 1) / ch;
+    }
+    int inc = n;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    if (lane == 31) wsum[warp] = inc;
+    if (__any_sync(0xffffffffu, bad) && lane == 0) atomicOr(&bad_s, 1);
+    __syncthreads();
+    int before = carry_s;
+    for (int w = 0; w < warp; ++w) before += wsum[w];
+    if (s_ < S) prefix[s_ + 1] = before + inc;
+    __syncthreads();
+    if (tid == 255) carry_s = before + inc;
+    __syncthreads();
   }
-  if (!good) {
-    for (int s = 0; s <= S; ++s) prefix[s] = 0;
-    umma::record_device_error(QPAM_DEV_BAD_CU_SEQLENS);
+  if (bad_s) {
+    for (int s_ = tid; s_ <= S; s_ += 256) prefix[s_] = 0;
+    if (tid == 0) umma::record_device_error(QPAM_DEV_BAD_CU_SEQLENS);
   }
 }
 
@@ -141,7 +164,7 @@ template <int D, typename T>
 static int launch_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
   // chunk-local state sums, then the carry over the chunk axis
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
+    k_chunk_prefix_checked<<<1, 256, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   if (L.grid_chunks > 0) {
@@ -202,7 +225,7 @@ static int scan_fwd_tc(const qpam_scan_args* a, const ScanLayout& L, cudaStream_
   ScanParams p = make_params(a, L);
   p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
+    k_chunk_prefix_checked<<<1, 256, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   int rc;
@@ -227,7 +250,7 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
   ScanParams p = make_params(a, L);
   p.y_token_major = token_major ? 1 : 0;
   if (a->cu_seqlens != nullptr) {
-    k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
+    k_chunk_prefix_checked<<<1, 256, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
     QPAM_LAUNCH_CHECK("k_chunk_prefix");
   }
   int rc = tc_states(p, L, a, st);
@@ -259,7 +282,7 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     ScanParams pf = p;
     pf.s_final = nullptr;
     if (a->cu_seqlens != nullptr) {
-      k_chunk_prefix_checked<<<1, 32, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
+      k_chunk_prefix_checked<<<1, 256, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
       QPAM_LAUNCH_CHECK("k_chunk_prefix");
     }
     rc = tc_states(pf, L, a, st);
