@@ -72,6 +72,10 @@ __device__ __forceinline__ void deint_write(unsigned char* tile, int row, int hb
 
 // ---- MMA issue (one thread) -----------------------------------------------------------------------------
 // X = A1 conj(B1)^T : Xr = ar br^T + ai bi^T, Xi = ai br^T - ar bi^T  (planes K-major, K = 64)
+// IMAG_SWAPPED: the two halves of Xi are accumulated in the other order, so that the job whose operands are swapped
+// (dk: v dy^H against dq: dy v^H) adds the same numbers in the same order and gets the negated imaginary part bit
+// for bit.
+template <bool IMAG_SWAPPED = false>
 __device__ __forceinline__ void bw_issue_scores(uint32_t slot, uint32_t a_r, uint32_t b_r) {
   using namespace umma;
   constexpr uint32_t id = idesc_bf16(128, 128, false, false);
@@ -83,12 +87,21 @@ __device__ __forceinline__ void bw_issue_scores(uint32_t slot, uint32_t a_r, uin
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk)
     mma_bf16(slot, smem_desc_sw128(a_i + kk * 32, 16, 1024), smem_desc_sw128(b_i + kk * 32, 16, 1024), id, true);
+  if (!IMAG_SWAPPED) {
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk)
-    mma_bf16(slot + 128, smem_desc_sw128(a_i + kk * 32, 16, 1024), smem_desc_sw128(b_r + kk * 32, 16, 1024), id, kk > 0);
+    for (int kk = 0; kk < 4; ++kk)
+      mma_bf16(slot + 128, smem_desc_sw128(a_i + kk * 32, 16, 1024), smem_desc_sw128(b_r + kk * 32, 16, 1024), id, kk > 0);
 #pragma unroll
-  for (int kk = 0; kk < 4; ++kk)
-    mma_bf16(slot + 128, smem_desc_sw128(a_r + kk * 32, 16, 1024), smem_desc_sw128(b_i + kk * 32, 16, 1024), idn, true);
+    for (int kk = 0; kk < 4; ++kk)
+      mma_bf16(slot + 128, smem_desc_sw128(a_r + kk * 32, 16, 1024), smem_desc_sw128(b_i + kk * 32, 16, 1024), idn, true);
+  } else {
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      mma_bf16(slot + 128, smem_desc_sw128(a_r + kk * 32, 16, 1024), smem_desc_sw128(b_i + kk * 32, 16, 1024), idn, kk > 0);
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk)
+      mma_bf16(slot + 128, smem_desc_sw128(a_i + kk * 32, 16, 1024), smem_desc_sw128(b_r + kk * 32, 16, 1024), id, true);
+  }
 }
 
 // TMEM column of the packed bf16 scores of k-step kk (16 score columns = 8 TMEM columns): the thread that
@@ -149,10 +162,11 @@ __device__ __forceinline__ void bw_issue_state(uint32_t slot, uint32_t a_r, uint
 
 // ---- epilogue 1: decay-masked scores of this thread's row, columns [32 cb, 32 cb + 32), as packed bf16 ------
 // fast path: T = [mask] cfac[col] X;  slow path (STRONG): T = [mask] scale exp(-|A_row - A_col|) X.
-template <bool LOWER, bool STRONG>
+// ROWW: the row's own factor `rowf` multiplies the weight before the score is rounded (see chunk_job).
+template <bool LOWER, bool STRONG, bool ROWW>
 __device__ __forceinline__ void bw_epi_scores_t(uint32_t tlane_slot, int q4, int cb, int r, int len,
                                                 const float* __restrict__ cfac, const float* __restrict__ Acum,
-                                                float scale) {
+                                                float scale, float rowf) {
   using namespace umma;
   const int c0 = 32 * cb;
   const bool dead = LOWER ? (c0 > q4 * 32 + 31) : (c0 + 31 < q4 * 32);      // warp-uniform
@@ -175,7 +189,8 @@ __device__ __forceinline__ void bw_epi_scores_t(uint32_t tlane_slot, int q4, int
           const int c = c0 + 16 * hh + j + e;
           bool on = full || (LOWER ? (c <= r) : (c >= r));
           if (!LOWER) on = on && (c < len);
-          const float w = STRONG ? scale * __expf(fminf(0.f, LOWER ? a_r - Acum[c] : Acum[c] - a_r)) : cfac[c];
+          const float w = STRONG ? scale * __expf(fminf(0.f, LOWER ? a_r - Acum[c] : Acum[c] - a_r))
+                                 : (ROWW ? rowf * cfac[c] : cfac[c]);
           d[e] = on ? w : 0.f;
         }
         const float r0 = __uint_as_float(hh ? xr1[j] : xr0[j]), r1 = __uint_as_float(hh ? xr1[j + 1] : xr0[j + 1]);
@@ -189,12 +204,12 @@ __device__ __forceinline__ void bw_epi_scores_t(uint32_t tlane_slot, int q4, int
   tmem_st16(tlane_slot + c0, tr);
   tmem_st16(tlane_slot + c0 + 16, ti);
 }
-template <bool LOWER>
+template <bool LOWER, bool ROWW = false>
 __device__ __forceinline__ void bw_epi_scores(uint32_t tlane_slot, int q4, int cb, int r, int len, bool strong,
                                               const float* __restrict__ cfac, const float* __restrict__ Acum,
-                                              float scale) {
-  if (strong) bw_epi_scores_t<LOWER, true>(tlane_slot, q4, cb, r, len, cfac, Acum, scale);
-  else bw_epi_scores_t<LOWER, false>(tlane_slot, q4, cb, r, len, cfac, Acum, scale);
+                                              float scale, float rowf = 1.f) {
+  if (strong) bw_epi_scores_t<LOWER, true, false>(tlane_slot, q4, cb, r, len, cfac, Acum, scale, 1.f);
+  else bw_epi_scores_t<LOWER, false, ROWW>(tlane_slot, q4, cb, r, len, cfac, Acum, scale, rowf);
 }
 
 // ---- epilogue 2: out[r][16 cb .. 16 cb + 16) = rf * acc -> global; optional part of Re<x_r, out_r>, x_r given as the
@@ -277,6 +292,14 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   constexpr bool LOWER = (MODE == M_FWD || MODE == M_DQ);       // mask col <= row
   constexpr bool OP_H = (MODE == M_DQ || MODE == M_DK);         // carried operand conj-transposed
   constexpr bool DOT = (MODE == M_DQ || MODE == M_DK);          // also leaves Re<x_row, out_row>, x = q (dq) or k (dk): mdot
+  // The decay gradient is a running sum of Re<q_t, dq_t> - Re<k_t, dk_t> over the chunk, in which the contribution of
+  // every (t, s) pair cancels -- exactly only if dq and dk are built from the SAME rounded scores.  So these two jobs
+  // put the whole weight e^{A_t - A_s} (row factor x column factor) into a score before it is rounded to bf16, which
+  // makes the dk job's scores the conjugate transpose of the dq job's bit for bit; the carried-state term gets its row
+  // factor from the A1 rows, rescaled between stage 1 and stage 3.  (With the row factor applied in epilogue 2 the two
+  // jobs rounded different numbers and the noise of up to 128 tokens piled up in the sum: 1-3 % of dgamma at decays
+  // around 0.5 per token.)  The forward and the dv job keep the row factor in epilogue 2.
+  constexpr bool ROWW = DOT;
   unsigned char* RA = smem;                  // A1: real plane, imaginary plane  (2 x [128 rows][128 B])
   unsigned char* RB = RA + 32768;            // B1 planes; after stage 1: carried state planes (2 x [64 rows][128 B])
   unsigned char* RC = RB + 32768;            // X2 planes
@@ -370,7 +393,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   const uint32_t a_r = smem_u32(RA), b_r = smem_u32(RB), x_r = smem_u32(RC);
   if (warp == 0 && elect_one()) {
     tc_fence_after();
-    bw_issue_scores(tmem, a_r, b_r);
+    bw_issue_scores<MODE == M_DK>(tmem, a_r, b_r);
     mma_commit(&bars[1]);
   }
   __syncwarp();
@@ -381,8 +404,27 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   const uint32_t tl = tmem + ((uint32_t)(q4 * 32) << 16);
   // epilogue 1: masked, decayed scores of columns [64 hf, 64 hf + 64) as packed bf16 pairs
 #pragma unroll 1
-  for (int cb = 2 * hf; cb < 2 * hf + 2; ++cb) bw_epi_scores<LOWER>(tl, q4, cb, r, L.len, strong, cfac, Acum, p.q_scale);
+  for (int cb = 2 * hf; cb < 2 * hf + 2; ++cb)
+    bw_epi_scores<LOWER, ROWW>(tl, q4, cb, r, L.len, strong, cfac, Acum, p.q_scale, ROWW ? rfac[r] : 1.f);
   tmem_st_wait();
+  if (ROWW && has_state && !strong) {
+    // stage 1 was the last reader of the unscaled A1 rows: thread (row r, plane hf) multiplies its 128 bytes by the
+    // row factor f = fh + fl (two bf16 numbers; x fh + x fl in one fused multiply-add rounds x f once), eight rows of a
+    // quarter-warp spread over all banks by the swizzle
+    const float f = rfac[r];
+    const __nv_bfloat16 fh = __float2bfloat16_rn(f), fl = __float2bfloat16_rn(f - __bfloat162float(fh));
+    const __nv_bfloat162 fh2 = __bfloat162bfloat162(fh), fl2 = __bfloat162bfloat162(fl);
+    unsigned char* prow = RA + hf * 16384;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4* pp = reinterpret_cast<uint4*>(prow + sw128(r, c));
+      uint4 x = *pp;
+      __nv_bfloat162* xs = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) xs[e] = __hfma2(xs[e], fh2, __hmul2(xs[e], fl2));
+      *pp = x;
+    }
+  }
   if (has_state) {
     // carried state planes (already multiplied by the chunk constant) into the B1 region: stage 1 has consumed it
 #pragma unroll
@@ -450,7 +492,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
 #pragma unroll
       for (int g = 0; g < 8; ++g) dpre[g >> 2][g & 3] = *reinterpret_cast<const uint4*>(RA + hf * 16384 + sw128(r, g));
     }
-    const float rf = strong ? 1.f : rfac[r];
+    const float rf = (strong || ROWW) ? 1.f : rfac[r];
     // A full chunk leaves through the X2 region, which every MMA has finished reading: each warp stages its 32 rows
     // x 128 bytes there and one TMA store moves the block (whole 128-byte lines instead of 16 bytes per lane and
     // row).  A ragged chunk (its rows past `len` belong to someone else) stores per lane.
