@@ -1,5 +1,6 @@
-"""Seeded random cases of the packed tensor-core scan (bf16, d = 64) against the fp64 oracle, sequence by sequence:
-output, final states and every gradient (dq, dk, dv, dgamma_k, dcoef_k).
+"""Seeded random cases of the packed scan against the fp64 oracle, sequence by sequence: output, final states and
+every gradient (dq, dk, dv, dgamma_k, dcoef_k) -- the tensor-core kernels (bf16, d = 64) and the fp32 kernels
+(d = 16, 32 or 64).
 
 Each case draws its own number of heads, states (1..4), sequences and sequence lengths (zero-length sequences and
 lengths that are not a multiple of the 128-token chunk included), an optional initial state, and a decay range that
@@ -15,11 +16,13 @@ from tests.helpers import rel_err
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-TOL = 2e-2        # bf16 tokens in, bf16 outputs: relative Frobenius error per tensor
+TOL = {torch.bfloat16: 2e-2,     # bf16 tokens in, bf16 outputs: relative Frobenius error per tensor
+       torch.float32: 1e-4}
 
 
-def _case(seed):
-    rng = np.random.default_rng(1000 + seed)
+def _case(seed, dtype=torch.bfloat16):
+    rng = np.random.default_rng(1000 + seed + (0 if dtype == torch.bfloat16 else 500))
+    d = 64 if dtype == torch.bfloat16 else int(rng.choice([16, 32, 64]))
     H = int(rng.integers(1, 4))
     K = int(rng.choice([1, 1, 2, 3, 4]))
     S = int(rng.integers(1, 5))
@@ -31,20 +34,20 @@ def _case(seed):
     T = int(lens.sum())
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     g = torch.Generator().manual_seed(seed)
-    q, k, v, dy = (torch.randn(1, H, T, 64, 2, generator=g).mul(0.125).bfloat16() for _ in range(4))
+    q, k, v, dy = (torch.randn(1, H, T, d, 2, generator=g).mul(0.125).to(dtype) for _ in range(4))
     # decay: sigmoid(N(0,1) + shift); shift < 0 puts 128-token products below e^-80
     shift = float(rng.choice([-1.0, 0.5, 2.0, 4.0]))
     gamma = torch.sigmoid(torch.randn(K, 1, H, T, generator=g) + shift)
     coef = torch.randn(K, 1, H, T, 2, generator=g) if K > 1 else None
-    s0 = torch.randn(K, S, H, 64, 64, 2, generator=g) * 0.05 if bool(rng.integers(0, 2)) else None
-    return dict(H=H, K=K, S=S, T=T, lens=lens, cu=cu, q=q, k=k, v=v, dy=dy, gamma=gamma, coef=coef, s0=s0, shift=shift)
+    s0 = torch.randn(K, S, H, d, d, 2, generator=g) * 0.05 if bool(rng.integers(0, 2)) else None
+    return dict(d=d, H=H, K=K, S=S, T=T, lens=lens, cu=cu, q=q, k=k, v=v, dy=dy, gamma=gamma, coef=coef, s0=s0, shift=shift)
 
 
-@pytest.mark.parametrize("seed", list(range(14)))
-def test_random_packed_case_forward_and_gradients(seed):
+@pytest.mark.parametrize("seed,dtype", [(i, torch.bfloat16) for i in range(14)] + [(i, torch.float32) for i in range(8)])
+def test_random_packed_case_forward_and_gradients(seed, dtype):
     from qllm2_b200 import _lib, ops
-    c = _case(seed)
-    K, S, T = c["K"], c["S"], c["T"]
+    c = _case(seed, dtype)
+    K, S, T, d = c["K"], c["S"], c["T"], c["d"]
     cu_t = torch.from_numpy(c["cu"])
     qd, kd, vd = (c[n].to(DEV).requires_grad_(True) for n in ("q", "k", "v"))
     gd = c["gamma"].to(DEV).requires_grad_(True)
@@ -83,13 +86,13 @@ def test_random_packed_case_forward_and_gradients(seed):
         bw = po.scan_backward(qc[None][(slice(None),) + sl], kc[None][(slice(None),) + sl],
                               vc[None][(slice(None),) + sl], gam[:, None, :, a:b], dyc[None][(slice(None),) + sl], **kw)
         ref["y"][:, a:b] = po.to_split(y_ref[0])
-        ref["s"][:, i] = po.to_split(np.asarray(s_ref).reshape(K, 1, c["H"], 64, 64)[:, 0])
+        ref["s"][:, i] = po.to_split(np.asarray(s_ref).reshape(K, 1, c["H"], d, d)[:, 0])
         for n in ("dq", "dk", "dv"):
             ref[n][:, a:b] = po.to_split(bw[n][0])
         ref["dgamma"][:, :, a:b] = bw["dgamma"][:, 0]
         if cf is not None:
             ref["dcoef"][:, :, a:b] = po.to_split(bw["dcoef"][:, 0])
-    what = f"seed {seed}: H={c['H']} K={K} lens={list(c['lens'])} s0={c['s0'] is not None} shift={c['shift']}"
+    what = f"seed {seed} {dtype}: d={d} H={c['H']} K={K} lens={list(c['lens'])} s0={c['s0'] is not None} shift={c['shift']}"
     for n in ("y", "y_inf", "s", "s_inf", "dq", "dk", "dv", "dgamma", "dcoef"):
         if got[n] is None:
             continue
@@ -98,4 +101,4 @@ def test_random_packed_case_forward_and_gradients(seed):
             assert not np.any(got[n]), f"{what}: {n} should be zero"
             continue
         e = rel_err(got[n], r)
-        assert e <= TOL, f"{what}: {n} rel {e:.3e} > {TOL:.0e}"
+        assert e <= TOL[dtype], f"{what}: {n} rel {e:.3e} > {TOL[dtype]:.0e}"
