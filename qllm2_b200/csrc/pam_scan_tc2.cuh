@@ -188,7 +188,7 @@ __device__ __forceinline__ void bw_epi_scores_t(uint32_t tlane_slot, int q4, int
         for (int e = 0; e < 2; ++e) {
           const int c = c0 + 16 * hh + j + e;
           bool on = full || (LOWER ? (c <= r) : (c >= r));
-          if (!LOWER) on = on && (c < len);
+          if (!LOWER && STRONG) on = on && (c < len);      // (the column factors of the fast path are zero past `len`)
           const float w = STRONG ? scale * __expf(fminf(0.f, LOWER ? a_r - Acum[c] : Acum[c] - a_r))
                                  : (ROWW ? rowf * cfac[c] : cfac[c]);
           d[e] = on ? w : 0.f;
@@ -313,7 +313,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, chunk_x);
   if (!L.valid) return;
-  if (tid == 32) *failed = device_error_now();
+  if (tid == 64) *failed = device_error_now();     // not on warp 1: its cumulative decay is the prologue's critical path
   const bool has_state = LOWER ? ((L.c > 0) || (p.s0 != nullptr)) : ((L.c < L.nc - 1) || (p.ds_final != nullptr));
   const int row0 = (L.b * p.H + h) * p.T + L.t0;
   if (tid == 0) {
