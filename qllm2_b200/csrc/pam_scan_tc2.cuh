@@ -316,6 +316,20 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   if (tid == 64) *failed = device_error_now();     // not on warp 1: its cumulative decay is the prologue's critical path
   const bool has_state = LOWER ? ((L.c > 0) || (p.s0 != nullptr)) : ((L.c < L.nc - 1) || (p.ds_final != nullptr));
   const int row0 = (L.b * p.H + h) * p.T + L.t0;
+  // carried state (fp32, 4 complex per item, 4 items per thread): requested before anything else, so that its way
+  // through the memory system runs beside the set-up and the cumulative decay instead of after them
+  float4 sraw[4][2];
+  if (has_state) {
+    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
+                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    const float4* sg = reinterpret_cast<const float4*>(st);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
+      sraw[it][0] = __ldg(sg + idx * 2);
+      sraw[it][1] = __ldg(sg + idx * 2 + 1);
+    }
+  }
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
@@ -359,16 +373,12 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     }
   }
   const float st_cst = strong ? 1.f : (LOWER ? __expf(a_mid) : __expf(a_last - a_mid));
-  // carried state, fetched early and kept as packed bf16 (4 complex per item, 4 items per thread)
+  // the carried state times the chunk constant, kept as packed bf16 until stage 1 has released the B1 region
   uint32_t st_r[4][2], st_i[4][2];
   if (has_state) {
-    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
-                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
-    const float4* sg = reinterpret_cast<const float4*>(st);
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
-      const float4 s01 = __ldg(sg + idx * 2), s23 = __ldg(sg + idx * 2 + 1);
+      const float4 s01 = sraw[it][0], s23 = sraw[it][1];
       st_r[it][0] = pack_bf162(st_cst * s01.x, st_cst * s01.z);
       st_r[it][1] = pack_bf162(st_cst * s23.x, st_cst * s23.z);
       st_i[it][0] = pack_bf162(st_cst * s01.y, st_cst * s01.w);
