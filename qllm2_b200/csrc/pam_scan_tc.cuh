@@ -29,11 +29,17 @@ __device__ __forceinline__ uint32_t pack_bf162(float a, float b) {
 }
 
 // inclusive cumulative sum of log(gamma + eps) over 128 tokens by one warp (4 tokens per lane)
-__device__ __forceinline__ void warp_cumsum128(float* A, const float* __restrict__ gamma, int len, float eps, int lane) {
+// (two halves, so that a caller can put other loads between the request for the decays and their first use)
+__device__ __forceinline__ void warp_cumsum128_load(float (&g)[4], const float* __restrict__ gamma, int len, int lane) {
+  const int t = 4 * lane;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) g[i] = (t + i < len) ? __ldg(gamma + t + i) : 1.f;
+}
+__device__ __forceinline__ void warp_cumsum128_finish(float* A, const float (&g)[4], int len, float eps, int lane) {
   const int t = 4 * lane;
   float x[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = (t + i < len) ? logf(gamma[t + i] + eps) : 0.f;
+  for (int i = 0; i < 4; ++i) x[i] = (t + i < len) ? logf(g[i] + eps) : 0.f;
   x[1] += x[0];
   x[2] += x[1];
   x[3] += x[2];
@@ -46,6 +52,11 @@ __device__ __forceinline__ void warp_cumsum128(float* A, const float* __restrict
   const float excl = incl - x[3];
 #pragma unroll
   for (int i = 0; i < 4; ++i) A[t + i] = excl + x[i];
+}
+__device__ __forceinline__ void warp_cumsum128(float* A, const float* __restrict__ gamma, int len, float eps, int lane) {
+  float g[4];
+  warp_cumsum128_load(g, gamma, len, lane);
+  warp_cumsum128_finish(A, g, len, eps, lane);
 }
 
 // ---------------------------------------------------------------------------------------------

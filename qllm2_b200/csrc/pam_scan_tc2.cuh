@@ -316,20 +316,8 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   if (tid == 64) *failed = device_error_now();     // not on warp 1: its cumulative decay is the prologue's critical path
   const bool has_state = LOWER ? ((L.c > 0) || (p.s0 != nullptr)) : ((L.c < L.nc - 1) || (p.ds_final != nullptr));
   const int row0 = (L.b * p.H + h) * p.T + L.t0;
-  // carried state (fp32, 4 complex per item, 4 items per thread): requested before anything else, so that its way
-  // through the memory system runs beside the set-up and the cumulative decay instead of after them
-  float4 sraw[4][2];
-  if (has_state) {
-    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
-                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
-    const float4* sg = reinterpret_cast<const float4*>(st);
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
-      sraw[it][0] = __ldg(sg + idx * 2);
-      sraw[it][1] = __ldg(sg + idx * 2 + 1);
-    }
-  }
+  float graw[4] = {1.f, 1.f, 1.f, 1.f};
+  if (warp == 1) warp_cumsum128_load(graw, p.gamma + gamma_base(p, 0, L.b, h, L.t0), L.len, lane);
   if (tid == 0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
@@ -345,8 +333,23 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     }
   }
   __syncwarp();
+  // carried state (fp32, 4 complex per item, 4 items per thread): requested here, so that its way through the memory
+  // system runs beside the set-up and the cumulative decay instead of after them (behind the decays and the tile
+  // requests, which the longest chains of the prologue hang on)
+  float4 sraw[4][2];
+  if (has_state) {
+    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
+                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    const float4* sg = reinterpret_cast<const float4*>(st);
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
+      sraw[it][0] = __ldg(sg + idx * 2);
+      sraw[it][1] = __ldg(sg + idx * 2 + 1);
+    }
+  }
   if (warp == 0) tmem_alloc<256>(tmem_slot);
-  if (warp == 1) warp_cumsum128(Acum, p.gamma + gamma_base(p, 0, L.b, h, L.t0), L.len, p.eps, lane);
+  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
