@@ -337,6 +337,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   // system runs beside the set-up and the cumulative decay instead of after them (behind the decays and the tile
   // requests, which the longest chains of the prologue hang on)
   float4 sraw[4][2];
+  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);      // before this warp queues up more loads
   if (has_state) {
     const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
                              : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
@@ -349,7 +350,6 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     }
   }
   if (warp == 0) tmem_alloc<256>(tmem_slot);
-  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
