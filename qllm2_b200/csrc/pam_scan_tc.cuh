@@ -39,7 +39,10 @@ __device__ __forceinline__ void warp_cumsum128_finish(float* A, const float (&g)
   const int t = 4 * lane;
   float x[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = (t + i < len) ? logf(g[i] + eps) : 0.f;
+  // hardware logarithm (absolute error <= 2^-22 per token on (0.5, 2): <= 3e-5 over a chunk, far below the bf16 scores the
+  // decays multiply); every tensor-core kernel forms its decays here, so chunk sums, carried states and outputs agree.
+  // The full-precision logf was ~500 clocks of the chain that the first barrier of a chunk job waits for.
+  for (int i = 0; i < 4; ++i) x[i] = (t + i < len) ? __logf(g[i] + eps) : 0.f;
   x[1] += x[0];
   x[2] += x[1];
   x[3] += x[2];
