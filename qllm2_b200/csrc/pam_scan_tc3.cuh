@@ -61,6 +61,15 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
     }
   }
   __syncwarp();
+  // the read-out weights of this thread's (state, token) entries: requested here, used after the first barrier
+  float2 craw[2] = {make_float2(1.f, 0.f), make_float2(1.f, 0.f)};
+  if (p.coef != nullptr) {
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const int e = tid + 256 * m, k = e / TC, t = e - k * TC;
+      if (e < K * TC && t < L.len) craw[m] = __ldg(reinterpret_cast<const float2*>(p.coef + gamma_base(p, k, L.b, h, L.t0 + t) * 2));
+    }
+  }
   if (warp == 0) tmem_alloc<256>(tmem_slot);
   if (warp >= 1 && warp <= K)
     warp_cumsum128(Acum + (warp - 1) * TC, p.gamma + gamma_base(p, warp - 1, L.b, h, L.t0), L.len, p.eps, lane);
@@ -80,15 +89,18 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_fwdK(const __grid_constant_
 #pragma unroll
   for (int k = 0; k < KMAX; ++k)
     if (k < K && Acum[k * TC + TC - 1] < STRONG_DECAY) strong_mask |= 1u << k;
-  for (int e = tid; e < K * TC; e += 256) {
-    const int k = e / TC, t = e - k * TC;
-    const bool strong = (strong_mask >> k) & 1u;
-    const float a = Acum[e], a_mid = Acum[k * TC + TC / 2 - 1];
-    cfac[e] = strong ? 1.f : __expf(a_mid - a);
-    float2 c = make_float2(1.f, 0.f);
-    if (p.coef != nullptr && t < L.len) c = *reinterpret_cast<const float2*>(p.coef + gamma_base(p, k, L.b, h, L.t0 + t) * 2);
-    const float rf = p.q_scale * (strong ? 1.f : __expf(a - a_mid));
-    rho[e] = make_float2(c.x * rf, c.y * rf);
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {          // KMAX * TC = 512 entries, two per thread
+    const int e = tid + 256 * m;
+    if (e < K * TC) {
+      const int k = e / TC;
+      const bool strong = (strong_mask >> k) & 1u;
+      const float a = Acum[e], a_mid = Acum[k * TC + TC / 2 - 1];
+      cfac[e] = strong ? 1.f : __expf(a_mid - a);
+      const float2 c = craw[m];
+      const float rf = p.q_scale * (strong ? 1.f : __expf(a - a_mid));
+      rho[e] = make_float2(c.x * rf, c.y * rf);
+    }
   }
   bool ok = mbar_wait(&bars[0], 0, 231);
   {
