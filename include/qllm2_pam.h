@@ -208,6 +208,12 @@ int qpam_ce_bwd_overlap(const qpam_ce_args* args, const float* lse, const float*
 /* Decode head: argmax_v (h @ w^T)[n, v] -> ids[N] (int64) and the winning logit (fp32). */
 int qpam_head_argmax(const qpam_ce_args* args, int64_t* ids, float* best, void* stream);
 
+/* Sampling decode head: logits[n, v] = (h @ w^T)[n, v] as bf16 rows of `ld` elements (ld >= V, a multiple of 8;
+ * `logits` 16-byte aligned) -- the tied-head product that V11LM.generate forms before its sampling block
+ * (v11/model.py:1218-1221), on the tensor-core GEMM of the cross-entropy (bf16 h and w with 16-byte aligned rows
+ * only: QPAM_EUNSUPPORTED otherwise).  targets / mask / workspace of `args` are not used. */
+int qpam_head_logits(const qpam_ce_args* args, void* logits, int64_t ld, void* stream);
+
 /* Token sampling on the device, one row of logits per sequence: the sampling block of V11LM.generate
  * (v11/model.py:1221-1244) -- logits / temperature, repetition penalty over the tokens already in the sequence
  * (x > 0 ? x / penalty : x * penalty), top-k (values below the k-th largest dropped, ties kept), top-p (in

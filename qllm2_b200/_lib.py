@@ -74,6 +74,7 @@ SIGNATURES = {
     "qpam_ce_bwd_overlap": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p]),
     "qpam_head_argmax": (c_int32, [C.POINTER(CEArgs), c_void_p, c_void_p, c_void_p]),
+    "qpam_head_logits": (c_int32, [C.POINTER(CEArgs), c_void_p, c_int64, c_void_p]),
     "qpam_sample_workspace_bytes": (c_size_t, [c_int32, c_int32]),
     "qpam_sample_logits": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int64, C.c_float, c_int32, C.c_float,
                                      C.c_float, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_void_p, c_int32,

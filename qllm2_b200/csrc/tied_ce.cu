@@ -226,6 +226,23 @@ extern "C" int qpam_ce_bwd_overlap(const qpam_ce_args* a, const float* lse, cons
   return rc;
 }
 
+extern "C" int qpam_head_logits(const qpam_ce_args* a, void* logits, int64_t ld, void* stream) {
+  QPAM_REQUIRE(a != nullptr && a->h && a->w, "head logits: args / h / w must not be NULL");
+  QPAM_REQUIRE(a->N >= 0 && a->V >= 1 && a->F >= 1 && a->V < ((int64_t)1 << 31), "head logits: bad N/V/F = %lld/%lld/%d",
+               (long long)a->N, (long long)a->V, a->F);
+  QPAM_REQUIRE(a->io_dtype == QPAM_F32 || a->io_dtype == QPAM_BF16, "head logits: io_dtype %d unknown", a->io_dtype);
+  QPAM_REQUIRE(logits != nullptr, "head logits: logits must not be NULL");
+  QPAM_REQUIRE(ld >= a->V && ld % 8 == 0 && ((uintptr_t)logits & 15) == 0,
+               "head logits: ld must be a multiple of 8 that covers V, logits 16-byte aligned (got ld %lld)", (long long)ld);
+  const CELayout L = ce_layout(a);
+  if (!tc_usable(a, L)) {
+    set_error("head logits: bf16 h and w with 16-byte aligned rows only (the tensor-core path)");
+    return QPAM_EUNSUPPORTED;
+  }
+  if (a->N == 0) return QPAM_OK;
+  return ce_tc_logits(a, L.tc, logits, ld, reinterpret_cast<cudaStream_t>(stream));
+}
+
 extern "C" int qpam_head_argmax(const qpam_ce_args* a, int64_t* ids, float* best, void* stream) {
   QPAM_REQUIRE(ids != nullptr, "head argmax: ids must not be NULL");
   return qpam_ce_partial(a, best, nullptr, nullptr, ids, stream);

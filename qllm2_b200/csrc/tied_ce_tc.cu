@@ -120,6 +120,32 @@ int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& pl, const CETcBuffers& 
   return QPAM_OK;
 }
 
+// ------------------------------------------------------------------ plain logits (sampling decode head)
+// out[N][ld] (bf16) = h w^T: the logits GEMM of the statistics pass with the accumulators leaving as bf16 tiles
+// through TMA stores; CTA pairs, a pair walks a few vocabulary tiles of its two row tiles.
+int ce_tc_logits(const qpam_ce_args* a, const CETcPlan& pl, void* out, int64_t ld, cudaStream_t st) {
+  auto kern = tc::k_tc_gemm<256, tc::EPI_STORE_BF16, false, false, 1, true>;
+  using CfgP = tc::Cfg<256, 1, true>;
+  int rc = opt_in_smem(kern, CfgP::SMEM_BYTES_STAGED);
+  if (rc) return rc;
+  CUtensorMap tmH, tmW, tmO;
+  if ((rc = make_map(&tmH, a->h, a->F, a->N, a->F, tc::BK, tc::BM))) return rc;
+  if ((rc = make_map(&tmW, a->w, a->F, a->V, a->F, tc::BK, 128))) return rc;
+  if ((rc = make_map(&tmO, out, a->V, a->N, ld, 64, 32))) return rc;
+  const unsigned row_tiles = (unsigned)((a->N + tc::BM - 1) / tc::BM);
+  tc::GemmParams p{};
+  p.n_tiles = pl.n_tiles;
+  p.tiles_per_cta = probs_tiles_per_cta(row_tiles, pl.n_tiles);
+  const unsigned n_groups = (unsigned)((pl.n_tiles + p.tiles_per_cta - 1) / p.tiles_per_cta);
+  p.kb_total = (a->F + tc::BK - 1) / tc::BK;
+  p.kb_per_split = p.kb_total;
+  p.M = a->N; p.N = a->V;
+  p.swap_xy = 1;
+  QPAM_CUDA(launch_pairs(kern, dim3((row_tiles + 1) & ~1u, n_groups, 1), 0, CfgP::SMEM_BYTES_STAGED, st, tmH, tmW, tmO, p));
+  QPAM_LAUNCH_CHECK("k_tc_gemm<logits>");
+  return QPAM_OK;
+}
+
 // ------------------------------------------------------------------ backward
 __global__ void k_reduce_splits_bf16(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int64_t n,
                                      int splits, int64_t split_stride) {

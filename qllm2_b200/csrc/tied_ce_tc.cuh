@@ -27,6 +27,8 @@ struct CETcBuffers {
 
 // per-row partial statistics [nsplit][N] via the tensor-core logits GEMM
 int ce_tc_partial(const qpam_ce_args* a, const CETcPlan& plan, const CETcBuffers& b, cudaStream_t st);
+// out[N][ld] (bf16) = h w^T through the same GEMM, tiles stored by TMA (ld a multiple of 8, out 16-byte aligned)
+int ce_tc_logits(const qpam_ce_args* a, const CETcPlan& plan, void* out, int64_t ld, cudaStream_t st);
 // dH, dW via recomputed probabilities (bf16 tiles) and two tensor-core GEMMs per row chunk
 // dh_ready_stream (may be NULL): a stream of the caller that is made to wait until dh is complete, while the
 // dw products continue on `st`

@@ -213,6 +213,8 @@ class FusedForward:
         """Tied-head logits [n, V] (float32) of rows lm [n, D, 2]: Re(lm . conj(E)) as one real GEMM
         (v11/model.py:1136-1139); only the sampling path needs them."""
         Hm = torch.cat([lm[..., 0], lm[..., 1]], dim=-1)
+        if Hm.dtype == torch.bfloat16 and self.w_vocab.dtype == torch.bfloat16:
+            return ops.head_logits(Hm, self.w_vocab).float()       # the cross-entropy's tensor-core GEMM, bf16 tiles out
         return F.linear(Hm, self.w_vocab).float()
 
     @torch.no_grad()

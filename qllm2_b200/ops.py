@@ -437,6 +437,23 @@ def ce_backward(h, w, targets, mask, lse, grad_scale, denom, *, ignore_index=-10
     return dh, dw
 
 
+def head_logits(h, w):
+    """Sampling decode head: bf16 logits [N, V] = h @ w^T (a view of rows padded to a multiple of 8 columns) on the
+    tensor-core GEMM of the cross-entropy; h [N,F] and w [V,F] bfloat16 with 16-byte aligned rows
+    (v11/model.py:1218-1221 forms the same product before its sampling block)."""
+    L = _lib.lib()
+    _require_cuda(h, w)
+    h, w = h.contiguous(), w.contiguous()
+    if h.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or h.dim() != 2 or w.dim() != 2 or h.shape[1] != w.shape[1]:
+        raise _lib.QPamError(f"head_logits: bfloat16 h [N,F] and w [V,F] expected; got {tuple(h.shape)} {h.dtype}, {tuple(w.shape)} {w.dtype}")
+    N, V = h.shape[0], w.shape[0]
+    ld = (V + 7) // 8 * 8
+    out = torch.empty(N, ld, dtype=torch.bfloat16, device=h.device)
+    a = _ce_args(h, w, None, None, -100, 0)
+    check(L.qpam_head_logits(C.byref(a), ptr(out), ld, stream_ptr()), "qpam_head_logits")
+    return out[:, :V]
+
+
 def head_argmax(h, w):
     """Greedy decode head: (ids int64 [N], best logit float32 [N]) of argmax_v (h @ w^T)."""
     row_max, _, _, row_arg = ce_row_stats(h, w, None)

@@ -225,7 +225,9 @@ class ContinuousBatcher:
             return self.ff.greedy_next(lm_rows) if self.ff is not None else self.model.greedy_next(lm_rows)
         if self.ff is not None:
             # logits in the model's dtype, as the reference forms them before its .float(); the kernel widens them
-            logits = torch.nn.functional.linear(torch.cat([lm_rows[..., 0], lm_rows[..., 1]], dim=-1), self.ff.w_vocab)
+            Hm = torch.cat([lm_rows[..., 0], lm_rows[..., 1]], dim=-1)
+            logits = (ops.head_logits(Hm, self.ff.w_vocab) if Hm.dtype == torch.bfloat16
+                      else torch.nn.functional.linear(Hm, self.ff.w_vocab))
         else:
             Hm, W = self.model.tied_head_matrices(lm_rows.unsqueeze(1))
             logits = (Hm @ W.to(Hm.dtype).T).float()

@@ -121,3 +121,19 @@ def test_vocabulary_shard_statistics_with_ragged_last_group():
         inside = (t >= a) & (t < b)
         want = torch.where(inside, lg.gather(1, (t - a).clamp(0, b - a - 1)[:, None])[:, 0], torch.zeros_like(mr))
         assert float((tz - want).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("N,F,V", [(256, 1536, 50261), (1, 64, 9), (130, 72, 1001), (300, 768, 4096)])
+def test_head_logits_bf16_tiles(N, F, V):
+    """Sampling decode head: bf16 logits of the tensor-core GEMM against the fp64 product of the same bf16 inputs
+    (relative to the largest logit: 2^-8, one bf16 rounding of the output)."""
+    g = torch.Generator().manual_seed(N + V)
+    h = torch.randn(N, F, generator=g).bfloat16()
+    w = (torch.randn(V, F, generator=g) * (4.0 / F ** 0.5)).bfloat16()
+    z = ops.head_logits(h.to(DEV), w.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert z.shape == (N, V) and z.dtype == torch.bfloat16
+    ref = ce_oracle.head_logits(h.float().numpy(), w.float().numpy())
+    err = np.abs(z.float().cpu().numpy() - ref).max() / np.abs(ref).max()
+    assert err <= 2.0 ** -8, err
