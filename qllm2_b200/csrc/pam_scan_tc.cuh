@@ -38,11 +38,18 @@ __device__ __forceinline__ void warp_cumsum128_load(float (&g)[4], const float* 
 __device__ __forceinline__ void warp_cumsum128_finish(float* A, const float (&g)[4], int len, float eps, int lane) {
   const int t = 4 * lane;
   float x[4];
+  // log(gamma + eps) without the full-precision logf (~500 clocks of the chain that the first barrier of a chunk job
+  // waits for).  Decays close to 1 are the ones whose errors would add up over thousands of tokens, so they get the
+  // series of log1p(u), u = x - 1 (exact by Sterbenz for x in [0.5, 2]), to fp32 rounding: |u| < 1/16, six terms,
+  // truncation < u^7/7 < 6e-10.  The rest takes the hardware logarithm (absolute error <= 2^-22 per token; such a
+  // sequence has forgotten a token after a few hundred steps, long before those errors add up to 1e-4).  Every
+  // tensor-core kernel forms its decays here, so chunk sums, carried states and outputs agree.
 #pragma unroll
-  // hardware logarithm (absolute error <= 2^-22 per token on (0.5, 2): <= 3e-5 over a chunk, far below the bf16 scores the
-  // decays multiply); every tensor-core kernel forms its decays here, so chunk sums, carried states and outputs agree.
-  // The full-precision logf was ~500 clocks of the chain that the first barrier of a chunk job waits for.
-  for (int i = 0; i < 4; ++i) x[i] = (t + i < len) ? __logf(g[i] + eps) : 0.f;
+  for (int i = 0; i < 4; ++i) {
+    const float xg = g[i] + eps, u = xg - 1.f;
+    const float series = u * fmaf(u, fmaf(u, fmaf(u, fmaf(u, fmaf(u, -1.f / 6.f, 0.2f), -0.25f), 1.f / 3.f), -0.5f), 1.f);
+    x[i] = (t + i < len) ? (fabsf(u) < 0.0625f ? series : __logf(xg)) : 0.f;
+  }
   x[1] += x[0];
   x[2] += x[1];
   x[3] += x[2];
