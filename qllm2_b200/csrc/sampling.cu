@@ -237,7 +237,41 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) k_sample_rows(SampleParams p) 
   // the descending cumulative mass first reaches the target; found by a 4-way search over the bit patterns of
   // (0, 1].  Every probe is one pass with a fixed reduction tree: no atomics, the same result on every run.
   uint32_t bits_min = 1u;                       // keeps every e > 0
-  if (p.top_p > 0.f && p.top_p < 1.f) {
+  if (p.top_p > 0.f && p.top_p < 1.f && compact && n_el <= 256) {
+    // a short list: one warp holds it in registers (eight per lane) and runs the same search with shuffles only
+    const float target = p.top_p * z;
+    if (tid < 32) {
+      float e8[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) e8[j] = (tid + 32 * j < n_el) ? ev[tid + 32 * j] : 0.f;
+      uint32_t lo = 1u, hi = 0x3f800001u;
+      while (hi - lo > 1u) {
+        const uint32_t step = (hi - lo) >> 2;
+        const uint32_t m2 = lo + ((hi - lo) >> 1);
+        const uint32_t m1 = step ? lo + step : m2, m3 = step ? m2 + step : m2;
+        float f1 = 0.f, f2 = 0.f, f3 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t eb = __float_as_uint(e8[j]);
+          f1 += eb >= m1 ? e8[j] : 0.f;
+          f2 += eb >= m2 ? e8[j] : 0.f;
+          f3 += eb >= m3 ? e8[j] : 0.f;
+        }
+        for (int o = 16; o; o >>= 1) {
+          f1 += __shfl_xor_sync(0xffffffffu, f1, o);
+          f2 += __shfl_xor_sync(0xffffffffu, f2, o);
+          f3 += __shfl_xor_sync(0xffffffffu, f3, o);
+        }
+        if (f3 >= target && m3 > m2) lo = m3;
+        else if (f2 >= target) { lo = m2; if (m3 > m2) hi = m3; }
+        else if (f1 >= target && m1 < m2) { lo = m1; hi = m2; }
+        else hi = (m1 < m2) ? m1 : m2;
+      }
+      if (tid == 0) sc->prefix = lo;
+    }
+    __syncthreads();
+    bits_min = sc->prefix;
+  } else if (p.top_p > 0.f && p.top_p < 1.f) {
     const float target = p.top_p * z;
     uint32_t lo = 1u, hi = 0x3f800001u;         // mass{>= lo} >= target > mass{>= hi}
     while (hi - lo > 1u) {

@@ -408,3 +408,20 @@ def test_expired_wait_sets_status_and_later_launches_skip():
     assert _lib.device_status() == 0
     assert _direct_forward(q, k, v, gamma, None, y, s_final) == 0
     assert _lib.device_status() == 0 and torch.isfinite(y.float()).all()
+
+
+def test_long_memory_decay_does_not_drift():
+    """16,384 tokens at a decay of 0.9999 per token (every token still weighs 0.19 at the end): an error in the
+    per-token log-decay that all tokens share would add up 16,384 times.  Final state and the last 512 outputs stay
+    at the bf16 level against the fp64 recurrence (v11/model.py:378-417)."""
+    T, H = 16384, 1
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(1, H, T, 64, 2, generator=g).mul(0.125).bfloat16() for _ in range(3))
+    gamma = torch.full((1, H, T), 0.9999)
+    y, s = ops.pam_scan(q.to(DEV), k.to(DEV), v.to(DEV), gamma.to(DEV))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    qc, kc, vc = (po.to_complex(t.float().numpy()) for t in (q, k, v))
+    y_ref, s_ref = po.scan_recurrence(qc, kc, vc, gamma.double().numpy())
+    assert rel_err(s.cpu().numpy(), po.to_split(s_ref)) < 4e-3
+    assert rel_err(y[0, :, -512:].float().cpu().numpy(), po.to_split(y_ref[0, :, -512:])) < 6e-3
