@@ -361,12 +361,19 @@ class V11PAMLayer(nn.Module):
 
         fused_mag = x.dtype in (torch.float32, torch.bfloat16) and (x.numel() // 2) % 4 == 0
         mag = None
-        dt = planar(self.dt_proj)
         pg = phase = score = None
-        if self.use_gsp:
-            if not self.gate_content_aware:
+        if self.use_gsp and self.gate_content_aware:
+            # dt_proj and protect_gate read the same rows: one product with the two weight matrices stacked (a Linear
+            # with a handful of outputs costs one pass over its input, forward and backward, whatever its width)
+            lins = (self.dt_proj, self.protect_gate)
+            w = torch.cat([l.weight.view(l.weight.shape[0], 2, D).transpose(1, 2).reshape(l.weight.shape[0], 2 * D) for l in lins])
+            both = F.linear(flat, w, torch.cat([l.bias for l in lins]))
+            dt, pg = both[..., :H], both[..., H:]
+        else:
+            dt = planar(self.dt_proj)
+            if self.use_gsp:
                 mag = FE.complex_magnitude(x) if fused_mag else _magnitude(x)
-            pg = planar(self.protect_gate) if self.gate_content_aware else self.protect_gate(mag)
+                pg = self.protect_gate(mag)
         if K > 1:
             if not self.routing_content_aware and mag is None:
                 mag = FE.complex_magnitude(x) if fused_mag else _magnitude(x)
