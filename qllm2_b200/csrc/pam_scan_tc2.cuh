@@ -25,7 +25,9 @@
 // chunk decays by less than e^-80 the factored form  e^{A_t - A_m} e^{A_m - A_s}  around the mid-chunk
 // value A_m is exact (every exponent stays inside [-80, 80]): the column factor goes into T, the row
 // factor into epi 2, where it also carries the decay of the carried-state term (chunk constant folded into
-// the state planes) -- 256 exponentials per chunk instead of 16 K.  A chunk that decays more strongly takes the
+// the state planes) -- 256 exponentials per chunk instead of 16 K.  (The dq and dk jobs put both factors into T
+// and rescale the A1 rows for the carried-state term instead: their scores must round alike, see chunk_job.)
+// A chunk that decays more strongly takes the
 // slow path: every score gets its own exp(A_t - A_s), and the carried-state product is formed first, rescaled
 // row by row in TMEM, and the score product accumulates onto it.  Both paths are exact for every gamma in (0, 1].
 // (Like the backward formulas, both assume gamma + eps <= 1, where the reference's min(., 0) clamp of the
