@@ -126,6 +126,19 @@ int qpam_scan_bwd(const qpam_scan_args* args, const void* dy, void* dq, void* dk
 int qpam_scan_bwd_accumulate(const qpam_scan_args* args, const void* dy, void* dq, void* dk, void* dv,
                              float* dgamma, const float* ds_final, float* ds0, int32_t states_valid, void* stream);
 
+/* K = 2..4 phase-routed states for TRAINING (tensor-core path: bf16, d = 64; QPAM_EUNSUPPORTED otherwise): the per-state
+ * outputs ys [K,B,H,T,d,2] (args->y and args->coef are ignored; the caller forms y = sum_k c_k ys_k, v11/model.py:766-781)
+ * and s_final [K,S,H,d,d,2].  The chunk sums of all states come from one pass over k and v
+ * (the reference's fused step shares the same products, v11/model.py:657-737); the workspace (sized with
+ * qpam_scan_workspace_bytes(args, 1)) keeps every state's chunk states for qpam_scan_bwd_state. */
+int qpam_scan_fwd_states(const qpam_scan_args* args, void* ys, void* stream);
+
+/* Backward of state `state` of a qpam_scan_fwd_states call (same args, same workspace): dy is the gradient of that state's
+ * output, dgamma [B,H,T] / ds_final / ds0 are that state's arrays; accumulate != 0 adds dq, dk, dv to what the buffers
+ * hold (the states share q, k, v: call state 0 with accumulate = 0, the others with 1). */
+int qpam_scan_bwd_state(const qpam_scan_args* args, int32_t state, const void* dy, void* dq, void* dk, void* dv,
+                        float* dgamma, const float* ds_final, float* ds0, int32_t accumulate, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * O(1) recurrent decode step over a pool of per-sequence state slots.
  *

@@ -61,6 +61,9 @@ SIGNATURES = {
                                 c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "qpam_scan_bwd_accumulate": (c_int32, [C.POINTER(ScanArgs), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_int32, c_void_p]),
+    "qpam_scan_fwd_states": (c_int32, [C.POINTER(ScanArgs), c_void_p, c_void_p]),
+    "qpam_scan_bwd_state": (c_int32, [C.POINTER(ScanArgs), c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_int32, c_void_p]),
     "qpam_decode_step": (c_int32, [c_void_p, c_int32, c_int64, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
                                    c_int32, c_void_p]),

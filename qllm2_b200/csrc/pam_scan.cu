@@ -195,6 +195,22 @@ static int scan_fwd_t(const qpam_scan_args* a, const ScanLayout& L, cudaStream_t
   return QPAM_OK;
 }
 
+// The view of ONE state k of a K-state problem as a single-state problem: every per-state array of the parameters
+// and of the workspace is laid out state-major, so the kernels written for one state run on it with shifted bases.
+static ScanParams one_state_view(const ScanParams& pK, const qpam_scan_args* a, const ScanLayout& L, int k) {
+  ScanParams p = pK;
+  const size_t per_state = (size_t)a->H * L.nslots;
+  p.K = 1;
+  p.gamma = pK.gamma + (size_t)k * a->B * a->H * a->T;
+  p.states = pK.states + (size_t)k * per_state * 64 * 64;
+  p.dstates = pK.dstates + (size_t)k * per_state * 64 * 64;
+  p.chunk_decay = pK.chunk_decay + (size_t)k * per_state;
+  if (pK.s0 != nullptr) p.s0 = pK.s0 + (size_t)k * a->S * a->H * 64 * 64 * 2;
+  p.s_final = nullptr;      // written by the K-state carry
+  p.coef = nullptr;
+  return p;
+}
+
 // chunk-local state sums on tensor cores, then the carry over the chunk axis
 static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_args* a, cudaStream_t st) {
   if (L.grid_chunks > 0 && a->K > 1) {      // all states from one load of the key / value tiles
@@ -269,12 +285,44 @@ static int scan_fwd_tcK(const qpam_scan_args* a, const ScanLayout& L, cudaStream
   return QPAM_OK;
 }
 
+// bf16 / d = 64 / K = 2..4 states, training form: the state sums of all states from ONE load of the key / value tiles
+// and one carry launch, as above, then the single-state output kernel once per state into ys[k] (a backward needs
+// every state's own output; the fused output kernel only leaves their weighted sum)
+static int scan_fwd_tc_states(const qpam_scan_args* a, const ScanLayout& L, void* ys, cudaStream_t st) {
+  ScanParams p = make_params(a, L);
+  if (a->cu_seqlens != nullptr) {
+    k_chunk_prefix_checked<<<1, 256, 0, st>>>(a->cu_seqlens, const_cast<int32_t*>(p.geom.chunk_prefix), a->S, L.ch, a->T);
+    QPAM_LAUNCH_CHECK("k_chunk_prefix");
+  }
+  int rc = tc_states(p, L, a, st);
+  if (rc) return rc;
+  if (L.grid_chunks == 0) return QPAM_OK;
+  tcs::ChunkMaps maps;
+  const int64_t rows = (int64_t)a->B * a->H * a->T;
+  if ((rc = make_map(&maps.a1, a->q, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.b1, a->k, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = make_map(&maps.x2, a->v, 128, rows, 128, 64, 128))) return rc;
+  if ((rc = set_smem(tcs::k_tc_chunk_fwd, tcs::CHUNK2_SMEM))) return rc;
+  for (int k = 0; k < a->K; ++k) {
+    ScanParams pk = one_state_view(p, a, L, k);
+    __nv_bfloat16* yk = reinterpret_cast<__nv_bfloat16*>(ys) + (size_t)k * rows * 128;
+    pk.y = yk;
+    if ((rc = make_map(&maps.out, yk, 128, rows, 128, 64, 32))) return rc;
+    tcs::k_tc_chunk_fwd<<<dim3(L.grid_chunks, a->H), 256, tcs::CHUNK2_SMEM, st>>>(maps, pk);
+    QPAM_LAUNCH_CHECK("k_tc_chunk<fwd>");
+  }
+  return QPAM_OK;
+}
+
 // bf16 / d = 64 / one state, backward: gradient state sums -> reverse carry (with the anchors of the decay
 // gradient) -> ONE launch for the dq, dv, dk jobs of every chunk -> dgamma.  Everything stays on the caller's stream.
+// state >= 0: `a` describes K states whose forward (qpam_scan_fwd_states) left its states in the workspace; the backward of
+// that one state runs on its slices (dgamma, ds_final, ds0 are that state's arrays)
 static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void* dy, void* dq, void* dk, void* dv,
                        float* dgamma, const float* ds_final, float* ds0, int states_valid, cudaStream_t st,
-                       bool accumulate = false) {
+                       bool accumulate = false, int state = -1) {
   ScanParams p = make_params(a, L);
+  if (state >= 0) p = one_state_view(p, a, L, state);
   p.dy = dy; p.dq = dq; p.dk = dk; p.dv = dv;
   p.dgamma = dgamma; p.dcoef = nullptr; p.ds_final = ds_final; p.ds0 = ds0;
   int rc;
@@ -288,7 +336,8 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
     rc = tc_states(pf, L, a, st);
     if (rc) return rc;
   }
-  float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors);
+  float* anchors = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_anchors) +
+                   (state > 0 ? (size_t)state * a->H * L.nslots * tcs::ANCHOR_PARTS : 0);
   p.dA_k = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + L.off_dak);
   if (L.grid_chunks > 0) {
     rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
@@ -466,6 +515,51 @@ extern "C" int qpam_scan_bwd_accumulate(const qpam_scan_args* a, const void* dy,
     return QPAM_EWORKSPACE;
   }
   return scan_bwd_tc(a, L, dy, dq, dk, dv, dgamma, ds_final, ds0, states_valid, reinterpret_cast<cudaStream_t>(stream), true);
+}
+
+// K = 2..4 states for training (tensor-core path only): per-state outputs ys [K,B,H,T,d,2] and s_final, the state
+// sums shared between the states; the workspace keeps every state's chunk states for qpam_scan_bwd_state.
+extern "C" int qpam_scan_fwd_states(const qpam_scan_args* a, void* ys, void* stream) {
+  int rc = check_scan_args(a);
+  if (rc) return rc;
+  QPAM_REQUIRE(ys != nullptr && ((uintptr_t)ys & 15) == 0, "scan fwd (states): ys must be a 16-byte aligned buffer");
+  qpam_scan_args probe = *a;
+  probe.y = ys;
+  probe.coef = nullptr;
+  if (!tc_fwdK_eligible(&probe)) {
+    set_error("scan fwd (states): offered on the tensor-core path only (bf16, d = 64, 2..4 states, 16-byte aligned tensors)");
+    return QPAM_EUNSUPPORTED;
+  }
+  const ScanLayout L = scan_layout(a, tcs::TC);
+  if (a->workspace_bytes < L.total_fwd) {
+    set_error("scan fwd (states): workspace %zu bytes < required %zu", a->workspace_bytes, L.total_fwd);
+    return QPAM_EWORKSPACE;
+  }
+  return scan_fwd_tc_states(a, L, ys, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Backward of state `state` of a qpam_scan_fwd_states call (same args, same workspace): dy is that state's output
+// gradient, dgamma / ds_final / ds0 that state's arrays; accumulate != 0 adds dq, dk, dv to what the buffers hold.
+extern "C" int qpam_scan_bwd_state(const qpam_scan_args* a, int32_t state, const void* dy, void* dq, void* dk, void* dv,
+                                   float* dgamma, const float* ds_final, float* ds0, int32_t accumulate, void* stream) {
+  int rc = check_scan_args(a);
+  if (rc) return rc;
+  QPAM_REQUIRE(dy && dq && dk && dv && dgamma, "scan bwd (state): dy/dq/dk/dv/dgamma must not be NULL");
+  QPAM_REQUIRE(state >= 0 && state < a->K, "scan bwd (state): state %d outside [0,%d)", state, a->K);
+  qpam_scan_args probe = *a;
+  probe.y = const_cast<void*>(dy);
+  probe.coef = nullptr;
+  if (!tc_fwdK_eligible(&probe) || a->T <= 0 || (((uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv) & 15) != 0) {
+    set_error("scan bwd (state): offered on the tensor-core path only (bf16, d = 64, 2..4 states, 16-byte aligned tensors)");
+    return QPAM_EUNSUPPORTED;
+  }
+  const ScanLayout L = scan_layout(a, tcs::TC);
+  if (a->workspace_bytes < L.total_bwd) {
+    set_error("scan bwd (state): workspace %zu bytes < required %zu", a->workspace_bytes, L.total_bwd);
+    return QPAM_EWORKSPACE;
+  }
+  return scan_bwd_tc(a, L, dy, dq, dk, dv, dgamma, ds_final, ds0, 1, reinterpret_cast<cudaStream_t>(stream),
+                     accumulate != 0, state);
 }
 
 // ---------------------------------------------------------------------------------------------

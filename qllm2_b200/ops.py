@@ -112,6 +112,19 @@ class _PamScanStatesFn(torch.autograd.Function):
         ys = torch.empty((K,) + tuple(q.shape), dtype=q.dtype, device=q.device)
         s_final = torch.empty(K, S, H, d, d, 2, dtype=torch.float32, device=q.device)
         need_bwd = any(t is not None and t.requires_grad for t in (q, k, v, gamma, s0))
+        if 2 <= K <= 4 and T > 0:
+            # one call: the chunk sums of all states from one pass over k and v, one carry launch, then the output
+            # kernel per state; the workspace keeps every state's chunk states for the per-state backward calls
+            a = _scan_args(q, k, v, gamma, None, s0, cu_seqlens, None, s_final, q_scale, eps, chunk)
+            ws = _workspace(L.qpam_scan_workspace_bytes(C.byref(a), 1 if need_bwd else 0), q.device)
+            a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            check(L.qpam_scan_fwd_states(C.byref(a), ptr(ys), stream_ptr()), "qpam_scan_fwd_states")
+            ctx.save_for_backward(q, k, v, gamma, s0, cu_seqlens, *([ws] if need_bwd else []))
+            ctx.cfg = (q_scale, eps, chunk, need_bwd)
+            ctx.shared = True
+            ctx.set_materialize_grads(False)
+            return ys, s_final
+        ctx.shared = False
         wss = []
         for kk in range(K):
             a = _scan_args(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1], cu_seqlens, ys[kk],
@@ -139,6 +152,15 @@ class _PamScanStatesFn(torch.autograd.Function):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         dgamma = torch.empty_like(gamma)
         ds0 = torch.empty_like(s0) if (s0 is not None and ctx.needs_input_grad[4]) else None
+        if ctx.shared:
+            a = _scan_args(q, k, v, gamma, None, s0, cu_seqlens, None, None, q_scale, eps, chunk)
+            a.workspace, a.workspace_bytes = wss[0].data_ptr(), wss[0].numel()
+            for kk in range(K):
+                dsf = None if ds_final is None else ds_final[kk:kk + 1]
+                d0 = None if ds0 is None else ds0[kk:kk + 1]
+                check(L.qpam_scan_bwd_state(C.byref(a), kk, ptr(dys[kk]), ptr(dq), ptr(dk), ptr(dv), ptr(dgamma[kk:kk + 1]),
+                                            ptr(dsf), ptr(d0), 1 if kk > 0 else 0, stream_ptr()), "qpam_scan_bwd_state")
+            return dq, dk, dv, dgamma, ds0, None, None, None, None
         for kk in range(K):
             a = _scan_args(q, k, v, gamma[kk:kk + 1], None, None if s0 is None else s0[kk:kk + 1], cu_seqlens, None, None,
                            q_scale, eps, chunk)
