@@ -221,7 +221,11 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   } else if (L.grid_chunks > 0) {
     int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H, a->K), 256, tcs::OUTER_SMEM, st>>>(p);
+    CUtensorMap mk, mv;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&mk, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&mv, a->v, 128, rows, 128, 64, 128))) return rc;
+    tcs::k_tc_chunk_outer<false><<<dim3(L.grid_chunks, a->H, a->K), 256, tcs::OUTER_SMEM, st>>>(mk, mv, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outer<state>");
   }
   k_state_scan<false><<<dim3(a->S, a->H * a->K, (64 * 64 / 2 + 255) / 256), 256, 0, st>>>(p, 64);
@@ -342,7 +346,11 @@ static int scan_bwd_tc(const qpam_scan_args* a, const ScanLayout& L, const void*
   if (L.grid_chunks > 0) {
     rc = set_smem(tcs::k_tc_chunk_outer<true>, tcs::OUTER_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(p);
+    CUtensorMap mq, mdy;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&mq, a->q, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&mdy, dy, 128, rows, 128, 64, 128))) return rc;
+    tcs::k_tc_chunk_outer<true><<<dim3(L.grid_chunks, a->H), 256, tcs::OUTER_SMEM, st>>>(mq, mdy, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outer<dstate>");
   }
   tcs::k_tc_state_scan_rev<<<dim3(a->S, a->H, 64 * 64 / 2 / 256), 256, 0, st>>>(p, anchors);

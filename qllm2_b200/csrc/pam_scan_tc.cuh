@@ -81,47 +81,63 @@ constexpr size_t OUTER_SMEM = 1024 + 65536 + 32768 + 1024;
 
 // DSTATE == true computes the gradient counterpart  G = sum_t scale e^{A_t} dy_t (x) conj(q_t)  (dy in
 // place of v, q in place of k) into dstate slot c.
+// The two token tiles (k and v, or q and dy; maps of [B*H*T rows][128 bf16], boxes of 64 x 128, 128-byte swizzle)
+// arrive by TMA in the regions that the operands are then built in: every thread reads its pieces, a barrier, and
+// the operands are written over them.
 template <bool DSTATE>
-__global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
+__global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant__ CUtensorMap mk,
+                                                           const __grid_constant__ CUtensorMap mv, ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;            // [2 blocks][256 rows][128 B]
   unsigned char* sB = smem + 65536;    // [256 rows][128 B]
   float* Acum = reinterpret_cast<float*>(smem + 65536 + 32768);  // [128]
-  uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + TC);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + TC);       // [0] MMAs  [1] token tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
   const int h = blockIdx.y;
   const int kst = blockIdx.z;                 // state (its decay weights the rows); grid z = K
-  const size_t tb = token_base(p, L.b, h, L.t0, TD);
-  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.q : p.k) + tb);
-  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(DSTATE ? p.dy : p.v) + tb);
-  // every global load of this thread is in flight before the first barrier
-  uint4 kxa[8], vxa[8];
+  float graw[4] = {1.f, 1.f, 1.f, 1.f};
+  if (warp == 1) warp_cumsum128_load(graw, p.gamma + gamma_base(p, kst, L.b, h, L.t0), L.len, lane);
+  if (tid == 0) {
+    mbar_init(&bar[0], 1);
+    mbar_init(&bar[1], 1);
+    fence_barrier_init();
+    const int row0 = (L.b * p.H + h) * p.T + L.t0;
+    mbar_arrive_expect_tx(&bar[1], 4 * 16384);
 #pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int idx = tid + 256 * it;
-    kxa[it] = make_uint4(0, 0, 0, 0);
-    vxa[it] = make_uint4(0, 0, 0, 0);
-    if ((idx >> 4) < L.len) {
-      kxa[it] = __ldg(kg + idx);
-      vxa[it] = __ldg(vg + idx);
+    for (int kb = 0; kb < 2; ++kb) {
+      tma_load_2d(sA + kb * 16384, &mk, &bar[1], kb * 64, row0);
+      tma_load_2d(sB + kb * 16384, &mv, &bar[1], kb * 64, row0);
     }
   }
-  if (tid == 0) {
-    mbar_init(bar, 1);
-    fence_barrier_init();
-  }
+  __syncwarp();
   if (warp == 0) tmem_alloc<64>(tmem_slot);
-  if (warp == 1) warp_cumsum128(Acum, p.gamma + gamma_base(p, kst, L.b, h, L.t0), L.len, p.eps, lane);
+  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const float a_last = Acum[TC - 1];
+  const bool tiles_ok = mbar_wait(&bar[1], 0, 202);
+  // this thread's 16-byte pieces of the two tiles (rows past the chunk's end belong to someone else: zeros)
+  uint4 kxa[8], vxa[8];
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int idx = tid + 256 * it;
+    const int row = idx >> 4, c16 = idx & 15;
+    const uint32_t off = (uint32_t)((c16 >> 3) * 16384) + sw128(row, c16 & 7);
+    kxa[it] = make_uint4(0, 0, 0, 0);
+    vxa[it] = make_uint4(0, 0, 0, 0);
+    if (row < L.len) {
+      kxa[it] = *reinterpret_cast<const uint4*>(sA + off);
+      vxa[it] = *reinterpret_cast<const uint4*>(sB + off);
+    }
+  }
+  __syncthreads();      // every piece has been read: the operands may overwrite the tiles
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int idx = tid + 256 * it;
@@ -157,10 +173,10 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(ScanParams p) {
 #pragma unroll
     for (int kk = 0; kk < 16; ++kk)
       mma_bf16(tmem, smem_desc_sw128(a0 + kk * 2048, 32768, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
-    mma_commit(bar);
+    mma_commit(&bar[0]);
   }
   __syncwarp();
-  const bool ok = mbar_wait(bar, 0, 201);
+  const bool ok = mbar_wait(&bar[0], 0, 201) && tiles_ok;
   tc_fence_after();
   if (ok) {
     // lane n' = 2j+c of the tile holds column i: state[i][j][c] sits at float offset i*128 + n'
