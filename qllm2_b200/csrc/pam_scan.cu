@@ -216,7 +216,11 @@ static int tc_states(const ScanParams& p, const ScanLayout& L, const qpam_scan_a
   if (L.grid_chunks > 0 && a->K > 1) {      // all states from one load of the key / value tiles
     int rc = set_smem(tcs::k_tc_chunk_outerK, tcs::OUTERK_SMEM);
     if (rc) return rc;
-    tcs::k_tc_chunk_outerK<<<dim3(L.grid_chunks, a->H), 256, tcs::OUTERK_SMEM, st>>>(p);
+    CUtensorMap mk, mv;
+    const int64_t rows = (int64_t)a->B * a->H * a->T;
+    if ((rc = make_map(&mk, a->k, 128, rows, 128, 64, 128))) return rc;
+    if ((rc = make_map(&mv, a->v, 128, rows, 128, 64, 128))) return rc;
+    tcs::k_tc_chunk_outerK<<<dim3(L.grid_chunks, a->H), 256, tcs::OUTERK_SMEM, st>>>(mk, mv, p);
     QPAM_LAUNCH_CHECK("k_tc_chunk_outerK");
   } else if (L.grid_chunks > 0) {
     int rc = set_smem(tcs::k_tc_chunk_outer<false>, tcs::OUTER_SMEM);

@@ -207,41 +207,58 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant
 // ---------------------------------------------------------------------------------------------
 constexpr size_t OUTERK_SMEM = 1024 + 65536 + 32768 + 4096;
 
-__global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(ScanParams p) {
+__global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(const __grid_constant__ CUtensorMap mk,
+                                                            const __grid_constant__ CUtensorMap mv, ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;            // [2 blocks][256 rows][128 B]
   unsigned char* sB = smem + 65536;    // [256 rows][128 B]
   float* Acum = reinterpret_cast<float*>(smem + 65536 + 32768);  // [KMAX][128]
-  uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + KMAX * TC);  // one per state
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + KMAX);
+  uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + KMAX * TC);  // one per state, [KMAX]: the token tiles
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + KMAX + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, blockIdx.x);
   if (!L.valid) return;
   const int h = blockIdx.y;
   const int K = p.K;
-  const size_t tb = token_base(p, L.b, h, L.t0, TD);
-  const uint4* kg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.k) + tb);
-  const uint4* vg = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.v) + tb);
+  float graw[4] = {1.f, 1.f, 1.f, 1.f};
+  if (warp >= 1 && warp <= K) warp_cumsum128_load(graw, p.gamma + gamma_base(p, warp - 1, L.b, h, L.t0), L.len, lane);
+  if (tid == 0) {
+    for (int k = 0; k < K; ++k) mbar_init(&bar[k], 1);
+    mbar_init(&bar[KMAX], 1);
+    fence_barrier_init();
+    // the key and value tiles arrive by TMA in the regions the operands are built in (see k_tc_chunk_outer)
+    const int row0 = (L.b * p.H + h) * p.T + L.t0;
+    mbar_arrive_expect_tx(&bar[KMAX], 4 * 16384);
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+      tma_load_2d(sA + kb * 16384, &mk, &bar[KMAX], kb * 64, row0);
+      tma_load_2d(sB + kb * 16384, &mv, &bar[KMAX], kb * 64, row0);
+    }
+  }
+  __syncwarp();
+  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  if (warp >= 1 && warp <= K) warp_cumsum128_finish(Acum + (warp - 1) * TC, graw, L.len, p.eps, lane);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  bool ok = mbar_wait(&bar[KMAX], 0, 206);
   uint4 kxa[8], vxa[8];
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int idx = tid + 256 * it;
+    const int row = idx >> 4, c16 = idx & 15;
+    const uint32_t off = (uint32_t)((c16 >> 3) * 16384) + sw128(row, c16 & 7);
     kxa[it] = make_uint4(0, 0, 0, 0);
     vxa[it] = make_uint4(0, 0, 0, 0);
-    if ((idx >> 4) < L.len) {
-      kxa[it] = __ldg(kg + idx);
-      vxa[it] = __ldg(vg + idx);
+    if (row < L.len) {
+      kxa[it] = *reinterpret_cast<const uint4*>(sA + off);
+      vxa[it] = *reinterpret_cast<const uint4*>(sB + off);
     }
   }
-  if (tid == 0) {
-    for (int k = 0; k < K; ++k) mbar_init(&bar[k], 1);
-    fence_barrier_init();
-  }
-  if (warp == 0) tmem_alloc<256>(tmem_slot);
-  if (warp >= 1 && warp <= K)
-    warp_cumsum128(Acum + (warp - 1) * TC, p.gamma + gamma_base(p, warp - 1, L.b, h, L.t0), L.len, p.eps, lane);
+  __syncthreads();      // every piece has been read: the operands may overwrite the tiles
   // the key operand, unweighted, once
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
@@ -260,11 +277,6 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(ScanParams p) {
     *reinterpret_cast<uint4*>(ablk + sw128(row, c16 & 7)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     *reinterpret_cast<uint4*>(ablk + sw128(128 + row, c16 & 7)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  bool ok = true;
   for (int k = 0; k < K; ++k) {
     if (k > 0) {                       // the previous state's MMAs must have read the value operand
       ok = mbar_wait(&bar[k - 1], 0, 205) && ok;
