@@ -70,29 +70,30 @@ __device__ __forceinline__ void warp_cumsum128(float* A, const float* __restrict
 }
 
 // ---------------------------------------------------------------------------------------------
-// Chunk-local state sum, transposed form:  D[2j+c][i] = (Re|Im) sum_s w_s v_s[i] conj(k_s[j])
-//   A (MN-major, M = 128 interleaved key columns, K = 256): rows s      : w_s * cj(k_s)
-//                                                           rows 128+s  : w_s * (ki, kr)
-//   B (MN-major, N = 64 value channels,          K = 256): rows s      : Re v_s
-//                                                           rows 128+s  : Im v_s
-// grid = (chunks, H); 256 threads; ~97 KB shared memory, 64 TMEM columns (two CTAs per SM).
+// Chunk-local state sum  U[i][j] = sum_s w_s v_s[i] conj(k_s[j])  in transposed form, from the key tile AS THE TMA
+// DELIVERS IT (interleaved re, im: no operand is built from it) and the value tile split into two weighted planes:
+//   A  (MN-major, M = 128 interleaved key columns n' = 2j + c, K = 128 tokens): k'[s][n']   (kr_j at 2j, ki_j at 2j+1)
+//   Br (MN-major, N = 64 value channels, K = 128): w_s Re v_s          D1[n'][i] = sum_s A[s][n'] Br[s][i]
+//   Bi (                  the same                ): w_s Im v_s          D2[n'][i] = sum_s A[s][n'] Bi[s][i]
+//   Re U[i][j] = D1[2j][i] + D2[2j+1][i],   Im U[i][j] = D2[2j][i] - D1[2j+1][i]:  neighbouring TMEM lanes, one shuffle.
+// grid = (chunks, H, K); 256 threads; 66 KB shared memory, 128 TMEM columns: three CTAs per SM.
 // ---------------------------------------------------------------------------------------------
-constexpr size_t OUTER_SMEM = 1024 + 65536 + 32768 + 1024;
+constexpr size_t OUTER_SMEM = 1024 + 32768 + 32768 + 1024;
 
 // DSTATE == true computes the gradient counterpart  G = sum_t scale e^{A_t} dy_t (x) conj(q_t)  (dy in
 // place of v, q in place of k) into dstate slot c.
 // The two token tiles (k and v, or q and dy; maps of [B*H*T rows][128 bf16], boxes of 64 x 128, 128-byte swizzle)
-// arrive by TMA in the regions that the operands are then built in: every thread reads its pieces, a barrier, and
-// the operands are written over them.
+// arrive by TMA; the value tile lands in the region its planes are then built in: every thread reads its pieces, a
+// barrier, and the planes are written over them.
 template <bool DSTATE>
-__global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant__ CUtensorMap mk,
+__global__ void __launch_bounds__(256, 3) k_tc_chunk_outer(const __grid_constant__ CUtensorMap mk,
                                                            const __grid_constant__ CUtensorMap mv, ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* sA = smem;            // [2 blocks][256 rows][128 B]
-  unsigned char* sB = smem + 65536;    // [256 rows][128 B]
-  float* Acum = reinterpret_cast<float*>(smem + 65536 + 32768);  // [128]
+  unsigned char* sA = smem;            // key tile: [2 boxes of 64 columns][128 rows][128 B]
+  unsigned char* sB = smem + 32768;    // value tile, then [256 rows][128 B]: rows s = w Re v_s, rows 128 + s = w Im v_s
+  float* Acum = reinterpret_cast<float*>(smem + 65536);          // [128]
   uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + TC);       // [0] MMAs  [1] token tiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 2);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -115,7 +116,7 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant
     }
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc<64>(tmem_slot);
+  if (warp == 0) tmem_alloc<128>(tmem_slot);
   if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
@@ -123,43 +124,31 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant
   const uint32_t tmem = *tmem_slot;
   const float a_last = Acum[TC - 1];
   const bool tiles_ok = mbar_wait(&bar[1], 0, 202);
-  // this thread's 16-byte pieces of the two tiles (rows past the chunk's end belong to someone else: zeros)
-  uint4 kxa[8], vxa[8];
+  // this thread's 16-byte pieces of the value tile (rows past the chunk's end belong to someone else: their zeros
+  // also cancel whatever the key tile holds in those rows)
+  uint4 vxa[8];
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int idx = tid + 256 * it;
     const int row = idx >> 4, c16 = idx & 15;
-    const uint32_t off = (uint32_t)((c16 >> 3) * 16384) + sw128(row, c16 & 7);
-    kxa[it] = make_uint4(0, 0, 0, 0);
     vxa[it] = make_uint4(0, 0, 0, 0);
-    if (row < L.len) {
-      kxa[it] = *reinterpret_cast<const uint4*>(sA + off);
-      vxa[it] = *reinterpret_cast<const uint4*>(sB + off);
-    }
+    if (row < L.len) vxa[it] = *reinterpret_cast<const uint4*>(sB + (c16 >> 3) * 16384 + sw128(row, c16 & 7));
   }
-  __syncthreads();      // every piece has been read: the operands may overwrite the tiles
+  __syncthreads();      // every piece has been read: the planes may overwrite the tile
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int idx = tid + 256 * it;
     const int row = idx >> 4, c16 = idx & 15;
-    const uint4 kx = kxa[it], vx = vxa[it];
+    const uint4 vx = vxa[it];
     const float w = DSTATE ? p.q_scale * __expf(Acum[row]) : __expf(fminf(0.f, a_last - Acum[row]));
-    const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w};
     const uint32_t vw[4] = {vx.x, vx.y, vx.z, vx.w};
-    uint32_t lo[4], hi[4];
     float vr[4], vi[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float2 kk = unpack_bf162(kw[e]);
-      lo[e] = pack_bf162(w * kk.x, -w * kk.y);
-      hi[e] = pack_bf162(w * kk.y, w * kk.x);
       const float2 vv = unpack_bf162(vw[e]);
-      vr[e] = vv.x;
-      vi[e] = vv.y;
+      vr[e] = w * vv.x;
+      vi[e] = w * vv.y;
     }
-    unsigned char* ablk = sA + (c16 >> 3) * 32768;
-    *reinterpret_cast<uint4*>(ablk + sw128(row, c16 & 7)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4*>(ablk + sw128(128 + row, c16 & 7)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     const uint32_t boff = (c16 & 1) * 8;
     *reinterpret_cast<uint2*>(sB + sw128(row, c16 >> 1) + boff) = make_uint2(pack_bf162(vr[0], vr[1]), pack_bf162(vr[2], vr[3]));
     *reinterpret_cast<uint2*>(sB + sw128(128 + row, c16 >> 1) + boff) = make_uint2(pack_bf162(vi[0], vi[1]), pack_bf162(vi[2], vi[3]));
@@ -171,30 +160,39 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outer(const __grid_constant
     constexpr uint32_t idesc = idesc_bf16(128, 64, true, true);
     const uint32_t a0 = smem_u32(sA), b0 = smem_u32(sB);
 #pragma unroll
-    for (int kk = 0; kk < 16; ++kk)
-      mma_bf16(tmem, smem_desc_sw128(a0 + kk * 2048, 32768, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
+    for (int kk = 0; kk < 8; ++kk)      // D1 = A^T Br: k-step = 16 tokens = 2048 bytes in either operand
+      mma_bf16(tmem, smem_desc_sw128(a0 + kk * 2048, 16384, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)      // D2 = A^T Bi
+      mma_bf16(tmem + 64, smem_desc_sw128(a0 + kk * 2048, 16384, 1024), smem_desc_sw128(b0 + 16384 + kk * 2048, 16, 1024), idesc, kk > 0);
     mma_commit(&bar[0]);
   }
   __syncwarp();
   const bool ok = mbar_wait(&bar[0], 0, 201) && tiles_ok;
   tc_fence_after();
-  if (ok) {
+  {
     // lane n' = 2j+c of the tile holds column i: state[i][j][c] sits at float offset i*128 + n'
     float2* slot = DSTATE ? p.dstates + state_base(p, kst, h, L.slot0 + L.c, TD)
                           : p.states + state_base(p, kst, h, L.slot0 + L.c + 1, TD);
     const int q4 = warp & 3, cc = warp >> 2;   // TMEM lane quarter, column half
     float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
-    float v[32];
-    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + cc * 32, v);
+    float d1[32], d2[32];
+    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + cc * 32, d1);
+    tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + 64 + cc * 32, d2);
+    const bool even = (lane & 1) == 0;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
-    if (!DSTATE && tid == 0) p.chunk_decay[((size_t)kst * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
+    for (int i = 0; i < 32; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, d2[i], 1);      // D2 of the neighbouring key column
+      const float u = even ? d1[i] + other : other - d1[i];
+      if (ok) dst[(size_t)(cc * 32 + i) * 128] = u;
+    }
+    if (ok && !DSTATE && tid == 0) p.chunk_decay[((size_t)kst * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc<64>(tmem);
+    tmem_dealloc<128>(tmem);
   }
 }
 
