@@ -481,8 +481,8 @@ def main():
 # DRAM bytes (read + written) per launch of the dominant kernels at the headline shape, from an ncu capture of
 # THIS build (one kernel, one launch): the figure the `traffic` field of the roofline reports
 NCU_TRAFFIC = {
-    "k_tc_chunk<dq,dv,dk>": {"bytes": 148383744 + 53251328, "source": "ncu --set full of this kernel, one launch (summary kept under profiles/); a constant of this build, not measured in this run"},
-    "k_tc_chunk<fwd>": {"bytes": 99535872 + 5937408, "source": "ncu --set full of this kernel, one launch (summary kept under profiles/); a constant of this build, not measured in this run"},
+    "k_tc_chunk<dq,dv,dk>": {"bytes": 148378624 + 53239552, "source": "ncu --set full of this kernel, one launch (summary kept under profiles/); a constant of this build, not measured in this run"},
+    "k_tc_chunk<fwd>": {"bytes": 99545856 + 5786368, "source": "ncu --set full of this kernel, one launch (summary kept under profiles/); a constant of this build, not measured in this run"},
 }
 
 
