@@ -46,6 +46,38 @@ def test_argument_errors_do_not_touch_the_gpu(lib):
     assert lib.qpam_decode_step(None, 0, 1, 1, 0, None, None, None, None, None, None, None, 1, 1, 64, 1, 0, None) == 1
 
 
+def test_tensor_core_only_entry_points_refuse_other_inputs_without_a_launch(lib):
+    """qpam_scan_fwd_states / qpam_scan_bwd_state / qpam_scan_bwd_accumulate / qpam_head_logits exist on the tensor-core
+    path only: anything else is refused with QPAM_EUNSUPPORTED (4) or QPAM_EINVAL (1) and a message, before any CUDA
+    call (the pointers below are fake and never dereferenced)."""
+    from qllm2_b200 import _lib
+    fake = 1 << 20                     # non-null, 256-byte aligned
+    a = _lib.ScanArgs()
+    a.q = a.k = a.v = a.gamma = a.workspace = fake
+    a.workspace_bytes = 1 << 30
+    a.B, a.H, a.T, a.d, a.K, a.S = 1, 2, 256, 64, 3, 1
+    a.io_dtype, a.q_scale, a.gamma_eps = _lib.QPAM_F32, 0.125, 1e-6
+    assert lib.qpam_scan_fwd_states(C.byref(a), fake, None) == 4           # fp32 tokens
+    assert b"tensor-core path" in lib.qpam_last_error()
+    assert lib.qpam_scan_fwd_states(C.byref(a), None, None) == 1           # no output buffer
+    a.io_dtype, a.K = _lib.QPAM_BF16, 1
+    assert lib.qpam_scan_fwd_states(C.byref(a), fake, None) == 4           # one state: use qpam_scan_fwd
+    a.K = 3
+    assert lib.qpam_scan_bwd_state(C.byref(a), 3, fake, fake, fake, fake, fake, None, None, 0, None) == 1
+    assert b"state 3" in lib.qpam_last_error()
+    a.d = 32
+    assert lib.qpam_scan_bwd_state(C.byref(a), 0, fake, fake, fake, fake, fake, None, None, 0, None) == 4
+    a.K = 1
+    assert lib.qpam_scan_bwd_accumulate(C.byref(a), fake, fake, fake, fake, fake, None, None, 1, None) == 4
+    ce = _lib.CEArgs()
+    ce.h = ce.w = fake
+    ce.N, ce.V, ce.F, ce.io_dtype = 256, 50261, 1536, _lib.QPAM_F32
+    assert lib.qpam_head_logits(C.byref(ce), fake, 50264, None) == 4        # fp32: the library GEMM's job
+    ce.io_dtype = _lib.QPAM_BF16
+    assert lib.qpam_head_logits(C.byref(ce), fake, 50261, None) == 1        # ld not a multiple of 8
+    assert lib.qpam_head_logits(C.byref(ce), None, 50264, None) == 1
+
+
 def test_workspace_sizes(lib):
     from qllm2_b200 import _lib
     a = _lib.ScanArgs()
