@@ -197,22 +197,22 @@ __global__ void __launch_bounds__(256, 3) k_tc_chunk_outer(const __grid_constant
 }
 
 // ---------------------------------------------------------------------------------------------
-// State sums of K states from ONE load of the key / value tiles (forward only, 2 <= K <= 4).  The decay
-// weights of a state scale the rows, so they are moved to the value operand: A (the unweighted key rows
-// cj(k_s), (ki, kr)) is built once, and for every state B_k = w^k_s (Re v_s, Im v_s) is rewritten from the
-// registers that hold the value tile, followed by its MMA chain into that state's 64 TMEM columns.
-// grid = (chunks, H); 256 threads; same shared memory as k_tc_chunk_outer, 256 TMEM columns.
+// State sums of K states from ONE load of the key / value tiles (forward only, 2 <= K <= 4).  As in k_tc_chunk_outer
+// the key tile is the A operand as the TMA delivers it and the decay weights sit on the value planes, so a state costs
+// one rewrite of the planes B_k = w^k_s (Re v_s ; Im v_s) from the registers that hold the value tile, its two MMA
+// chains into the same 128 TMEM columns, and its epilogue; the states follow one another.
+// grid = (chunks, H); 256 threads; 70 KB shared memory, 128 TMEM columns: three CTAs per SM.
 // ---------------------------------------------------------------------------------------------
-constexpr size_t OUTERK_SMEM = 1024 + 65536 + 32768 + 4096;
+constexpr size_t OUTERK_SMEM = 1024 + 65536 + 4096;
 
-__global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(const __grid_constant__ CUtensorMap mk,
+__global__ void __launch_bounds__(256, 3) k_tc_chunk_outerK(const __grid_constant__ CUtensorMap mk,
                                                             const __grid_constant__ CUtensorMap mv, ScanParams p) {
   using namespace umma;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* sA = smem;            // [2 blocks][256 rows][128 B]
-  unsigned char* sB = smem + 65536;    // [256 rows][128 B]
-  float* Acum = reinterpret_cast<float*>(smem + 65536 + 32768);  // [KMAX][128]
+  unsigned char* sA = smem;            // key tile: [2 boxes of 64 columns][128 rows][128 B]
+  unsigned char* sB = smem + 32768;    // value tile, then per state [256 rows][128 B]: w Re v_s ; w Im v_s
+  float* Acum = reinterpret_cast<float*>(smem + 65536);           // [KMAX][128]
   uint64_t* bar = reinterpret_cast<uint64_t*>(Acum + KMAX * TC);  // one per state, [KMAX]: the token tiles
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + KMAX + 1);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -226,7 +226,6 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(const __grid_constan
     for (int k = 0; k < K; ++k) mbar_init(&bar[k], 1);
     mbar_init(&bar[KMAX], 1);
     fence_barrier_init();
-    // the key and value tiles arrive by TMA in the regions the operands are built in (see k_tc_chunk_outer)
     const int row0 = (L.b * p.H + h) * p.T + L.t0;
     mbar_arrive_expect_tx(&bar[KMAX], 4 * 16384);
 #pragma unroll
@@ -236,50 +235,30 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(const __grid_constan
     }
   }
   __syncwarp();
-  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  if (warp == 0) tmem_alloc<128>(tmem_slot);
   if (warp >= 1 && warp <= K) warp_cumsum128_finish(Acum + (warp - 1) * TC, graw, L.len, p.eps, lane);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   bool ok = mbar_wait(&bar[KMAX], 0, 206);
-  uint4 kxa[8], vxa[8];
+  // this thread's 16-byte pieces of the value tile (rows past the chunk's end: zeros, which also cancel whatever the
+  // key tile holds in those rows)
+  uint4 vxa[8];
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int idx = tid + 256 * it;
     const int row = idx >> 4, c16 = idx & 15;
-    const uint32_t off = (uint32_t)((c16 >> 3) * 16384) + sw128(row, c16 & 7);
-    kxa[it] = make_uint4(0, 0, 0, 0);
     vxa[it] = make_uint4(0, 0, 0, 0);
-    if (row < L.len) {
-      kxa[it] = *reinterpret_cast<const uint4*>(sA + off);
-      vxa[it] = *reinterpret_cast<const uint4*>(sB + off);
-    }
+    if (row < L.len) vxa[it] = *reinterpret_cast<const uint4*>(sB + (c16 >> 3) * 16384 + sw128(row, c16 & 7));
   }
-  __syncthreads();      // every piece has been read: the operands may overwrite the tiles
-  // the key operand, unweighted, once
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int idx = tid + 256 * it;
-    const int row = idx >> 4, c16 = idx & 15;
-    const uint4 kx = kxa[it];
-    const uint32_t kw[4] = {kx.x, kx.y, kx.z, kx.w};
-    uint32_t lo[4], hi[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 kk = unpack_bf162(kw[e]);
-      lo[e] = pack_bf162(kk.x, -kk.y);
-      hi[e] = pack_bf162(kk.y, kk.x);
-    }
-    unsigned char* ablk = sA + (c16 >> 3) * 32768;
-    *reinterpret_cast<uint4*>(ablk + sw128(row, c16 & 7)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4*>(ablk + sw128(128 + row, c16 & 7)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-  }
+  const int q4 = warp & 3, cc = warp >> 2;   // epilogue: TMEM lane quarter, column half
+  const bool even = (lane & 1) == 0;
   for (int k = 0; k < K; ++k) {
-    if (k > 0) {                       // the previous state's MMAs must have read the value operand
-      ok = mbar_wait(&bar[k - 1], 0, 205) && ok;
-      tc_fence_after();
-    }
+    // every piece has been read (k = 0) / the previous state's MMAs have read the planes and its epilogue the
+    // accumulators (k > 0: every thread waited for them below)
+    tc_fence_before();
+    __syncthreads();
     const float a_last = Acum[k * TC + TC - 1];
 #pragma unroll
     for (int it = 0; it < 8; ++it) {
@@ -306,31 +285,38 @@ __global__ void __launch_bounds__(256, 2) k_tc_chunk_outerK(const __grid_constan
       constexpr uint32_t idesc = idesc_bf16(128, 64, true, true);
       const uint32_t a0 = smem_u32(sA), b0 = smem_u32(sB);
 #pragma unroll
-      for (int kk = 0; kk < 16; ++kk)
-        mma_bf16(tmem + k * 64, smem_desc_sw128(a0 + kk * 2048, 32768, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
+      for (int kk = 0; kk < 8; ++kk)      // D1 = A^T Br
+        mma_bf16(tmem, smem_desc_sw128(a0 + kk * 2048, 16384, 1024), smem_desc_sw128(b0 + kk * 2048, 16, 1024), idesc, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)      // D2 = A^T Bi
+        mma_bf16(tmem + 64, smem_desc_sw128(a0 + kk * 2048, 16384, 1024), smem_desc_sw128(b0 + 16384 + kk * 2048, 16, 1024), idesc, kk > 0);
       mma_commit(&bar[k]);
     }
     __syncwarp();
-  }
-  ok = mbar_wait(&bar[K - 1], 0, 206) && ok;
-  tc_fence_after();
-  if (ok) {
-    const int q4 = warp & 3, cc = warp >> 2;   // TMEM lane quarter, column half
-    for (int k = 0; k < K; ++k) {
-      float2* slot = p.states + state_base(p, k, h, L.slot0 + L.c + 1, TD);
-      float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
-      float v[32];
-      tmem_ld32(tmem + ((uint32_t)(q4 * 32) << 16) + k * 64 + cc * 32, v);
+    ok = mbar_wait(&bar[k], 0, 205) && ok;
+    tc_fence_after();
+    // Re U = D1[2j] + D2[2j+1], Im U = D2[2j] - D1[2j+1]: lane n' = 2j+c holds column i, state[i][j][c] at i*128 + n'
+    float2* slot = p.states + state_base(p, k, h, L.slot0 + L.c + 1, TD);
+    float* dst = reinterpret_cast<float*>(slot) + (q4 * 32 + lane);
+#pragma unroll 1
+    for (int hh = 0; hh < 2; ++hh) {          // 16 columns at a time: the value tile stays in registers beside them
+      float d1[16], d2[16];
+      const uint32_t col = (uint32_t)(cc * 32 + hh * 16);
+      tmem_ld16x2(tmem + ((uint32_t)(q4 * 32) << 16) + col, d1, tmem + ((uint32_t)(q4 * 32) << 16) + 64 + col, d2);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) dst[(size_t)(cc * 32 + i) * 128] = v[i];
-      if (tid == 0) p.chunk_decay[((size_t)k * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(Acum[k * TC + TC - 1]);
+      for (int i = 0; i < 16; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, d2[i], 1);
+        const float u = even ? d1[i] + other : other - d1[i];
+        if (ok) dst[(size_t)(col + i) * 128] = u;
+      }
     }
+    if (ok && tid == 0) p.chunk_decay[((size_t)k * p.H + h) * p.nslots + L.slot0 + L.c + 1] = __expf(a_last);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    tmem_dealloc<256>(tmem);
+    tmem_dealloc<128>(tmem);
   }
 }
 
