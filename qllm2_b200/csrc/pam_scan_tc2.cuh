@@ -309,8 +309,8 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   float* dots = Acum + TC;                              // [2][128]
   float* cfac = dots + 2 * TC;                          // [128]
   float* rfac = cfac + TC;                              // [128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(rfac + TC);  // [0] tma, [1] scores, [2] outputs, [3] slow path: state product
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(rfac + TC);  // [0] tma, [1] scores, [2] outputs, [3] state product, [4] carried state
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
   int* failed = reinterpret_cast<int*>(tmem_slot + 1);      // error word as found at the start of this CTA
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const ChunkLoc L = locate_chunk(p.geom, chunk_x);
@@ -322,7 +322,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   if (warp == 1) warp_cumsum128_load(graw, p.gamma + gamma_base(p, 0, L.b, h, L.t0), L.len, lane);
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
     fence_barrier_init();
     // the token tiles are requested first: the prologue below (TMEM allocation, cumulative decay, factors,
     // carried-state prefetch) runs while they are in flight
@@ -335,22 +335,7 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     }
   }
   __syncwarp();
-  // carried state (fp32, 4 complex per item, 4 items per thread): requested here, so that its way through the memory
-  // system runs beside the set-up and the cumulative decay instead of after them (behind the decays and the tile
-  // requests, which the longest chains of the prologue hang on)
-  float4 sraw[4][2];
-  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);      // before this warp queues up more loads
-  if (has_state) {
-    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
-                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
-    const float4* sg = reinterpret_cast<const float4*>(st);
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
-      sraw[it][0] = __ldg(sg + idx * 2);
-      sraw[it][1] = __ldg(sg + idx * 2 + 1);
-    }
-  }
+  if (warp == 1) warp_cumsum128_finish(Acum, graw, L.len, p.eps, lane);
   if (warp == 0) tmem_alloc<256>(tmem_slot);
   tc_fence_before();
   __syncthreads();
@@ -377,19 +362,6 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
       rfac[tid] = up;
     }
   }
-  const float st_cst = strong ? 1.f : (LOWER ? __expf(a_mid) : __expf(a_last - a_mid));
-  // the carried state times the chunk constant, kept as packed bf16 until stage 1 has released the B1 region
-  uint32_t st_r[4][2], st_i[4][2];
-  if (has_state) {
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const float4 s01 = sraw[it][0], s23 = sraw[it][1];
-      st_r[it][0] = pack_bf162(st_cst * s01.x, st_cst * s01.z);
-      st_r[it][1] = pack_bf162(st_cst * s23.x, st_cst * s23.z);
-      st_i[it][0] = pack_bf162(st_cst * s01.y, st_cst * s01.w);
-      st_i[it][1] = pack_bf162(st_cst * s23.y, st_cst * s23.w);
-    }
-  }
   bool ok = mbar_wait(&bars[0], 0, 221);
   {
     // de-interleave the three tiles in place (read all, barrier, write all)
@@ -414,6 +386,14 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
   __syncwarp();
   ok = mbar_wait(&bars[1], 0, 222) && ok;
   tc_fence_after();
+  if (has_state && tid == 0) {
+    // stage 1 has released the B1 region: the carried state (fp32, 32 KB, contiguous) comes into it by one bulk copy
+    // while epilogue 1 runs
+    const float2* st = LOWER ? p.states + state_base(p, 0, h, L.slot0 + L.c, TD)
+                             : p.dstates + state_base(p, 0, h, L.slot0 + L.c + 1, TD);
+    mbar_arrive_expect_tx(&bars[4], 32768);
+    bulk_load_1d(RB, st, 32768, &bars[4]);
+  }
   const int q4 = warp & 3, hf = warp >> 2;
   const int r = q4 * 32 + lane;                               // this thread's row (TMEM lane)
   const uint32_t tl = tmem + ((uint32_t)(q4 * 32) << 16);
@@ -441,7 +421,25 @@ __device__ __forceinline__ void chunk_job(const CUtensorMap* __restrict__ ma1, c
     }
   }
   if (has_state) {
-    // carried state planes (already multiplied by the chunk constant) into the B1 region: stage 1 has consumed it
+    // the carried state has landed as fp32 [i][j] (re, im): every thread reads its four items (4 complex each; the two
+    // 16-byte halves in an order that keeps a quarter-warp on distinct banks), a barrier, and the bf16 planes, times the
+    // chunk constant, are written over it
+    ok = mbar_wait(&bars[4], 0, 226) && ok;
+    const float st_cst = strong ? 1.f : (LOWER ? __expf(a_mid) : __expf(a_last - a_mid));
+    const int flip = (lane >> 2) & 1;
+    uint32_t st_r[4][2], st_i[4][2];
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + 256 * it;          // (i, c16): state[i][4*c16 .. +3]
+      const float4 a = *reinterpret_cast<const float4*>(RB + idx * 32 + flip * 16);
+      const float4 b = *reinterpret_cast<const float4*>(RB + idx * 32 + (flip ^ 1) * 16);
+      const float4 s01 = flip ? b : a, s23 = flip ? a : b;
+      st_r[it][0] = pack_bf162(st_cst * s01.x, st_cst * s01.z);
+      st_r[it][1] = pack_bf162(st_cst * s23.x, st_cst * s23.z);
+      st_i[it][0] = pack_bf162(st_cst * s01.y, st_cst * s01.w);
+      st_i[it][1] = pack_bf162(st_cst * s23.y, st_cst * s23.w);
+    }
+    __syncthreads();
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
       const int idx = tid + 256 * it;

@@ -107,6 +107,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+// Untiled bulk copy global -> this CTA's shared memory, counted on `bar` (both addresses 16-byte aligned, bytes a multiple
+// of 16); no multicast.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 // TMA store of one box from shared memory (128-byte swizzled like the loads) to global memory; coordinates must not
 // be negative, x times the element size a multiple of 16 bytes.  The issuing thread commits the group and, before the
 // shared-memory block is written again, waits until the engine has read it.
